@@ -1,0 +1,1262 @@
+// Host side of libaot_cuda: context, kernel launchers, the device-resident State
+// and the operator API that mirrors the reference's GPU backend slot
+// (crates/aot-kernels/src/metal.rs `Gpu`), the interpreted forward pass
+// (crates/aot-codegen/src/emit.rs:243-333, 466-516) and the extern "C" surface
+// declared in include/aot_cuda.h.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/aot_cuda.h"
+#include "gemv.cuh"
+#include "ops.cuh"
+
+using namespace aot;
+
+// ---- errors ------------------------------------------------------------------------
+static thread_local std::string g_last_error;
+
+static int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+#define CU_TRY(expr)                                                                                  \
+  do {                                                                                                \
+    cudaError_t e_ = (expr);                                                                          \
+    if (e_ != cudaSuccess) return fail(AOTCU_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_));      \
+  } while (0)
+
+#define ARG_CHECK(cond, ...)                                  \
+  do {                                                        \
+    if (!(cond)) return fail(AOTCU_ERR_BAD_ARG, __VA_ARGS__); \
+  } while (0)
+
+static_assert(sizeof(aotcu_block_q8_0) == 36 && sizeof(aotcu_block_q8_k) == 292, "block layout");
+
+// ---- context --------------------------------------------------------------------------
+struct aotcu_ctx {
+  int device = 0;
+  int n_sm = 0;
+  size_t max_smem = 0;
+  cudaStream_t stream = nullptr;
+  int* d_err = nullptr;
+  bool pdl = false;
+  uint64_t launches = 0;
+};
+
+constexpr size_t WEIGHT_PAD = 256;
+
+static int ctx_set_device(aotcu_ctx* c) {
+  CU_TRY(cudaSetDevice(c->device));
+  return 0;
+}
+
+template <class... KArgs, class... Args>
+static int launch(aotcu_ctx* c, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = c->stream;
+  cudaLaunchAttribute attr[1];
+  if (c->pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+  if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  c->launches++;
+  return 0;
+}
+
+static int grid_for(aotcu_ctx* c, size_t work_items, int per_block) {
+  size_t g = (work_items + per_block - 1) / per_block;
+  size_t cap = (size_t)c->n_sm * 8;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+// ---- GEMV / matmul launcher ------------------------------------------------------------
+struct GemvCall {
+  GemvSeg seg[3];
+  int nseg = 1;
+  int pair = 0;
+  size_t cols = 0;
+  const void* x = nullptr;
+  int x_mode = 0;  // 0 reference-layout blocks (or f32 for float kinds), 1 block images
+  size_t m = 1;
+  int epilogue = EPI_STORE;
+};
+
+static int check_weight_alignment(int kind, const void* w) {
+  uintptr_t a = (uintptr_t)w;
+  uintptr_t need = (kind == Q4_K || kind == Q5_K) ? 16 : (kind == F32 ? 4 : 2);
+  ARG_CHECK((a % need) == 0, "weights of kind %d must be %zu-byte aligned", kind, (size_t)need);
+  return 0;
+}
+
+static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
+  ARG_CHECK(call.nseg >= 1 && call.nseg <= 3, "1..3 matrices per launch");
+  const int act = kind_act(call.seg[0].kind);
+  size_t span = 0, max_rb = 0;
+  for (int s = 0; s < call.nseg; s++) {
+    const GemvSeg& sg = call.seg[s];
+    ARG_CHECK(sg.kind >= 0 && sg.kind < N_KINDS, "unknown weight kind %d", sg.kind);
+    ARG_CHECK(kind_act(sg.kind) == act, "matrices of one launch must share the activation format");
+    ARG_CHECK(sg.w && sg.out, "null weight or output pointer");
+    ARG_CHECK(sg.rows > 0, "rows must be positive");
+    if (int rc = check_weight_alignment(sg.kind, sg.w)) return rc;
+    size_t rb = kind_row_bytes(sg.kind, call.cols);
+    max_rb = rb > max_rb ? rb : max_rb;
+    span += (size_t)sg.rows;
+  }
+  ARG_CHECK(call.cols > 0 && call.cols % (size_t)kind_block(call.seg[0].kind) == 0,
+            "cols (%zu) must be a positive multiple of the block size", call.cols);
+  ARG_CHECK(call.x, "null activation pointer");
+  ARG_CHECK(call.m >= 1, "m must be at least 1");
+  if (call.pair) {
+    ARG_CHECK(call.nseg == 2 && call.seg[0].rows == call.seg[1].rows, "pair mode needs two matrices of equal rows");
+    span = (size_t)call.seg[0].rows;
+  }
+  ARG_CHECK(span < (1u << 30) && call.cols < (1u << 24), "matrix too large");
+
+  GemvParams P = {};
+  for (int s = 0; s < call.nseg; s++) P.seg[s] = call.seg[s];
+  P.nseg = call.nseg;
+  P.pair = call.pair;
+  P.cols = (int)call.cols;
+  P.span_rows = (int)span;
+  P.x = call.x;
+  P.x_image = call.x_mode == 1;
+  P.m = (int)call.m;
+  P.epilogue = call.epilogue;
+  P.err = c->d_err;
+
+  if (act == ACT_F32) {
+    ARG_CHECK(((uintptr_t)call.x % 4) == 0, "activations must be 4-byte aligned");
+    int rows_per_block = 32;
+    int grid = (int)((span + rows_per_block - 1) / rows_per_block);
+    int cap = c->n_sm * 8;
+    grid = grid > cap ? cap : grid;
+    return launch(c, gemv_float_kernel, dim3(grid), dim3(256), 0, P);
+  }
+  ARG_CHECK(((uintptr_t)call.x % (P.x_image ? 16 : 4)) == 0, "activation blocks are misaligned");
+
+  const int mult = call.pair ? 2 : 1;
+  int grid = c->n_sm;
+  if (span < (size_t)grid * 4) grid = (int)((span + 3) / 4);
+  int rows_per_cta = (int)((span + grid - 1) / grid);
+  grid = (int)((span + rows_per_cta - 1) / rows_per_cta);
+  const size_t STAGE_MAX = 48 * 1024;
+  int tile_rows = (int)(STAGE_MAX / (max_rb * mult));
+  if (tile_rows > GEMV_TRP / mult) tile_rows = GEMV_TRP / mult;
+  if (tile_rows > rows_per_cta) tile_rows = rows_per_cta;
+  if (tile_rows < 1) tile_rows = 1;
+  size_t stage_bytes = (((size_t)tile_rows * mult * max_rb + 15) & ~(size_t)15) + 256;
+  size_t fixed;
+  if (act == ACT_Q8_K) {
+    size_t nb = call.cols / 256;
+    fixed = nb * XK_STRIDE + 2 * nb * GEMV_TRP * sizeof(float) + 8 * sizeof(uint64_t);
+  } else {
+    size_t nb = call.cols / 32;
+    fixed = ((nb * X0_STRIDE + 15) & ~(size_t)15) + 2 * GEMV_TRP * sizeof(float) + 8 * sizeof(uint64_t);
+  }
+  ARG_CHECK(fixed + stage_bytes <= c->max_smem, "a single row tile (%zu bytes) does not fit in shared memory",
+            fixed + stage_bytes);
+  int n_tiles = (rows_per_cta + tile_rows - 1) / tile_rows;
+  int n_stages = (int)((c->max_smem - fixed) / stage_bytes);
+  if (n_stages > n_tiles) n_stages = n_tiles;
+  if (n_stages > 8) n_stages = 8;
+  P.rows_per_cta = rows_per_cta;
+  P.tile_rows = tile_rows;
+  P.stage_bytes = (int)stage_bytes;
+  P.n_stages = n_stages;
+  size_t smem = (size_t)n_stages * stage_bytes + fixed;
+  if (act == ACT_Q8_K) return launch(c, gemv_q8k_kernel, dim3(grid), dim3(GEMV_THREADS), smem, P);
+  return launch(c, gemv_q80_kernel, dim3(grid), dim3(GEMV_THREADS), smem, P);
+}
+
+// ---- parity export: integer block sums -------------------------------------------------------
+__global__ void block_sums_kernel(int kind, const uint8_t* w, const uint8_t* x, int rows, int nb, int32_t* sumi,
+                                  int32_t* summ) {
+  // One thread per (row, block), straight from global memory with byte reads; this
+  // is a checker for the integer arithmetic, not a fast path.
+  for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < (size_t)rows * nb;
+       it += (size_t)gridDim.x * blockDim.x) {
+    const int b = (int)(it % nb);
+    const uint8_t* wb = w + it * kind_size(kind);
+    auto w32 = [&](const uint8_t* p, int i) -> uint32_t {
+      return (uint32_t)p[4 * i] | ((uint32_t)p[4 * i + 1] << 8) | ((uint32_t)p[4 * i + 2] << 16) |
+             ((uint32_t)p[4 * i + 3] << 24);
+    };
+    if (kind_act(kind) == ACT_Q8_K) {
+      const BlockQ8_K* y = reinterpret_cast<const BlockQ8_K*>(x) + b;
+      auto yw = [&](int i) -> uint32_t { return w32(reinterpret_cast<const uint8_t*>(y->qs), i); };
+      if (kind == Q6_K) {
+        sumi[it] = q6k_block_sum([&](int i) { return w32(wb, i); }, yw, y->bsums);
+      } else {
+        const bool q5 = kind == Q5_K;
+        K4Scales s = k4_unpack(w32(wb + 4, 0), w32(wb + 4, 1), w32(wb + 4, 2));
+        const uint8_t* qs = wb + (q5 ? 48 : 16);
+        const uint8_t* qh = wb + 16;
+        int si, sm;
+        if (q5)
+          k4_block_sums<true>(s, [&](int i) { return w32(qs, i); }, [&](int i) { return w32(qh, i); }, yw, y->bsums, si, sm);
+        else
+          k4_block_sums<false>(s, [&](int i) { return w32(qs, i); }, [&](int i) { return w32(qh, i); }, yw, y->bsums, si, sm);
+        sumi[it] = si;
+        if (summ) summ[it] = sm;
+      }
+    } else {
+      const BlockQ8_0* y = reinterpret_cast<const BlockQ8_0*>(x) + b;
+      int s = 0;
+      for (int k = 0; k < 8; k++) {
+        uint32_t y4 = w32(reinterpret_cast<const uint8_t*>(y->qs), k);
+        if (kind == Q8_0) s += q8_0_lane(w32(wb + 2, k), y4);
+        else if (kind == Q4_0) s += q4_0_lane(w32(wb + 2, k & 3), k, y4);
+        else s += q5_0_lane(w32(wb + 6, k & 3), w32(wb + 2, 0), k, y4);
+      }
+      sumi[it] = s;
+    }
+  }
+}
+
+// ---- device State + model (the `Gpu` of metal.rs) ------------------------------------------------
+struct aotcu_gpu {
+  aotcu_ctx* c = nullptr;
+  aotcu_model_head head;
+  std::vector<aotcu_layer> layers;
+  size_t n_ctx = 0, max_batch = 1;
+  uint8_t* d_weights = nullptr;
+  size_t weights_len = 0;
+  float* bufs[AOTCU_N_BUFS] = {};
+  size_t buf_len[AOTCU_N_BUFS] = {};
+  float* rope_table = nullptr;        // n_ctx x rot_dim
+  float* rope_table_local = nullptr;  // swa layers
+  uint8_t* aqk = nullptr;             // Q8_K block images, max_batch rows of max(dim, q_dim, hidden)
+  uint8_t* aq0 = nullptr;             // Q8_0 block images
+  float* attn_scratch = nullptr;      // scores for contexts that do not fit shared memory
+  int* d_step = nullptr;              // {token, pos, n_generated}
+  int* d_tokens = nullptr;            // prompt batch ids
+  int* d_history = nullptr;           // generated ids
+  int* d_out_token = nullptr;
+  int* h_pinned = nullptr;            // staging for step / tokens
+  size_t history_cap = 0;
+  bool need_q8k = false, need_q80 = false;
+  // What the quantized-activation buffers currently hold.
+  struct QSrc {
+    const float* ptr = nullptr;
+    size_t n = 0, m = 0;
+    bool q8k = false, q80 = false;
+  } qsrc;
+  bool use_graph = true;
+  cudaGraphExec_t decode_graph[2] = {nullptr, nullptr};  // [want_logits]
+  cudaGraphExec_t gen_graph = nullptr;
+  uint64_t decode_graph_kernels[2] = {0, 0};  // kernel nodes per replay
+  uint64_t gen_graph_kernels = 0;
+  int smem_scores = 0;
+};
+
+static size_t xb_width(const aotcu_dims& d) {
+  size_t qd = (size_t)d.n_head * d.head_dim;
+  return (size_t)d.dim > qd ? (size_t)d.dim : qd;
+}
+
+static int tensor_check(const aotcu_gpu* g, const aotcu_tensor& t, const char* name) {
+  ARG_CHECK(t.kind >= 0 && t.kind < N_KINDS, "tensor %s: unknown kind %d", name, t.kind);
+  ARG_CHECK(t.cols % (uint64_t)kind_block(t.kind) == 0, "tensor %s: cols not a multiple of the block size", name);
+  uint64_t need = t.rows * kind_row_bytes(t.kind, t.cols);
+  ARG_CHECK(t.off + need <= g->weights_len, "tensor %s lies outside the weights (%llu + %llu > %zu)", name,
+            (unsigned long long)t.off, (unsigned long long)need, g->weights_len);
+  ARG_CHECK(t.off % 32 == 0, "tensor %s: offset %llu is not 32-byte aligned", name, (unsigned long long)t.off);
+  return 0;
+}
+
+static const uint8_t* wptr(const aotcu_gpu* g, const aotcu_tensor& t) { return g->d_weights + t.off; }
+static const float* wf32(const aotcu_gpu* g, const aotcu_tensor& t) { return reinterpret_cast<const float*>(g->d_weights + t.off); }
+
+static void note_write(aotcu_gpu* g, const float* p) {
+  // A write to the buffer whose quantized image is cached invalidates the image.
+  if (g->qsrc.ptr && p == g->qsrc.ptr) g->qsrc = aotcu_gpu::QSrc();
+}
+
+// Make sure the block images of `src` (m rows of n floats) exist for `act`.
+static int ensure_quantized(aotcu_gpu* g, const float* src, size_t n, size_t m, int act) {
+  if (act == ACT_F32) return 0;
+  aotcu_ctx* c = g->c;
+  bool same = g->qsrc.ptr == src && g->qsrc.n == n && g->qsrc.m == m;
+  if (!same) {
+    g->qsrc = aotcu_gpu::QSrc();
+    g->qsrc.ptr = src;
+    g->qsrc.n = n;
+    g->qsrc.m = m;
+  }
+  if (act == ACT_Q8_K && !g->qsrc.q8k) {
+    ARG_CHECK(n % 256 == 0, "row length %zu is not a multiple of 256", n);
+    int nblk = (int)(n * m / 256);
+    if (int rc = launch(c, quantize_q8k_kernel, dim3(grid_for(c, nblk, 8)), dim3(256), 0, src, g->aqk, nblk, 1)) return rc;
+    g->qsrc.q8k = true;
+  }
+  if (act == ACT_Q8_0 && !g->qsrc.q80) {
+    ARG_CHECK(n % 32 == 0, "row length %zu is not a multiple of 32", n);
+    int nblk = (int)(n * m / 32);
+    if (int rc = launch(c, quantize_q80_kernel, dim3(grid_for(c, nblk, 8)), dim3(256), 0, src, g->aq0, nblk, 1)) return rc;
+    g->qsrc.q80 = true;
+  }
+  return 0;
+}
+
+static const void* act_images(const aotcu_gpu* g, int act, const float* src) {
+  return act == ACT_Q8_K ? (const void*)g->aqk : act == ACT_Q8_0 ? (const void*)g->aq0 : (const void*)src;
+}
+
+static int gpu_rmsnorm(aotcu_gpu* g, float* dst, size_t dst_stride, const float* src, size_t src_stride, const float* w,
+                       size_t n, size_t m, float eps, int accumulate, bool quantize) {
+  aotcu_ctx* c = g->c;
+  RmsnormParams P = {};
+  P.x = src;
+  P.w = w;
+  P.out = dst;
+  P.n = (int)n;
+  P.x_stride = (int)src_stride;
+  P.out_stride = (int)dst_stride;
+  P.eps = eps;
+  P.accumulate = accumulate;
+  bool q = quantize && !accumulate && dst_stride == n;
+  P.q8k_out = (q && g->need_q8k && n % 256 == 0) ? g->aqk : nullptr;
+  P.q80_out = (q && g->need_q80 && n % 32 == 0) ? g->aq0 : nullptr;
+  size_t smem = (2 * n + 4) * sizeof(float);
+  ARG_CHECK(smem <= c->max_smem, "rmsnorm row of %zu floats does not fit shared memory", n);
+  note_write(g, dst);
+  if (int rc = launch(c, rmsnorm_kernel, dim3((unsigned)m), dim3(256), smem, P)) return rc;
+  if (q) {
+    g->qsrc = aotcu_gpu::QSrc();
+    g->qsrc.ptr = dst;
+    g->qsrc.n = n;
+    g->qsrc.m = m;
+    g->qsrc.q8k = P.q8k_out != nullptr;
+    g->qsrc.q80 = P.q80_out != nullptr;
+  }
+  return 0;
+}
+
+// dst (+)= W . src for m rows (Gpu::mv / Gpu::matmul).
+static int gpu_matmul(aotcu_gpu* g, float* dst, const aotcu_tensor& t, const float* src, size_t m, int accumulate) {
+  int act = kind_act(t.kind);
+  if (int rc = ensure_quantized(g, src, t.cols, m, act)) return rc;
+  GemvCall call;
+  call.seg[0] = GemvSeg{wptr(g, t), dst, (int)t.rows, t.kind};
+  call.nseg = 1;
+  call.cols = t.cols;
+  call.x = act_images(g, act, src);
+  call.x_mode = 1;
+  call.m = m;
+  call.epilogue = accumulate ? EPI_ACCUM : EPI_STORE;
+  note_write(g, dst);
+  return launch_gemv(g->c, call);
+}
+
+static int gpu_mv3(aotcu_gpu* g, float* const dst[3], const aotcu_tensor* const t[3], const float* src, size_t m) {
+  // One launch per activation format (the reference fuses only when all three kinds
+  // are equal, emit.rs:256-272; mixed K-quants still share Q8_K activations here).
+  bool done[3] = {false, false, false};
+  for (int a = 0; a < 3; a++) {
+    if (done[a]) continue;
+    int act = kind_act(t[a]->kind);
+    GemvCall call;
+    call.nseg = 0;
+    for (int b = a; b < 3; b++) {
+      if (!done[b] && kind_act(t[b]->kind) == act && t[b]->cols == t[a]->cols) {
+        call.seg[call.nseg++] = GemvSeg{wptr(g, *t[b]), dst[b], (int)t[b]->rows, t[b]->kind};
+        done[b] = true;
+        note_write(g, dst[b]);
+      }
+    }
+    if (int rc = ensure_quantized(g, src, t[a]->cols, m, act)) return rc;
+    call.cols = t[a]->cols;
+    call.x = act_images(g, act, src);
+    call.x_mode = 1;
+    call.m = m;
+    if (int rc = launch_gemv(g->c, call)) return rc;
+  }
+  return 0;
+}
+
+static int gpu_gate_up(aotcu_gpu* g, float* hb, float* hb2, const aotcu_tensor& gate, const aotcu_tensor& up,
+                       const float* src, size_t m) {
+  ARG_CHECK(!g->head.dims.gelu, "GeGLU models are not supported yet");
+  aotcu_ctx* c = g->c;
+  if (gate.kind == up.kind && gate.rows == up.rows && gate.cols == up.cols) {
+    int act = kind_act(gate.kind);
+    if (int rc = ensure_quantized(g, src, gate.cols, m, act)) return rc;
+    GemvCall call;
+    call.seg[0] = GemvSeg{wptr(g, gate), hb, (int)gate.rows, gate.kind};
+    call.seg[1] = GemvSeg{wptr(g, up), hb2, (int)up.rows, up.kind};
+    call.nseg = 2;
+    call.pair = 1;
+    call.cols = gate.cols;
+    call.x = act_images(g, act, src);
+    call.x_mode = 1;
+    call.m = m;
+    call.epilogue = EPI_SILU_MUL;
+    note_write(g, hb);
+    note_write(g, hb2);
+    return launch_gemv(c, call);
+  }
+  if (int rc = gpu_matmul(g, hb, gate, src, m, 0)) return rc;
+  if (int rc = gpu_matmul(g, hb2, up, src, m, 0)) return rc;
+  size_t n = m * gate.rows;
+  return launch(c, silu_mul_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, hb, (const float*)hb2, n);
+}
+
+static int gpu_qk_post(aotcu_gpu* g, size_t li, const int* pos_ptr, size_t pos0, size_t m, bool batch) {
+  const aotcu_dims& d = g->head.dims;
+  const aotcu_layer& l = g->layers[li];
+  size_t kvd = (size_t)d.n_kv_head * d.head_dim;
+  QkPostParams P = {};
+  P.q = g->bufs[batch ? AOTCU_BUF_BQ : AOTCU_BUF_Q];
+  P.k = g->bufs[batch ? AOTCU_BUF_BK : AOTCU_BUF_K];
+  P.v = g->bufs[batch ? AOTCU_BUF_BV : AOTCU_BUF_V];
+  P.k_cache = g->bufs[AOTCU_BUF_KCACHE] + li * g->n_ctx * kvd;
+  P.v_cache = g->bufs[AOTCU_BUF_VCACHE] + li * g->n_ctx * kvd;
+  P.q_norm = d.qk_norm ? wf32(g, l.q_norm) : nullptr;
+  P.k_norm = d.qk_norm ? wf32(g, l.k_norm) : nullptr;
+  P.rope_table = l.local_attn ? g->rope_table_local : g->rope_table;
+  P.pos_ptr = pos_ptr;
+  P.pos0 = (int)pos0;
+  P.n_head = d.n_head;
+  P.n_kv_head = d.n_kv_head;
+  P.head_dim = d.head_dim;
+  P.rot_dim = d.rot_dim;
+  P.neox = d.rope_neox;
+  P.eps = d.eps;
+  note_write(g, P.q);
+  return launch(g->c, qk_post_kernel, dim3(d.n_head + d.n_kv_head, (unsigned)m), dim3(128), 0, P);
+}
+
+static int launch_attention(aotcu_ctx* c, float* out, const float* q, const float* kc, const float* vc, float* scratch,
+                            const int* pos_ptr, size_t pos0, size_t m, int n_head, int n_kv_head, int head_dim,
+                            size_t n_ctx, size_t window, int smem_scores) {
+  AttnParams P = {};
+  P.out = out;
+  P.q = q;
+  P.k_cache = kc;
+  P.v_cache = vc;
+  P.scratch = scratch;
+  P.pos_ptr = pos_ptr;
+  P.pos0 = (int)pos0;
+  P.n_head = n_head;
+  P.n_kv_head = n_kv_head;
+  P.head_dim = head_dim;
+  P.ctx = (int)n_ctx;
+  P.window = (int)window;
+  P.smem_scores = smem_scores;
+  P.scale = 1.0f / sqrtf((float)head_dim);
+  size_t smem = ((size_t)head_dim + (size_t)smem_scores + 4) * sizeof(float);
+  return launch(c, attention_kernel, dim3(n_head, (unsigned)m), dim3(256), smem, P);
+}
+
+static int gpu_attention(aotcu_gpu* g, float* out, const float* q, size_t li, const int* pos_ptr, size_t pos0, size_t m,
+                         size_t window) {
+  const aotcu_dims& d = g->head.dims;
+  size_t kvd = (size_t)d.n_kv_head * d.head_dim;
+  note_write(g, out);
+  return launch_attention(g->c, out, q, g->bufs[AOTCU_BUF_KCACHE] + li * g->n_ctx * kvd,
+                          g->bufs[AOTCU_BUF_VCACHE] + li * g->n_ctx * kvd, g->attn_scratch, pos_ptr, pos0, m, d.n_head,
+                          d.n_kv_head, d.head_dim, g->n_ctx, window, g->smem_scores);
+}
+
+// ---- the generated forward pass, interpreted (emit.rs) -----------------------------------------------
+// One transformer block for m tokens. `pos_ptr` (device) is used by decode steps so a
+// captured graph can be replayed for any position; batches pass pos0 by value.
+static int layer_forward(aotcu_gpu* g, size_t li, const int* pos_ptr, size_t pos0, size_t m, bool batch) {
+  const aotcu_dims& d = g->head.dims;
+  const aotcu_layer& l = g->layers[li];
+  aotcu_ctx* c = g->c;
+  const size_t dim = d.dim, qd = (size_t)d.n_head * d.head_dim, kvd = (size_t)d.n_kv_head * d.head_dim;
+  float* x = g->bufs[batch ? AOTCU_BUF_BX : AOTCU_BUF_X];
+  float* xb = g->bufs[batch ? AOTCU_BUF_BXB : AOTCU_BUF_XB];
+  float* xb2 = g->bufs[batch ? AOTCU_BUF_BXB2 : AOTCU_BUF_XB2];
+  float* q = g->bufs[batch ? AOTCU_BUF_BQ : AOTCU_BUF_Q];
+  float* k = g->bufs[batch ? AOTCU_BUF_BK : AOTCU_BUF_K];
+  float* v = g->bufs[batch ? AOTCU_BUF_BV : AOTCU_BUF_V];
+  float* hb = g->bufs[batch ? AOTCU_BUF_BHB : AOTCU_BUF_HB];
+  float* hb2 = g->bufs[batch ? AOTCU_BUF_BHB2 : AOTCU_BUF_HB2];
+  const size_t window = l.local_attn ? (size_t)d.swa_window : 0;
+
+  // emit.rs:250-272
+  if (int rc = gpu_rmsnorm(g, xb, dim, x, dim, wf32(g, l.attn_norm), dim, m, d.eps, 0, true)) return rc;
+  float* const qkv[3] = {q, k, v};
+  const aotcu_tensor* const wqkv[3] = {&l.wq, &l.wk, &l.wv};
+  if (int rc = gpu_mv3(g, qkv, wqkv, xb, m)) return rc;
+  if (d.qkv_bias) {  // emit.rs:273-277
+    if (int rc = launch(c, add_bias_rows_kernel, dim3(grid_for(c, qd * m, 256)), dim3(256), 0, q, wf32(g, l.bq), qd, m)) return rc;
+    if (int rc = launch(c, add_bias_rows_kernel, dim3(grid_for(c, kvd * m, 256)), dim3(256), 0, k, wf32(g, l.bk), kvd, m)) return rc;
+    if (int rc = launch(c, add_bias_rows_kernel, dim3(grid_for(c, kvd * m, 256)), dim3(256), 0, v, wf32(g, l.bv), kvd, m)) return rc;
+  }
+  // emit.rs:278-286: q/k norm, rope, store_kv
+  if (int rc = gpu_qk_post(g, li, pos_ptr, pos0, m, batch)) return rc;
+  // emit.rs:287
+  if (int rc = gpu_attention(g, xb, q, li, pos_ptr, pos0, m, window)) return rc;
+  // emit.rs:288-295
+  if (d.post_norms) {
+    if (int rc = gpu_matmul(g, xb2, l.wo, xb, m, 0)) return rc;
+    if (int rc = gpu_rmsnorm(g, x, dim, xb2, dim, wf32(g, l.attn_post_norm), dim, m, d.eps, 1, false)) return rc;
+  } else {
+    if (int rc = gpu_matmul(g, x, l.wo, xb, m, 1)) return rc;
+  }
+  // emit.rs:297-331
+  if (int rc = gpu_rmsnorm(g, xb, dim, x, dim, wf32(g, l.ffn_norm), dim, m, d.eps, 0, true)) return rc;
+  if (int rc = gpu_gate_up(g, hb, hb2, l.gate, l.up, xb, m)) return rc;
+  if (d.post_norms) {
+    if (int rc = gpu_matmul(g, xb2, l.down, hb, m, 0)) return rc;
+    if (int rc = gpu_rmsnorm(g, x, dim, xb2, dim, wf32(g, l.ffn_post_norm), dim, m, d.eps, 1, false)) return rc;
+  } else {
+    if (int rc = gpu_matmul(g, x, l.down, hb, m, 1)) return rc;
+  }
+  return 0;
+}
+
+static int embed(aotcu_gpu* g, float* dst, const int* d_tokens, size_t m) {
+  const aotcu_dims& d = g->head.dims;
+  const aotcu_tensor& e = g->head.token_embd;
+  note_write(g, dst);
+  return launch(g->c, embed_rows_kernel, dim3((d.dim + 255) / 256, (unsigned)m), dim3(256), 0, dst, wptr(g, e), d_tokens,
+                (int)e.kind, (int)d.dim, kind_row_bytes(e.kind, e.cols), sqrtf((float)d.dim), (int)d.embd_scale);
+}
+
+static int logits_from(aotcu_gpu* g, const float* xrow) {
+  const aotcu_dims& d = g->head.dims;
+  const aotcu_tensor& out_t = g->head.output.present ? g->head.output : g->head.token_embd;
+  float* xb = g->bufs[AOTCU_BUF_XB];
+  if (int rc = gpu_rmsnorm(g, xb, d.dim, xrow, d.dim, wf32(g, g->head.output_norm), d.dim, 1, d.eps, 0, true)) return rc;
+  return gpu_matmul(g, g->bufs[AOTCU_BUF_LOGITS], out_t, xb, 1, 0);
+}
+
+// Enqueue one decode step reading {token, pos} from g->d_step.
+static int enqueue_decode(aotcu_gpu* g, int want_logits, bool with_argmax) {
+  const aotcu_dims& d = g->head.dims;
+  g->qsrc = aotcu_gpu::QSrc();
+  if (int rc = embed(g, g->bufs[AOTCU_BUF_X], g->d_step, 1)) return rc;
+  for (int i = 0; i < d.n_layer; i++)
+    if (int rc = layer_forward(g, (size_t)i, g->d_step + 1, 0, 1, false)) return rc;
+  if (want_logits) {
+    if (int rc = logits_from(g, g->bufs[AOTCU_BUF_X])) return rc;
+    if (with_argmax) {
+      if (int rc = launch(g->c, argmax_kernel, dim3(1), dim3(1024), 0, (const float*)g->bufs[AOTCU_BUF_LOGITS], (int)d.vocab,
+                          g->d_out_token, g->d_step, g->d_history, (int)g->history_cap))
+        return rc;
+    }
+  }
+  g->qsrc = aotcu_gpu::QSrc();
+  return 0;
+}
+
+static int capture_graph(aotcu_gpu* g, cudaGraphExec_t* exec, uint64_t* n_kernels, int want_logits, bool with_argmax) {
+  aotcu_ctx* c = g->c;
+  cudaGraph_t graph = nullptr;
+  CU_TRY(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+  uint64_t before = c->launches;
+  int rc = enqueue_decode(g, want_logits, with_argmax);
+  cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+  *n_kernels = c->launches - before;
+  c->launches = before;  // captured, not launched
+  if (rc) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+  e = cudaGraphInstantiate(exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+static int check_device_errors(aotcu_ctx* c) {
+  int h = 0;
+  CU_TRY(cudaMemcpyAsync(&h, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  if (h) {
+    CU_TRY(cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream));
+    if (h & DEVERR_MBAR_TIMEOUT) return fail(AOTCU_ERR_TIMEOUT, "a bounded device-side wait expired (error word %d)", h);
+    return fail(AOTCU_ERR_CUDA, "device error word %d", h);
+  }
+  return 0;
+}
+
+// =====================================================================================
+// extern "C"
+// =====================================================================================
+extern "C" {
+
+const char* aotcu_last_error(void) { return g_last_error.c_str(); }
+const char* aotcu_version(void) { return "aot-cuda 0.1 (sm_100a)"; }
+size_t aotcu_row_bytes(int kind, size_t cols) { return kind_row_bytes(kind, cols); }
+
+int aotcu_init(int device, aotcu_ctx** out) {
+  ARG_CHECK(out, "out is NULL");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0)
+    return fail(AOTCU_ERR_CUDA, "no CUDA device (%s); this library has no CPU path", e == cudaSuccess ? "count 0" : cudaGetErrorString(e));
+  ARG_CHECK(device >= 0 && device < n, "device %d out of range (have %d)", device, n);
+  CU_TRY(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  CU_TRY(cudaGetDeviceProperties(&prop, device));
+  if (prop.major < 10) return fail(AOTCU_ERR_UNSUPPORTED, "device %s is sm_%d%d; this library is built for sm_100a only", prop.name, prop.major, prop.minor);
+  aotcu_ctx* c = new aotcu_ctx();
+  c->device = device;
+  c->n_sm = prop.multiProcessorCount;
+  c->max_smem = prop.sharedMemPerBlockOptin;
+  CU_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  CU_TRY(cudaMalloc(&c->d_err, sizeof(int)));
+  CU_TRY(cudaMemset(c->d_err, 0, sizeof(int)));
+  CU_TRY(cudaFuncSetAttribute(gemv_q8k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  CU_TRY(cudaFuncSetAttribute(gemv_q80_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  CU_TRY(cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  CU_TRY(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  *out = c;
+  return 0;
+}
+
+void aotcu_free(aotcu_ctx* c) {
+  if (!c) return;
+  cudaSetDevice(c->device);
+  if (c->stream) {
+    cudaStreamSynchronize(c->stream);
+    cudaStreamDestroy(c->stream);
+  }
+  cudaFree(c->d_err);
+  delete c;
+}
+
+int aotcu_sync(aotcu_ctx* c) {
+  ARG_CHECK(c, "ctx is NULL");
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  return 0;
+}
+
+int aotcu_malloc(aotcu_ctx* c, size_t bytes, void** p) {
+  ARG_CHECK(c && p, "NULL argument");
+  if (int rc = ctx_set_device(c)) return rc;
+  CU_TRY(cudaMalloc(p, bytes + WEIGHT_PAD));
+  CU_TRY(cudaMemsetAsync((uint8_t*)*p + bytes, 0, WEIGHT_PAD, c->stream));
+  return 0;
+}
+
+int aotcu_dev_free(aotcu_ctx* c, void* p) {
+  ARG_CHECK(c, "ctx is NULL");
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  CU_TRY(cudaFree(p));
+  return 0;
+}
+
+int aotcu_h2d(aotcu_ctx* c, void* dst, const void* src, size_t bytes) {
+  ARG_CHECK(c && (bytes == 0 || (dst && src)), "NULL argument");
+  CU_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->stream));
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  return 0;
+}
+
+int aotcu_d2h(aotcu_ctx* c, void* dst, const void* src, size_t bytes) {
+  ARG_CHECK(c && (bytes == 0 || (dst && src)), "NULL argument");
+  CU_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  return 0;
+}
+
+int aotcu_device_status(aotcu_ctx* c) {
+  ARG_CHECK(c, "ctx is NULL");
+  return check_device_errors(c);
+}
+
+// ---- kernel level ---------------------------------------------------------------------
+int aotcu_quantize_q8_0(aotcu_ctx* c, const float* x, size_t n, aotcu_block_q8_0* out) {
+  ARG_CHECK(c && x && out, "NULL argument");
+  ARG_CHECK(n % 32 == 0, "n (%zu) is not a multiple of 32", n);
+  if (n == 0) return 0;
+  int nblk = (int)(n / 32);
+  return launch(c, quantize_q80_kernel, dim3(grid_for(c, nblk, 8)), dim3(256), 0, x, (uint8_t*)out, nblk, 0);
+}
+
+int aotcu_quantize_q8_k(aotcu_ctx* c, const float* x, size_t n, aotcu_block_q8_k* out) {
+  ARG_CHECK(c && x && out, "NULL argument");
+  ARG_CHECK(n % 256 == 0, "n (%zu) is not a multiple of 256", n);
+  if (n == 0) return 0;
+  int nblk = (int)(n / 256);
+  return launch(c, quantize_q8k_kernel, dim3(grid_for(c, nblk, 8)), dim3(256), 0, x, (uint8_t*)out, nblk, 0);
+}
+
+int aotcu_dequant_rows(aotcu_ctx* c, int kind, const uint8_t* table, const int32_t* row_ids, size_t n_rows, size_t cols,
+                       float* out) {
+  ARG_CHECK(c && table && row_ids && out, "NULL argument");
+  ARG_CHECK(kind >= 0 && kind < N_KINDS, "unknown kind %d", kind);
+  ARG_CHECK(cols % (size_t)kind_block(kind) == 0, "cols not a multiple of the block size");
+  if (n_rows == 0 || cols == 0) return 0;
+  return launch(c, embed_rows_kernel, dim3((unsigned)((cols + 255) / 256), (unsigned)n_rows), dim3(256), 0, out, table,
+                (const int*)row_ids, kind, (int)cols, kind_row_bytes(kind, cols), 1.0f, 0);
+}
+
+int aotcu_matvec(aotcu_ctx* c, int kind, float* out, const uint8_t* w, const void* x, size_t rows, size_t cols) {
+  return aotcu_matmul(c, kind, out, w, x, 1, rows, cols);
+}
+
+#define MATVEC_FN(name, KIND, XT)                                                                              \
+  int aotcu_matvec_##name(aotcu_ctx* c, float* out, const uint8_t* w, const XT* x, size_t rows, size_t cols) { \
+    return aotcu_matmul(c, KIND, out, w, x, 1, rows, cols);                                                    \
+  }
+MATVEC_FN(q4_0, AOTCU_Q4_0, aotcu_block_q8_0)
+MATVEC_FN(q5_0, AOTCU_Q5_0, aotcu_block_q8_0)
+MATVEC_FN(q8_0, AOTCU_Q8_0, aotcu_block_q8_0)
+MATVEC_FN(q4_k, AOTCU_Q4_K, aotcu_block_q8_k)
+MATVEC_FN(q5_k, AOTCU_Q5_K, aotcu_block_q8_k)
+MATVEC_FN(q6_k, AOTCU_Q6_K, aotcu_block_q8_k)
+MATVEC_FN(f16, AOTCU_F16, float)
+MATVEC_FN(bf16, AOTCU_BF16, float)
+MATVEC_FN(f32, AOTCU_F32, float)
+
+int aotcu_matmul(aotcu_ctx* c, int kind, float* out, const uint8_t* w, const void* xs, size_t m, size_t rows,
+                 size_t cols) {
+  ARG_CHECK(c, "ctx is NULL");
+  ARG_CHECK(kind >= 0 && kind < N_KINDS, "unknown kind %d", kind);
+  if (rows == 0 || m == 0) return 0;
+  GemvCall call;
+  call.seg[0] = GemvSeg{w, out, (int)rows, kind};
+  call.nseg = 1;
+  call.cols = cols;
+  call.x = xs;
+  call.x_mode = 0;
+  call.m = m;
+  return launch_gemv(c, call);
+}
+
+int aotcu_matvec2(aotcu_ctx* c, int kind, float* out_a, float* out_b, const uint8_t* w_a, const uint8_t* w_b,
+                  const void* x, size_t rows, size_t cols) {
+  ARG_CHECK(c, "ctx is NULL");
+  ARG_CHECK(kind >= 0 && kind < N_KINDS, "unknown kind %d", kind);
+  if (rows == 0) return 0;
+  GemvCall call;
+  call.seg[0] = GemvSeg{w_a, out_a, (int)rows, kind};
+  call.seg[1] = GemvSeg{w_b, out_b, (int)rows, kind};
+  call.nseg = 2;
+  call.pair = 1;
+  call.cols = cols;
+  call.x = x;
+  return launch_gemv(c, call);
+}
+
+int aotcu_matvec3(aotcu_ctx* c, const int kinds[3], float* const outs[3], const uint8_t* const ws[3], const void* x,
+                  const size_t rows[3], size_t cols) {
+  ARG_CHECK(c && kinds && outs && ws && rows, "NULL argument");
+  GemvCall call;
+  call.nseg = 0;
+  for (int i = 0; i < 3; i++) {
+    ARG_CHECK(kinds[i] >= 0 && kinds[i] < N_KINDS, "unknown kind %d", kinds[i]);
+    if (rows[i] == 0) continue;
+    call.seg[call.nseg++] = GemvSeg{ws[i], outs[i], (int)rows[i], kinds[i]};
+  }
+  if (call.nseg == 0) return 0;
+  call.cols = cols;
+  call.x = x;
+  return launch_gemv(c, call);
+}
+
+int aotcu_block_sums(aotcu_ctx* c, int kind, const uint8_t* w, const void* x, size_t rows, size_t cols, int32_t* sumi,
+                     int32_t* summ) {
+  ARG_CHECK(c && w && x && sumi, "NULL argument");
+  ARG_CHECK(kind >= AOTCU_Q4_0 && kind <= AOTCU_Q6_K, "kind %d has no integer block sums", kind);
+  ARG_CHECK(cols % (size_t)kind_block(kind) == 0, "cols not a multiple of the block size");
+  int nb = (int)(cols / kind_block(kind));
+  if (rows == 0 || nb == 0) return 0;
+  return launch(c, block_sums_kernel, dim3(grid_for(c, rows * nb, 128)), dim3(128), 0, kind, w, (const uint8_t*)x,
+                (int)rows, nb, sumi, summ);
+}
+
+int aotcu_rmsnorm(aotcu_ctx* c, float* out, const float* x, const float* w, size_t n, size_t m, float eps) {
+  ARG_CHECK(c && out && x && w, "NULL argument");
+  if (n == 0 || m == 0) return 0;
+  RmsnormParams P = {};
+  P.x = x;
+  P.w = w;
+  P.out = out;
+  P.n = (int)n;
+  P.x_stride = P.out_stride = (int)n;
+  P.eps = eps;
+  size_t smem = (2 * n + 4) * sizeof(float);
+  ARG_CHECK(smem <= c->max_smem, "row of %zu floats does not fit shared memory", n);
+  return launch(c, rmsnorm_kernel, dim3((unsigned)m), dim3(256), smem, P);
+}
+
+int aotcu_rmsnorm_heads(aotcu_ctx* c, float* x, const float* w, size_t n_heads, size_t head_dim, float eps) {
+  ARG_CHECK(c && x && w, "NULL argument");
+  ARG_CHECK(head_dim >= 1 && head_dim <= 256, "head_dim %zu out of range (1..256)", head_dim);
+  if (n_heads == 0) return 0;
+  return launch(c, rmsnorm_heads_kernel, dim3((unsigned)n_heads), dim3(128), 0, x, w, (int)head_dim, eps);
+}
+
+int aotcu_rope(aotcu_ctx* c, float* x, size_t m, size_t n_heads, size_t head_dim, size_t rot_dim, const float* cs,
+               int neox) {
+  ARG_CHECK(c && x && cs, "NULL argument");
+  ARG_CHECK(rot_dim <= head_dim && rot_dim % 2 == 0, "rot_dim %zu invalid for head_dim %zu", rot_dim, head_dim);
+  size_t total = m * n_heads * (rot_dim / 2);
+  if (total == 0) return 0;
+  return launch(c, rope_kernel, dim3(grid_for(c, total, 256)), dim3(256), 0, x, (int)m, (int)n_heads, (int)head_dim,
+                (int)rot_dim, cs, (int)rot_dim, neox);
+}
+
+int aotcu_silu_mul(aotcu_ctx* c, float* h, const float* up, size_t n) {
+  ARG_CHECK(c && h && up, "NULL argument");
+  if (n == 0) return 0;
+  return launch(c, silu_mul_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, h, up, n);
+}
+
+int aotcu_add_inplace(aotcu_ctx* c, float* x, const float* y, size_t n) {
+  ARG_CHECK(c && x && y, "NULL argument");
+  if (n == 0) return 0;
+  return launch(c, add_inplace_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, x, y, n);
+}
+
+int aotcu_add_bias_rows(aotcu_ctx* c, float* x, const float* b, size_t n, size_t m) {
+  ARG_CHECK(c && x && b, "NULL argument");
+  if (n * m == 0) return 0;
+  return launch(c, add_bias_rows_kernel, dim3(grid_for(c, n * m, 256)), dim3(256), 0, x, b, n, m);
+}
+
+int aotcu_scale_inplace(aotcu_ctx* c, float* x, float s, size_t n) {
+  ARG_CHECK(c && x, "NULL argument");
+  if (n == 0) return 0;
+  return launch(c, scale_inplace_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, x, s, n);
+}
+
+int aotcu_attention(aotcu_ctx* c, float* out, const float* q, const float* k_cache, const float* v_cache,
+                    size_t n_head, size_t n_kv_head, size_t head_dim, size_t ctx_len, size_t pos0, size_t m,
+                    size_t window) {
+  ARG_CHECK(c && out && q && k_cache && v_cache, "NULL argument");
+  ARG_CHECK(n_kv_head > 0 && n_head % n_kv_head == 0, "n_head must be a multiple of n_kv_head");
+  ARG_CHECK(head_dim % 4 == 0 && head_dim <= 256, "head_dim %zu must be a multiple of 4, at most 256", head_dim);
+  ARG_CHECK(pos0 + m <= ctx_len, "positions exceed the context");
+  if (m == 0) return 0;
+  size_t cap = (c->max_smem / sizeof(float)) - head_dim - 64;
+  ARG_CHECK(ctx_len <= cap, "context %zu too long for the stand-alone attention entry point (max %zu)", ctx_len, cap);
+  return launch_attention(c, out, q, k_cache, v_cache, nullptr, nullptr, pos0, m, (int)n_head, (int)n_kv_head,
+                          (int)head_dim, ctx_len, window, (int)ctx_len);
+}
+
+int aotcu_argmax(aotcu_ctx* c, const float* x, size_t n, int32_t* out_token) {
+  ARG_CHECK(c && x && out_token, "NULL argument");
+  ARG_CHECK(n >= 1 && n < (1u << 31), "n out of range");
+  return launch(c, argmax_kernel, dim3(1), dim3(1024), 0, x, (int)n, (int*)out_token, (int*)nullptr, (int*)nullptr, 0);
+}
+
+// ---- backend level -----------------------------------------------------------------------
+int aotcu_gpu_new(aotcu_ctx* c, const aotcu_model_head* head, const aotcu_layer* layers, const uint8_t* weights,
+                  size_t weights_len, size_t n_ctx, size_t max_batch, aotcu_gpu** out) {
+  ARG_CHECK(c && head && layers && weights && out, "NULL argument");
+  const aotcu_dims& d = head->dims;
+  ARG_CHECK(d.dim > 0 && d.hidden > 0 && d.n_layer > 0 && d.n_head > 0 && d.n_kv_head > 0 && d.head_dim > 0 && d.vocab > 0,
+            "dimensions must be positive");
+  ARG_CHECK(d.n_head % d.n_kv_head == 0, "n_head must be a multiple of n_kv_head");
+  ARG_CHECK(d.head_dim % 4 == 0 && d.head_dim <= 256, "head_dim %d must be a multiple of 4, at most 256", d.head_dim);
+  ARG_CHECK(d.rot_dim % 2 == 0 && d.rot_dim <= d.head_dim, "rot_dim %d invalid", d.rot_dim);
+  ARG_CHECK(n_ctx >= 1, "context must hold at least one token");
+  if (d.gelu) return fail(AOTCU_ERR_UNSUPPORTED, "GeGLU (gemma) models are not supported yet");
+  if (int rc = ctx_set_device(c)) return rc;
+  aotcu_gpu* g = new aotcu_gpu();
+  g->c = c;
+  g->head = *head;
+  g->layers.assign(layers, layers + d.n_layer);
+  g->n_ctx = n_ctx;
+  g->max_batch = max_batch < 1 ? 1 : max_batch;
+  g->weights_len = weights_len;
+
+  auto bail = [&](int rc) {
+    aotcu_gpu_free(g);
+    return rc;
+  };
+  // Tensor table checks (the reference trusts its generator; a C caller may not be one).
+  {
+    struct N {
+      const char* n;
+      const aotcu_tensor* t;
+      bool opt;
+    };
+    std::vector<N> ts = {{"token_embd", &g->head.token_embd, false}, {"output_norm", &g->head.output_norm, false},
+                         {"output", &g->head.output, true}, {"rope_freqs", &g->head.rope_freqs, true}};
+    for (auto& l : g->layers) {
+      ts.push_back({"attn_norm", &l.attn_norm, false});
+      ts.push_back({"wq", &l.wq, false});
+      ts.push_back({"wk", &l.wk, false});
+      ts.push_back({"wv", &l.wv, false});
+      ts.push_back({"wo", &l.wo, false});
+      ts.push_back({"ffn_norm", &l.ffn_norm, false});
+      ts.push_back({"gate", &l.gate, false});
+      ts.push_back({"up", &l.up, false});
+      ts.push_back({"down", &l.down, false});
+      ts.push_back({"bq", &l.bq, !d.qkv_bias});
+      ts.push_back({"bk", &l.bk, !d.qkv_bias});
+      ts.push_back({"bv", &l.bv, !d.qkv_bias});
+      ts.push_back({"q_norm", &l.q_norm, !d.qk_norm});
+      ts.push_back({"k_norm", &l.k_norm, !d.qk_norm});
+      ts.push_back({"attn_post_norm", &l.attn_post_norm, !d.post_norms});
+      ts.push_back({"ffn_post_norm", &l.ffn_post_norm, !d.post_norms});
+    }
+    for (auto& e : ts) {
+      if (e.opt && !e.t->present) continue;
+      if (int rc = tensor_check(g, *e.t, e.n)) return bail(rc);
+      int a = kind_act(e.t->kind);
+      if (e.t->rows > 1 || e.t == &g->head.token_embd) {
+        g->need_q8k |= a == ACT_Q8_K;
+        g->need_q80 |= a == ACT_Q8_0;
+      }
+    }
+  }
+  const size_t dim = d.dim, qd = (size_t)d.n_head * d.head_dim, kvd = (size_t)d.n_kv_head * d.head_dim;
+  const size_t xbw = xb_width(d), b = g->max_batch > 1 ? g->max_batch : 0;
+  const size_t lens[AOTCU_N_BUFS] = {dim, xbw, dim, qd, kvd, kvd, (size_t)d.hidden, (size_t)d.hidden, (size_t)d.vocab,
+                                     (size_t)d.n_layer * n_ctx * kvd, (size_t)d.n_layer * n_ctx * kvd, (size_t)d.rot_dim,
+                                     b * dim, b * xbw, b * dim, b * qd, b * kvd, b * kvd, b * d.hidden, b * d.hidden,
+                                     b * d.rot_dim, d.swa_window > 0 ? (size_t)d.rot_dim : 0,
+                                     d.swa_window > 0 ? b * d.rot_dim : 0};
+  cudaError_t e;
+#define G_TRY(expr)                                                                       \
+  do {                                                                                    \
+    e = (expr);                                                                           \
+    if (e != cudaSuccess) return bail(fail(AOTCU_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e))); \
+  } while (0)
+  for (int i = 0; i < AOTCU_N_BUFS; i++) {
+    g->buf_len[i] = lens[i];
+    if (lens[i] == 0) continue;
+    G_TRY(cudaMalloc(&g->bufs[i], lens[i] * sizeof(float) + 64));
+    G_TRY(cudaMemsetAsync(g->bufs[i], 0, lens[i] * sizeof(float) + 64, c->stream));
+  }
+  // Weights: one upload, padded so aligned-superset tile copies stay inside.
+  G_TRY(cudaMalloc(&g->d_weights, weights_len + WEIGHT_PAD));
+  G_TRY(cudaMemcpyAsync(g->d_weights, weights, weights_len, cudaMemcpyHostToDevice, c->stream));
+  G_TRY(cudaMemsetAsync(g->d_weights + weights_len, 0, WEIGHT_PAD, c->stream));
+  // RoPE rows for every position (state.rs:308-319, ops.rs:28-34), host libm.
+  {
+    const size_t half = d.rot_dim / 2;
+    std::vector<float> ff;
+    if (g->head.rope_freqs.present) {
+      ff.resize(half);
+      memcpy(ff.data(), weights + g->head.rope_freqs.off, half * sizeof(float));
+    }
+    auto build = [&](float base, float scale, float** dev) -> cudaError_t {
+      std::vector<float> inv(half), tab(n_ctx * d.rot_dim);
+      for (size_t i = 0; i < half; i++) {
+        float f = powf(base, -(2.0f * (float)i) / (float)d.rot_dim);
+        if (!ff.empty()) f /= ff[i];
+        inv[i] = f;
+      }
+      for (size_t p = 0; p < n_ctx; p++) {
+        float pf = (float)p / scale;
+        for (size_t i = 0; i < half; i++) {
+          float a = pf * inv[i];
+          tab[p * d.rot_dim + 2 * i] = cosf(a);
+          tab[p * d.rot_dim + 2 * i + 1] = sinf(a);
+        }
+      }
+      cudaError_t er = cudaMalloc(dev, tab.size() * sizeof(float));
+      if (er != cudaSuccess) return er;
+      er = cudaMemcpyAsync(*dev, tab.data(), tab.size() * sizeof(float), cudaMemcpyHostToDevice, c->stream);
+      if (er != cudaSuccess) return er;
+      return cudaStreamSynchronize(c->stream);
+    };
+    G_TRY(build(d.rope_base, d.rope_scale, &g->rope_table));
+    if (d.swa_window > 0) G_TRY(build(d.rope_base_local, d.rope_scale_local, &g->rope_table_local));
+  }
+  {
+    size_t widest = xbw > (size_t)d.hidden ? xbw : (size_t)d.hidden;
+    size_t rows = g->max_batch;
+    G_TRY(cudaMalloc(&g->aqk, rows * (widest / 256 + 1) * XIMG_K));
+    G_TRY(cudaMalloc(&g->aq0, rows * (widest / 32 + 1) * XIMG_0));
+  }
+  // Attention scores: shared memory when the context fits, else a global scratch.
+  {
+    size_t cap = c->max_smem / sizeof(float) - d.head_dim - 64;
+    if (n_ctx <= cap && n_ctx <= 32768) {
+      g->smem_scores = (int)n_ctx;
+    } else {
+      g->smem_scores = 0;
+      G_TRY(cudaMalloc(&g->attn_scratch, g->max_batch * d.n_head * n_ctx * sizeof(float)));
+    }
+  }
+  g->history_cap = n_ctx;
+  G_TRY(cudaMalloc(&g->d_step, 4 * sizeof(int)));
+  G_TRY(cudaMemsetAsync(g->d_step, 0, 4 * sizeof(int), c->stream));
+  G_TRY(cudaMalloc(&g->d_tokens, g->max_batch * sizeof(int)));
+  G_TRY(cudaMalloc(&g->d_history, g->history_cap * sizeof(int)));
+  G_TRY(cudaMalloc(&g->d_out_token, sizeof(int)));
+  G_TRY(cudaMallocHost(&g->h_pinned, (g->max_batch + 8) * sizeof(int)));
+  G_TRY(cudaStreamSynchronize(c->stream));
+#undef G_TRY
+  *out = g;
+  return 0;
+}
+
+void aotcu_gpu_free(aotcu_gpu* g) {
+  if (!g) return;
+  cudaSetDevice(g->c->device);
+  cudaStreamSynchronize(g->c->stream);
+  for (int i = 0; i < 2; i++)
+    if (g->decode_graph[i]) cudaGraphExecDestroy(g->decode_graph[i]);
+  if (g->gen_graph) cudaGraphExecDestroy(g->gen_graph);
+  for (int i = 0; i < AOTCU_N_BUFS; i++) cudaFree(g->bufs[i]);
+  cudaFree(g->d_weights);
+  cudaFree(g->rope_table);
+  cudaFree(g->rope_table_local);
+  cudaFree(g->aqk);
+  cudaFree(g->aq0);
+  cudaFree(g->attn_scratch);
+  cudaFree(g->d_step);
+  cudaFree(g->d_tokens);
+  cudaFree(g->d_history);
+  cudaFree(g->d_out_token);
+  if (g->h_pinned) cudaFreeHost(g->h_pinned);
+  delete g;
+}
+
+int aotcu_gpu_buf(aotcu_gpu* g, int buf, float** p, size_t* n) {
+  ARG_CHECK(g && buf >= 0 && buf < AOTCU_N_BUFS, "bad buffer id %d", buf);
+  if (p) *p = g->bufs[buf];
+  if (n) *n = g->buf_len[buf];
+  return 0;
+}
+
+int aotcu_gpu_read(aotcu_gpu* g, int buf, size_t off, float* dst, size_t n) {
+  ARG_CHECK(g && buf >= 0 && buf < AOTCU_N_BUFS && dst, "bad argument");
+  ARG_CHECK(off + n <= g->buf_len[buf], "read of %zu floats at %zu exceeds buffer %d (%zu)", n, off, buf, g->buf_len[buf]);
+  return aotcu_d2h(g->c, dst, g->bufs[buf] + off, n * sizeof(float));
+}
+
+int aotcu_gpu_write(aotcu_gpu* g, int buf, size_t off, const float* src, size_t n) {
+  ARG_CHECK(g && buf >= 0 && buf < AOTCU_N_BUFS && src, "bad argument");
+  ARG_CHECK(off + n <= g->buf_len[buf], "write of %zu floats at %zu exceeds buffer %d (%zu)", n, off, buf, g->buf_len[buf]);
+  note_write(g, g->bufs[buf]);
+  return aotcu_h2d(g->c, g->bufs[buf] + off, src, n * sizeof(float));
+}
+
+int aotcu_gpu_begin(aotcu_gpu* g) {
+  ARG_CHECK(g, "gpu is NULL");
+  g->qsrc = aotcu_gpu::QSrc();
+  return ctx_set_device(g->c);
+}
+
+int aotcu_gpu_finish(aotcu_gpu* g) {
+  ARG_CHECK(g, "gpu is NULL");
+  return check_device_errors(g->c);
+}
+
+static int buf_ptr(aotcu_gpu* g, int buf, size_t off, size_t need, float** p) {
+  ARG_CHECK(buf >= 0 && buf < AOTCU_N_BUFS, "bad buffer id %d", buf);
+  ARG_CHECK(off + need <= g->buf_len[buf], "range %zu+%zu exceeds buffer %d (%zu floats)", off, need, buf, g->buf_len[buf]);
+  *p = g->bufs[buf] + off;
+  return 0;
+}
+
+int aotcu_gpu_rmsnorm(aotcu_gpu* g, int dst, size_t dst_off, int src, size_t src_off, const aotcu_tensor* w, size_t n,
+                      size_t m, float eps, int accumulate) {
+  ARG_CHECK(g && w, "NULL argument");
+  if (int rc = tensor_check(g, *w, "norm weight")) return rc;
+  ARG_CHECK(w->kind == AOTCU_F32 && w->rows * w->cols >= n, "norm weights must be f32 with at least n elements");
+  float *pd, *ps;
+  if (int rc = buf_ptr(g, dst, dst_off, n * m, &pd)) return rc;
+  if (int rc = buf_ptr(g, src, src_off, n * m, &ps)) return rc;
+  return gpu_rmsnorm(g, pd, n, ps, n, wf32(g, *w), n, m, eps, accumulate, true);
+}
+
+int aotcu_gpu_matmul(aotcu_gpu* g, int dst, size_t dst_off, const aotcu_tensor* w, int src, size_t src_off, size_t m,
+                     int accumulate) {
+  ARG_CHECK(g && w, "NULL argument");
+  ARG_CHECK(m >= 1 && m <= g->max_batch, "m (%zu) out of range 1..%zu", m, g->max_batch);
+  if (int rc = tensor_check(g, *w, "matrix")) return rc;
+  float *pd, *ps;
+  if (int rc = buf_ptr(g, dst, dst_off, w->rows * m, &pd)) return rc;
+  if (int rc = buf_ptr(g, src, src_off, w->cols * m, &ps)) return rc;
+  return gpu_matmul(g, pd, *w, ps, m, accumulate);
+}
+
+int aotcu_gpu_mv3(aotcu_gpu* g, const int dst[3], const size_t dst_off[3], const aotcu_tensor* const w[3], int src,
+                  size_t m) {
+  ARG_CHECK(g && dst && dst_off && w, "NULL argument");
+  ARG_CHECK(m >= 1 && m <= g->max_batch, "m (%zu) out of range 1..%zu", m, g->max_batch);
+  float* pd[3];
+  float* ps;
+  for (int i = 0; i < 3; i++) {
+    if (int rc = tensor_check(g, *w[i], "q/k/v matrix")) return rc;
+    ARG_CHECK(w[i]->cols == w[0]->cols, "q/k/v matrices must share cols");
+    if (int rc = buf_ptr(g, dst[i], dst_off[i], w[i]->rows * m, &pd[i])) return rc;
+  }
+  if (int rc = buf_ptr(g, src, 0, w[0]->cols * m, &ps)) return rc;
+  return gpu_mv3(g, pd, w, ps, m);
+}
+
+int aotcu_gpu_gate_up(aotcu_gpu* g, int dst, const aotcu_tensor* gate, const aotcu_tensor* up, int src, size_t m) {
+  ARG_CHECK(g && gate && up, "NULL argument");
+  ARG_CHECK(m >= 1 && m <= g->max_batch, "m (%zu) out of range 1..%zu", m, g->max_batch);
+  if (int rc = tensor_check(g, *gate, "gate")) return rc;
+  if (int rc = tensor_check(g, *up, "up")) return rc;
+  ARG_CHECK(gate->rows == up->rows && gate->cols == up->cols, "gate and up must have the same shape");
+  const bool batch = dst == AOTCU_BUF_BHB;
+  ARG_CHECK(dst == AOTCU_BUF_HB || dst == AOTCU_BUF_BHB, "gate_up writes Hb or Bhb");
+  float *pd, *p2, *ps;
+  if (int rc = buf_ptr(g, dst, 0, gate->rows * m, &pd)) return rc;
+  if (int rc = buf_ptr(g, batch ? AOTCU_BUF_BHB2 : AOTCU_BUF_HB2, 0, gate->rows * m, &p2)) return rc;
+  if (int rc = buf_ptr(g, src, 0, gate->cols * m, &ps)) return rc;
+  return gpu_gate_up(g, pd, p2, *gate, *up, ps, m);
+}
+
+int aotcu_gpu_qk_post(aotcu_gpu* g, size_t layer, size_t pos0, size_t m) {
+  ARG_CHECK(g, "gpu is NULL");
+  ARG_CHECK(layer < (size_t)g->head.dims.n_layer, "layer %zu out of range", layer);
+  ARG_CHECK(m >= 1 && m <= g->max_batch && pos0 + m <= g->n_ctx, "positions exceed the context");
+  return gpu_qk_post(g, layer, nullptr, pos0, m, m > 1);
+}
+
+int aotcu_gpu_attention(aotcu_gpu* g, int dst, int q, size_t layer, size_t pos0, size_t m, size_t window) {
+  ARG_CHECK(g, "gpu is NULL");
+  const aotcu_dims& d = g->head.dims;
+  ARG_CHECK(layer < (size_t)d.n_layer, "layer %zu out of range", layer);
+  ARG_CHECK(m >= 1 && m <= g->max_batch && pos0 + m <= g->n_ctx, "positions exceed the context");
+  float *pd, *pq;
+  size_t qd = (size_t)d.n_head * d.head_dim;
+  if (int rc = buf_ptr(g, dst, 0, qd * m, &pd)) return rc;
+  if (int rc = buf_ptr(g, q, 0, qd * m, &pq)) return rc;
+  return gpu_attention(g, pd, pq, layer, nullptr, pos0, m, window);
+}
+
+// ---- step level ----------------------------------------------------------------------------
+static int set_step(aotcu_gpu* g, uint32_t token, size_t pos, int n_generated) {
+  aotcu_ctx* c = g->c;
+  // The staging words may still be in flight from the previous step.
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  g->h_pinned[0] = (int)token;
+  g->h_pinned[1] = (int)pos;
+  g->h_pinned[2] = n_generated;
+  g->h_pinned[3] = 0;
+  CU_TRY(cudaMemcpyAsync(g->d_step, g->h_pinned, 4 * sizeof(int), cudaMemcpyHostToDevice, c->stream));
+  return 0;
+}
+
+int aotcu_forward(aotcu_gpu* g, uint32_t token, size_t pos, int want_logits) {
+  ARG_CHECK(g, "gpu is NULL");
+  const aotcu_dims& d = g->head.dims;
+  // emit.rs:467-468
+  ARG_CHECK(token < (uint32_t)d.vocab, "token id out of range");
+  ARG_CHECK(pos < g->n_ctx, "position exceeds the context");
+  if (int rc = ctx_set_device(g->c)) return rc;
+  if (int rc = set_step(g, token, pos, 0)) return rc;
+  want_logits = want_logits ? 1 : 0;
+  if (g->use_graph) {
+    if (!g->decode_graph[want_logits])
+      if (int rc = capture_graph(g, &g->decode_graph[want_logits], &g->decode_graph_kernels[want_logits], want_logits, false)) return rc;
+    CU_TRY(cudaGraphLaunch(g->decode_graph[want_logits], g->c->stream));
+    g->c->launches += g->decode_graph_kernels[want_logits];
+  } else {
+    if (int rc = enqueue_decode(g, want_logits, false)) return rc;
+  }
+  return check_device_errors(g->c);
+}
+
+int aotcu_forward_batch(aotcu_gpu* g, const uint32_t* tokens, size_t n, size_t pos0, int want_logits) {
+  ARG_CHECK(g && tokens, "NULL argument");
+  const aotcu_dims& d = g->head.dims;
+  // emit.rs:493-494
+  ARG_CHECK(g->max_batch > 1 && n >= 1 && n <= g->max_batch, "batch size out of range");
+  ARG_CHECK(pos0 + n <= g->n_ctx, "positions exceed the context");
+  for (size_t i = 0; i < n; i++) ARG_CHECK(tokens[i] < (uint32_t)d.vocab, "token id out of range");
+  aotcu_ctx* c = g->c;
+  if (int rc = ctx_set_device(c)) return rc;
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  for (size_t i = 0; i < n; i++) g->h_pinned[8 + i] = (int)tokens[i];
+  CU_TRY(cudaMemcpyAsync(g->d_tokens, g->h_pinned + 8, n * sizeof(int), cudaMemcpyHostToDevice, c->stream));
+  g->qsrc = aotcu_gpu::QSrc();
+  if (int rc = embed(g, g->bufs[AOTCU_BUF_BX], g->d_tokens, n)) return rc;
+  for (int i = 0; i < d.n_layer; i++)
+    if (int rc = layer_forward(g, (size_t)i, nullptr, pos0, n, true)) return rc;
+  if (want_logits)
+    if (int rc = logits_from(g, g->bufs[AOTCU_BUF_BX] + (n - 1) * d.dim)) return rc;
+  g->qsrc = aotcu_gpu::QSrc();
+  return check_device_errors(c);
+}
+
+int aotcu_logits(aotcu_gpu* g, float* host_dst) {
+  ARG_CHECK(g && host_dst, "NULL argument");
+  return aotcu_d2h(g->c, host_dst, g->bufs[AOTCU_BUF_LOGITS], (size_t)g->head.dims.vocab * sizeof(float));
+}
+
+int aotcu_generate(aotcu_gpu* g, uint32_t token, size_t pos, size_t n_steps, uint32_t* out_tokens, float* elapsed_ms) {
+  ARG_CHECK(g && out_tokens, "NULL argument");
+  const aotcu_dims& d = g->head.dims;
+  ARG_CHECK(token < (uint32_t)d.vocab, "token id out of range");
+  ARG_CHECK(pos + n_steps <= g->n_ctx, "positions exceed the context");
+  ARG_CHECK(n_steps <= g->history_cap, "too many steps");
+  if (n_steps == 0) return 0;
+  aotcu_ctx* c = g->c;
+  if (int rc = ctx_set_device(c)) return rc;
+  if (int rc = set_step(g, token, pos, 0)) return rc;
+  if (g->use_graph && !g->gen_graph)
+    if (int rc = capture_graph(g, &g->gen_graph, &g->gen_graph_kernels, 1, true)) return rc;
+  cudaEvent_t e0, e1;
+  CU_TRY(cudaEventCreate(&e0));
+  CU_TRY(cudaEventCreate(&e1));
+  CU_TRY(cudaEventRecord(e0, c->stream));
+  for (size_t s = 0; s < n_steps; s++) {
+    if (g->use_graph) {
+      CU_TRY(cudaGraphLaunch(g->gen_graph, c->stream));
+      c->launches += g->gen_graph_kernels;
+    } else {
+      if (int rc = enqueue_decode(g, 1, true)) return rc;
+    }
+  }
+  CU_TRY(cudaEventRecord(e1, c->stream));
+  CU_TRY(cudaMemcpyAsync(out_tokens, g->d_history, n_steps * sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  if (elapsed_ms) CU_TRY(cudaEventElapsedTime(elapsed_ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return check_device_errors(c);
+}
+
+uint64_t aotcu_gpu_dispatches(aotcu_gpu* g) { return g ? g->c->launches : 0; }
+
+int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
+  ARG_CHECK(g && name, "NULL argument");
+  if (!strcmp(name, "graph")) {
+    g->use_graph = value != 0;
+    return 0;
+  }
+  if (!strcmp(name, "pdl")) {
+    if (g->c->pdl != (value != 0)) {
+      // Captured graphs bake the launch attributes in; drop them.
+      CU_TRY(cudaStreamSynchronize(g->c->stream));
+      for (int i = 0; i < 2; i++)
+        if (g->decode_graph[i]) {
+          cudaGraphExecDestroy(g->decode_graph[i]);
+          g->decode_graph[i] = nullptr;
+        }
+      if (g->gen_graph) {
+        cudaGraphExecDestroy(g->gen_graph);
+        g->gen_graph = nullptr;
+      }
+    }
+    g->c->pdl = value != 0;
+    return 0;
+  }
+  return fail(AOTCU_ERR_BAD_ARG, "unknown option %s", name);
+}
+
+}  // extern "C"
+

@@ -1,0 +1,108 @@
+// Test-only harness: compiles the library's host/device arithmetic headers as plain
+// C++ so the per-block integer sums, the f32 operation order, the element
+// dequantizers and the exact expf can be checked against the oracle on a machine
+// without a GPU. Nothing in the product links this file.
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../aot-llm_b200/csrc/blockmath.cuh"
+#include "../../aot-llm_b200/csrc/expf_exact.cuh"
+
+using namespace aot;
+
+static inline uint32_t w32(const uint8_t* p, int i) {
+  return (uint32_t)p[4 * i] | ((uint32_t)p[4 * i + 1] << 8) | ((uint32_t)p[4 * i + 2] << 16) | ((uint32_t)p[4 * i + 3] << 24);
+}
+
+extern "C" {
+
+void hc_expf(const float* x, float* y, size_t n) {
+  for (size_t i = 0; i < n; i++) y[i] = expf_exact(x[i]);
+}
+
+// Number of inputs in bit-pattern range [lo, hi) stepping by `step` where expf_exact
+// and the C library's expf differ (NaNs skipped).
+uint64_t hc_expf_mismatches(uint32_t lo, uint32_t hi, uint32_t step) {
+  uint64_t bad = 0;
+  for (uint64_t u = lo; u < hi; u += step) {
+    float x = u2f((uint32_t)u);
+    if (x != x) continue;
+    if (f2u(expf_exact(x)) != f2u(expf(x))) bad++;
+  }
+  return bad;
+}
+
+float hc_half(uint16_t h) { return half_bits_to_float(h); }
+
+void hc_dequant_row(int kind, const uint8_t* row, float* out, size_t n) {
+  for (size_t e = 0; e < n; e++) out[e] = dequant_elem(kind, row, e);
+}
+
+// One full dot product assembled the way the GPU kernels assemble it.
+float hc_dot(int kind, const uint8_t* w, const void* xv, size_t cols, int32_t* sumi_out, int32_t* summ_out) {
+  if (kind_act(kind) == ACT_Q8_K) {
+    const BlockQ8_K* x = (const BlockQ8_K*)xv;
+    float sum = 0.0f;
+    for (size_t b = 0; b < cols / 256; b++) {
+      const uint8_t* wb = w + b * kind_size(kind);
+      const BlockQ8_K* y = &x[b];
+      auto yw = [&](int i) { return w32((const uint8_t*)y->qs, i); };
+      float term;
+      if (kind == Q6_K) {
+        int si = q6k_block_sum([&](int i) { return w32(wb, i); }, yw, y->bsums);
+        if (sumi_out) sumi_out[b] = si;
+        term = q6k_term(half_bits_to_float(w32(wb, 52) & 0xFFFF), y->d, si);
+      } else {
+        const bool q5 = kind == Q5_K;
+        K4Scales s = k4_unpack(w32(wb + 4, 0), w32(wb + 4, 1), w32(wb + 4, 2));
+        const uint8_t* qs = wb + (q5 ? 48 : 16);
+        const uint8_t* qh = wb + 16;
+        int si, sm;
+        if (q5) k4_block_sums<true>(s, [&](int i) { return w32(qs, i); }, [&](int i) { return w32(qh, i); }, yw, y->bsums, si, sm);
+        else k4_block_sums<false>(s, [&](int i) { return w32(qs, i); }, [&](int i) { return w32(qh, i); }, yw, y->bsums, si, sm);
+        if (sumi_out) sumi_out[b] = si;
+        if (summ_out) summ_out[b] = sm;
+        uint32_t h = w32(wb, 0);
+        term = k4_term(half_bits_to_float(h & 0xFFFF), half_bits_to_float(h >> 16), y->d, si, sm);
+      }
+      sum = fadd(sum, term);
+    }
+    return sum;
+  }
+  if (kind_act(kind) == ACT_Q8_0) {
+    const BlockQ8_0* x = (const BlockQ8_0*)xv;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (size_t b = 0; b < cols / 32; b++) {
+      const uint8_t* wb = w + b * kind_size(kind);
+      const BlockQ8_0* y = &x[b];
+      uint32_t h = (uint32_t)wb[0] | ((uint32_t)wb[1] << 8);
+      float d = fmul(half_bits_to_float(h), y->d);
+      int tot = 0;
+      for (int k = 0; k < 8; k++) {
+        uint32_t y4 = w32((const uint8_t*)y->qs, k);
+        int p;
+        if (kind == Q8_0) p = q8_0_lane(w32(wb + 2, k), y4);
+        else if (kind == Q4_0) p = q4_0_lane(w32(wb + 2, k & 3), k, y4);
+        else p = q5_0_lane(w32(wb + 6, k & 3), w32(wb + 2, 0), k, y4);
+        tot += p;
+        acc[k] = ffma(d, i2f(p), acc[k]);
+      }
+      if (sumi_out) sumi_out[b] = tot;
+    }
+    return hsum8(acc);
+  }
+  const float* x = (const float*)xv;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  size_t n8 = cols & ~(size_t)7;
+  auto wf = [&](size_t j) {
+    if (kind == F32) return u2f(w32(w, (int)j));
+    uint32_t h = (uint32_t)w[2 * j] | ((uint32_t)w[2 * j + 1] << 8);
+    return kind == F16 ? half_bits_to_float(h) : bf16_bits_to_float(h);
+  };
+  for (size_t j = 0; j < n8; j++) acc[j & 7] = ffma(wf(j), x[j], acc[j & 7]);
+  float sum = hsum8(acc);
+  for (size_t j = n8; j < cols; j++) sum = fadd(sum, fmul(wf(j), x[j]));
+  return sum;
+}
+
+}  // extern "C"
