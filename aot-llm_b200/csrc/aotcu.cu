@@ -619,7 +619,8 @@ int aotcu_init(int device, aotcu_ctx** out) {
   aotcu_ctx* c = new aotcu_ctx();
   c->device = device;
   c->n_sm = prop.multiProcessorCount;
-  c->max_smem = prop.sharedMemPerBlockOptin;
+  // Keep 1 KiB back for the kernels' small static shared arrays.
+  c->max_smem = prop.sharedMemPerBlockOptin - 1024;
   CU_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   CU_TRY(cudaMalloc(&c->d_err, sizeof(int)));
   CU_TRY(cudaMemset(c->d_err, 0, sizeof(int)));

@@ -1,0 +1,123 @@
+"""Whole-step parity: the interpreted forward pass on the GPU against the oracle's."""
+import numpy as np
+import pytest
+
+from conftest import assert_bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_both(pkg, ob, ctx, spec, tokens, n_ctx=64, max_batch=16):
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, max_batch)
+    om = ob.model_from_spec(spec, n_ctx, max_batch, n_threads=4)
+    return g, om
+
+
+@pytest.mark.parametrize("arch", ["llama", "qwen3", "qwen2"])
+def test_tiny_models_all_kinds_bit_exact(pkg, ob, ctx, arch):
+    spec = pkg.model.tiny(arch, n_layer=3)
+    tokens = [5, 17, 300, 42, 7, 7, 1]
+    g, om = _run_both(pkg, ob, ctx, spec, tokens)
+    for graph in (0, 1):
+        g.set_option("graph", graph)
+        for pos, t in enumerate(tokens):
+            g.forward(t, pos, True)
+            om.forward(t, pos, True)
+            assert_bits_equal(g.read("X"), om.buf("x"), f"{arch} x pos {pos} graph {graph}")
+            assert_bits_equal(g.logits(), om.logits(), f"{arch} logits pos {pos} graph {graph}")
+    d = spec.head.dims
+    kvd = d.n_kv_head * d.head_dim
+    assert_bits_equal(g.read("KCache", len(tokens) * kvd), om.buf("k_cache")[:len(tokens) * kvd], "k cache layer 0")
+    assert_bits_equal(g.read("VCache", len(tokens) * kvd), om.buf("v_cache")[:len(tokens) * kvd], "v cache layer 0")
+    # batched prompt path == oracle's batched path == single-token path
+    g2, om2 = _run_both(pkg, ob, ctx, spec, tokens)
+    g2.forward_batch(tokens, 0, True)
+    om2.forward_batch(tokens, 0, True)
+    assert_bits_equal(g2.logits(), om2.logits(), f"{arch} forward_batch")
+    assert_bits_equal(g2.logits(), g.logits(), f"{arch} batch vs single")
+    assert_bits_equal(g2.read("Bx", len(tokens) * d.dim), om2.buf("bx")[:len(tokens) * d.dim], "bx")
+    # continue token by token after a batch, then another batch at an offset
+    g2.forward(9, len(tokens), True)
+    om2.forward(9, len(tokens), True)
+    assert_bits_equal(g2.logits(), om2.logits(), "decode after batch")
+    g2.forward_batch([4, 5, 6], len(tokens) + 1, True)
+    om2.forward_batch([4, 5, 6], len(tokens) + 1, True)
+    assert_bits_equal(g2.logits(), om2.logits(), "second batch")
+    ctx.device_status()
+
+
+def test_greedy_generate_on_device_matches_oracle(pkg, ob, ctx):
+    spec = pkg.model.tiny("llama", n_layer=3)
+    prompt = [3, 99, 250, 8]
+    g, om = _run_both(pkg, ob, ctx, spec, prompt, n_ctx=64)
+    g.forward_batch(prompt, 0, True)
+    om.forward_batch(prompt, 0, True)
+    first = ob.argmax(om.logits())
+    assert int(np.argmax(g.logits())) == first
+    n = 40
+    ids, ms = g.generate(first, len(prompt), n)
+    want, tok = [], first
+    for i in range(n):
+        om.forward(tok, len(prompt) + i, True)
+        tok = ob.argmax(om.logits())
+        want.append(tok)
+    assert ids.tolist() == want
+    assert ms > 0 and g.dispatches() > 0
+
+
+def test_operator_level_api_matches_step(pkg, ob, ctx):
+    """Driving one block through the Gpu operator calls (the sequence the reference's
+    emit_gpu_forwards writes) gives the same bits as aotcu_forward."""
+    spec = pkg.model.tiny("llama", n_layer=1, kinds=lambda l, t: 6 if t != "output" else 8)
+    d = spec.head.dims
+    g, om = _run_both(pkg, ob, ctx, spec, [])
+    om.forward(11, 0, False)
+    om.forward(12, 1, False)
+    g.forward(11, 0, False)
+    l = spec.layers[0]
+    x0 = ob.dequant_row(spec.head.token_embd.kind,
+                        spec.weights[spec.head.token_embd.off + 12 * pkg.lib.row_bytes(6, d.dim):][:pkg.lib.row_bytes(6, d.dim)].copy(), d.dim)
+    g.begin()
+    g.write("X", x0)
+    g.rmsnorm("Xb", "X", l.attn_norm, d.dim, 1, d.eps)
+    g.mv3(["Q", "K", "V"], [l.wq, l.wk, l.wv], "Xb")
+    g.qk_post(0, 1)
+    g.attention("Xb", "Q", 0, 1)
+    g.mv("X", l.wo, "Xb", accumulate=True)
+    g.rmsnorm("Xb", "X", l.ffn_norm, d.dim, 1, d.eps)
+    g.gate_up("Hb", l.gate, l.up, "Xb")
+    g.mv("X", l.down, "Hb", accumulate=True)
+    g.finish()
+    assert_bits_equal(g.read("X"), om.buf("x"), "operator-level block")
+
+
+def test_forward_bounds_match_generated_asserts(pkg, ctx):
+    spec = pkg.model.tiny("llama", n_layer=1)
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 8, 4)
+    for bad in (lambda: g.forward(spec.head.dims.vocab, 0), lambda: g.forward(1, 8),
+                lambda: g.forward_batch([1] * 5, 0), lambda: g.forward_batch([1, 2], 7)):
+        with pytest.raises(pkg.AotCudaError):
+            bad()
+    g.forward(1, 0)
+
+
+def test_tinyllama_shape_greedy_128_identical(pkg, ob, ctx):
+    """BASELINE config 1: TinyLlama-shaped Q4_K_M model, 6-token prompt, 128 greedy tokens."""
+    spec = pkg.model.tinyllama()
+    prompt = np.random.default_rng(7).integers(0, 32000, 6).tolist()
+    n_ctx, n_gen = 160, 128
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 8)
+    om = ob.model_from_spec(spec, n_ctx, 8)
+    g.forward_batch(prompt, 0, True)
+    om.forward_batch(prompt, 0, True)
+    assert_bits_equal(g.logits(), om.logits(), "prompt logits")
+    first = ob.argmax(om.logits())
+    ids, ms = g.generate(first, len(prompt), n_gen - 1)
+    want, tok = [], first
+    for i in range(n_gen - 1):
+        om.forward(tok, len(prompt) + i, True)
+        tok = ob.argmax(om.logits())
+        want.append(tok)
+    assert ids.tolist() == want
+    assert_bits_equal(g.logits(), om.logits(), "final logits")
+    print(f"\n[tinyllama-shape] {n_gen - 1} decode steps in {ms:.1f} ms -> {(n_gen - 1) / ms * 1e3:.0f} tok/s")
