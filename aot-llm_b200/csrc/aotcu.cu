@@ -53,6 +53,7 @@ struct aotcu_ctx {
   int* d_err = nullptr;
   bool pdl = false;
   uint64_t launches = 0;
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
 };
 
 constexpr size_t WEIGHT_PAD = 256;
@@ -640,6 +641,8 @@ void aotcu_free(aotcu_ctx* c) {
     cudaStreamDestroy(c->stream);
   }
   cudaFree(c->d_err);
+  if (c->t0) cudaEventDestroy(c->t0);
+  if (c->t1) cudaEventDestroy(c->t1);
   delete c;
 }
 
@@ -675,6 +678,24 @@ int aotcu_d2h(aotcu_ctx* c, void* dst, const void* src, size_t bytes) {
   ARG_CHECK(c && (bytes == 0 || (dst && src)), "NULL argument");
   CU_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
   CU_TRY(cudaStreamSynchronize(c->stream));
+  return 0;
+}
+
+int aotcu_timer_start(aotcu_ctx* c) {
+  ARG_CHECK(c, "ctx is NULL");
+  if (!c->t0) {
+    CU_TRY(cudaEventCreate(&c->t0));
+    CU_TRY(cudaEventCreate(&c->t1));
+  }
+  CU_TRY(cudaEventRecord(c->t0, c->stream));
+  return 0;
+}
+
+int aotcu_timer_stop(aotcu_ctx* c, float* ms) {
+  ARG_CHECK(c && ms && c->t0, "timer was not started");
+  CU_TRY(cudaEventRecord(c->t1, c->stream));
+  CU_TRY(cudaEventSynchronize(c->t1));
+  CU_TRY(cudaEventElapsedTime(ms, c->t0, c->t1));
   return 0;
 }
 
@@ -1259,5 +1280,100 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
   return fail(AOTCU_ERR_BAD_ARG, "unknown option %s", name);
 }
 
-}  // extern "C"
 
+// Times only the matrix products of one decode step (q/k/v, wo, gate/up, down of every
+// layer, then the output head), back to back in one CUDA graph, `iters` replays. The
+// layers' weights are distinct and together far larger than L2, so every launch
+// streams from HBM. Used by the benchmark to quote the GEMV kernel's bandwidth.
+int aotcu_bench_gemv_sweep(aotcu_gpu* g, int iters, float* ms_per_sweep, uint64_t* launches_per_sweep,
+                           uint64_t* bytes_per_sweep) {
+  ARG_CHECK(g && iters >= 1 && ms_per_sweep, "bad argument");
+  aotcu_ctx* c = g->c;
+  const aotcu_dims& d = g->head.dims;
+  if (int rc = ctx_set_device(c)) return rc;
+  uint64_t bytes = 0;
+  auto tensor_bytes = [&](const aotcu_tensor& t) { bytes += t.len + 4 * t.cols + 4 * t.rows; };
+  auto one = [&](const aotcu_tensor& t, float* dst) -> int {
+    ARG_CHECK(kind_act(t.kind) == ACT_Q8_K, "the sweep handles K-quant matrices only");
+    GemvCall call;
+    call.seg[0] = GemvSeg{wptr(g, t), dst, (int)t.rows, t.kind};
+    call.cols = t.cols;
+    call.x = g->aqk;
+    call.x_mode = 1;
+    tensor_bytes(t);
+    return launch_gemv(c, call);
+  };
+  CU_TRY(cudaMemsetAsync(g->aqk, 0, (xb_width(d) > (size_t)d.hidden ? xb_width(d) : (size_t)d.hidden) / 256 * XIMG_K, c->stream));
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t before = c->launches;
+  CU_TRY(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+  int rc = 0;
+  for (int li = 0; li < d.n_layer && !rc; li++) {
+    const aotcu_layer& l = g->layers[li];
+    GemvCall qkv;
+    qkv.nseg = 3;
+    const aotcu_tensor* w3[3] = {&l.wq, &l.wk, &l.wv};
+    float* o3[3] = {g->bufs[AOTCU_BUF_Q], g->bufs[AOTCU_BUF_K], g->bufs[AOTCU_BUF_V]};
+    for (int i = 0; i < 3; i++) {
+      if (kind_act(w3[i]->kind) != ACT_Q8_K) rc = fail(AOTCU_ERR_UNSUPPORTED, "the sweep handles K-quant matrices only");
+      qkv.seg[i] = GemvSeg{wptr(g, *w3[i]), o3[i], (int)w3[i]->rows, w3[i]->kind};
+      tensor_bytes(*w3[i]);
+    }
+    qkv.cols = l.wq.cols;
+    qkv.x = g->aqk;
+    qkv.x_mode = 1;
+    if (!rc) rc = launch_gemv(c, qkv);
+    if (!rc) rc = one(l.wo, g->bufs[AOTCU_BUF_XB2]);
+    if (!rc) {
+      GemvCall gu;
+      gu.seg[0] = GemvSeg{wptr(g, l.gate), g->bufs[AOTCU_BUF_HB], (int)l.gate.rows, l.gate.kind};
+      gu.seg[1] = GemvSeg{wptr(g, l.up), g->bufs[AOTCU_BUF_HB2], (int)l.up.rows, l.up.kind};
+      gu.nseg = 2;
+      gu.pair = l.gate.kind == l.up.kind ? 1 : 0;
+      gu.cols = l.gate.cols;
+      gu.x = g->aqk;
+      gu.x_mode = 1;
+      gu.epilogue = gu.pair ? EPI_SILU_MUL : EPI_STORE;
+      tensor_bytes(l.gate);
+      tensor_bytes(l.up);
+      if (kind_act(l.gate.kind) != ACT_Q8_K || kind_act(l.up.kind) != ACT_Q8_K) rc = fail(AOTCU_ERR_UNSUPPORTED, "the sweep handles K-quant matrices only");
+      if (!rc) rc = launch_gemv(c, gu);
+    }
+    if (!rc) rc = one(l.down, g->bufs[AOTCU_BUF_XB2]);
+  }
+  if (!rc) rc = one(g->head.output.present ? g->head.output : g->head.token_embd, g->bufs[AOTCU_BUF_LOGITS]);
+  cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+  uint64_t n_launch = c->launches - before;
+  c->launches = before;
+  if (rc) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  for (int i = 0; i < 2; i++) cudaGraphLaunch(exec, c->stream);  // warm-up
+  cudaEventRecord(e0, c->stream);
+  for (int i = 0; i < iters; i++) cudaGraphLaunch(exec, c->stream);
+  cudaEventRecord(e1, c->stream);
+  e = cudaStreamSynchronize(c->stream);
+  float ms = 0;
+  cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaGraphExecDestroy(exec);
+  if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "gemv sweep: %s", cudaGetErrorString(e));
+  c->launches += n_launch * (uint64_t)(iters + 2);
+  *ms_per_sweep = ms / (float)iters;
+  if (launches_per_sweep) *launches_per_sweep = n_launch;
+  if (bytes_per_sweep) *bytes_per_sweep = bytes;
+  g->qsrc = aotcu_gpu::QSrc();
+  return check_device_errors(c);
+}
+
+}  // extern "C"

@@ -77,6 +77,14 @@ class Context:
     def sync(self):
         check(L.load().aotcu_sync(self.h))
 
+    def timer_start(self):
+        check(L.load().aotcu_timer_start(self.h))
+
+    def timer_stop(self) -> float:
+        ms = C.c_float(0)
+        check(L.load().aotcu_timer_stop(self.h, C.byref(ms)))
+        return ms.value
+
     def device_status(self):
         check(L.load().aotcu_device_status(self.h))
 
@@ -293,6 +301,13 @@ class Gpu:
         ms = C.c_float(0)
         check(L.load().aotcu_generate(self.h, token, pos, n_steps, ptr(out), C.byref(ms)))
         return out, ms.value
+
+    def gemv_sweep(self, iters: int = 20):
+        """(ms per sweep, launches per sweep, algorithmic bytes per sweep) of the decode
+        step's matrix products alone."""
+        ms, n, b = C.c_float(0), C.c_uint64(0), C.c_uint64(0)
+        check(L.load().aotcu_bench_gemv_sweep(self.h, iters, C.byref(ms), C.byref(n), C.byref(b)))
+        return ms.value, n.value, b.value
 
     def dispatches(self) -> int:
         return L.load().aotcu_gpu_dispatches(self.h)

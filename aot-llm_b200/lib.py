@@ -93,6 +93,8 @@ SYMBOLS = {
     "aotcu_h2d": (_i, [_vp, _vp, _vp, _sz]),
     "aotcu_d2h": (_i, [_vp, _vp, _vp, _sz]),
     "aotcu_device_status": (_i, [_vp]),
+    "aotcu_timer_start": (_i, [_vp]),
+    "aotcu_timer_stop": (_i, [_vp, C.POINTER(_f)]),
     "aotcu_quantize_q8_0": (_i, [_vp, _vp, _sz, _vp]),
     "aotcu_quantize_q8_k": (_i, [_vp, _vp, _sz, _vp]),
     "aotcu_dequant_rows": (_i, [_vp, _i, _vp, _vp, _sz, _sz, _vp]),
@@ -132,6 +134,7 @@ SYMBOLS = {
     "aotcu_generate": (_i, [_vp, _u32, _sz, _sz, _vp, C.POINTER(_f)]),
     "aotcu_gpu_dispatches": (C.c_uint64, [_vp]),
     "aotcu_gpu_set_option": (_i, [_vp, C.c_char_p, _i]),
+    "aotcu_bench_gemv_sweep": (_i, [_vp, _i, C.POINTER(_f), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "aotcu_synth_quantize_row": (_i, [_i, _vp, _sz, _vp]),
     "aotcu_synth_tensor": (_i, [_i, _sz, _sz, _f, _f, C.c_uint64, _vp]),
     "aotcu_synth_blocks": (_i, [_i, _sz, C.c_uint64, _vp]),

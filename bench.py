@@ -1,0 +1,288 @@
+"""Benchmark of the hot path: batch-1 greedy decode of the synthetic
+TinyLlama-shaped Q4_K_M model (BASELINE.json configs[1]).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one decode token (one pass of the forward path). `value` is tokens/s with
+everything resident in HBM (device-side greedy loop, CUDA-graph replays, device
+timing); `e2e` is the same metric through the host-facing call (token id in, logits
+out to host memory, host argmax, every step). With --gpus N > 1 (one rank per GPU,
+launched by torchrun) each rank decodes its own replica: the model does not shard
+(its FFN width is not a multiple of 4 super-blocks), so scaling is weak and there is
+no data-path collective.
+
+`--impl reference` times the reference's CPU implementation of the same path on the
+host cores: the C++ restatement in oracle/ (the reference itself is Rust and no Rust
+toolchain exists here), with the reference's default thread count min(cores, 8).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import __graft_entry__ as graft  # noqa: E402
+
+METRIC = "decode_tokens_per_s"
+UNIT = "tok/s"
+PROMPT_SEED, PROMPT_LEN = 7, 6
+N_CTX = 2048
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs
+    (read-only queries)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake_slowdown": 0x80, "sw_power_cap": 0x4}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._t:
+            self._t.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def prompt_tokens(vocab: int):
+    return np.random.default_rng(PROMPT_SEED).integers(0, vocab, PROMPT_LEN).tolist()
+
+
+def cpu_decode(spec, steps: int, warmup: int, threads: int):
+    """Times `steps` decode tokens of the oracle after the prompt and `warmup` tokens."""
+    from oracle import binding as ob
+    om = ob.model_from_spec(spec, PROMPT_LEN + warmup + steps + 2, 8, n_threads=threads)
+    om.forward_batch(prompt_tokens(spec.head.dims.vocab), 0, True)
+    tok, pos = ob.argmax(om.logits()), PROMPT_LEN
+    for _ in range(warmup):
+        om.forward(tok, pos, True)
+        tok, pos = ob.argmax(om.logits()), pos + 1
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        om.forward(tok, pos, True)
+        tok, pos = ob.argmax(om.logits()), pos + 1
+    dt = time.perf_counter() - t0
+    om.close()
+    return steps / dt, dt
+
+
+def workload_config(spec):
+    d = spec.head.dims
+    return {"workload": "configs[1]: TinyLlama-shaped Llama decode, Q4_K_M mix, random-init weights, 6-token prompt then greedy decode",
+            "dim": d.dim, "hidden": d.hidden, "n_layer": d.n_layer, "n_head": d.n_head, "n_kv_head": d.n_kv_head,
+            "head_dim": d.head_dim, "vocab": d.vocab, "context": N_CTX, "batch": 1,
+            "weight_bytes_per_token": spec.weight_bytes_per_token(),
+            "l2_policy": "inputs_larger_than_l2 (633 MB of weights streamed per step, L2 is 126 MB)"}
+
+
+def run_reference(args, rank: int, world: int):
+    if rank != 0:
+        return
+    pkg = graft.import_package()
+    spec = pkg.model.tinyllama()
+    cores = os.cpu_count() or 1
+    threads = min(cores, 8)  # the reference's default (crates/aot-kernels/src/app.rs:214-216)
+    steps = max(1, min(args.steps, 64))
+    warmup = max(1, min(args.warmup, 4))
+    tps, dt = cpu_decode(spec, steps, warmup, threads)
+    cfg = workload_config(spec)
+    sample = f"{steps} decode steps after the {PROMPT_LEN}-token prompt and {warmup} warm-up tokens"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": 0, "steps": steps,
+        "warmup": warmup, "ms_per_step": 1e3 / tps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 block dot products with f32 accumulation (Q8 activations x Q4_K/Q6_K weights)",
+        "data": "synthetic", "config": cfg,
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                         "host_cores": cores,
+                         "note": "C++ restatement of the reference's AVX2 kernel table and forward pass (oracle/); the Rust reference cannot be built here"},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    pkg = graft.import_package()
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_mod
+        torch.cuda.set_device(local_rank)
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+
+    def barrier():
+        if dist:
+            dist.barrier()
+
+    def max_over_ranks(v: float) -> float:
+        if not dist:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    spec = pkg.model.tinyllama()
+    d = spec.head.dims
+    ctx = pkg.Context(local_rank)
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, N_CTX, 8)
+    if args.pdl:
+        g.set_option("pdl", 1)
+    prompt = prompt_tokens(d.vocab)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    # ---- device-resident throughput -----------------------------------------------------
+    g.forward_batch(prompt, 0, True)
+    first = int(np.argmax(g.logits()))
+    warm_ids, _ = g.generate(first, PROMPT_LEN, warmup)
+    ctx.sync()
+    barrier()
+    launches0 = g.dispatches()
+    with ClockSampler(local_rank) as clk:
+        ids, ms = g.generate(int(warm_ids[-1]), PROMPT_LEN + warmup, steps)
+        ctx.sync()
+    barrier()
+    launches = g.dispatches() - launches0
+    ms = max_over_ranks(ms)
+    tps = world * steps / (ms * 1e-3)
+
+    # ---- end to end through the host-facing step call --------------------------------------
+    e2e_steps = min(steps, 64)
+    g.forward_batch(prompt, 0, True)
+    tok, pos = int(np.argmax(g.logits())), PROMPT_LEN
+    for _ in range(3):
+        g.forward(tok, pos, True)
+        tok, pos = int(np.argmax(g.logits())), pos + 1
+    ctx.sync()
+    barrier()
+    ctx.timer_start()                      # CUDA events on the launching stream
+    for _ in range(e2e_steps):
+        g.forward(tok, pos, True)          # token id + position go host -> device
+        tok, pos = int(np.argmax(g.logits())), pos + 1  # vocab floats come device -> host
+    e2e_s = max_over_ranks(ctx.timer_stop() * 1e-3)
+    barrier()
+    e2e_tps = world * e2e_steps / e2e_s
+
+    # ---- the dominant kernel alone: the quantized matrix-vector products -------------------
+    sweep_ms, sweep_launches, sweep_bytes = g.gemv_sweep(20)
+    peak, peak_src = measured_peak_gbs()
+    gemv_gbs = sweep_bytes / (sweep_ms * 1e-3) / 1e9
+    mid_pos = PROMPT_LEN + warmup + steps // 2
+    step_bytes = spec.weight_bytes_per_token() + spec.kv_bytes_per_position() * (mid_pos + 1)
+    step_gbs = step_bytes / (ms * 1e-3 / steps) / 1e9
+
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        threads = min(cores, 8)
+        cpu_steps = 24
+        cpu_tps, cpu_dt = cpu_decode(spec, cpu_steps, 2, threads)
+        cpu = {"value": cpu_tps, "unit": UNIT, "cores": threads, "kind": "port", "host_cores": cores,
+               "sample": f"{cpu_steps} decode steps of the same model after the prompt and 2 warm-up tokens ({cpu_dt:.1f} s)"}
+
+    out = {
+        "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 block dot products with f32 accumulation (Q8 activations x Q4_K/Q6_K weights)",
+        "data": "synthetic", "config": workload_config(spec),
+        "clocks": clk.summary(),
+        "e2e": {"value": e2e_tps, "unit": UNIT, "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4 * d.vocab,
+                "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": "gemv_q8k_kernel", "achieved": gemv_gbs, "peak": peak, "unit": "GB/s",
+                     "frac": gemv_gbs / peak, "peak_source": peak_src, "traffic": None,
+                     "launches_per_step": int(sweep_launches), "algorithmic_bytes_per_step": int(sweep_bytes),
+                     "avg_launch_us": sweep_ms * 1e3 / sweep_launches,
+                     "how": "the step's matrix products alone, back to back in one CUDA graph, CUDA events, 20 replays"},
+        "step_roofline": {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
+                          "algorithmic_bytes_per_step": int(step_bytes), "roofline_tok_s": peak * 1e9 / step_bytes},
+        "generated_head": [int(x) for x in ids[:8]],
+    }
+    if cpu:
+        out["cpu_baseline"] = cpu
+    print(json.dumps(out))
+    if dist:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--pdl", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    graft.build()
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -74,6 +74,10 @@ int aotcu_malloc(aotcu_ctx* ctx, size_t bytes, void** dev_ptr);
 int aotcu_dev_free(aotcu_ctx* ctx, void* dev_ptr);
 int aotcu_h2d(aotcu_ctx* ctx, void* dev_dst, const void* host_src, size_t bytes);
 int aotcu_d2h(aotcu_ctx* ctx, void* host_dst, const void* dev_src, size_t bytes);
+/* Device-side stopwatch on the context's stream (CUDA events): everything enqueued
+ * between start and stop, including the gaps the host leaves, is timed. */
+int aotcu_timer_start(aotcu_ctx* ctx);
+int aotcu_timer_stop(aotcu_ctx* ctx, float* elapsed_ms);
 /* Reads and clears the device error word (bounded waits that expired, ...). */
 int aotcu_device_status(aotcu_ctx* ctx);
 
@@ -240,6 +244,13 @@ uint64_t aotcu_gpu_dispatches(aotcu_gpu* g);
  * (replay decode steps as a CUDA graph, default 1), "pdl" (programmatic dependent
  * launch between kernels, default 0). */
 int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value);
+
+/* Benchmark helper (no counterpart in the reference; its per-op figures come from
+ * `bench_ops`, crates/aot-kernels/tests/metal.rs:456-641): times only the matrix
+ * products of one decode step, back to back, and reports milliseconds per sweep,
+ * kernel launches per sweep and the algorithmic bytes (weights + x + y) they move. */
+int aotcu_bench_gemv_sweep(aotcu_gpu* g, int iters, float* ms_per_sweep, uint64_t* launches_per_sweep,
+                           uint64_t* bytes_per_sweep);
 
 /* ---- synthetic test data (the encoders of crates/aot-kernels/src/quantize.rs) */
 /* quantize_row (quantize.rs:16-294): encodes n floats as one row of `kind` into

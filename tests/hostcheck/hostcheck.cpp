@@ -7,6 +7,9 @@
 
 #include "../../aot-llm_b200/csrc/blockmath.cuh"
 #include "../../aot-llm_b200/csrc/expf_exact.cuh"
+#include "../../aot-llm_b200/csrc/seqsum.cuh"
+
+#include <vector>
 
 using namespace aot;
 
@@ -103,6 +106,64 @@ float hc_dot(int kind, const uint8_t* w, const void* xv, size_t cols, int32_t* s
   float sum = hsum8(acc);
   for (size_t j = n8; j < cols; j++) sum = fadd(sum, fmul(wf(j), x[j]));
   return sum;
+}
+
+
+// The parallel evaluation of the sequential sum, simulated with T "threads" that own
+// contiguous chunks (the same steps as the device routine: serial head, per-chunk
+// composition, exclusive scan over chunks, replay to find the first term that leaves
+// the binade, one real add, repeat). Returns the sum; *rounds receives the number of
+// scan rounds.
+float hc_seqsum(const float* p, size_t n, int T, int head, int* rounds) {
+  float s = 0.0f;
+  size_t i0 = 0;
+  for (; i0 < n && (int)i0 < head; i0++) s = fadd(s, p[i0]);
+  int nr = 0;
+  while (i0 < n) {
+    uint32_t sb = f2u(s);
+    if ((sb >> 23) == 255) {  // inf / nan: finish serially
+      for (; i0 < n; i0++) s = fadd(s, p[i0]);
+      break;
+    }
+    nr++;
+    int e, m0;
+    sum_decompose(sb, e, m0);
+    size_t rem = n - i0, C = (rem + T - 1) / T;
+    std::vector<SumFn> comp(T), pre(T);
+    for (int t = 0; t < T; t++) {
+      SumFn f = sumfn_identity();
+      for (size_t i = i0 + t * C; i < i0 + (t + 1) * C && i < n; i++) f = sumfn_compose(f, sumfn_elem(f2u(p[i]), e));
+      comp[t] = f;
+    }
+    SumFn run = sumfn_identity();
+    for (int t = 0; t < T; t++) {
+      pre[t] = run;
+      run = sumfn_compose(run, comp[t]);
+    }
+    size_t ov = n;
+    int m_at = 0, m_final = sumfn_apply(run, m0);
+    for (int t = 0; t < T && ov == n; t++) {
+      int m = sumfn_apply(pre[t], m0);
+      if (m >= SUMFN_LIMIT) break;
+      for (size_t i = i0 + t * C; i < i0 + (t + 1) * C && i < n; i++) {
+        int m2 = sumfn_apply(sumfn_elem(f2u(p[i]), e), m);
+        if (m2 >= SUMFN_LIMIT) {
+          ov = i;
+          m_at = m;
+          break;
+        }
+        m = m2;
+      }
+    }
+    if (ov == n) {
+      s = u2f(sum_pack(e, m_final));
+      break;
+    }
+    s = fadd(u2f(sum_pack(e, m_at)), p[ov]);
+    i0 = ov + 1;
+  }
+  if (rounds) *rounds = nr;
+  return s;
 }
 
 }  // extern "C"
