@@ -9,11 +9,13 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <algorithm>
 #include <string>
 #include <vector>
 
 #include "../../include/aot_cuda.h"
 #include "gemv.cuh"
+#include "mega.cuh"
 #include "ops.cuh"
 
 using namespace aot;
@@ -263,6 +265,12 @@ struct aotcu_gpu {
     bool q8k = false, q80 = false;
   } qsrc;
   bool use_graph = true;
+  // Persistent one-kernel decode step (mega.cuh), when the model qualifies.
+  bool mega_ok = false, use_mega = true;
+  StepLayer* d_step_layers = nullptr;
+  unsigned* d_grid_bar = nullptr;
+  StepParams step_params = {};
+  size_t mega_smem = 0;
   cudaGraphExec_t decode_graph[2] = {nullptr, nullptr};  // [want_logits]
   cudaGraphExec_t gen_graph = nullptr;
   uint64_t decode_graph_kernels[2] = {0, 0};  // kernel nodes per replay
@@ -546,8 +554,113 @@ static int logits_from(aotcu_gpu* g, const float* xrow) {
   return gpu_matmul(g, g->bufs[AOTCU_BUF_LOGITS], out_t, xb, 1, 0);
 }
 
+
+// Decide whether the one-kernel decode step can run this model and build its
+// description. It handles the plain Llama / Qwen3 block (K-quant matrices, optional
+// per-head q/k norm, either RoPE layout); everything else keeps the per-operator path.
+static int mega_setup(aotcu_gpu* g) {
+  aotcu_ctx* c = g->c;
+  const aotcu_dims& d = g->head.dims;
+  const aotcu_tensor& out_t = g->head.output.present ? g->head.output : g->head.token_embd;
+  const size_t qd = (size_t)d.n_head * d.head_dim;
+  bool ok = !d.qkv_bias && !d.post_norms && !d.gelu && !d.embd_scale && d.swa_window == 0 && d.dim % 256 == 0 &&
+            d.hidden % 256 == 0 && qd % 256 == 0 && d.head_dim % 4 == 0 && kind_act(out_t.kind) == ACT_Q8_K;
+  for (const auto& l : g->layers) {
+    const aotcu_tensor* ts[7] = {&l.wq, &l.wk, &l.wv, &l.wo, &l.gate, &l.up, &l.down};
+    for (auto t : ts) ok = ok && kind_act(t->kind) == ACT_Q8_K;
+    ok = ok && l.gate.kind == l.up.kind && l.gate.rows == l.up.rows && !l.local_attn;
+  }
+  if (!ok) return 0;
+  const int stage_bytes = 32768;
+  const int v_chunk = 8192 / d.head_dim;
+  size_t nb_max = std::max(std::max((size_t)d.dim, (size_t)d.hidden), qd) / 256;
+  size_t scratch = std::max((size_t)2 * d.dim, (size_t)4 * d.head_dim + ((g->n_ctx + 3) & ~(size_t)3) + (size_t)v_chunk * d.head_dim) * sizeof(float);
+  scratch = (scratch + 127) & ~(size_t)127;
+  size_t fixed = nb_max * XK_STRIDE + scratch + MEGA_TAIL_BYTES;
+  if (fixed + 2 * (size_t)stage_bytes > c->max_smem) return 0;
+  // The largest row of any matrix must fit one stage.
+  size_t max_rb = 0;
+  for (const auto& l : g->layers) {
+    const aotcu_tensor* ts[7] = {&l.wq, &l.wk, &l.wv, &l.wo, &l.gate, &l.up, &l.down};
+    for (auto t : ts) max_rb = std::max(max_rb, (size_t)kind_row_bytes(t->kind, t->cols));
+  }
+  max_rb = std::max(max_rb, (size_t)kind_row_bytes(out_t.kind, out_t.cols));
+  if (2 * max_rb + 192 > (size_t)stage_bytes) return 0;
+  int n_stages = (int)((c->max_smem - fixed) / stage_bytes);
+  if (n_stages > 8) n_stages = 8;
+  // One CTA per SM must be resident for the grid barriers.
+  CU_TRY(cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  g->mega_smem = (size_t)n_stages * stage_bytes + fixed;
+  int per_sm = 0;
+  CU_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, MEGA_THREADS, g->mega_smem));
+  if (per_sm < 1) return 0;
+
+  auto seg = [&](const aotcu_tensor& t) { return GemvSeg{wptr(g, t), nullptr, (int)t.rows, t.kind}; };
+  std::vector<StepLayer> hl(d.n_layer);
+  for (int i = 0; i < d.n_layer; i++) {
+    const aotcu_layer& l = g->layers[i];
+    hl[i].attn_norm = wf32(g, l.attn_norm);
+    hl[i].ffn_norm = wf32(g, l.ffn_norm);
+    hl[i].q_norm = d.qk_norm ? wf32(g, l.q_norm) : nullptr;
+    hl[i].k_norm = d.qk_norm ? wf32(g, l.k_norm) : nullptr;
+    hl[i].wq = seg(l.wq);
+    hl[i].wk = seg(l.wk);
+    hl[i].wv = seg(l.wv);
+    hl[i].wo = seg(l.wo);
+    hl[i].gate = seg(l.gate);
+    hl[i].up = seg(l.up);
+    hl[i].down = seg(l.down);
+  }
+  CU_TRY(cudaMalloc(&g->d_step_layers, hl.size() * sizeof(StepLayer)));
+  CU_TRY(cudaMemcpy(g->d_step_layers, hl.data(), hl.size() * sizeof(StepLayer), cudaMemcpyHostToDevice));
+  CU_TRY(cudaMalloc(&g->d_grid_bar, sizeof(unsigned)));
+  StepParams& P = g->step_params;
+  P.dim = d.dim; P.hidden = d.hidden; P.n_layer = d.n_layer; P.n_head = d.n_head; P.n_kv_head = d.n_kv_head;
+  P.head_dim = d.head_dim; P.rot_dim = d.rot_dim; P.vocab = d.vocab; P.n_ctx = (int)g->n_ctx;
+  P.eps = d.eps; P.qk_norm = d.qk_norm; P.neox = d.rope_neox;
+  P.layers = g->d_step_layers;
+  P.output_norm = wf32(g, g->head.output_norm);
+  P.output = seg(out_t);
+  P.token_embd = wptr(g, g->head.token_embd);
+  P.embd_kind = g->head.token_embd.kind;
+  P.embd_row_bytes = kind_row_bytes(g->head.token_embd.kind, g->head.token_embd.cols);
+  P.x = g->bufs[AOTCU_BUF_X]; P.xb = g->bufs[AOTCU_BUF_XB]; P.q = g->bufs[AOTCU_BUF_Q]; P.k = g->bufs[AOTCU_BUF_K];
+  P.v = g->bufs[AOTCU_BUF_V]; P.hb = g->bufs[AOTCU_BUF_HB]; P.hb2 = g->bufs[AOTCU_BUF_HB2];
+  P.logits = g->bufs[AOTCU_BUF_LOGITS]; P.k_cache = g->bufs[AOTCU_BUF_KCACHE]; P.v_cache = g->bufs[AOTCU_BUF_VCACHE];
+  P.rope_table = g->rope_table;
+  P.step = g->d_step; P.history = g->d_history; P.history_cap = (int)g->history_cap; P.out_token = g->d_out_token;
+  P.grid_bar = g->d_grid_bar; P.err = c->d_err;
+  P.n_stages = n_stages; P.stage_bytes = stage_bytes; P.scratch_bytes = (int)scratch; P.v_chunk = v_chunk;
+  g->mega_ok = true;
+  return 0;
+}
+
+static int enqueue_mega(aotcu_gpu* g, int want_logits, bool with_argmax) {
+  aotcu_ctx* c = g->c;
+  StepParams P = g->step_params;
+  P.want_logits = want_logits;
+  P.with_argmax = with_argmax ? 1 : 0;
+  CU_TRY(cudaMemsetAsync(g->d_grid_bar, 0, sizeof(unsigned), c->stream));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(c->n_sm);
+  cfg.blockDim = dim3(MEGA_THREADS);
+  cfg.dynamicSmemBytes = g->mega_smem;
+  cfg.stream = c->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_step_kernel, P);
+  if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "decode_step_kernel launch: %s", cudaGetErrorString(e));
+  c->launches++;
+  g->qsrc = aotcu_gpu::QSrc();
+  return 0;
+}
+
 // Enqueue one decode step reading {token, pos} from g->d_step.
 static int enqueue_decode(aotcu_gpu* g, int want_logits, bool with_argmax) {
+  if (g->mega_ok && g->use_mega) return enqueue_mega(g, want_logits, with_argmax);
   const aotcu_dims& d = g->head.dims;
   g->qsrc = aotcu_gpu::QSrc();
   if (int rc = embed(g, g->bufs[AOTCU_BUF_X], g->d_step, 1)) return rc;
@@ -1024,6 +1137,7 @@ int aotcu_gpu_new(aotcu_ctx* c, const aotcu_model_head* head, const aotcu_layer*
   G_TRY(cudaMallocHost(&g->h_pinned, (g->max_batch + 8) * sizeof(int)));
   G_TRY(cudaStreamSynchronize(c->stream));
 #undef G_TRY
+  if (int rc = mega_setup(g)) return bail(rc);
   *out = g;
   return 0;
 }
@@ -1046,6 +1160,8 @@ void aotcu_gpu_free(aotcu_gpu* g) {
   cudaFree(g->d_tokens);
   cudaFree(g->d_history);
   cudaFree(g->d_out_token);
+  cudaFree(g->d_step_layers);
+  cudaFree(g->d_grid_bar);
   if (g->h_pinned) cudaFreeHost(g->h_pinned);
   delete g;
 }
@@ -1260,6 +1376,24 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
     g->use_graph = value != 0;
     return 0;
   }
+  if (!strcmp(name, "mega")) {
+    if (value && !g->mega_ok) return fail(AOTCU_ERR_UNSUPPORTED, "this model cannot use the one-kernel decode step");
+    if (g->use_mega != (value != 0)) {
+      CU_TRY(cudaStreamSynchronize(g->c->stream));
+      for (int i = 0; i < 2; i++)
+        if (g->decode_graph[i]) {
+          cudaGraphExecDestroy(g->decode_graph[i]);
+          g->decode_graph[i] = nullptr;
+        }
+      if (g->gen_graph) {
+        cudaGraphExecDestroy(g->gen_graph);
+        g->gen_graph = nullptr;
+      }
+    }
+    g->use_mega = value != 0;
+    return 0;
+  }
+  if (!strcmp(name, "mega_available")) return g->mega_ok ? 1 : 0;
   if (!strcmp(name, "pdl")) {
     if (g->c->pdl != (value != 0)) {
       // Captured graphs bake the launch attributes in; drop them.

@@ -223,7 +223,8 @@ struct TilePart {
 };
 
 // Parts of the tile that covers rows [t0, t1) of the row space.
-__device__ __forceinline__ int tile_parts(const GemvParams& P, int t0, int t1, size_t row_bytes[3], TilePart parts[3]) {
+template <class OpT>
+__device__ __forceinline__ int tile_parts(const OpT& P, int t0, int t1, const size_t row_bytes[3], TilePart parts[3]) {
   int n = 0;
   uint32_t soff = 0;
   if (P.pair) {

@@ -1,0 +1,781 @@
+// One decode step (crates/aot-codegen/src/emit.rs:243-333, 466-486) as a single
+// persistent kernel: one CTA per SM, a producer warp that streams this CTA's
+// share of every weight matrix of the step through a shared-memory ring with 1-D
+// bulk copies (it runs ahead across phases, because weights never depend on
+// activations), 31 consumer warps that do the arithmetic, and grid-wide
+// barriers between the phases of a block. All results are bit-identical to the
+// reference's CPU path (see blockmath.cuh, seqsum.cuh, expf_exact.cuh).
+#pragma once
+#include <cuda_fp16.h>
+
+#include "blockmath.cuh"
+#include "device_utils.cuh"
+#include "expf_exact.cuh"
+#include "gemv.cuh"
+#include "ops.cuh"
+#include "seqsum.cuh"
+
+namespace aot {
+
+// ---- a group of warps inside a CTA that synchronise on a named barrier ---------------
+struct CtaGroup {
+  int tid;       // thread index inside the group
+  int nthreads;  // multiple of 32
+  int bar_id;    // hardware barrier id (0 = the whole CTA, like __syncthreads)
+  __device__ __forceinline__ void sync() const {
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory");
+  }
+};
+
+// ---- exact sequential-order sum of non-negative floats in shared memory --------------
+struct SeqSumScratch {
+  SumFn warp_tot[32];
+  SumFn warp_pre[32];
+  float s;
+  int i0;
+  int ov;
+  int m_at;
+  int m_final;
+};
+
+__device__ __forceinline__ SumFn sumfn_shfl_up(const SumFn& f, int off) {
+  SumFn o;
+  o.a0 = __shfl_up_sync(0xffffffffu, f.a0, off);
+  o.a1 = __shfl_up_sync(0xffffffffu, f.a1, off);
+  return o;
+}
+
+// Inclusive scan (composition in lane order) across one warp.
+__device__ __forceinline__ SumFn sumfn_warp_scan(SumFn f, int lane) {
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    SumFn o = sumfn_shfl_up(f, off);
+    if (lane >= off) f = sumfn_compose(o, f);
+  }
+  return f;
+}
+
+// (((0 + p[0]) + p[1]) + ...) with the rounding of a scalar f32 loop. Every thread of
+// the group calls it and receives the result. `head` terms are added serially first
+// (the running sum changes binade at almost every step there).
+__device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const CtaGroup& g, int head = 48) {
+  const int tid = g.tid, T = g.nthreads, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
+  g.sync();
+  if (tid == 0) {
+    float s = 0.0f;
+    int h = n < head ? n : head;
+    for (int i = 0; i < h; i++) s = fadd(s, p[i]);
+    sc->s = s;
+    sc->i0 = h;
+  }
+  g.sync();
+  for (int round = 0; round <= n; ++round) {
+    float s = sc->s;
+    const int i0 = sc->i0;
+    if (i0 >= n) return s;
+    const uint32_t sb = f2u(s);
+    if ((sb >> 23) == 255u) {  // inf / nan: no binade structure left, finish serially
+      g.sync();
+      if (tid == 0) {
+        for (int i = i0; i < n; i++) s = fadd(s, p[i]);
+        sc->s = s;
+        sc->i0 = n;
+      }
+      g.sync();
+      return sc->s;
+    }
+    int e, m0;
+    sum_decompose(sb, e, m0);
+    const int rem = n - i0, C = (rem + T - 1) / T;
+    const int lo = i0 + tid * C, hi = min(lo + C, n);
+    SumFn f = sumfn_identity();
+    for (int i = lo; i < hi; i++) f = sumfn_compose(f, sumfn_elem(f2u(p[i]), e));
+    SumFn inc = sumfn_warp_scan(f, lane);
+    if (lane == 31) sc->warp_tot[warp] = inc;
+    if (tid == 0) sc->ov = n;
+    g.sync();
+    if (warp == 0) {
+      SumFn w = lane < nwarps ? sc->warp_tot[lane] : sumfn_identity();
+      SumFn winc = sumfn_warp_scan(w, lane);
+      SumFn wex = sumfn_shfl_up(winc, 1);
+      if (lane == 0) wex = sumfn_identity();
+      sc->warp_pre[lane] = wex;
+      if (lane == 31) sc->m_final = sumfn_apply(winc, m0);
+    }
+    g.sync();
+    SumFn ex = sumfn_shfl_up(inc, 1);
+    if (lane == 0) ex = sumfn_identity();
+    const SumFn pre = sumfn_compose(sc->warp_pre[warp], ex);
+    int m = sumfn_apply(pre, m0);
+    if (m < SUMFN_LIMIT) {
+      for (int i = lo; i < hi; i++) {
+        int m2 = sumfn_apply(sumfn_elem(f2u(p[i]), e), m);
+        if (m2 >= SUMFN_LIMIT) {  // at most one thread gets here: the mantissa is monotone
+          sc->ov = i;
+          sc->m_at = m;
+          break;
+        }
+        m = m2;
+      }
+    }
+    g.sync();
+    const int ov = sc->ov;
+    if (ov == n) return u2f(sum_pack(e, sc->m_final));
+    g.sync();
+    if (tid == 0) {
+      sc->s = fadd(u2f(sum_pack(e, sc->m_at)), p[ov]);
+      sc->i0 = ov + 1;
+    }
+    g.sync();
+  }
+  return sc->s;
+}
+
+// ---- warp-per-row dot products, four lanes per 256-weight super-block -----------------
+__device__ __forceinline__ float half_to_float_hw(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+
+// Lane (b = lane/4, c = lane%4) of a warp: quarter c of block b. Returns the two
+// integers of the whole block (summed over the four lanes) to all four lanes.
+template <bool Q5>
+__device__ __forceinline__ void quarter_k4(const uint8_t* wb, const uint8_t* xb, int c, int& sumi, int& summ) {
+  U4 hdr = lds128(wb);
+  K4Scales s = k4_unpack(hdr.y, hdr.z, hdr.w);
+  const uint8_t* qs = wb + (Q5 ? 48 : 16) + 32 * c;
+  U4 wa = lds128(qs), wc = lds128(qs + 16);
+  U4 y0 = lds128(xb + 64 * c), y1 = lds128(xb + 64 * c + 16), y2 = lds128(xb + 64 * c + 32), y3 = lds128(xb + 64 * c + 48);
+  U4 h0{0, 0, 0, 0}, h1{0, 0, 0, 0};
+  if (Q5) {
+    h0 = lds128(wb + 16);
+    h1 = lds128(wb + 32);
+  }
+  int s_lo = 0, s_hi = 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    uint32_t w = i < 4 ? u4_get(wa, i) : u4_get(wc, i - 4);
+    uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+    if (Q5) {
+      uint32_t h = i < 4 ? u4_get(h0, i) : u4_get(h1, i - 4);
+      lo |= ((h >> (2 * c)) & 0x01010101u) << 4;
+      hi |= ((h >> (2 * c + 1)) & 0x01010101u) << 4;
+    }
+    s_lo = __dp4a((int)lo, (int)(i < 4 ? u4_get(y0, i) : u4_get(y1, i - 4)), s_lo);
+    s_hi = __dp4a((int)hi, (int)(i < 4 ? u4_get(y2, i) : u4_get(y3, i - 4)), s_hi);
+  }
+  const uint32_t scw = c < 2 ? s.sc_lo : s.sc_hi, mw = c < 2 ? s.m_lo : s.m_hi;
+  const int sh = (c & 1) * 16;
+  const int sc0 = (scw >> sh) & 0xFF, sc1 = (scw >> (sh + 8)) & 0xFF;
+  const int m0 = (mw >> sh) & 0xFF, m1 = (mw >> (sh + 8)) & 0xFF;
+  // bsums[4c..4c+3]: pairs (4c,4c+1) for sub-block 2c and (4c+2,4c+3) for 2c+1
+  const int2 bs = *reinterpret_cast<const int2*>(xb + XK_BSUMS + 8 * c);
+  int si = sc0 * s_lo + sc1 * s_hi;
+  int sm = m0 * ((int)(short)(bs.x & 0xFFFF) + (bs.x >> 16)) + m1 * ((int)(short)(bs.y & 0xFFFF) + (bs.y >> 16));
+  si += __shfl_xor_sync(0xffffffffu, si, 1);
+  sm += __shfl_xor_sync(0xffffffffu, sm, 1);
+  si += __shfl_xor_sync(0xffffffffu, si, 2);
+  sm += __shfl_xor_sync(0xffffffffu, sm, 2);
+  sumi = si;
+  summ = sm;
+}
+
+// Q6_K: lane c covers half n = c/2 of the block and elements l in [16*(c%2), +16) of
+// each of its four 32-element quarters.
+__device__ __forceinline__ int quarter_q6k(const uint8_t* wb, const uint8_t* xb, int c) {
+  const uint32_t sh = ((uint32_t)(uintptr_t)wb & 2u) * 8u;
+  const uint32_t* p = reinterpret_cast<const uint32_t*>((uintptr_t)wb & ~(uintptr_t)3);
+  auto wload = [&](int k) -> uint32_t { return funnel_r(p[k], p[k + 1], sh); };
+  const int n = c >> 1, half = c & 1;
+  U4 y1 = lds128(xb + 128 * n + 16 * half), y2 = lds128(xb + 128 * n + 32 + 16 * half),
+     y3 = lds128(xb + 128 * n + 64 + 16 * half), y4 = lds128(xb + 128 * n + 96 + 16 * half);
+  int a1 = 0, a2 = 0, a3 = 0, a4 = 0;
+#pragma unroll
+  for (int ii = 0; ii < 4; ii++) {
+    const int i = 4 * half + ii;
+    uint32_t l0 = wload(16 * n + i), l32 = wload(16 * n + 8 + i), h = wload(32 + 8 * n + i);
+    uint32_t q1 = (l0 & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
+    uint32_t q2 = (l32 & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
+    uint32_t q3 = ((l0 >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
+    uint32_t q4 = ((l32 >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
+    a1 = __dp4a((int)q1, (int)u4_get(y1, ii), a1);
+    a2 = __dp4a((int)q2, (int)u4_get(y2, ii), a2);
+    a3 = __dp4a((int)q3, (int)u4_get(y3, ii), a3);
+    a4 = __dp4a((int)q4, (int)u4_get(y4, ii), a4);
+  }
+  // scales 8n..8n+7 are words 48+2n, 49+2n; this lane uses bytes half, half+2, half+4, half+6
+  const uint32_t s01 = wload(48 + 2 * n), s23 = wload(49 + 2 * n);
+  const int g = 8 * n + half;
+  const int c1 = (int)(int8_t)((s01 >> (8 * half)) & 0xFF), c2 = (int)(int8_t)((s01 >> (8 * half + 16)) & 0xFF);
+  const int c3 = (int)(int8_t)((s23 >> (8 * half)) & 0xFF), c4 = (int)(int8_t)((s23 >> (8 * half + 16)) & 0xFF);
+  const int16_t* bs = reinterpret_cast<const int16_t*>(xb + XK_BSUMS);
+  int tot = c1 * a1 + c2 * a2 + c3 * a3 + c4 * a4;
+  tot -= 32 * (c1 * (int)bs[g] + c2 * (int)bs[g + 2] + c3 * (int)bs[g + 4] + c4 * (int)bs[g + 6]);
+  tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+  tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+  return tot;
+}
+
+// Dot product of one K-quant row (in shared memory) with the Q8_K activation images,
+// computed by one warp; terms are added in block order. All lanes return the sum.
+__device__ __forceinline__ float warp_row_dot_kq(int kind, const uint8_t* row, const uint8_t* sx, int nb) {
+  const int lane = threadIdx.x & 31, bl = lane >> 2, c = lane & 3;
+  const int bs = kind_size(kind);
+  float sum = 0.0f;
+  for (int g0 = 0; g0 < nb; g0 += 8) {
+    const int b = g0 + bl;
+    const bool active = b < nb;
+    // Idle lanes recompute the last block so every lane reaches the shuffles.
+    const int bb = active ? b : nb - 1;
+    const uint8_t* wb = row + (size_t)bb * bs;
+    const uint8_t* xb = sx + bb * XK_STRIDE;
+    float term;
+    if (kind == Q6_K) {
+      int si = quarter_q6k(wb, xb, c);
+      const uint32_t sh = ((uint32_t)(uintptr_t)(wb + 208) & 2u) * 8u;
+      const uint32_t* p = reinterpret_cast<const uint32_t*>((uintptr_t)(wb + 208) & ~(uintptr_t)3);
+      float d_w = half_to_float_hw((p[0] >> sh) & 0xFFFFu);
+      term = q6k_term(d_w, *reinterpret_cast<const float*>(xb + XK_D), si);
+    } else {
+      int si, sm;
+      if (kind == Q5_K) quarter_k4<true>(wb, xb, c, si, sm); else quarter_k4<false>(wb, xb, c, si, sm);
+      const uint32_t h = *reinterpret_cast<const uint32_t*>(wb);
+      term = k4_term(half_to_float_hw(h & 0xFFFFu), half_to_float_hw(h >> 16), *reinterpret_cast<const float*>(xb + XK_D), si, sm);
+    }
+    const int nbg = min(8, nb - g0);
+    float t[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) t[j] = __shfl_sync(0xffffffffu, term, 4 * j);
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      if (j < nbg) sum = fadd(sum, t[j]);
+  }
+  return sum;
+}
+
+
+// ---- step description (built once by the host, lives in global memory) ------------------
+struct StepLayer {
+  const float* attn_norm;
+  const float* ffn_norm;
+  const float* q_norm;
+  const float* k_norm;
+  GemvSeg wq, wk, wv, wo, gate, up, down;  // `out` is filled in by the kernel
+};
+
+struct StepParams {
+  int dim, hidden, n_layer, n_head, n_kv_head, head_dim, rot_dim, vocab, n_ctx;
+  float eps;
+  int qk_norm, neox;
+  const StepLayer* layers;
+  const float* output_norm;
+  GemvSeg output;
+  const uint8_t* token_embd;
+  int embd_kind;
+  size_t embd_row_bytes;
+  float *x, *xb, *q, *k, *v, *hb, *hb2, *logits, *k_cache, *v_cache;
+  const float* rope_table;
+  int* step;  // {token, pos, n_generated}
+  int* history;
+  int history_cap;
+  int* out_token;
+  int want_logits, with_argmax;
+  unsigned* grid_bar;  // arrival counter, zero at launch
+  int* err;
+  int n_stages, stage_bytes;
+  int scratch_bytes;   // f32 scratch region (norm rows, attention)
+  int v_chunk;         // positions per staged V chunk
+};
+
+// One matrix-product phase as both the producer and the consumers see it.
+struct MegaOp {
+  GemvSeg seg[3];
+  int nseg, pair, cols, span_rows, rows_per_cta, tile_rows, epilogue;
+};
+
+__device__ __forceinline__ MegaOp make_op(const GemvSeg* segs, int nseg, int pair, int cols, int epilogue, int stage_bytes) {
+  MegaOp op;
+  size_t max_rb = 1;
+  int span = 0;
+  for (int i = 0; i < 3; i++) {
+    if (i < nseg) {
+      op.seg[i] = segs[i];
+      size_t rb = kind_row_bytes(segs[i].kind, cols);
+      max_rb = rb > max_rb ? rb : max_rb;
+      span += segs[i].rows;
+    } else {
+      op.seg[i] = GemvSeg{nullptr, nullptr, 0, 0};
+    }
+  }
+  op.nseg = nseg;
+  op.pair = pair;
+  op.cols = cols;
+  op.span_rows = pair ? segs[0].rows : span;
+  op.rows_per_cta = (op.span_rows + gridDim.x - 1) / gridDim.x;
+  const int mult = pair ? 2 : 1;
+  int tr = (int)((size_t)(stage_bytes - 192) / (max_rb * mult));
+  op.tile_rows = tr < 1 ? 1 : tr;
+  op.epilogue = epilogue;
+  return op;
+}
+
+// ---- shared-memory ring --------------------------------------------------------------------
+struct Ring {
+  uint8_t* stages;
+  uint64_t* full;
+  uint64_t* empty;
+  int n_stages, stage_bytes;
+  volatile int* abort;  // set when any bounded wait of this CTA expired
+  int* err;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool ring_wait(const Ring& R, uint64_t* bar, uint32_t parity) {
+  for (uint32_t it = 0; it < (1u << 22); ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*R.abort) return false;
+  }
+  *R.abort = 1;
+  if (R.err) atomicOr(R.err, DEVERR_MBAR_TIMEOUT);
+  return false;
+}
+
+struct OpSchedule {
+  int c0, c1, n_tiles;
+  size_t row_bytes[3];
+};
+__device__ __forceinline__ OpSchedule op_schedule(const MegaOp& op) {
+  OpSchedule S;
+  for (int s = 0; s < 3; s++) S.row_bytes[s] = s < op.nseg ? kind_row_bytes(op.seg[s].kind, op.cols) : 0;
+  S.c0 = blockIdx.x * op.rows_per_cta;
+  S.c1 = min(S.c0 + op.rows_per_cta, op.span_rows);
+  S.n_tiles = S.c1 > S.c0 ? (S.c1 - S.c0 + op.tile_rows - 1) / op.tile_rows : 0;
+  return S;
+}
+
+// Producer side (one thread): request every tile of this CTA's share of `op`.
+__device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, uint32_t& pt) {
+  const OpSchedule S = op_schedule(op);
+  for (int t = 0; t < S.n_tiles; t++, pt++) {
+    const int st = pt % R.n_stages;
+    const uint32_t k = pt / R.n_stages;
+    if (!ring_wait(R, &R.empty[st], (k & 1u) ^ 1u)) return;
+    TilePart parts[3];
+    const int t0 = S.c0 + t * op.tile_rows, t1 = min(t0 + op.tile_rows, S.c1);
+    const int np = tile_parts(op, t0, t1, S.row_bytes, parts);
+    uint32_t total = 0;
+    for (int i = 0; i < np; i++) total += bulk_superset_bytes(parts[i].src, parts[i].len);
+    mbar_expect_tx(&R.full[st], total);
+    for (int i = 0; i < np; i++)
+      bulk_g2s_superset(R.stages + (size_t)st * R.stage_bytes + parts[i].soff, parts[i].src, parts[i].len, &R.full[st]);
+  }
+}
+
+// Consumer side (every consumer warp): rows of each tile are dealt to warps round robin.
+// `sx` holds the Q8_K images of the activation vector. Returns false after a failed wait.
+__device__ __forceinline__ bool consume_op(const MegaOp& op, const Ring& R, uint32_t& ct, const uint8_t* sx, int warp,
+                                           int n_warps) {
+  const OpSchedule S = op_schedule(op);
+  const int lane = threadIdx.x & 31;
+  const int nb = op.cols / 256;
+  for (int t = 0; t < S.n_tiles; t++, ct++) {
+    const int st = ct % R.n_stages;
+    const uint32_t k = ct / R.n_stages;
+    if (!ring_wait(R, &R.full[st], k & 1u)) return false;
+    TilePart parts[3];
+    const int t0 = S.c0 + t * op.tile_rows, t1 = min(t0 + op.tile_rows, S.c1);
+    const int np = tile_parts(op, t0, t1, S.row_bytes, parts);
+    const uint8_t* stage = R.stages + (size_t)st * R.stage_bytes;
+    const int R_rows = t1 - t0;
+    if (op.pair) {
+      const uint8_t* base0 = stage + parts[0].soff + ((uintptr_t)parts[0].src & 15u);
+      const uint8_t* base1 = stage + parts[1].soff + ((uintptr_t)parts[1].src & 15u);
+      for (int u = warp; u < R_rows; u += n_warps) {
+        float g = warp_row_dot_kq(op.seg[0].kind, base0 + (size_t)u * S.row_bytes[0], sx, nb);
+        float up = warp_row_dot_kq(op.seg[1].kind, base1 + (size_t)u * S.row_bytes[1], sx, nb);
+        if (lane == 0) {
+          const int r = t0 + u;
+          op.seg[0].out[r] = op.epilogue == EPI_SILU_MUL ? silu_mul_exact(g, up) : g;
+          op.seg[1].out[r] = up;
+        }
+      }
+    } else {
+      for (int u = warp; u < R_rows; u += n_warps) {
+        int lr = u, pi = 0;
+        while (pi < np - 1 && lr >= parts[pi].rows) {
+          lr -= parts[pi].rows;
+          pi++;
+        }
+        const TilePart& tp = parts[pi];
+        const uint8_t* row = stage + tp.soff + ((uintptr_t)tp.src & 15u) + (size_t)lr * S.row_bytes[tp.seg];
+        float v = warp_row_dot_kq(op.seg[tp.seg].kind, row, sx, nb);
+        if (lane == 0) {
+          float* o = op.seg[tp.seg].out + tp.row0 + lr;
+          *o = op.epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&R.empty[st]);
+  }
+  return true;
+}
+
+
+// ---- grid-wide barrier for the consumer warps ---------------------------------------------
+// Arrival counter in global memory, zero at launch, never reset: barrier number k
+// completes when it reaches k * gridDim.x. The spin is bounded; when it gives up the
+// error word is set and every later barrier returns at once, so the kernel drains.
+__device__ __forceinline__ bool grid_sync(const StepParams& P, const CtaGroup& g, unsigned& target, volatile int* abort) {
+  g.sync();
+  if (g.tid == 0) {
+    target += gridDim.x;
+    if (!*abort) {
+      __threadfence();
+      atomicAdd(P.grid_bar, 1u);
+      bool ok = false;
+      for (uint32_t it = 0; it < (1u << 24); ++it) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.grid_bar) : "memory");
+        if (v >= target) {
+          ok = true;
+          break;
+        }
+        if ((it & 1023u) == 1023u && *(volatile int*)P.err) break;
+      }
+      if (!ok) {
+        *abort = 1;
+        atomicOr(P.err, DEVERR_GRID_TIMEOUT);
+      }
+    }
+  }
+  g.sync();
+  return !*abort;
+}
+
+// ---- activation phases -----------------------------------------------------------------------
+struct MegaSmem {
+  uint8_t* sx;          // Q8_K images of the current activation vector
+  float* scr;           // f32 scratch
+  SeqSumScratch* ss;
+  float* red;           // 32 floats
+};
+
+// x -> rmsnorm -> Q8_K images in shared memory (ops.rs:7-18 then quant.rs:248-283).
+// `src` is global (read past L1) or, for the embedding, already in scr[0..n).
+__device__ __forceinline__ void phase_norm_quant(const float* src, bool src_in_scr, const float* w, int n, float eps,
+                                                 const MegaSmem& M, const CtaGroup& g) {
+  float* row = M.scr;
+  float* sq = M.scr + n;
+  for (int i = g.tid; i < n; i += g.nthreads) {
+    float v = src_in_scr ? row[i] : __ldcg(src + i);
+    row[i] = v;
+    sq[i] = fmul(v, v);
+  }
+  float ss = group_seq_sum(sq, n, M.ss, g);
+  float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
+  g.sync();
+  for (int i = g.tid; i < n; i += g.nthreads) row[i] = fmul(fmul(row[i], r), w[i]);
+  g.sync();
+  const int warp = g.tid >> 5, nw = g.nthreads >> 5;
+  for (int b = warp; b < n / 256; b += nw) warp_quantize_q8k<false>(row + b * 256, M.sx + b * XK_STRIDE, 1);
+  g.sync();
+}
+
+// A vector another CTA produced -> Q8_K images.
+__device__ __forceinline__ void phase_quant(const float* src, int n, const MegaSmem& M, const CtaGroup& g) {
+  const int warp = g.tid >> 5, nw = g.nthreads >> 5;
+  for (int b = warp; b < n / 256; b += nw) warp_quantize_q8k<true>(src + b * 256, M.sx + b * XK_STRIDE, 1);
+  g.sync();
+}
+
+// Per-head q/k norm, RoPE, KV store and attention for head `h` (ops.rs:74-87, 40-70,
+// 152-157, 185-218), by the consumer warps of one CTA.
+__device__ void phase_attention(const StepParams& P, int li, int h, int pos, const MegaSmem& M, const CtaGroup& g) {
+  const int hd = P.head_dim, kvd = P.n_kv_head * hd, gqa = P.n_head / P.n_kv_head, kvh = h / gqa;
+  const int n = pos + 1, tid = g.tid, T = g.nthreads;
+  float* sq = M.scr;            // hd
+  float* sk = sq + hd;          // hd
+  float* sv = sk + hd;          // hd
+  float* sp = sv + hd;          // hd (squares)
+  float* sc = sp + hd;          // n_ctx scores
+  float* vbuf = sc + ((P.n_ctx + 3) & ~3);  // v_chunk x hd, 16-byte aligned
+  const StepLayer& L = P.layers[li];
+  float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd;
+  float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd;
+  for (int i = tid; i < hd; i += T) {
+    sq[i] = __ldcg(P.q + h * hd + i);
+    sk[i] = __ldcg(P.k + kvh * hd + i);
+    sv[i] = __ldcg(P.v + kvh * hd + i);
+  }
+  g.sync();
+  if (P.qk_norm) {
+    for (int which = 0; which < 2; which++) {
+      float* v = which ? sk : sq;
+      const float* nw = which ? L.k_norm : L.q_norm;
+      for (int i = tid; i < hd; i += T) sp[i] = fmul(v[i], v[i]);
+      float ss = group_seq_sum(sp, hd, M.ss, g, 1 << 30);
+      float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)hd), P.eps)));
+      g.sync();
+      for (int i = tid; i < hd; i += T) v[i] = fmul(fmul(v[i], r), nw[i]);
+      g.sync();
+    }
+  }
+  {
+    const float* cs = P.rope_table + (size_t)pos * P.rot_dim;
+    const int half = P.rot_dim / 2;
+    for (int j = tid; j < 2 * half; j += T) {
+      float* v = j < half ? sq : sk;
+      const int i = j < half ? j : j - half;
+      const int i0 = P.neox ? i : 2 * i, i1 = P.neox ? i + half : 2 * i + 1;
+      const float c = cs[2 * i], s = cs[2 * i + 1];
+      const float x0 = v[i0], x1 = v[i1];
+      v[i0] = fsub(fmul(x0, c), fmul(x1, s));
+      v[i1] = fadd(fmul(x0, s), fmul(x1, c));
+    }
+  }
+  g.sync();
+  if (h % gqa == 0) {
+    for (int i = tid; i < hd; i += T) {
+      kc[(size_t)pos * kvd + kvh * hd + i] = sk[i];
+      vc[(size_t)pos * kvd + kvh * hd + i] = sv[i];
+    }
+  }
+  // scores
+  const float scale = 1.0f / sqrtf((float)hd);
+  float lmax = -INFINITY;
+  for (int t = tid; t < n; t += T) {
+    float s = 0.0f;
+    if (t == pos) {
+      for (int i = 0; i < hd; i++) s = fadd(s, fmul(sq[i], sk[i]));
+    } else {
+      const float4* kt = reinterpret_cast<const float4*>(kc + (size_t)t * kvd + kvh * hd);
+#pragma unroll 4
+      for (int i = 0; i < hd / 4; i++) {
+        float4 kk = kt[i];
+        s = fadd(s, fmul(sq[4 * i], kk.x));
+        s = fadd(s, fmul(sq[4 * i + 1], kk.y));
+        s = fadd(s, fmul(sq[4 * i + 2], kk.z));
+        s = fadd(s, fmul(sq[4 * i + 3], kk.w));
+      }
+    }
+    s = fmul(s, scale);
+    sc[t] = s;
+    lmax = fmaxf(lmax, s);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
+  if ((tid & 31) == 0) M.red[tid >> 5] = lmax;
+  g.sync();
+  float mx = M.red[0];
+  for (int w = 1; w < (T >> 5); w++) mx = fmaxf(mx, M.red[w]);
+  for (int t = tid; t < n; t += T) sc[t] = expf_exact(fsub(sc[t], mx));
+  float sum = group_seq_sum(sc, n, M.ss, g);
+  float inv = fdiv(1.0f, sum);
+  g.sync();
+  for (int t = tid; t < n; t += T) sc[t] = fmul(sc[t], inv);
+  // value mix, positions in order; cached rows are staged through shared memory in chunks
+  float o = 0.0f;
+  for (int c0 = 0; c0 < n; c0 += P.v_chunk) {
+    const int cn = min(P.v_chunk, n - c0);
+    g.sync();
+    for (int j = tid; j < cn * (hd / 4); j += T) {
+      const int t = c0 + j / (hd / 4), i4 = j % (hd / 4);
+      float4 vv;
+      if (t == pos) vv = reinterpret_cast<const float4*>(sv)[i4];
+      else vv = reinterpret_cast<const float4*>(vc + (size_t)t * kvd + kvh * hd)[i4];
+      reinterpret_cast<float4*>(vbuf)[j] = vv;
+    }
+    g.sync();
+    if (tid < hd) {
+#pragma unroll 8
+      for (int t = 0; t < cn; t++) o = fadd(o, fmul(sc[c0 + t], vbuf[t * hd + tid]));
+    }
+  }
+  if (tid < hd) P.xb[h * hd + tid] = o;
+}
+
+// Greedy argmax of the logits (sampler.rs:99-109) and the cursor update, CTA 0 only.
+__device__ void phase_argmax(const StepParams& P, const MegaSmem& M, const CtaGroup& g) {
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = g.tid; i < P.vocab; i += g.nthreads) {
+    float v = __ldcg(P.logits + i);
+    if (v > best) {
+      best = v;
+      idx = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float v2 = __shfl_xor_sync(0xffffffffu, best, o);
+    int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (v2 > best || (v2 == best && i2 < idx)) {
+      best = v2;
+      idx = i2;
+    }
+  }
+  int* redi = reinterpret_cast<int*>(M.red + 32);
+  if ((g.tid & 31) == 0) {
+    M.red[g.tid >> 5] = best;
+    redi[g.tid >> 5] = idx;
+  }
+  g.sync();
+  if (g.tid == 0) {
+    for (int w = 1; w < (g.nthreads >> 5); w++) {
+      if (M.red[w] > best || (M.red[w] == best && redi[w] < idx)) {
+        best = M.red[w];
+        idx = redi[w];
+      }
+    }
+    if (idx == 0x7fffffff) idx = 0;
+    if (P.out_token) *P.out_token = idx;
+    int gcount = P.step[2];
+    if (P.history && gcount < P.history_cap) P.history[gcount] = idx;
+    P.step[0] = idx;
+    P.step[1] = P.step[1] + 1;
+    P.step[2] = gcount + 1;
+  }
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------
+constexpr int MEGA_THREADS = 1024;
+constexpr int MEGA_CONSUMER_WARPS = 31;
+constexpr int MEGA_BAR_BYTES = 128;     // up to 8 stages x (full, empty)
+constexpr int MEGA_SEQSUM_BYTES = 544;  // sizeof(SeqSumScratch) rounded up to 16
+static_assert(sizeof(SeqSumScratch) <= MEGA_SEQSUM_BYTES, "SeqSumScratch layout");
+// Bytes of shared memory besides the ring stages, the activation images and the scratch.
+constexpr int MEGA_TAIL_BYTES = MEGA_BAR_BYTES + MEGA_SEQSUM_BYTES + 64 * 4 + 16;
+
+__global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const StepParams P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  // [stages][sx images][scratch][barriers 128 B][SeqSumScratch 544 B][red 64 floats][abort]
+  const int nb_max = (max(max(P.dim, P.hidden), P.n_head * P.head_dim)) / 256;
+  uint8_t* stages = smem;
+  uint8_t* sx = stages + (size_t)P.n_stages * P.stage_bytes;
+  uint8_t* cur = sx + (size_t)nb_max * XK_STRIDE;  // 16-byte aligned: 304 = 19 * 16
+  float* scr = reinterpret_cast<float*>(cur);
+  cur += P.scratch_bytes;                          // a multiple of 128
+  uint64_t* bars = reinterpret_cast<uint64_t*>(cur);
+  cur += MEGA_BAR_BYTES;
+  SeqSumScratch* ssc = reinterpret_cast<SeqSumScratch*>(cur);
+  cur += MEGA_SEQSUM_BYTES;
+  float* red = reinterpret_cast<float*>(cur);
+  cur += 64 * sizeof(float);
+  volatile int* abort = reinterpret_cast<volatile int*>(cur);
+
+  Ring R;
+  R.stages = stages;
+  R.full = bars;
+  R.empty = bars + P.n_stages;
+  R.n_stages = P.n_stages;
+  R.stage_bytes = P.stage_bytes;
+  R.abort = abort;
+  R.err = P.err;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P.n_stages; s++) {
+      mbar_init(&R.full[s], 1);
+      mbar_init(&R.empty[s], MEGA_CONSUMER_WARPS);
+    }
+    *abort = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const int warp = threadIdx.x >> 5;
+  const int qd = P.n_head * P.head_dim;
+
+  if (warp == MEGA_CONSUMER_WARPS) {
+    // ---- producer warp: one thread walks every matrix product of the step ----
+    if ((threadIdx.x & 31) == 0) {
+      uint32_t pt = 0;
+      for (int li = 0; li < P.n_layer && !*abort; li++) {
+        const StepLayer& L = P.layers[li];
+        GemvSeg qkv[3] = {L.wq, L.wk, L.wv};
+        produce_op(make_op(qkv, 3, 0, P.dim, EPI_STORE, P.stage_bytes), R, pt);
+        produce_op(make_op(&L.wo, 1, 0, qd, EPI_ACCUM, P.stage_bytes), R, pt);
+        GemvSeg gu[2] = {L.gate, L.up};
+        produce_op(make_op(gu, 2, 1, P.dim, EPI_SILU_MUL, P.stage_bytes), R, pt);
+        produce_op(make_op(&L.down, 1, 0, P.hidden, EPI_ACCUM, P.stage_bytes), R, pt);
+      }
+      if (P.want_logits && !*abort) produce_op(make_op(&P.output, 1, 0, P.dim, EPI_STORE, P.stage_bytes), R, pt);
+    }
+    return;
+  }
+
+  // ---- consumer warps ----
+  CtaGroup g{(int)threadIdx.x, MEGA_CONSUMER_WARPS * 32, 1};
+  MegaSmem M{sx, scr, ssc, red};
+  uint32_t ct = 0;
+  unsigned bar_target = 0;
+  const int token = P.step[0], pos = P.step[1];
+
+  // embedding row (quant.rs:300-443 via emit.rs:469): every CTA keeps a copy, CTA 0 publishes it
+  {
+    const uint8_t* row = P.token_embd + (size_t)token * P.embd_row_bytes;
+    for (int e = g.tid; e < P.dim; e += g.nthreads) {
+      float v = dequant_elem(P.embd_kind, row, (size_t)e);
+      scr[e] = v;
+      if (blockIdx.x == 0) P.x[e] = v;
+    }
+    g.sync();
+  }
+
+  bool ok = true;
+  for (int li = 0; li < P.n_layer; li++) {
+    const StepLayer& L = P.layers[li];
+    // A: attn norm + q/k/v
+    phase_norm_quant(P.x, li == 0, L.attn_norm, P.dim, P.eps, M, g);
+    {
+      GemvSeg qkv[3] = {L.wq, L.wk, L.wv};
+      qkv[0].out = P.q;
+      qkv[1].out = P.k;
+      qkv[2].out = P.v;
+      consume_op(make_op(qkv, 3, 0, P.dim, EPI_STORE, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
+    }
+    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    // B: attention, one head per CTA
+    for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
+      if (ok) phase_attention(P, li, h, pos, M, g);
+      g.sync();
+    }
+    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    // C: wo, joined into the residual stream
+    phase_quant(P.xb, qd, M, g);
+    {
+      GemvSeg wo = L.wo;
+      wo.out = P.x;
+      consume_op(make_op(&wo, 1, 0, qd, EPI_ACCUM, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
+    }
+    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    // D: ffn norm + gate/up + SiLU
+    phase_norm_quant(P.x, false, L.ffn_norm, P.dim, P.eps, M, g);
+    {
+      GemvSeg gu[2] = {L.gate, L.up};
+      gu[0].out = P.hb;
+      gu[1].out = P.hb2;
+      consume_op(make_op(gu, 2, 1, P.dim, EPI_SILU_MUL, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
+    }
+    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    // E: down, joined into the residual stream
+    phase_quant(P.hb, P.hidden, M, g);
+    {
+      GemvSeg dn = L.down;
+      dn.out = P.x;
+      consume_op(make_op(&dn, 1, 0, P.hidden, EPI_ACCUM, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
+    }
+    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+  }
+  if (P.want_logits) {
+    phase_norm_quant(P.x, false, P.output_norm, P.dim, P.eps, M, g);
+    GemvSeg out = P.output;
+    out.out = P.logits;
+    consume_op(make_op(&out, 1, 0, P.dim, EPI_STORE, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
+    if (P.with_argmax) {
+      ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+      if (blockIdx.x == 0 && ok) phase_argmax(P, M, g);
+    }
+  }
+}
+
+}  // namespace aot

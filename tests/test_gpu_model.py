@@ -121,3 +121,46 @@ def test_tinyllama_shape_greedy_128_identical(pkg, ob, ctx):
     assert ids.tolist() == want
     assert_bits_equal(g.logits(), om.logits(), "final logits")
     print(f"\n[tinyllama-shape] {n_gen - 1} decode steps in {ms:.1f} ms -> {(n_gen - 1) / ms * 1e3:.0f} tok/s")
+
+
+def _kquant_kinds(layer, tensor):
+    if tensor == "output":
+        return 8
+    return [6, 8, 7][(layer + len(tensor)) % 3]  # Q4_K / Q6_K / Q5_K mix
+
+
+@pytest.mark.parametrize("arch", ["llama", "qwen3"])
+def test_one_kernel_decode_step_bit_exact(pkg, ob, ctx, arch):
+    """The persistent one-kernel decode step against the oracle and against the
+    per-operator path, position by position, then a greedy run on the device."""
+    spec = pkg.model.tiny(arch, n_layer=3, kinds=_kquant_kinds, dim=512, hidden=768, vocab=600)
+    n_ctx = 96
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 8)
+    om = ob.model_from_spec(spec, n_ctx, 8, n_threads=4)
+    tokens = [5, 17, 300, 42, 7, 7, 1, 599, 0]
+    for mega in (1, 0):
+        g.set_option("mega", mega)
+        for graph in (0, 1):
+            g.set_option("graph", graph)
+            om2 = ob.model_from_spec(spec, n_ctx, 8, n_threads=4)
+            for pos, t in enumerate(tokens):
+                g.forward(t, pos, True)
+                om2.forward(t, pos, True)
+                assert_bits_equal(g.read("X"), om2.buf("x"), f"{arch} x pos {pos} mega {mega} graph {graph}")
+                assert_bits_equal(g.logits(), om2.logits(), f"{arch} logits pos {pos} mega {mega} graph {graph}")
+    g.set_option("mega", 1)
+    g.set_option("graph", 1)
+    prompt = tokens[:4]
+    g.forward_batch(prompt, 0, True)
+    om.forward_batch(prompt, 0, True)
+    first = ob.argmax(om.logits())
+    n = 70
+    ids, ms = g.generate(first, len(prompt), n)
+    want, tok = [], first
+    for i in range(n):
+        om.forward(tok, len(prompt) + i, True)
+        tok = ob.argmax(om.logits())
+        want.append(tok)
+    assert ids.tolist() == want
+    assert_bits_equal(g.logits(), om.logits(), "logits after the greedy run")
+    ctx.device_status()
