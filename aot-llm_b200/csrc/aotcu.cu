@@ -595,22 +595,45 @@ static int mega_setup(aotcu_gpu* g) {
   CU_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, MEGA_THREADS, g->mega_smem));
   if (per_sm < 1) return 0;
 
-  auto seg = [&](const aotcu_tensor& t) { return GemvSeg{wptr(g, t), nullptr, (int)t.rows, t.kind}; };
-  std::vector<StepLayer> hl(d.n_layer);
+  auto seg = [&](const aotcu_tensor& t, float* out) { return GemvSeg{wptr(g, t), out, (int)t.rows, t.kind}; };
+  auto make_op = [&](std::initializer_list<GemvSeg> segs, int pair, int cols, int epilogue) {
+    MegaOp op = {};
+    size_t max_rb = 1;
+    int span = 0, i = 0;
+    for (const GemvSeg& sg : segs) {
+      op.seg[i] = sg;
+      op.row_bytes[i] = (uint32_t)kind_row_bytes(sg.kind, cols);
+      max_rb = std::max(max_rb, (size_t)op.row_bytes[i]);
+      span += sg.rows;
+      i++;
+    }
+    op.nseg = i;
+    op.pair = pair;
+    op.cols = cols;
+    op.span_rows = pair ? op.seg[0].rows : span;
+    op.rows_per_cta = (op.span_rows + c->n_sm - 1) / c->n_sm;
+    int tr = (int)((size_t)(stage_bytes - 192) / (max_rb * (pair ? 2 : 1)));
+    op.tile_rows = tr < 1 ? 1 : tr;
+    op.epilogue = epilogue;
+    return op;
+  };
+  float* const X = g->bufs[AOTCU_BUF_X];
+  std::vector<StepLayer> hl(d.n_layer + 1);
   for (int i = 0; i < d.n_layer; i++) {
     const aotcu_layer& l = g->layers[i];
     hl[i].attn_norm = wf32(g, l.attn_norm);
     hl[i].ffn_norm = wf32(g, l.ffn_norm);
     hl[i].q_norm = d.qk_norm ? wf32(g, l.q_norm) : nullptr;
     hl[i].k_norm = d.qk_norm ? wf32(g, l.k_norm) : nullptr;
-    hl[i].wq = seg(l.wq);
-    hl[i].wk = seg(l.wk);
-    hl[i].wv = seg(l.wv);
-    hl[i].wo = seg(l.wo);
-    hl[i].gate = seg(l.gate);
-    hl[i].up = seg(l.up);
-    hl[i].down = seg(l.down);
+    hl[i].qkv = make_op({seg(l.wq, g->bufs[AOTCU_BUF_Q]), seg(l.wk, g->bufs[AOTCU_BUF_K]), seg(l.wv, g->bufs[AOTCU_BUF_V])},
+                        0, d.dim, EPI_STORE);
+    hl[i].wo = make_op({seg(l.wo, X)}, 0, (int)qd, EPI_ACCUM);
+    hl[i].gu = make_op({seg(l.gate, g->bufs[AOTCU_BUF_HB]), seg(l.up, g->bufs[AOTCU_BUF_HB2])}, 1, d.dim, EPI_SILU_MUL);
+    hl[i].down = make_op({seg(l.down, X)}, 0, d.hidden, EPI_ACCUM);
   }
+  // The output head rides in the slot after the last layer (only its qkv field is used).
+  hl[d.n_layer] = StepLayer{};
+  hl[d.n_layer].qkv = make_op({seg(out_t, g->bufs[AOTCU_BUF_LOGITS])}, 0, d.dim, EPI_STORE);
   CU_TRY(cudaMalloc(&g->d_step_layers, hl.size() * sizeof(StepLayer)));
   CU_TRY(cudaMemcpy(g->d_step_layers, hl.data(), hl.size() * sizeof(StepLayer), cudaMemcpyHostToDevice));
   CU_TRY(cudaMalloc(&g->d_grid_bar, sizeof(unsigned)));
@@ -620,7 +643,7 @@ static int mega_setup(aotcu_gpu* g) {
   P.eps = d.eps; P.qk_norm = d.qk_norm; P.neox = d.rope_neox;
   P.layers = g->d_step_layers;
   P.output_norm = wf32(g, g->head.output_norm);
-  P.output = seg(out_t);
+  P.out_op = &g->d_step_layers[d.n_layer].qkv;
   P.token_embd = wptr(g, g->head.token_embd);
   P.embd_kind = g->head.token_embd.kind;
   P.embd_row_bytes = kind_row_bytes(g->head.token_embd.kind, g->head.token_embd.cols);
@@ -635,9 +658,12 @@ static int mega_setup(aotcu_gpu* g) {
   return 0;
 }
 
-static int enqueue_mega(aotcu_gpu* g, int want_logits, bool with_argmax) {
+static int enqueue_mega(aotcu_gpu* g, int want_logits, bool with_argmax, unsigned long long* prof = nullptr,
+                        int prof_cta = 0) {
   aotcu_ctx* c = g->c;
   StepParams P = g->step_params;
+  P.prof = prof;
+  P.prof_cta = prof_cta;
   P.want_logits = want_logits;
   P.with_argmax = with_argmax ? 1 : 0;
   CU_TRY(cudaMemsetAsync(g->d_grid_bar, 0, sizeof(unsigned), c->stream));
@@ -1508,6 +1534,31 @@ int aotcu_bench_gemv_sweep(aotcu_gpu* g, int iters, float* ms_per_sweep, uint64_
   if (bytes_per_sweep) *bytes_per_sweep = bytes;
   g->qsrc = aotcu_gpu::QSrc();
   return check_device_errors(c);
+}
+
+
+// Runs one decode step of the one-kernel path with phase timestamps: out[0..15] are the
+// SM cycles CTA `cta` spent in each phase, summed over layers (0 embed, 1 attn norm,
+// 2 q/k/v, 3 barrier, 4 attention, 5 barrier, 6 quantize, 7 wo, 8 barrier, 9 ffn norm,
+// 10 gate/up, 11 barrier, 12 quantize, 13 down, 14 barrier, 15 head).
+int aotcu_gpu_profile_step(aotcu_gpu* g, uint32_t token, size_t pos, int cta, uint64_t out[32]) {
+  ARG_CHECK(g && out, "NULL argument");
+  ARG_CHECK(g->mega_ok, "this model cannot use the one-kernel decode step");
+  ARG_CHECK(token < (uint32_t)g->head.dims.vocab && pos < g->n_ctx, "token or position out of range");
+  aotcu_ctx* c = g->c;
+  if (int rc = ctx_set_device(c)) return rc;
+  unsigned long long* d = nullptr;
+  CU_TRY(cudaMalloc(&d, 32 * sizeof(unsigned long long)));
+  CU_TRY(cudaMemsetAsync(d, 0, 32 * sizeof(unsigned long long), c->stream));
+  int rc = set_step(g, token, pos, 0);
+  if (!rc) rc = enqueue_mega(g, 1, false, d, cta);
+  if (!rc) rc = check_device_errors(c);
+  if (!rc) {
+    cudaError_t e = cudaMemcpy(out, d, 32 * sizeof(uint64_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) rc = fail(AOTCU_ERR_CUDA, "profile copy: %s", cudaGetErrorString(e));
+  }
+  cudaFree(d);
+  return rc;
 }
 
 }  // extern "C"

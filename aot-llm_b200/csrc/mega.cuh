@@ -28,14 +28,20 @@ struct CtaGroup {
 };
 
 // ---- exact sequential-order sum of non-negative floats in shared memory --------------
+// (((0 + p[0]) + p[1]) + ...) with the rounding of a scalar f32 loop (see seqsum.cuh).
+// Terms are cut into 32-element segments. The binade in which each segment starts is
+// predicted from an inexact prefix sum; every warp builds the exact composite
+// "mantissa -> mantissa" function of its segments for the predicted binade; one thread
+// then walks the segments, applying a composite when the prediction holds and the
+// result stays inside the binade, and otherwise adding that segment's 32 terms one by
+// one. A wrong prediction costs time, never accuracy.
+constexpr int SEQSUM_SEGS = 128;  // segments per pass (4096 terms)
+
 struct SeqSumScratch {
-  SumFn warp_tot[32];
-  SumFn warp_pre[32];
+  float est[SEQSUM_SEGS];     // per-segment inexact sums, then predicted start values
+  SumFn comp[SEQSUM_SEGS];
+  int epred[SEQSUM_SEGS];
   float s;
-  int i0;
-  int ov;
-  int m_at;
-  int m_final;
 };
 
 __device__ __forceinline__ SumFn sumfn_shfl_up(const SumFn& f, int off) {
@@ -55,76 +61,118 @@ __device__ __forceinline__ SumFn sumfn_warp_scan(SumFn f, int lane) {
   return f;
 }
 
-// (((0 + p[0]) + p[1]) + ...) with the rounding of a scalar f32 loop. Every thread of
-// the group calls it and receives the result. `head` terms are added serially first
-// (the running sum changes binade at almost every step there).
-__device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const CtaGroup& g, int head = 48) {
-  const int tid = g.tid, T = g.nthreads, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
-  g.sync();
-  if (tid == 0) {
-    float s = 0.0f;
-    int h = n < head ? n : head;
-    for (int i = 0; i < h; i++) s = fadd(s, p[i]);
-    sc->s = s;
-    sc->i0 = h;
+__device__ __forceinline__ float serial_add_run(float s, const float* p, int n) {
+  int i = 0;
+  for (; i + 8 <= n; i += 8) {
+    float a0 = p[i], a1 = p[i + 1], a2 = p[i + 2], a3 = p[i + 3], a4 = p[i + 4], a5 = p[i + 5], a6 = p[i + 6],
+          a7 = p[i + 7];
+    s = fadd(s, a0);
+    s = fadd(s, a1);
+    s = fadd(s, a2);
+    s = fadd(s, a3);
+    s = fadd(s, a4);
+    s = fadd(s, a5);
+    s = fadd(s, a6);
+    s = fadd(s, a7);
   }
+  for (; i < n; i++) s = fadd(s, p[i]);
+  return s;
+}
+
+// Every thread of the group calls it and receives the result.
+__device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const CtaGroup& g) {
+  const int tid = g.tid, lane = tid & 31, warp = tid >> 5, nwarps = g.nthreads >> 5;
   g.sync();
-  for (int round = 0; round <= n; ++round) {
-    float s = sc->s;
-    const int i0 = sc->i0;
-    if (i0 >= n) return s;
-    const uint32_t sb = f2u(s);
-    if ((sb >> 23) == 255u) {  // inf / nan: no binade structure left, finish serially
-      g.sync();
-      if (tid == 0) {
-        for (int i = i0; i < n; i++) s = fadd(s, p[i]);
-        sc->s = s;
-        sc->i0 = n;
-      }
-      g.sync();
-      return sc->s;
-    }
-    int e, m0;
-    sum_decompose(sb, e, m0);
-    const int rem = n - i0, C = (rem + T - 1) / T;
-    const int lo = i0 + tid * C, hi = min(lo + C, n);
-    SumFn f = sumfn_identity();
-    for (int i = lo; i < hi; i++) f = sumfn_compose(f, sumfn_elem(f2u(p[i]), e));
-    SumFn inc = sumfn_warp_scan(f, lane);
-    if (lane == 31) sc->warp_tot[warp] = inc;
-    if (tid == 0) sc->ov = n;
-    g.sync();
+  if (n <= 128) {
+    // short sums: one warp, terms handed to the add chain by shuffles
     if (warp == 0) {
-      SumFn w = lane < nwarps ? sc->warp_tot[lane] : sumfn_identity();
-      SumFn winc = sumfn_warp_scan(w, lane);
-      SumFn wex = sumfn_shfl_up(winc, 1);
-      if (lane == 0) wex = sumfn_identity();
-      sc->warp_pre[lane] = wex;
-      if (lane == 31) sc->m_final = sumfn_apply(winc, m0);
+      float s = 0.0f;
+      for (int c = 0; c < n; c += 32) {
+        const float v = c + lane < n ? p[c + lane] : 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; k++) s = fadd(s, __shfl_sync(0xffffffffu, v, k));
+      }
+      if (lane == 0) sc->s = s;
     }
     g.sync();
-    SumFn ex = sumfn_shfl_up(inc, 1);
-    if (lane == 0) ex = sumfn_identity();
-    const SumFn pre = sumfn_compose(sc->warp_pre[warp], ex);
-    int m = sumfn_apply(pre, m0);
-    if (m < SUMFN_LIMIT) {
-      for (int i = lo; i < hi; i++) {
-        int m2 = sumfn_apply(sumfn_elem(f2u(p[i]), e), m);
-        if (m2 >= SUMFN_LIMIT) {  // at most one thread gets here: the mantissa is monotone
-          sc->ov = i;
-          sc->m_at = m;
-          break;
+    return sc->s;
+  }
+  if (tid == 0) sc->s = 0.0f;
+  for (int base = 0; base < n; base += SEQSUM_SEGS * 32) {
+    const int len = min(n - base, SEQSUM_SEGS * 32), S = (len + 31) >> 5;
+    // 1. inexact per-segment sums
+    for (int seg = warp; seg < S; seg += nwarps) {
+      const int i = seg * 32 + lane;
+      float v = i < len ? p[base + i] : 0.0f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) sc->est[seg] = v;
+    }
+    g.sync();
+    // 2. predicted value at the start of every segment (one warp)
+    if (warp == 0) {
+      float run = sc->s;
+      for (int c = 0; c < S; c += 32) {
+        const float x = c + lane < S ? sc->est[c + lane] : 0.0f;
+        float inc = x;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          float y = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += y;
         }
-        m = m2;
+        if (c + lane < S) sc->est[c + lane] = run + (inc - x);
+        run += __shfl_sync(0xffffffffu, inc, 31);
       }
     }
     g.sync();
-    const int ov = sc->ov;
-    if (ov == n) return u2f(sum_pack(e, sc->m_final));
+    // 3. exact composite of every segment for its predicted binade
+    for (int seg = warp; seg < S; seg += nwarps) {
+      uint32_t b = f2u(sc->est[seg]);
+      if ((b >> 23) >= 255u || (b >> 31)) b = 0;
+      int e, m;
+      sum_decompose(b, e, m);
+      const int i = seg * 32 + lane;
+      SumFn f = i < len ? sumfn_elem(f2u(p[base + i]), e) : sumfn_identity();
+      f = sumfn_warp_scan(f, lane);
+      if (lane == 31) {
+        sc->comp[seg] = f;
+        sc->epred[seg] = e;
+      }
+    }
     g.sync();
-    if (tid == 0) {
-      sc->s = fadd(u2f(sum_pack(e, sc->m_at)), p[ov]);
-      sc->i0 = ov + 1;
+    // 4. the walk, by one warp with uniform control flow: every lane carries the same
+    // state, lane j of a chunk owns segment j's composite, and values reach the chain
+    // by shuffles issued one segment ahead.
+    if (warp == 0) {
+      int e, m;
+      sum_decompose(f2u(sc->s), e, m);
+      for (int c = 0; c < S; c += 32) {
+        const int seg = c + lane, cnt = min(32, S - c);
+        const SumFn f = seg < S ? sc->comp[seg] : sumfn_identity();
+        const int ep = seg < S ? sc->epred[seg] : -1;
+        int a0n = __shfl_sync(0xffffffffu, f.a0, 0), a1n = __shfl_sync(0xffffffffu, f.a1, 0),
+            epn = __shfl_sync(0xffffffffu, ep, 0);
+        for (int j = 0; j < cnt; j++) {
+          const int a0 = a0n, a1 = a1n, epj = epn;
+          const int jn = j + 1 < cnt ? j + 1 : j;
+          a0n = __shfl_sync(0xffffffffu, f.a0, jn);
+          a1n = __shfl_sync(0xffffffffu, f.a1, jn);
+          epn = __shfl_sync(0xffffffffu, ep, jn);
+          const int m2 = m + ((m & 1) ? a1 : a0);
+          if (epj == e && m2 < SUMFN_LIMIT && e != 255) {
+            m = m2;
+          } else {
+            // serial adds for this segment; the 32 terms come from the lanes (zeros past the end)
+            const int i = (c + j) * 32 + lane;
+            const float v = i < len ? p[base + i] : 0.0f;
+            float s = u2f(sum_pack(e, m));
+#pragma unroll
+            for (int k = 0; k < 32; k++) s = fadd(s, __shfl_sync(0xffffffffu, v, k));
+            sum_decompose(f2u(s), e, m);
+          }
+        }
+      }
+      if (lane == 0) sc->s = u2f(sum_pack(e, m));
     }
     g.sync();
   }
@@ -252,12 +300,21 @@ __device__ __forceinline__ float warp_row_dot_kq(int kind, const uint8_t* row, c
 
 
 // ---- step description (built once by the host, lives in global memory) ------------------
+// One matrix-product phase as both the producer and the consumers see it. The row
+// space (concatenated rows, or shared rows in pair mode) is split evenly over the
+// grid; a CTA walks its share in tiles of `tile_rows` rows.
+struct MegaOp {
+  GemvSeg seg[3];
+  uint32_t row_bytes[3];
+  int nseg, pair, cols, span_rows, rows_per_cta, tile_rows, epilogue;
+};
+
 struct StepLayer {
   const float* attn_norm;
   const float* ffn_norm;
   const float* q_norm;
   const float* k_norm;
-  GemvSeg wq, wk, wv, wo, gate, up, down;  // `out` is filled in by the kernel
+  MegaOp qkv, wo, gu, down;
 };
 
 struct StepParams {
@@ -266,7 +323,7 @@ struct StepParams {
   int qk_norm, neox;
   const StepLayer* layers;
   const float* output_norm;
-  GemvSeg output;
+  const MegaOp* out_op;
   const uint8_t* token_embd;
   int embd_kind;
   size_t embd_row_bytes;
@@ -282,39 +339,9 @@ struct StepParams {
   int n_stages, stage_bytes;
   int scratch_bytes;   // f32 scratch region (norm rows, attention)
   int v_chunk;         // positions per staged V chunk
+  unsigned long long* prof;  // optional: cycles per phase, accumulated by one CTA
+  int prof_cta;
 };
-
-// One matrix-product phase as both the producer and the consumers see it.
-struct MegaOp {
-  GemvSeg seg[3];
-  int nseg, pair, cols, span_rows, rows_per_cta, tile_rows, epilogue;
-};
-
-__device__ __forceinline__ MegaOp make_op(const GemvSeg* segs, int nseg, int pair, int cols, int epilogue, int stage_bytes) {
-  MegaOp op;
-  size_t max_rb = 1;
-  int span = 0;
-  for (int i = 0; i < 3; i++) {
-    if (i < nseg) {
-      op.seg[i] = segs[i];
-      size_t rb = kind_row_bytes(segs[i].kind, cols);
-      max_rb = rb > max_rb ? rb : max_rb;
-      span += segs[i].rows;
-    } else {
-      op.seg[i] = GemvSeg{nullptr, nullptr, 0, 0};
-    }
-  }
-  op.nseg = nseg;
-  op.pair = pair;
-  op.cols = cols;
-  op.span_rows = pair ? segs[0].rows : span;
-  op.rows_per_cta = (op.span_rows + gridDim.x - 1) / gridDim.x;
-  const int mult = pair ? 2 : 1;
-  int tr = (int)((size_t)(stage_bytes - 192) / (max_rb * mult));
-  op.tile_rows = tr < 1 ? 1 : tr;
-  op.epilogue = epilogue;
-  return op;
-}
 
 // ---- shared-memory ring --------------------------------------------------------------------
 struct Ring {
@@ -324,6 +351,18 @@ struct Ring {
   int n_stages, stage_bytes;
   volatile int* abort;  // set when any bounded wait of this CTA expired
   int* err;
+};
+
+// Position of a producer or consumer in the ring: stage index and use parity.
+struct RingPos {
+  int st;
+  uint32_t parity;
+  __device__ __forceinline__ void advance(int n_stages) {
+    if (++st == n_stages) {
+      st = 0;
+      parity ^= 1u;
+    }
+  }
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -340,87 +379,111 @@ __device__ __forceinline__ bool ring_wait(const Ring& R, uint64_t* bar, uint32_t
   return false;
 }
 
-struct OpSchedule {
-  int c0, c1, n_tiles;
-  size_t row_bytes[3];
-};
-__device__ __forceinline__ OpSchedule op_schedule(const MegaOp& op) {
-  OpSchedule S;
-  for (int s = 0; s < 3; s++) S.row_bytes[s] = s < op.nseg ? kind_row_bytes(op.seg[s].kind, op.cols) : 0;
-  S.c0 = blockIdx.x * op.rows_per_cta;
-  S.c1 = min(S.c0 + op.rows_per_cta, op.span_rows);
-  S.n_tiles = S.c1 > S.c0 ? (S.c1 - S.c0 + op.tile_rows - 1) / op.tile_rows : 0;
-  return S;
+// Byte ranges of the tile covering rows [t0, t1) of the op's row space.
+__device__ __forceinline__ int op_tile_parts(const MegaOp& op, int t0, int t1, TilePart parts[3]) {
+  if (op.pair || op.nseg == 1) {
+    const int np = op.pair ? 2 : 1;
+    uint32_t soff = 0;
+#pragma unroll
+    for (int s = 0; s < 2; s++) {
+      if (s < np) {
+        TilePart& tp = parts[s];
+        tp.seg = s;
+        tp.row0 = t0;
+        tp.rows = t1 - t0;
+        tp.src = op.seg[s].w + (size_t)t0 * op.row_bytes[s];
+        tp.len = (uint32_t)(t1 - t0) * op.row_bytes[s];
+        tp.soff = soff;
+        soff += bulk_superset_bytes(tp.src, tp.len) + 16;
+      }
+    }
+    return np;
+  }
+  int n = 0, base = 0;
+  uint32_t soff = 0;
+  for (int s = 0; s < op.nseg; s++) {
+    const int a = max(t0, base), b = min(t1, base + op.seg[s].rows);
+    if (a < b) {
+      TilePart& tp = parts[n++];
+      tp.seg = s;
+      tp.row0 = a - base;
+      tp.rows = b - a;
+      tp.src = op.seg[s].w + (size_t)(a - base) * op.row_bytes[s];
+      tp.len = (uint32_t)(b - a) * op.row_bytes[s];
+      tp.soff = soff;
+      soff += bulk_superset_bytes(tp.src, tp.len) + 16;
+    }
+    base += op.seg[s].rows;
+  }
+  return n;
 }
 
 // Producer side (one thread): request every tile of this CTA's share of `op`.
-__device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, uint32_t& pt) {
-  const OpSchedule S = op_schedule(op);
-  for (int t = 0; t < S.n_tiles; t++, pt++) {
-    const int st = pt % R.n_stages;
-    const uint32_t k = pt / R.n_stages;
-    if (!ring_wait(R, &R.empty[st], (k & 1u) ^ 1u)) return;
+__device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, RingPos& pp) {
+  const int c0 = blockIdx.x * op.rows_per_cta, c1 = min(c0 + op.rows_per_cta, op.span_rows);
+  for (int t0 = c0; t0 < c1; t0 += op.tile_rows) {
+    if (!ring_wait(R, &R.empty[pp.st], pp.parity ^ 1u)) return;
     TilePart parts[3];
-    const int t0 = S.c0 + t * op.tile_rows, t1 = min(t0 + op.tile_rows, S.c1);
-    const int np = tile_parts(op, t0, t1, S.row_bytes, parts);
+    const int t1 = min(t0 + op.tile_rows, c1);
+    const int np = op_tile_parts(op, t0, t1, parts);
     uint32_t total = 0;
     for (int i = 0; i < np; i++) total += bulk_superset_bytes(parts[i].src, parts[i].len);
-    mbar_expect_tx(&R.full[st], total);
+    mbar_expect_tx(&R.full[pp.st], total);
     for (int i = 0; i < np; i++)
-      bulk_g2s_superset(R.stages + (size_t)st * R.stage_bytes + parts[i].soff, parts[i].src, parts[i].len, &R.full[st]);
+      bulk_g2s_superset(R.stages + (size_t)pp.st * R.stage_bytes + parts[i].soff, parts[i].src, parts[i].len, &R.full[pp.st]);
+    pp.advance(R.n_stages);
   }
 }
 
 // Consumer side (every consumer warp): rows of each tile are dealt to warps round robin.
-// `sx` holds the Q8_K images of the activation vector. Returns false after a failed wait.
-__device__ __forceinline__ bool consume_op(const MegaOp& op, const Ring& R, uint32_t& ct, const uint8_t* sx, int warp,
+// `sx` holds the Q8_K images of the activation vector.
+__device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp,
                                            int n_warps) {
-  const OpSchedule S = op_schedule(op);
+  const int c0 = blockIdx.x * op.rows_per_cta, c1 = min(c0 + op.rows_per_cta, op.span_rows);
   const int lane = threadIdx.x & 31;
-  const int nb = op.cols / 256;
-  for (int t = 0; t < S.n_tiles; t++, ct++) {
-    const int st = ct % R.n_stages;
-    const uint32_t k = ct / R.n_stages;
-    if (!ring_wait(R, &R.full[st], k & 1u)) return false;
-    TilePart parts[3];
-    const int t0 = S.c0 + t * op.tile_rows, t1 = min(t0 + op.tile_rows, S.c1);
-    const int np = tile_parts(op, t0, t1, S.row_bytes, parts);
-    const uint8_t* stage = R.stages + (size_t)st * R.stage_bytes;
+  const int nb = op.cols >> 8;
+  for (int t0 = c0; t0 < c1; t0 += op.tile_rows) {
+    if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
+    const int t1 = min(t0 + op.tile_rows, c1);
+    const uint8_t* stage = R.stages + (size_t)cp.st * R.stage_bytes;
     const int R_rows = t1 - t0;
-    if (op.pair) {
-      const uint8_t* base0 = stage + parts[0].soff + ((uintptr_t)parts[0].src & 15u);
-      const uint8_t* base1 = stage + parts[1].soff + ((uintptr_t)parts[1].src & 15u);
-      for (int u = warp; u < R_rows; u += n_warps) {
-        float g = warp_row_dot_kq(op.seg[0].kind, base0 + (size_t)u * S.row_bytes[0], sx, nb);
-        float up = warp_row_dot_kq(op.seg[1].kind, base1 + (size_t)u * S.row_bytes[1], sx, nb);
-        if (lane == 0) {
-          const int r = t0 + u;
-          op.seg[0].out[r] = op.epilogue == EPI_SILU_MUL ? silu_mul_exact(g, up) : g;
-          op.seg[1].out[r] = up;
+    if (warp < R_rows) {
+      TilePart parts[3];
+      const int np = op_tile_parts(op, t0, t1, parts);
+      if (op.pair) {
+        const uint8_t* base0 = stage + parts[0].soff + ((uintptr_t)parts[0].src & 15u);
+        const uint8_t* base1 = stage + parts[1].soff + ((uintptr_t)parts[1].src & 15u);
+        for (int u = warp; u < R_rows; u += n_warps) {
+          float g = warp_row_dot_kq(op.seg[0].kind, base0 + (size_t)u * op.row_bytes[0], sx, nb);
+          float up = warp_row_dot_kq(op.seg[1].kind, base1 + (size_t)u * op.row_bytes[1], sx, nb);
+          if (lane == 0) {
+            const int r = t0 + u;
+            op.seg[0].out[r] = op.epilogue == EPI_SILU_MUL ? silu_mul_exact(g, up) : g;
+            op.seg[1].out[r] = up;
+          }
         }
-      }
-    } else {
-      for (int u = warp; u < R_rows; u += n_warps) {
-        int lr = u, pi = 0;
-        while (pi < np - 1 && lr >= parts[pi].rows) {
-          lr -= parts[pi].rows;
-          pi++;
-        }
-        const TilePart& tp = parts[pi];
-        const uint8_t* row = stage + tp.soff + ((uintptr_t)tp.src & 15u) + (size_t)lr * S.row_bytes[tp.seg];
-        float v = warp_row_dot_kq(op.seg[tp.seg].kind, row, sx, nb);
-        if (lane == 0) {
-          float* o = op.seg[tp.seg].out + tp.row0 + lr;
-          *o = op.epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
+      } else {
+        for (int u = warp; u < R_rows; u += n_warps) {
+          int lr = u, pi = 0;
+          while (pi < np - 1 && lr >= parts[pi].rows) {
+            lr -= parts[pi].rows;
+            pi++;
+          }
+          const TilePart& tp = parts[pi];
+          const uint8_t* row = stage + tp.soff + ((uintptr_t)tp.src & 15u) + (size_t)lr * op.row_bytes[tp.seg];
+          float v = warp_row_dot_kq(op.seg[tp.seg].kind, row, sx, nb);
+          if (lane == 0) {
+            float* o = op.seg[tp.seg].out + tp.row0 + lr;
+            *o = op.epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
+          }
         }
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&R.empty[st]);
+    if (lane == 0) mbar_arrive(&R.empty[cp.st]);
+    cp.advance(R.n_stages);
   }
-  return true;
 }
-
 
 // ---- grid-wide barrier for the consumer warps ---------------------------------------------
 // Arrival counter in global memory, zero at launch, never reset: barrier number k
@@ -453,6 +516,19 @@ __device__ __forceinline__ bool grid_sync(const StepParams& P, const CtaGroup& g
   return !*abort;
 }
 
+// Optional sub-phase cycle counters (slots 16..31 of the profile array).
+struct SubProf {
+  unsigned long long* prof;
+  long long last;
+  __device__ __forceinline__ void mark(int slot) {
+    if (prof) {
+      long long now = clock64();
+      prof[slot] += (unsigned long long)(now - last);
+      last = now;
+    }
+  }
+};
+
 // ---- activation phases -----------------------------------------------------------------------
 struct MegaSmem {
   uint8_t* sx;          // Q8_K images of the current activation vector
@@ -464,7 +540,8 @@ struct MegaSmem {
 // x -> rmsnorm -> Q8_K images in shared memory (ops.rs:7-18 then quant.rs:248-283).
 // `src` is global (read past L1) or, for the embedding, already in scr[0..n).
 __device__ __forceinline__ void phase_norm_quant(const float* src, bool src_in_scr, const float* w, int n, float eps,
-                                                 const MegaSmem& M, const CtaGroup& g) {
+                                                 const MegaSmem& M, const CtaGroup& g, SubProf sp = SubProf{nullptr, 0}) {
+  sp.last = clock64();
   float* row = M.scr;
   float* sq = M.scr + n;
   for (int i = g.tid; i < n; i += g.nthreads) {
@@ -472,14 +549,19 @@ __device__ __forceinline__ void phase_norm_quant(const float* src, bool src_in_s
     row[i] = v;
     sq[i] = fmul(v, v);
   }
+  g.sync();
+  sp.mark(16);
   float ss = group_seq_sum(sq, n, M.ss, g);
+  sp.mark(17);
   float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
   g.sync();
   for (int i = g.tid; i < n; i += g.nthreads) row[i] = fmul(fmul(row[i], r), w[i]);
   g.sync();
+  sp.mark(18);
   const int warp = g.tid >> 5, nw = g.nthreads >> 5;
   for (int b = warp; b < n / 256; b += nw) warp_quantize_q8k<false>(row + b * 256, M.sx + b * XK_STRIDE, 1);
   g.sync();
+  sp.mark(19);
 }
 
 // A vector another CTA produced -> Q8_K images.
@@ -491,7 +573,9 @@ __device__ __forceinline__ void phase_quant(const float* src, int n, const MegaS
 
 // Per-head q/k norm, RoPE, KV store and attention for head `h` (ops.rs:74-87, 40-70,
 // 152-157, 185-218), by the consumer warps of one CTA.
-__device__ void phase_attention(const StepParams& P, int li, int h, int pos, const MegaSmem& M, const CtaGroup& g) {
+__device__ void phase_attention(const StepParams& P, int li, int h, int pos, const MegaSmem& M, const CtaGroup& g,
+                                SubProf pf = SubProf{nullptr, 0}) {
+  pf.last = clock64();
   const int hd = P.head_dim, kvd = P.n_kv_head * hd, gqa = P.n_head / P.n_kv_head, kvh = h / gqa;
   const int n = pos + 1, tid = g.tid, T = g.nthreads;
   float* sq = M.scr;            // hd
@@ -514,7 +598,7 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
       float* v = which ? sk : sq;
       const float* nw = which ? L.k_norm : L.q_norm;
       for (int i = tid; i < hd; i += T) sp[i] = fmul(v[i], v[i]);
-      float ss = group_seq_sum(sp, hd, M.ss, g, 1 << 30);
+      float ss = group_seq_sum(sp, hd, M.ss, g);
       float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)hd), P.eps)));
       g.sync();
       for (int i = tid; i < hd; i += T) v[i] = fmul(fmul(v[i], r), nw[i]);
@@ -541,6 +625,7 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
       vc[(size_t)pos * kvd + kvh * hd + i] = sv[i];
     }
   }
+  pf.mark(20);
   // scores
   const float scale = 1.0f / sqrtf((float)hd);
   float lmax = -INFINITY;
@@ -567,10 +652,14 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
   for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
   if ((tid & 31) == 0) M.red[tid >> 5] = lmax;
   g.sync();
+  pf.mark(21);
   float mx = M.red[0];
   for (int w = 1; w < (T >> 5); w++) mx = fmaxf(mx, M.red[w]);
   for (int t = tid; t < n; t += T) sc[t] = expf_exact(fsub(sc[t], mx));
+  g.sync();
+  pf.mark(22);
   float sum = group_seq_sum(sc, n, M.ss, g);
+  pf.mark(23);
   float inv = fdiv(1.0f, sum);
   g.sync();
   for (int t = tid; t < n; t += T) sc[t] = fmul(sc[t], inv);
@@ -593,6 +682,7 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
     }
   }
   if (tid < hd) P.xb[h * hd + tid] = o;
+  pf.mark(24);
 }
 
 // Greedy argmax of the logits (sampler.rs:99-109) and the cursor update, CTA 0 only.
@@ -642,14 +732,14 @@ __device__ void phase_argmax(const StepParams& P, const MegaSmem& M, const CtaGr
 constexpr int MEGA_THREADS = 1024;
 constexpr int MEGA_CONSUMER_WARPS = 31;
 constexpr int MEGA_BAR_BYTES = 128;     // up to 8 stages x (full, empty)
-constexpr int MEGA_SEQSUM_BYTES = 544;  // sizeof(SeqSumScratch) rounded up to 16
+constexpr int MEGA_SEQSUM_BYTES = 2064;  // sizeof(SeqSumScratch) rounded up to 16
 static_assert(sizeof(SeqSumScratch) <= MEGA_SEQSUM_BYTES, "SeqSumScratch layout");
 // Bytes of shared memory besides the ring stages, the activation images and the scratch.
 constexpr int MEGA_TAIL_BYTES = MEGA_BAR_BYTES + MEGA_SEQSUM_BYTES + 64 * 4 + 16;
 
 __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const StepParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  // [stages][sx images][scratch][barriers 128 B][SeqSumScratch 544 B][red 64 floats][abort]
+  // [stages][sx images][scratch][barriers 128 B][SeqSumScratch][red 64 floats][abort]
   const int nb_max = (max(max(P.dim, P.hidden), P.n_head * P.head_dim)) / 256;
   uint8_t* stages = smem;
   uint8_t* sx = stages + (size_t)P.n_stages * P.stage_bytes;
@@ -688,17 +778,15 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   if (warp == MEGA_CONSUMER_WARPS) {
     // ---- producer warp: one thread walks every matrix product of the step ----
     if ((threadIdx.x & 31) == 0) {
-      uint32_t pt = 0;
+      RingPos pp{0, 0u};
       for (int li = 0; li < P.n_layer && !*abort; li++) {
         const StepLayer& L = P.layers[li];
-        GemvSeg qkv[3] = {L.wq, L.wk, L.wv};
-        produce_op(make_op(qkv, 3, 0, P.dim, EPI_STORE, P.stage_bytes), R, pt);
-        produce_op(make_op(&L.wo, 1, 0, qd, EPI_ACCUM, P.stage_bytes), R, pt);
-        GemvSeg gu[2] = {L.gate, L.up};
-        produce_op(make_op(gu, 2, 1, P.dim, EPI_SILU_MUL, P.stage_bytes), R, pt);
-        produce_op(make_op(&L.down, 1, 0, P.hidden, EPI_ACCUM, P.stage_bytes), R, pt);
+        produce_op(L.qkv, R, pp);
+        produce_op(L.wo, R, pp);
+        produce_op(L.gu, R, pp);
+        produce_op(L.down, R, pp);
       }
-      if (P.want_logits && !*abort) produce_op(make_op(&P.output, 1, 0, P.dim, EPI_STORE, P.stage_bytes), R, pt);
+      if (P.want_logits && !*abort) produce_op(*P.out_op, R, pp);
     }
     return;
   }
@@ -706,9 +794,19 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   // ---- consumer warps ----
   CtaGroup g{(int)threadIdx.x, MEGA_CONSUMER_WARPS * 32, 1};
   MegaSmem M{sx, scr, ssc, red};
-  uint32_t ct = 0;
+  RingPos cp{0, 0u};
   unsigned bar_target = 0;
   const int token = P.step[0], pos = P.step[1];
+  const bool prof_on = P.prof && (int)blockIdx.x == P.prof_cta && g.tid == 0;
+  long long prof_last = clock64();
+#define MEGA_PROF(slot)                                 \
+  do {                                                  \
+    if (prof_on) {                                      \
+      long long now_ = clock64();                       \
+      P.prof[slot] += (unsigned long long)(now_ - prof_last); \
+      prof_last = now_;                                 \
+    }                                                   \
+  } while (0)
 
   // embedding row (quant.rs:300-443 via emit.rs:469): every CTA keeps a copy, CTA 0 publishes it
   {
@@ -720,62 +818,58 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     }
     g.sync();
   }
+  MEGA_PROF(0);
 
   bool ok = true;
   for (int li = 0; li < P.n_layer; li++) {
     const StepLayer& L = P.layers[li];
     // A: attn norm + q/k/v
-    phase_norm_quant(P.x, li == 0, L.attn_norm, P.dim, P.eps, M, g);
-    {
-      GemvSeg qkv[3] = {L.wq, L.wk, L.wv};
-      qkv[0].out = P.q;
-      qkv[1].out = P.k;
-      qkv[2].out = P.v;
-      consume_op(make_op(qkv, 3, 0, P.dim, EPI_STORE, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
-    }
+    phase_norm_quant(P.x, li == 0, L.attn_norm, P.dim, P.eps, M, g, SubProf{prof_on ? P.prof : nullptr, 0});
+    MEGA_PROF(1);
+    consume_op(L.qkv, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
+    MEGA_PROF(2);
     ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    MEGA_PROF(3);
     // B: attention, one head per CTA
     for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
-      if (ok) phase_attention(P, li, h, pos, M, g);
+      if (ok) phase_attention(P, li, h, pos, M, g, SubProf{prof_on ? P.prof : nullptr, 0});
       g.sync();
     }
-    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    MEGA_PROF(4);
+    ok = grid_sync(P, g, bar_target, abort);
+    MEGA_PROF(5);
     // C: wo, joined into the residual stream
     phase_quant(P.xb, qd, M, g);
-    {
-      GemvSeg wo = L.wo;
-      wo.out = P.x;
-      consume_op(make_op(&wo, 1, 0, qd, EPI_ACCUM, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
-    }
-    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    MEGA_PROF(6);
+    consume_op(L.wo, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
+    MEGA_PROF(7);
+    ok = grid_sync(P, g, bar_target, abort);
+    MEGA_PROF(8);
     // D: ffn norm + gate/up + SiLU
     phase_norm_quant(P.x, false, L.ffn_norm, P.dim, P.eps, M, g);
-    {
-      GemvSeg gu[2] = {L.gate, L.up};
-      gu[0].out = P.hb;
-      gu[1].out = P.hb2;
-      consume_op(make_op(gu, 2, 1, P.dim, EPI_SILU_MUL, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
-    }
-    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    MEGA_PROF(9);
+    consume_op(L.gu, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
+    MEGA_PROF(10);
+    ok = grid_sync(P, g, bar_target, abort);
+    MEGA_PROF(11);
     // E: down, joined into the residual stream
     phase_quant(P.hb, P.hidden, M, g);
-    {
-      GemvSeg dn = L.down;
-      dn.out = P.x;
-      consume_op(make_op(&dn, 1, 0, P.hidden, EPI_ACCUM, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
-    }
-    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    MEGA_PROF(12);
+    consume_op(L.down, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
+    MEGA_PROF(13);
+    ok = grid_sync(P, g, bar_target, abort);
+    MEGA_PROF(14);
   }
   if (P.want_logits) {
     phase_norm_quant(P.x, false, P.output_norm, P.dim, P.eps, M, g);
-    GemvSeg out = P.output;
-    out.out = P.logits;
-    consume_op(make_op(&out, 1, 0, P.dim, EPI_STORE, P.stage_bytes), R, ct, sx, warp, MEGA_CONSUMER_WARPS);
+    consume_op(*P.out_op, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
     if (P.with_argmax) {
       ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
       if (blockIdx.x == 0 && ok) phase_argmax(P, M, g);
     }
   }
+  MEGA_PROF(15);
+#undef MEGA_PROF
 }
 
 }  // namespace aot

@@ -309,6 +309,11 @@ class Gpu:
         check(L.load().aotcu_bench_gemv_sweep(self.h, iters, C.byref(ms), C.byref(n), C.byref(b)))
         return ms.value, n.value, b.value
 
+    def profile_step(self, token: int, pos: int, cta: int = 0) -> np.ndarray:
+        out = np.zeros(32, dtype=np.uint64)
+        check(L.load().aotcu_gpu_profile_step(self.h, token, pos, cta, ptr(out)))
+        return out
+
     def dispatches(self) -> int:
         return L.load().aotcu_gpu_dispatches(self.h)
 

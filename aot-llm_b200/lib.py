@@ -135,6 +135,7 @@ SYMBOLS = {
     "aotcu_gpu_dispatches": (C.c_uint64, [_vp]),
     "aotcu_gpu_set_option": (_i, [_vp, C.c_char_p, _i]),
     "aotcu_bench_gemv_sweep": (_i, [_vp, _i, C.POINTER(_f), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "aotcu_gpu_profile_step": (_i, [_vp, _u32, _sz, _i, _vp]),
     "aotcu_synth_quantize_row": (_i, [_i, _vp, _sz, _vp]),
     "aotcu_synth_tensor": (_i, [_i, _sz, _sz, _f, _f, C.c_uint64, _vp]),
     "aotcu_synth_blocks": (_i, [_i, _sz, C.c_uint64, _vp]),

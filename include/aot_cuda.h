@@ -252,6 +252,11 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value);
 int aotcu_bench_gemv_sweep(aotcu_gpu* g, int iters, float* ms_per_sweep, uint64_t* launches_per_sweep,
                            uint64_t* bytes_per_sweep);
 
+/* Tuning aid for the one-kernel decode step (no counterpart in the reference): runs
+ * one step and returns the SM cycles CTA `cta` spent in each of its 16 phases
+ * (slots 16..31: sub-phases of the first norm and of attention). */
+int aotcu_gpu_profile_step(aotcu_gpu* g, uint32_t token, size_t pos, int cta, uint64_t out[32]);
+
 /* ---- synthetic test data (the encoders of crates/aot-kernels/src/quantize.rs) */
 /* quantize_row (quantize.rs:16-294): encodes n floats as one row of `kind` into
  * out (row_bytes(kind, n) bytes). Host memory, CPU code: this is data

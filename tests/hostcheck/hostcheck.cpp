@@ -166,4 +166,50 @@ float hc_seqsum(const float* p, size_t n, int T, int head, int* rounds) {
   return s;
 }
 
+
+// The speculative segmented evaluation used on the device: 32-term segments, the
+// starting binade of each segment predicted from an inexact prefix sum, one exact
+// composite per segment, then a serial walk that applies a composite when the
+// prediction holds and the result stays inside the binade, and otherwise adds the
+// segment's terms one by one. *fallbacks receives the number of serial segments.
+float hc_seqsum_seg(const float* p, size_t n, int* fallbacks) {
+  const size_t S = (n + 31) / 32;
+  std::vector<float> est(S + 1, 0.0f);
+  for (size_t g = 0; g < S; g++) {
+    float t = 0.0f;  // any estimate works; use a pairwise-looking sum
+    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) t += p[i];
+    est[g + 1] = est[g] + t;
+  }
+  std::vector<SumFn> comp(S);
+  std::vector<int> epred(S);
+  for (size_t g = 0; g < S; g++) {
+    int e, m;
+    uint32_t b = f2u(est[g]);
+    if ((b >> 23) == 255) b = 0x7f000000u;
+    sum_decompose(b, e, m);
+    epred[g] = e;
+    SumFn f = sumfn_identity();
+    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) f = sumfn_compose(f, sumfn_elem(f2u(p[i]), e));
+    comp[g] = f;
+  }
+  float s = 0.0f;
+  int nf = 0;
+  for (size_t g = 0; g < S; g++) {
+    uint32_t sb = f2u(s);
+    int e, m;
+    sum_decompose(sb, e, m);
+    if ((sb >> 23) != 255 && e == epred[g]) {
+      int m2 = sumfn_apply(comp[g], m);
+      if (m2 < SUMFN_LIMIT) {
+        s = u2f(sum_pack(e, m2));
+        continue;
+      }
+    }
+    nf++;
+    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) s = fadd(s, p[i]);
+  }
+  if (fallbacks) *fallbacks = nf;
+  return s;
+}
+
 }  // extern "C"

@@ -126,7 +126,8 @@ def test_tinyllama_shape_greedy_128_identical(pkg, ob, ctx):
 def _kquant_kinds(layer, tensor):
     if tensor == "output":
         return 8
-    return [6, 8, 7][(layer + len(tensor)) % 3]  # Q4_K / Q6_K / Q5_K mix
+    name = "gate" if tensor == "up" else tensor  # gate and up share a kind (fused launch)
+    return [6, 8, 7][(layer + len(name)) % 3]  # Q4_K / Q6_K / Q5_K mix
 
 
 @pytest.mark.parametrize("arch", ["llama", "qwen3"])
