@@ -576,7 +576,8 @@ static int mega_setup(aotcu_gpu* g) {
   size_t nb_max = std::max(std::max((size_t)d.dim, (size_t)d.hidden), qd) / 256;
   size_t scratch = std::max((size_t)2 * d.dim, (size_t)4 * d.head_dim + ((g->n_ctx + 3) & ~(size_t)3) + (size_t)v_chunk * d.head_dim) * sizeof(float);
   scratch = (scratch + 127) & ~(size_t)127;
-  size_t fixed = nb_max * XK_STRIDE + scratch + MEGA_TAIL_BYTES;
+  const size_t table_bytes = (((size_t)d.n_layer + 1) * sizeof(StepLayer) + 15) & ~(size_t)15;
+  size_t fixed = nb_max * XK_STRIDE + scratch + MEGA_TAIL_BYTES + table_bytes;
   if (fixed + 2 * (size_t)stage_bytes > c->max_smem) return 0;
   // The largest row of any matrix must fit one stage.
   size_t max_rb = 0;
@@ -634,7 +635,7 @@ static int mega_setup(aotcu_gpu* g) {
   // The output head rides in the slot after the last layer (only its qkv field is used).
   hl[d.n_layer] = StepLayer{};
   hl[d.n_layer].qkv = make_op({seg(out_t, g->bufs[AOTCU_BUF_LOGITS])}, 0, d.dim, EPI_STORE);
-  CU_TRY(cudaMalloc(&g->d_step_layers, hl.size() * sizeof(StepLayer)));
+  CU_TRY(cudaMalloc(&g->d_step_layers, hl.size() * sizeof(StepLayer) + 16));
   CU_TRY(cudaMemcpy(g->d_step_layers, hl.data(), hl.size() * sizeof(StepLayer), cudaMemcpyHostToDevice));
   CU_TRY(cudaMalloc(&g->d_grid_bar, sizeof(unsigned)));
   StepParams& P = g->step_params;
@@ -653,7 +654,7 @@ static int mega_setup(aotcu_gpu* g) {
   P.rope_table = g->rope_table;
   P.step = g->d_step; P.history = g->d_history; P.history_cap = (int)g->history_cap; P.out_token = g->d_out_token;
   P.grid_bar = g->d_grid_bar; P.err = c->d_err;
-  P.n_stages = n_stages; P.stage_bytes = stage_bytes; P.scratch_bytes = (int)scratch; P.v_chunk = v_chunk;
+  P.n_stages = n_stages; P.stage_bytes = stage_bytes; P.scratch_bytes = (int)scratch; P.v_chunk = v_chunk; P.table_bytes = (int)table_bytes;
   g->mega_ok = true;
   return 0;
 }

@@ -39,47 +39,18 @@ constexpr int SEQSUM_SEGS = 128;  // segments per pass (4096 terms)
 
 struct SeqSumScratch {
   float est[SEQSUM_SEGS];     // per-segment inexact sums, then predicted start values
-  SumFn comp[SEQSUM_SEGS];
-  int epred[SEQSUM_SEGS];
+  int csum[SEQSUM_SEGS];      // integer mantissa increment of the segment in its predicted binade
+  int epred[SEQSUM_SEGS];     // predicted exponent field, or -1 when the segment needs term-by-term adds
   float s;
 };
 
-__device__ __forceinline__ SumFn sumfn_shfl_up(const SumFn& f, int off) {
-  SumFn o;
-  o.a0 = __shfl_up_sync(0xffffffffu, f.a0, off);
-  o.a1 = __shfl_up_sync(0xffffffffu, f.a1, off);
-  return o;
-}
-
-// Inclusive scan (composition in lane order) across one warp.
-__device__ __forceinline__ SumFn sumfn_warp_scan(SumFn f, int lane) {
-#pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    SumFn o = sumfn_shfl_up(f, off);
-    if (lane >= off) f = sumfn_compose(o, f);
-  }
-  return f;
-}
-
-__device__ __forceinline__ float serial_add_run(float s, const float* p, int n) {
-  int i = 0;
-  for (; i + 8 <= n; i += 8) {
-    float a0 = p[i], a1 = p[i + 1], a2 = p[i + 2], a3 = p[i + 3], a4 = p[i + 4], a5 = p[i + 5], a6 = p[i + 6],
-          a7 = p[i + 7];
-    s = fadd(s, a0);
-    s = fadd(s, a1);
-    s = fadd(s, a2);
-    s = fadd(s, a3);
-    s = fadd(s, a4);
-    s = fadd(s, a5);
-    s = fadd(s, a6);
-    s = fadd(s, a7);
-  }
-  for (; i < n; i++) s = fadd(s, p[i]);
-  return s;
-}
-
 // Every thread of the group calls it and receives the result.
+//
+// Inside one binade and without exact ties, adding a whole segment is adding the integer
+// C = sum_i round(p_i / ulp) to the mantissa, so the walk over segments is an integer
+// prefix sum (one warp, one scan per 32 segments). A segment is handled term by term,
+// with real f32 adds, when its predicted binade is wrong, when the mantissa would leave
+// the binade inside it, or when one of its terms is an exact tie.
 __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const CtaGroup& g) {
   const int tid = g.tid, lane = tid & 31, warp = tid >> 5, nwarps = g.nthreads >> 5;
   g.sync();
@@ -125,51 +96,59 @@ __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const C
       }
     }
     g.sync();
-    // 3. exact composite of every segment for its predicted binade
+    // 3. integer increment of every segment for its predicted binade
     for (int seg = warp; seg < S; seg += nwarps) {
       uint32_t b = f2u(sc->est[seg]);
       if ((b >> 23) >= 255u || (b >> 31)) b = 0;
       int e, m;
       sum_decompose(b, e, m);
       const int i = seg * 32 + lane;
-      SumFn f = i < len ? sumfn_elem(f2u(p[base + i]), e) : sumfn_identity();
-      f = sumfn_warp_scan(f, lane);
-      if (lane == 31) {
-        sc->comp[seg] = f;
-        sc->epred[seg] = e;
+      const SumFn f = i < len ? sumfn_elem(f2u(p[base + i]), e) : sumfn_identity();
+      const bool bad = f.a0 != f.a1 || f.a0 >= SUMFN_SAT;
+      int c = f.a0 > (1 << 25) ? (1 << 25) : f.a0;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+      const unsigned any_bad = __ballot_sync(0xffffffffu, bad);
+      if (lane == 0) {
+        sc->csum[seg] = c;
+        sc->epred[seg] = any_bad ? -1 : e;
       }
     }
     g.sync();
-    // 4. the walk, by one warp with uniform control flow: every lane carries the same
-    // state, lane j of a chunk owns segment j's composite, and values reach the chain
-    // by shuffles issued one segment ahead.
+    // 4. the walk (one warp, uniform control flow)
     if (warp == 0) {
       int e, m;
       sum_decompose(f2u(sc->s), e, m);
-      for (int c = 0; c < S; c += 32) {
-        const int seg = c + lane, cnt = min(32, S - c);
-        const SumFn f = seg < S ? sc->comp[seg] : sumfn_identity();
-        const int ep = seg < S ? sc->epred[seg] : -1;
-        int a0n = __shfl_sync(0xffffffffu, f.a0, 0), a1n = __shfl_sync(0xffffffffu, f.a1, 0),
-            epn = __shfl_sync(0xffffffffu, ep, 0);
-        for (int j = 0; j < cnt; j++) {
-          const int a0 = a0n, a1 = a1n, epj = epn;
-          const int jn = j + 1 < cnt ? j + 1 : j;
-          a0n = __shfl_sync(0xffffffffu, f.a0, jn);
-          a1n = __shfl_sync(0xffffffffu, f.a1, jn);
-          epn = __shfl_sync(0xffffffffu, ep, jn);
-          const int m2 = m + ((m & 1) ? a1 : a0);
-          if (epj == e && m2 < SUMFN_LIMIT && e != 255) {
-            m = m2;
-          } else {
-            // serial adds for this segment; the 32 terms come from the lanes (zeros past the end)
-            const int i = (c + j) * 32 + lane;
-            const float v = i < len ? p[base + i] : 0.0f;
-            float s = u2f(sum_pack(e, m));
+      for (int c0 = 0; c0 < S; c0 += 32) {
+        const int seg = c0 + lane;
+        const int cs = seg < S ? sc->csum[seg] : 0;
+        const int ep = seg < S ? sc->epred[seg] : -2;
+        int pre = cs;  // inclusive prefix of the increments
 #pragma unroll
-            for (int k = 0; k < 32; k++) s = fadd(s, __shfl_sync(0xffffffffu, v, k));
-            sum_decompose(f2u(s), e, m);
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, pre, o);
+          if (lane >= o) pre += y;
+        }
+        int j0 = 0, pbase = 0;
+        for (int guard = 0; guard < 33; guard++) {
+          const bool stop = lane >= j0 && (ep != e || m + (pre - pbase) >= SUMFN_LIMIT);
+          const unsigned mask = __ballot_sync(0xffffffffu, stop);
+          const int js = mask ? __ffs(mask) - 1 : 32;
+          if (js > j0) {
+            const int pend = __shfl_sync(0xffffffffu, pre, js - 1);
+            m += pend - pbase;
+            pbase = pend;
           }
+          if (js >= 32 || c0 + js >= S) break;
+          // segment c0 + js term by term
+          const int i = (c0 + js) * 32 + lane;
+          const float v = i < len ? p[base + i] : 0.0f;
+          float s = u2f(sum_pack(e, m));
+#pragma unroll
+          for (int k = 0; k < 32; k++) s = fadd(s, __shfl_sync(0xffffffffu, v, k));
+          sum_decompose(f2u(s), e, m);
+          pbase = __shfl_sync(0xffffffffu, pre, js);
+          j0 = js + 1;
         }
       }
       if (lane == 0) sc->s = u2f(sum_pack(e, m));
@@ -299,6 +278,154 @@ __device__ __forceinline__ float warp_row_dot_kq(int kind, const uint8_t* row, c
 }
 
 
+// ---- lane-per-block dot products ---------------------------------------------------------
+// One lane decodes one whole 256-weight super-block; the L = 2^k >= blocks-per-row lanes
+// of a group cover one row, a warp covers 32/L rows at once. Fewer instructions per
+// weight byte than the four-lane split above, which matters because these phases are
+// bound by instruction issue, not by HBM.
+__device__ __forceinline__ U4 lds128s(uint32_t a) {
+  U4 v;
+  asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32s(uint32_t a) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+
+template <bool Q5>
+__device__ __forceinline__ float block_term_k4(uint32_t wb, uint32_t xb) {
+  const U4 hdr = lds128s(wb);
+  const K4Scales s = k4_unpack(hdr.y, hdr.z, hdr.w);
+  U4 h0{0, 0, 0, 0}, h1{0, 0, 0, 0};
+  uint32_t qs = wb + 16;
+  if (Q5) {
+    h0 = lds128s(wb + 16);
+    h1 = lds128s(wb + 32);
+    qs = wb + 48;
+  }
+  int sumi = 0;
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    const U4 wa = lds128s(qs + 32 * c), wc = lds128s(qs + 32 * c + 16);
+    const U4 y0 = lds128s(xb + 64 * c), y1 = lds128s(xb + 64 * c + 16), y2 = lds128s(xb + 64 * c + 32),
+             y3 = lds128s(xb + 64 * c + 48);
+    int s_lo = 0, s_hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const uint32_t w = i < 4 ? u4_get(wa, i) : u4_get(wc, i - 4);
+      uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+      if (Q5) {
+        const uint32_t h = i < 4 ? u4_get(h0, i) : u4_get(h1, i - 4);
+        lo |= ((h >> (2 * c)) & 0x01010101u) << 4;
+        hi |= ((h >> (2 * c + 1)) & 0x01010101u) << 4;
+      }
+      s_lo = __dp4a((int)lo, (int)(i < 4 ? u4_get(y0, i) : u4_get(y1, i - 4)), s_lo);
+      s_hi = __dp4a((int)hi, (int)(i < 4 ? u4_get(y2, i) : u4_get(y3, i - 4)), s_hi);
+    }
+    const uint32_t scw = c < 2 ? s.sc_lo : s.sc_hi;
+    sumi += byte_of(scw, (2 * c) & 3) * s_lo + byte_of(scw, (2 * c + 1) & 3) * s_hi;
+  }
+  const U4 b0 = lds128s(xb + XK_BSUMS), b1 = lds128s(xb + XK_BSUMS + 16);
+  const uint32_t m01 = __byte_perm(s.m_lo, 0, 0x1100), m23 = __byte_perm(s.m_lo, 0, 0x3322);
+  const uint32_t m45 = __byte_perm(s.m_hi, 0, 0x1100), m67 = __byte_perm(s.m_hi, 0, 0x3322);
+  int summ = 0;
+  summ = dp2a_lo(b0.x, m01, summ);
+  summ = dp2a_hi(b0.y, m01, summ);
+  summ = dp2a_lo(b0.z, m23, summ);
+  summ = dp2a_hi(b0.w, m23, summ);
+  summ = dp2a_lo(b1.x, m45, summ);
+  summ = dp2a_hi(b1.y, m45, summ);
+  summ = dp2a_lo(b1.z, m67, summ);
+  summ = dp2a_hi(b1.w, m67, summ);
+  const float d_x = __uint_as_float(lds32s(xb + XK_D));
+  return k4_term(half_to_float_hw(hdr.x & 0xFFFFu), half_to_float_hw(hdr.x >> 16), d_x, sumi, summ);
+}
+
+__device__ __forceinline__ float block_term_q6k(uint32_t wb, uint32_t xb) {
+  // Blocks are 2-byte aligned: four consecutive words come from five aligned ones.
+  const uint32_t sh = (wb & 2u) * 8u, p = wb & ~3u;
+  auto load4 = [&](int k, uint32_t w[4]) {
+    uint32_t a0 = lds32s(p + 4 * k), a1 = lds32s(p + 4 * k + 4), a2 = lds32s(p + 4 * k + 8), a3 = lds32s(p + 4 * k + 12),
+             a4 = lds32s(p + 4 * k + 16);
+    w[0] = funnel_r(a0, a1, sh);
+    w[1] = funnel_r(a1, a2, sh);
+    w[2] = funnel_r(a2, a3, sh);
+    w[3] = funnel_r(a3, a4, sh);
+  };
+  uint32_t scw[4];
+  load4(48, scw);
+  int total = 0;
+#pragma unroll
+  for (int n = 0; n < 2; n++) {
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+      uint32_t l0[4], l32[4], h[4];
+      load4(16 * n + 4 * half, l0);
+      load4(16 * n + 8 + 4 * half, l32);
+      load4(32 + 8 * n + 4 * half, h);
+      const U4 y1 = lds128s(xb + 128 * n + 16 * half), y2 = lds128s(xb + 128 * n + 32 + 16 * half),
+               y3 = lds128s(xb + 128 * n + 64 + 16 * half), y4 = lds128s(xb + 128 * n + 96 + 16 * half);
+      int a1 = 0, a2 = 0, a3 = 0, a4 = 0;
+#pragma unroll
+      for (int ii = 0; ii < 4; ii++) {
+        const uint32_t q1 = (l0[ii] & 0x0F0F0F0Fu) | ((h[ii] << 4) & 0x30303030u);
+        const uint32_t q2 = (l32[ii] & 0x0F0F0F0Fu) | ((h[ii] << 2) & 0x30303030u);
+        const uint32_t q3 = ((l0[ii] >> 4) & 0x0F0F0F0Fu) | (h[ii] & 0x30303030u);
+        const uint32_t q4 = ((l32[ii] >> 4) & 0x0F0F0F0Fu) | ((h[ii] >> 2) & 0x30303030u);
+        a1 = __dp4a((int)q1, (int)u4_get(y1, ii), a1);
+        a2 = __dp4a((int)q2, (int)u4_get(y2, ii), a2);
+        a3 = __dp4a((int)q3, (int)u4_get(y3, ii), a3);
+        a4 = __dp4a((int)q4, (int)u4_get(y4, ii), a4);
+      }
+      const int g = 8 * n + half;
+      total += (int)(int8_t)byte_of(scw[g >> 2], g & 3) * a1;
+      total += (int)(int8_t)byte_of(scw[(g + 2) >> 2], (g + 2) & 3) * a2;
+      total += (int)(int8_t)byte_of(scw[(g + 4) >> 2], (g + 4) & 3) * a3;
+      total += (int)(int8_t)byte_of(scw[(g + 6) >> 2], (g + 6) & 3) * a4;
+    }
+  }
+  const U4 b0 = lds128s(xb + XK_BSUMS), b1 = lds128s(xb + XK_BSUMS + 16);
+  int bias = 0;
+  bias = dp2a_lo(b0.x, scw[0], bias);
+  bias = dp2a_hi(b0.y, scw[0], bias);
+  bias = dp2a_lo(b0.z, scw[1], bias);
+  bias = dp2a_hi(b0.w, scw[1], bias);
+  bias = dp2a_lo(b1.x, scw[2], bias);
+  bias = dp2a_hi(b1.y, scw[2], bias);
+  bias = dp2a_lo(b1.z, scw[3], bias);
+  bias = dp2a_hi(b1.w, scw[3], bias);
+  const uint32_t da = wb + 208;
+  const uint32_t dw = lds32s(da & ~3u) >> ((da & 2u) * 8u);
+  const float d_x = __uint_as_float(lds32s(xb + XK_D));
+  return q6k_term(half_to_float_hw(dw & 0xFFFFu), d_x, total - 32 * bias);
+}
+
+// Dot products of the rows a warp owns in one pass: lane = (group gi = lane / L, block
+// slot bl = lane % L). `row` is this lane's row in shared memory (0 when the group has
+// no row), `kind` its weight kind. Returns the row's sum to every lane of its group,
+// block terms added in block order (matvec.rs:84-106).
+__device__ __forceinline__ float group_row_dot(uint32_t row, int kind, uint32_t sx, int nb, int L) {
+  const int lane = threadIdx.x & 31, bl = lane & (L - 1), gbase = lane & ~(L - 1);
+  const int bs = kind_size(kind);
+  float sum = 0.0f;
+  for (int g0 = 0; g0 < nb; g0 += L) {
+    const int b = g0 + bl;
+    float term = 0.0f;
+    if (row != 0 && b < nb) {
+      const uint32_t wb = row + (uint32_t)b * bs, xb = sx + (uint32_t)b * XK_STRIDE;
+      if (kind == Q4_K) term = block_term_k4<false>(wb, xb);
+      else if (kind == Q6_K) term = block_term_q6k(wb, xb);
+      else term = block_term_k4<true>(wb, xb);
+    }
+    __syncwarp();
+    const int cnt = min(L, nb - g0);
+    for (int j = 0; j < cnt; j++) sum = fadd(sum, __shfl_sync(0xffffffffu, term, gbase + j));
+  }
+  return sum;
+}
+
 // ---- step description (built once by the host, lives in global memory) ------------------
 // One matrix-product phase as both the producer and the consumers see it. The row
 // space (concatenated rows, or shared rows in pair mode) is split evenly over the
@@ -339,6 +466,7 @@ struct StepParams {
   int n_stages, stage_bytes;
   int scratch_bytes;   // f32 scratch region (norm rows, attention)
   int v_chunk;         // positions per staged V chunk
+  int table_bytes;     // bytes of the StepLayer table staged in shared memory (n_layer + 1 entries)
   unsigned long long* prof;  // optional: cycles per phase, accumulated by one CTA
   int prof_cta;
 };
@@ -435,50 +563,84 @@ __device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, Ring
   }
 }
 
-// Consumer side (every consumer warp): rows of each tile are dealt to warps round robin.
-// `sx` holds the Q8_K images of the activation vector.
+// Consumer side (every consumer warp). A warp pass covers 32/L rows (L lanes per row);
+// passes are dealt to warps round robin, continuing across tiles (`rot`), so that
+// consecutive small tiles keep all warps busy at once. In pair mode the lower half of
+// the warp takes gate rows and the upper half the matching up rows, and the SiLU gate
+// is applied in the epilogue. `sx` holds the Q8_K images of the activation vector;
+// `op` lives in shared memory.
 __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp,
                                            int n_warps) {
-  const int c0 = blockIdx.x * op.rows_per_cta, c1 = min(c0 + op.rows_per_cta, op.span_rows);
+  const int rows_per_cta = op.rows_per_cta, span = op.span_rows, tile_rows = op.tile_rows, pair = op.pair;
+  const int epilogue = op.epilogue, nb = op.cols >> 8;
+  const int c0 = blockIdx.x * rows_per_cta, c1 = min(c0 + rows_per_cta, span);
   const int lane = threadIdx.x & 31;
-  const int nb = op.cols >> 8;
-  for (int t0 = c0; t0 < c1; t0 += op.tile_rows) {
+  int L = 1;
+  while (L < nb && L < 32) L <<= 1;
+  const int G = 32 / L;                             // rows per warp pass
+  const bool split = pair && G >= 2;                // gate | up halves of one warp
+  const int rows_per_pass = split ? G / 2 : G;
+  const int gi = lane / L;
+  const uint32_t sxa = smem_addr(sx);
+  int rot = 0;
+  for (int t0 = c0; t0 < c1; t0 += tile_rows) {
     if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
-    const int t1 = min(t0 + op.tile_rows, c1);
-    const uint8_t* stage = R.stages + (size_t)cp.st * R.stage_bytes;
+    const int t1 = min(t0 + tile_rows, c1);
+    const uint32_t stage = smem_addr(R.stages + (size_t)cp.st * R.stage_bytes);
     const int R_rows = t1 - t0;
-    if (warp < R_rows) {
+    const int n_pass = (R_rows + rows_per_pass - 1) / rows_per_pass;
+    int ps = warp - rot;
+    if (ps < 0) ps += n_warps;
+    if (ps < n_pass) {
       TilePart parts[3];
       const int np = op_tile_parts(op, t0, t1, parts);
-      if (op.pair) {
-        const uint8_t* base0 = stage + parts[0].soff + ((uintptr_t)parts[0].src & 15u);
-        const uint8_t* base1 = stage + parts[1].soff + ((uintptr_t)parts[1].src & 15u);
-        for (int u = warp; u < R_rows; u += n_warps) {
-          float g = warp_row_dot_kq(op.seg[0].kind, base0 + (size_t)u * op.row_bytes[0], sx, nb);
-          float up = warp_row_dot_kq(op.seg[1].kind, base1 + (size_t)u * op.row_bytes[1], sx, nb);
-          if (lane == 0) {
-            const int r = t0 + u;
-            op.seg[0].out[r] = op.epilogue == EPI_SILU_MUL ? silu_mul_exact(g, up) : g;
-            op.seg[1].out[r] = up;
+      for (; ps < n_pass; ps += n_warps) {
+        if (pair) {
+          const uint32_t base0 = stage + parts[0].soff + ((uint32_t)(uintptr_t)parts[0].src & 15u);
+          const uint32_t base1 = stage + parts[1].soff + ((uint32_t)(uintptr_t)parts[1].src & 15u);
+          if (split) {
+            const int which = gi >= rows_per_pass ? 1 : 0;
+            const int u = ps * rows_per_pass + (gi - which * rows_per_pass);
+            const uint32_t row = u < R_rows ? (which ? base1 : base0) + (uint32_t)u * op.row_bytes[which] : 0u;
+            const float v = group_row_dot(row, op.seg[which].kind, sxa, nb, L);
+            const float up = __shfl_down_sync(0xffffffffu, v, 16);
+            if (u < R_rows && which == 0 && (lane & (L - 1)) == 0) {
+              const int r = t0 + u;
+              op.seg[0].out[r] = epilogue == EPI_SILU_MUL ? silu_mul_exact(v, up) : v;
+              op.seg[1].out[r] = up;
+            }
+          } else {
+            const int u = ps;  // one row per pass: gate, then up
+            const float g = group_row_dot(base0 + (uint32_t)u * op.row_bytes[0], op.seg[0].kind, sxa, nb, L);
+            const float up = group_row_dot(base1 + (uint32_t)u * op.row_bytes[1], op.seg[1].kind, sxa, nb, L);
+            if (lane == 0) {
+              const int r = t0 + u;
+              op.seg[0].out[r] = epilogue == EPI_SILU_MUL ? silu_mul_exact(g, up) : g;
+              op.seg[1].out[r] = up;
+            }
           }
-        }
-      } else {
-        for (int u = warp; u < R_rows; u += n_warps) {
-          int lr = u, pi = 0;
-          while (pi < np - 1 && lr >= parts[pi].rows) {
-            lr -= parts[pi].rows;
-            pi++;
+        } else {
+          const int u = ps * G + gi;
+          uint32_t row = 0;
+          int kind = Q4_K, pi = 0, lr = u;
+          if (u < R_rows) {
+            while (pi < np - 1 && lr >= parts[pi].rows) {
+              lr -= parts[pi].rows;
+              pi++;
+            }
+            const TilePart& tp = parts[pi];
+            row = stage + tp.soff + ((uint32_t)(uintptr_t)tp.src & 15u) + (uint32_t)lr * op.row_bytes[tp.seg];
+            kind = op.seg[tp.seg].kind;
           }
-          const TilePart& tp = parts[pi];
-          const uint8_t* row = stage + tp.soff + ((uintptr_t)tp.src & 15u) + (size_t)lr * op.row_bytes[tp.seg];
-          float v = warp_row_dot_kq(op.seg[tp.seg].kind, row, sx, nb);
-          if (lane == 0) {
-            float* o = op.seg[tp.seg].out + tp.row0 + lr;
-            *o = op.epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
+          const float v = group_row_dot(row, kind, sxa, nb, L);
+          if (u < R_rows && (lane & (L - 1)) == 0) {
+            float* o = op.seg[parts[pi].seg].out + parts[pi].row0 + lr;
+            *o = epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
           }
         }
       }
     }
+    rot = (rot + n_pass) % n_warps;
     __syncwarp();
     if (lane == 0) mbar_arrive(&R.empty[cp.st]);
     cp.advance(R.n_stages);
@@ -584,7 +746,8 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
   float* sp = sv + hd;          // hd (squares)
   float* sc = sp + hd;          // n_ctx scores
   float* vbuf = sc + ((P.n_ctx + 3) & ~3);  // v_chunk x hd, 16-byte aligned
-  const StepLayer& L = P.layers[li];
+  const float* const q_norm_w = P.layers[li].q_norm;
+  const float* const k_norm_w = P.layers[li].k_norm;
   float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd;
   float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd;
   for (int i = tid; i < hd; i += T) {
@@ -596,7 +759,7 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
   if (P.qk_norm) {
     for (int which = 0; which < 2; which++) {
       float* v = which ? sk : sq;
-      const float* nw = which ? L.k_norm : L.q_norm;
+      const float* nw = which ? k_norm_w : q_norm_w;
       for (int i = tid; i < hd; i += T) sp[i] = fmul(v[i], v[i]);
       float ss = group_seq_sum(sp, hd, M.ss, g);
       float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)hd), P.eps)));
@@ -753,6 +916,15 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   float* red = reinterpret_cast<float*>(cur);
   cur += 64 * sizeof(float);
   volatile int* abort = reinterpret_cast<volatile int*>(cur);
+  cur += 16;
+  // The step's tensor table (one StepLayer per layer + the output head), copied from
+  // global memory once so that no phase waits on a descriptor load.
+  StepLayer* const table = reinterpret_cast<StepLayer*>(cur);
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(P.layers);
+    uint4* dst = reinterpret_cast<uint4*>(table);
+    for (int i = threadIdx.x; i < P.table_bytes / 16; i += blockDim.x) dst[i] = src[i];
+  }
 
   Ring R;
   R.stages = stages;
@@ -780,13 +952,13 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     if ((threadIdx.x & 31) == 0) {
       RingPos pp{0, 0u};
       for (int li = 0; li < P.n_layer && !*abort; li++) {
-        const StepLayer& L = P.layers[li];
+        const StepLayer& L = table[li];
         produce_op(L.qkv, R, pp);
         produce_op(L.wo, R, pp);
         produce_op(L.gu, R, pp);
         produce_op(L.down, R, pp);
       }
-      if (P.want_logits && !*abort) produce_op(*P.out_op, R, pp);
+      if (P.want_logits && !*abort) produce_op(table[P.n_layer].qkv, R, pp);
     }
     return;
   }
@@ -822,7 +994,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
 
   bool ok = true;
   for (int li = 0; li < P.n_layer; li++) {
-    const StepLayer& L = P.layers[li];
+    const StepLayer& L = table[li];
     // A: attn norm + q/k/v
     phase_norm_quant(P.x, li == 0, L.attn_norm, P.dim, P.eps, M, g, SubProf{prof_on ? P.prof : nullptr, 0});
     MEGA_PROF(1);
@@ -862,7 +1034,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   }
   if (P.want_logits) {
     phase_norm_quant(P.x, false, P.output_norm, P.dim, P.eps, M, g);
-    consume_op(*P.out_op, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
+    consume_op(table[P.n_layer].qkv, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
     if (P.with_argmax) {
       ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
       if (blockIdx.x == 0 && ok) phase_argmax(P, M, g);

@@ -212,4 +212,49 @@ float hc_seqsum_seg(const float* p, size_t n, int* fallbacks) {
   return s;
 }
 
+
+// Mirror of the device routine's final form: per 32-term segment an integer increment
+// C = sum round(p/u) for the predicted binade, flagged "bad" when a term is an exact
+// tie or leaves the binade; the walk adds integer prefix sums over runs of good
+// segments and falls back to term-by-term adds for bad ones.
+float hc_seqsum_int(const float* p, size_t n, int* fallbacks) {
+  const size_t S = (n + 31) / 32;
+  std::vector<float> est(S + 1, 0.0f);
+  for (size_t g = 0; g < S; g++) {
+    float t = 0.0f;
+    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) t += p[i];
+    est[g + 1] = est[g] + t;
+  }
+  std::vector<int> csum(S), epred(S);
+  for (size_t g = 0; g < S; g++) {
+    uint32_t b = f2u(est[g]);
+    if ((b >> 23) >= 255u || (b >> 31)) b = 0;
+    int e, m;
+    sum_decompose(b, e, m);
+    long long C = 0;
+    bool bad = false;
+    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) {
+      SumFn f = sumfn_elem(f2u(p[i]), e);
+      if (f.a0 != f.a1 || f.a0 >= SUMFN_SAT) bad = true;
+      C += f.a0 > (1 << 25) ? (1 << 25) : f.a0;
+    }
+    csum[g] = (int)C;
+    epred[g] = bad ? -1 : e;
+  }
+  int e, m, nf = 0;
+  sum_decompose(0u, e, m);
+  for (size_t g = 0; g < S; g++) {
+    if (epred[g] == e && m + csum[g] < SUMFN_LIMIT) {
+      m += csum[g];
+      continue;
+    }
+    nf++;
+    float s = u2f(sum_pack(e, m));
+    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) s = fadd(s, p[i]);
+    sum_decompose(f2u(s), e, m);
+  }
+  if (fallbacks) *fallbacks = nf;
+  return u2f(sum_pack(e, m));
+}
+
 }  // extern "C"
