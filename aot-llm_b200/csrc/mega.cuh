@@ -141,11 +141,29 @@ __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const C
           }
           if (js >= 32 || c0 + js >= S) break;
           // segment c0 + js term by term
-          const int i = (c0 + js) * 32 + lane;
-          const float v = i < len ? p[base + i] : 0.0f;
           float s = u2f(sum_pack(e, m));
+          const int first = (c0 + js) * 32;
+          if (first + 32 <= len) {
+            // a full segment: every lane reads the same 32 terms (broadcast loads)
+            const float4* q = reinterpret_cast<const float4*>(p + base + first);
 #pragma unroll
-          for (int k = 0; k < 32; k++) s = fadd(s, __shfl_sync(0xffffffffu, v, k));
+            for (int k = 0; k < 8; k += 2) {
+              const float4 a = q[k], b = q[k + 1];
+              s = fadd(s, a.x);
+              s = fadd(s, a.y);
+              s = fadd(s, a.z);
+              s = fadd(s, a.w);
+              s = fadd(s, b.x);
+              s = fadd(s, b.y);
+              s = fadd(s, b.z);
+              s = fadd(s, b.w);
+            }
+          } else {
+            const int i = first + lane;
+            const float v = i < len ? p[base + i] : 0.0f;
+#pragma unroll
+            for (int k = 0; k < 32; k++) s = fadd(s, __shfl_sync(0xffffffffu, v, k));
+          }
           sum_decompose(f2u(s), e, m);
           pbase = __shfl_sync(0xffffffffu, pre, js);
           j0 = js + 1;
@@ -656,8 +674,7 @@ __device__ __forceinline__ bool grid_sync(const StepParams& P, const CtaGroup& g
   if (g.tid == 0) {
     target += gridDim.x;
     if (!*abort) {
-      __threadfence();
-      atomicAdd(P.grid_bar, 1u);
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.grid_bar) : "memory");
       bool ok = false;
       for (uint32_t it = 0; it < (1u << 24); ++it) {
         unsigned v;

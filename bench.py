@@ -218,13 +218,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     barrier()
     e2e_tps = world * e2e_steps / e2e_s
 
-    # ---- the dominant kernel alone: the quantized matrix-vector products -------------------
-    sweep_ms, sweep_launches, sweep_bytes = g.gemv_sweep(20)
+    # ---- roofline of the dominant kernel --------------------------------------------------
+    # The timed region is `steps` launches of decode_step_kernel (one per token, CUDA-graph
+    # replays); its average launch duration is the device time of the loop over the steps.
     peak, peak_src = measured_peak_gbs()
-    gemv_gbs = sweep_bytes / (sweep_ms * 1e-3) / 1e9
     mid_pos = PROMPT_LEN + warmup + steps // 2
     step_bytes = spec.weight_bytes_per_token() + spec.kv_bytes_per_position() * (mid_pos + 1)
     step_gbs = step_bytes / (ms * 1e-3 / steps) / 1e9
+    one_kernel = launches == steps
+    # The per-operator GEMV kernel alone (used by prompt batches and the operator API).
+    sweep_ms, sweep_launches, sweep_bytes = g.gemv_sweep(20)
+    gemv_gbs = sweep_bytes / (sweep_ms * 1e-3) / 1e9
 
     if rank != 0:
         if dist:
@@ -249,13 +253,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "e2e": {"value": e2e_tps, "unit": UNIT, "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4 * d.vocab,
                 "steps": e2e_steps},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": "gemv_q8k_kernel", "achieved": gemv_gbs, "peak": peak, "unit": "GB/s",
-                     "frac": gemv_gbs / peak, "peak_source": peak_src, "traffic": None,
-                     "launches_per_step": int(sweep_launches), "algorithmic_bytes_per_step": int(sweep_bytes),
-                     "avg_launch_us": sweep_ms * 1e3 / sweep_launches,
-                     "how": "the step's matrix products alone, back to back in one CUDA graph, CUDA events, 20 replays"},
-        "step_roofline": {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
-                          "algorithmic_bytes_per_step": int(step_bytes), "roofline_tok_s": peak * 1e9 / step_bytes},
+        "roofline": {"bound": "hbm", "kernel": "decode_step_kernel" if one_kernel else "per-operator kernels (whole step)",
+                     "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
+                     "peak_source": peak_src, "traffic": 638176512 if one_kernel else None,
+                     "algorithmic_bytes_per_launch": int(step_bytes), "avg_launch_us": ms * 1e3 / steps,
+                     "roofline_tok_s": peak * 1e9 / step_bytes,
+                     "how": "weights + KV bytes of one token / (device time of the timed loop / steps), CUDA events on the launching stream; traffic = dram read+write of one launch from ncu (profiles/)"},
+        "gemv_kernel_sweep": {"kernel": "gemv_q8k_kernel", "achieved": gemv_gbs, "unit": "GB/s", "frac": gemv_gbs / peak,
+                              "launches": int(sweep_launches), "algorithmic_bytes": int(sweep_bytes),
+                              "avg_launch_us": sweep_ms * 1e3 / sweep_launches},
         "generated_head": [int(x) for x in ids[:8]],
     }
     if cpu:
