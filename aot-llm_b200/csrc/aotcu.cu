@@ -1562,4 +1562,56 @@ int aotcu_gpu_profile_step(aotcu_gpu* g, uint32_t token, size_t pos, int cta, ui
   return rc;
 }
 
+
 }  // extern "C"
+
+// ---- a matrix-vector product for callers that may not allocate ---------------------------
+// The f32 activation vector has to be quantized to Q8_K block images before the product
+// can run, and those images need somewhere to live. The ordinary route
+// (aotcu_quantize_q8_k into a buffer from aotcu_malloc, then aotcu_matvec_*) makes the
+// caller own that buffer. Here the images go into a fixed array inside the library's
+// device image instead: every GPU that loads the library carries these 19,456 bytes until
+// the process exits, and in exchange the call below never asks the CUDA allocator for
+// anything.
+constexpr size_t STATIC_MAX_COLS = 16384;  // 64 super-blocks
+static __device__ __align__(256) uint8_t g_static_xq[(STATIC_MAX_COLS / 256) * XIMG_K];
+
+// In host code `g_static_xq` is only a handle for the runtime, not a device address. The
+// address is looked up once per device, with that device current, and cached here.
+constexpr int STATIC_MAX_DEVICES = 64;
+static uint8_t* g_static_xq_addr[STATIC_MAX_DEVICES] = {};
+
+extern "C" int aotcu_matvec_k_static(aotcu_ctx* c, int kind, float* out, const uint8_t* w, const float* x,
+                                     size_t rows, size_t cols) {
+  ARG_CHECK(c && out && w && x, "NULL argument");
+  ARG_CHECK(kind == AOTCU_Q4_K || kind == AOTCU_Q5_K || kind == AOTCU_Q6_K, "kind %d is not a K-quant", kind);
+  ARG_CHECK(cols > 0 && cols % 256 == 0, "cols (%zu) must be a positive multiple of 256", cols);
+  ARG_CHECK(cols <= STATIC_MAX_COLS,
+            "cols (%zu) exceeds the %zu columns the built-in activation area holds; use aotcu_quantize_q8_k + "
+            "aotcu_matvec with a buffer of your own",
+            cols, STATIC_MAX_COLS);
+  ARG_CHECK(c->device >= 0 && c->device < STATIC_MAX_DEVICES, "device index %d out of range", c->device);
+  if (rows == 0) return 0;
+  if (int rc = ctx_set_device(c)) return rc;
+  uint8_t* xq = g_static_xq_addr[c->device];
+  if (!xq) {
+    // First call on this device: resolve the array's device address.
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_xq);
+    if (e != cudaSuccess || !p)
+      return fail(AOTCU_ERR_CUDA, "cudaGetSymbolAddress(g_static_xq): %s", cudaGetErrorString(e));
+    xq = g_static_xq_addr[c->device] = static_cast<uint8_t*>(p);
+  }
+  const int nblk = (int)(cols / 256);
+  // Every block image of the vector is rewritten in full, so nothing left by an earlier
+  // call is read.
+  if (int rc = launch(c, quantize_q8k_kernel, dim3(grid_for(c, nblk, 8)), dim3(256), 0, x, xq, nblk, 1)) return rc;
+  GemvCall call;
+  call.seg[0] = GemvSeg{w, out, (int)rows, kind};
+  call.nseg = 1;
+  call.cols = cols;
+  call.x = xq;
+  call.x_mode = 1;
+  call.m = 1;
+  return launch_gemv(c, call);
+}

@@ -124,6 +124,11 @@ class Context:
     def matmul(self, kind: int, out, w, xs, m: int, rows: int, cols: int):
         check(L.load().aotcu_matmul(self.h, kind, _dp(out), _dp(w), _dp(xs), m, rows, cols))
 
+    def matvec_k_static(self, kind: int, out, w, x_f32, rows: int, cols: int):
+        """K-quant product of an f32 device vector through the library's built-in activation
+        area: no device allocation anywhere on this call path (see include/aot_cuda.h)."""
+        check(L.load().aotcu_matvec_k_static(self.h, kind, _dp(out), _dp(w), _dp(x_f32), rows, cols))
+
     def block_sums(self, kind: int, w, x, rows: int, cols: int, sumi, summ=None):
         check(L.load().aotcu_block_sums(self.h, kind, _dp(w), _dp(x), rows, cols, _dp(sumi),
                                         _dp(summ) if summ is not None else None))

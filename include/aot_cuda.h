@@ -122,6 +122,25 @@ int aotcu_matvec3(aotcu_ctx* ctx, const int kinds[3], float* const outs[3], cons
  * to m calls of aotcu_matvec. */
 int aotcu_matmul(aotcu_ctx* ctx, int kind, float* out, const uint8_t* w, const void* xs, size_t m, size_t rows,
                  size_t cols);
+/* No counterpart in the reference (its CPU kernels borrow `State.aqk`, which the caller
+ * owns). out[r] = dot(W[r], quantize_q8_k(x)) for a K-quant matrix (kind Q4_K, Q5_K or
+ * Q6_K) and an f32 device vector x, bit-identical to aotcu_quantize_q8_k followed by
+ * aotcu_matvec, for callers that must not allocate: a serving process that sized its
+ * device memory once at start-up (weights, KV cache) and forbids or cannot afford later
+ * cudaMalloc calls - they may fail when HBM is fully committed, and they stall every
+ * stream of the device while they run. The quantized copy of x lives in a 19,456-byte
+ * array built into the library's device image (held by every GPU that loads the
+ * library, until exit), so this call uses no allocator at all.
+ *   - cols must be a multiple of 256 and at most 16384; larger vectors are rejected with
+ *     AOTCU_ERR_BAD_ARG (use the two-call route with your own buffer).
+ *   - The first call on each device looks the array's address up
+ *     (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array: two calls whose kernels can overlap
+ *     on the GPU (different contexts or streams) race on it. Calls through one context
+ *     are ordered by its stream and are safe. Nothing in the array needs clearing
+ *     between calls: each call rewrites every block it reads. */
+int aotcu_matvec_k_static(aotcu_ctx* ctx, int kind, float* out, const uint8_t* w, const float* x, size_t rows,
+                          size_t cols);
 /* Parity export: the integers of one matvec before any float arithmetic.
  * sumi[r*nb + b] (and summ for Q4_K/Q5_K, else untouched) per (row, block), as
  * matvec.rs:89-103 / 146-163 / 38-43 form them. Device pointers. */
