@@ -268,7 +268,8 @@ struct aotcu_gpu {
   // Persistent one-kernel decode step (mega.cuh), when the model qualifies.
   bool mega_ok = false, use_mega = true;
   StepLayer* d_step_layers = nullptr;
-  unsigned* d_grid_bar = nullptr;
+  unsigned* d_grid_bar = nullptr;     // [0] barrier arrivals of one launch, [1] launch count
+  LLWord* d_ll = nullptr;             // tagged activation vectors of the one-kernel step
   StepParams step_params = {};
   size_t mega_smem = 0;
   cudaGraphExec_t decode_graph[2] = {nullptr, nullptr};  // [want_logits]
@@ -570,6 +571,10 @@ static int mega_setup(aotcu_gpu* g) {
     for (auto t : ts) ok = ok && kind_act(t->kind) == ACT_Q8_K;
     ok = ok && l.gate.kind == l.up.kind && l.gate.rows == l.up.rows && !l.local_attn;
   }
+  // Every CTA must own a row of every product (the tagged hand-over between phases relies
+  // on it), and phase ids must fit the tag's low 10 bits.
+  const size_t kvd = (size_t)d.n_kv_head * d.head_dim;
+  ok = ok && d.n_layer <= 200 && (size_t)d.dim >= (size_t)c->n_sm && (size_t)d.hidden >= (size_t)c->n_sm;
   if (!ok) return 0;
   const int stage_bytes = 32768;
   const int v_chunk = 8192 / d.head_dim;
@@ -597,8 +602,9 @@ static int mega_setup(aotcu_gpu* g) {
   if (per_sm < 1) return 0;
 
   auto seg = [&](const aotcu_tensor& t, float* out) { return GemvSeg{wptr(g, t), out, (int)t.rows, t.kind}; };
-  auto make_op = [&](std::initializer_list<GemvSeg> segs, int pair, int cols, int epilogue) {
+  auto make_op = [&](std::initializer_list<GemvSeg> segs, int pair, int cols, int epilogue, int ll) {
     MegaOp op = {};
+    op.ll = ll;
     size_t max_rb = 1;
     int span = 0, i = 0;
     for (const GemvSeg& sg : segs) {
@@ -618,7 +624,18 @@ static int mega_setup(aotcu_gpu* g) {
     op.epilogue = epilogue;
     return op;
   };
-  float* const X = g->bufs[AOTCU_BUF_X];
+  // Tagged vectors: residual, q, k, v, attention output, activated hidden. Zeroed once:
+  // tag 0 is never waited for.
+  const size_t ll_words = (size_t)d.dim + qd + 2 * kvd + qd + (size_t)d.hidden;
+  CU_TRY(cudaMalloc(&g->d_ll, ll_words * sizeof(LLWord)));
+  CU_TRY(cudaMemset(g->d_ll, 0, ll_words * sizeof(LLWord)));
+  LLWord* const xl = g->d_ll;
+  LLWord* const ql = xl + d.dim;
+  LLWord* const kl = ql + qd;
+  LLWord* const vl = kl + kvd;
+  LLWord* const attl = vl + kvd;
+  LLWord* const hbl = attl + qd;
+  auto as_out = [](LLWord* p) { return reinterpret_cast<float*>(p); };
   std::vector<StepLayer> hl(d.n_layer + 1);
   for (int i = 0; i < d.n_layer; i++) {
     const aotcu_layer& l = g->layers[i];
@@ -626,18 +643,18 @@ static int mega_setup(aotcu_gpu* g) {
     hl[i].ffn_norm = wf32(g, l.ffn_norm);
     hl[i].q_norm = d.qk_norm ? wf32(g, l.q_norm) : nullptr;
     hl[i].k_norm = d.qk_norm ? wf32(g, l.k_norm) : nullptr;
-    hl[i].qkv = make_op({seg(l.wq, g->bufs[AOTCU_BUF_Q]), seg(l.wk, g->bufs[AOTCU_BUF_K]), seg(l.wv, g->bufs[AOTCU_BUF_V])},
-                        0, d.dim, EPI_STORE);
-    hl[i].wo = make_op({seg(l.wo, X)}, 0, (int)qd, EPI_ACCUM);
-    hl[i].gu = make_op({seg(l.gate, g->bufs[AOTCU_BUF_HB]), seg(l.up, g->bufs[AOTCU_BUF_HB2])}, 1, d.dim, EPI_SILU_MUL);
-    hl[i].down = make_op({seg(l.down, X)}, 0, d.hidden, EPI_ACCUM);
+    hl[i].qkv = make_op({seg(l.wq, as_out(ql)), seg(l.wk, as_out(kl)), seg(l.wv, as_out(vl))}, 0, d.dim, EPI_STORE, 1);
+    hl[i].wo = make_op({seg(l.wo, as_out(xl))}, 0, (int)qd, EPI_ACCUM, 1);
+    hl[i].gu = make_op({seg(l.gate, as_out(hbl)), seg(l.up, nullptr)}, 1, d.dim, EPI_SILU_MUL, 1);
+    hl[i].down = make_op({seg(l.down, as_out(xl))}, 0, d.hidden, EPI_ACCUM, 1);
   }
   // The output head rides in the slot after the last layer (only its qkv field is used).
   hl[d.n_layer] = StepLayer{};
-  hl[d.n_layer].qkv = make_op({seg(out_t, g->bufs[AOTCU_BUF_LOGITS])}, 0, d.dim, EPI_STORE);
+  hl[d.n_layer].qkv = make_op({seg(out_t, g->bufs[AOTCU_BUF_LOGITS])}, 0, d.dim, EPI_STORE, 0);
   CU_TRY(cudaMalloc(&g->d_step_layers, hl.size() * sizeof(StepLayer) + 16));
   CU_TRY(cudaMemcpy(g->d_step_layers, hl.data(), hl.size() * sizeof(StepLayer), cudaMemcpyHostToDevice));
-  CU_TRY(cudaMalloc(&g->d_grid_bar, sizeof(unsigned)));
+  CU_TRY(cudaMalloc(&g->d_grid_bar, 2 * sizeof(unsigned)));
+  CU_TRY(cudaMemset(g->d_grid_bar, 0, 2 * sizeof(unsigned)));
   StepParams& P = g->step_params;
   P.dim = d.dim; P.hidden = d.hidden; P.n_layer = d.n_layer; P.n_head = d.n_head; P.n_kv_head = d.n_kv_head;
   P.head_dim = d.head_dim; P.rot_dim = d.rot_dim; P.vocab = d.vocab; P.n_ctx = (int)g->n_ctx;
@@ -648,9 +665,10 @@ static int mega_setup(aotcu_gpu* g) {
   P.token_embd = wptr(g, g->head.token_embd);
   P.embd_kind = g->head.token_embd.kind;
   P.embd_row_bytes = kind_row_bytes(g->head.token_embd.kind, g->head.token_embd.cols);
-  P.x = g->bufs[AOTCU_BUF_X]; P.xb = g->bufs[AOTCU_BUF_XB]; P.q = g->bufs[AOTCU_BUF_Q]; P.k = g->bufs[AOTCU_BUF_K];
-  P.v = g->bufs[AOTCU_BUF_V]; P.hb = g->bufs[AOTCU_BUF_HB]; P.hb2 = g->bufs[AOTCU_BUF_HB2];
+  P.xl = xl; P.ql = ql; P.kl = kl; P.vl = vl; P.attl = attl; P.hbl = hbl;
+  P.x = g->bufs[AOTCU_BUF_X];
   P.logits = g->bufs[AOTCU_BUF_LOGITS]; P.k_cache = g->bufs[AOTCU_BUF_KCACHE]; P.v_cache = g->bufs[AOTCU_BUF_VCACHE];
+  P.epoch = g->d_grid_bar + 1;
   P.rope_table = g->rope_table;
   P.step = g->d_step; P.history = g->d_history; P.history_cap = (int)g->history_cap; P.out_token = g->d_out_token;
   P.grid_bar = g->d_grid_bar; P.err = c->d_err;
@@ -1189,6 +1207,7 @@ void aotcu_gpu_free(aotcu_gpu* g) {
   cudaFree(g->d_out_token);
   cudaFree(g->d_step_layers);
   cudaFree(g->d_grid_bar);
+  cudaFree(g->d_ll);
   if (g->h_pinned) cudaFreeHost(g->h_pinned);
   delete g;
 }

@@ -2,8 +2,10 @@
 // persistent kernel: one CTA per SM, a producer warp that streams this CTA's
 // share of every weight matrix of the step through a shared-memory ring with 1-D
 // bulk copies (it runs ahead across phases, because weights never depend on
-// activations), 31 consumer warps that do the arithmetic, and grid-wide
-// barriers between the phases of a block. All results are bit-identical to the
+// activations) and consumer warps that do the arithmetic. Activation vectors pass
+// from one phase to the next as tagged 64-bit words (value + phase tag in one store),
+// so a consumer starts as soon as the words it needs have arrived; the only grid-wide
+// barrier left is the one in front of the argmax. All results are bit-identical to the
 // reference's CPU path (see blockmath.cuh, seqsum.cuh, expf_exact.cuh).
 #pragma once
 #include <cuda_fp16.h>
@@ -24,6 +26,19 @@ struct CtaGroup {
   int bar_id;    // hardware barrier id (0 = the whole CTA, like __syncthreads)
   __device__ __forceinline__ void sync() const {
     asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory");
+  }
+};
+
+// Optional sub-phase cycle counters (slots 16..31 of the profile array).
+struct SubProf {
+  unsigned long long* prof;
+  long long last;
+  __device__ __forceinline__ void mark(int slot) {
+    if (prof) {
+      long long now = clock64();
+      atomicAdd(&prof[slot], (unsigned long long)(now - last));  // fire and forget: no wait for the old value
+      last = now;
+    }
   }
 };
 
@@ -51,7 +66,7 @@ struct SeqSumScratch {
 // prefix sum (one warp, one scan per 32 segments). A segment is handled term by term,
 // with real f32 adds, when its predicted binade is wrong, when the mantissa would leave
 // the binade inside it, or when one of its terms is an exact tie.
-__device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const CtaGroup& g) {
+__device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const CtaGroup& g, SubProf* sp = nullptr) {
   const int tid = g.tid, lane = tid & 31, warp = tid >> 5, nwarps = g.nthreads >> 5;
   g.sync();
   if (n <= 128) {
@@ -71,57 +86,108 @@ __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const C
   if (tid == 0) sc->s = 0.0f;
   for (int base = 0; base < n; base += SEQSUM_SEGS * 32) {
     const int len = min(n - base, SEQSUM_SEGS * 32), S = (len + 31) >> 5;
-    // 1. inexact per-segment sums
-    for (int seg = warp; seg < S; seg += nwarps) {
-      const int i = seg * 32 + lane;
-      float v = i < len ? p[base + i] : 0.0f;
+    // 1. inexact per-segment sums; a warp takes four segments at a time so that their
+    //    shuffle chains overlap
+    for (int seg0 = warp * 4; seg0 < S; seg0 += nwarps * 4) {
+      float v[4];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0) sc->est[seg] = v;
+      for (int u = 0; u < 4; u++) {
+        const int i = (seg0 + u) * 32 + lane;
+        v[u] = i < len ? p[base + i] : 0.0f;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] += __shfl_xor_sync(0xffffffffu, v[u], o);
+      }
+      if (lane < 4 && seg0 + lane < S) sc->est[seg0 + lane] = lane == 0 ? v[0] : lane == 1 ? v[1] : lane == 2 ? v[2] : v[3];
     }
     g.sync();
-    // 2. predicted value at the start of every segment (one warp)
+    if (sp) sp->mark(26);
+    // 2. predicted value at the start of every segment (one warp, the four 32-segment
+    //    chunks scanned side by side)
     if (warp == 0) {
-      float run = sc->s;
-      for (int c = 0; c < S; c += 32) {
-        const float x = c + lane < S ? sc->est[c + lane] : 0.0f;
-        float inc = x;
+      float x[4], inc[4];
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          float y = __shfl_up_sync(0xffffffffu, inc, o);
-          if (lane >= o) inc += y;
+      for (int u = 0; u < 4; u++) {
+        x[u] = u * 32 + lane < S ? sc->est[u * 32 + lane] : 0.0f;
+        inc[u] = x[u];
+      }
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          const float y = __shfl_up_sync(0xffffffffu, inc[u], o);
+          if (lane >= o) inc[u] += y;
         }
-        if (c + lane < S) sc->est[c + lane] = run + (inc - x);
-        run += __shfl_sync(0xffffffffu, inc, 31);
       }
-    }
-    g.sync();
-    // 3. integer increment of every segment for its predicted binade
-    for (int seg = warp; seg < S; seg += nwarps) {
-      uint32_t b = f2u(sc->est[seg]);
-      if ((b >> 23) >= 255u || (b >> 31)) b = 0;
-      int e, m;
-      sum_decompose(b, e, m);
-      const int i = seg * 32 + lane;
-      const SumFn f = i < len ? sumfn_elem(f2u(p[base + i]), e) : sumfn_identity();
-      const bool bad = f.a0 != f.a1 || f.a0 >= SUMFN_SAT;
-      int c = f.a0 > (1 << 25) ? (1 << 25) : f.a0;
+      float run = sc->s;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-      const unsigned any_bad = __ballot_sync(0xffffffffu, bad);
-      if (lane == 0) {
-        sc->csum[seg] = c;
-        sc->epred[seg] = any_bad ? -1 : e;
+      for (int u = 0; u < 4; u++) {
+        if (u * 32 + lane < S) sc->est[u * 32 + lane] = run + (inc[u] - x[u]);
+        run += __shfl_sync(0xffffffffu, inc[u], 31);
       }
     }
     g.sync();
+    if (sp) sp->mark(27);
+    // 3. integer increment of every segment for its predicted binade, four segments per
+    //    warp at a time
+    for (int seg0 = warp * 4; seg0 < S; seg0 += nwarps * 4) {
+      int c[4], e[4];
+      bool bad[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int seg = seg0 + u;
+        uint32_t b = seg < S ? f2u(sc->est[seg]) : 0u;
+        if ((b >> 23) >= 255u || (b >> 31)) b = 0;
+        int m;
+        sum_decompose(b, e[u], m);
+        const int i = seg * 32 + lane;
+        const SumFn f = i < len ? sumfn_elem(f2u(p[base + i]), e[u]) : sumfn_identity();
+        bad[u] = f.a0 != f.a1 || f.a0 >= SUMFN_SAT;
+        c[u] = f.a0 > (1 << 25) ? (1 << 25) : f.a0;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) c[u] += __shfl_xor_sync(0xffffffffu, c[u], o);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const unsigned any_bad = __ballot_sync(0xffffffffu, bad[u]);
+        if (lane == u && seg0 + u < S) {
+          sc->csum[seg0 + u] = c[u];
+          sc->epred[seg0 + u] = any_bad ? -1 : e[u];
+        }
+      }
+    }
+    g.sync();
+    if (sp) sp->mark(28);
     // 4. the walk (one warp, uniform control flow)
     if (warp == 0) {
       int e, m;
-      sum_decompose(f2u(sc->s), e, m);
+      // The first terms of a sum are about as large as the sum itself: binade changes and
+      // ties at every step. They go through one plain add chain (every lane the same).
+      int head_segs = 0;
+      if (base == 0 && len >= 128) {
+        float s = sc->s;
+        const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll 4
+        for (int k = 0; k < 32; k++) {
+          const float4 a = q[k];
+          s = fadd(s, a.x);
+          s = fadd(s, a.y);
+          s = fadd(s, a.z);
+          s = fadd(s, a.w);
+        }
+        sum_decompose(f2u(s), e, m);
+        head_segs = 4;
+      } else {
+        sum_decompose(f2u(sc->s), e, m);
+      }
       for (int c0 = 0; c0 < S; c0 += 32) {
         const int seg = c0 + lane;
-        const int cs = seg < S ? sc->csum[seg] : 0;
+        const int cs = seg < S && seg >= head_segs ? sc->csum[seg] : 0;
         const int ep = seg < S ? sc->epred[seg] : -2;
         int pre = cs;  // inclusive prefix of the increments
 #pragma unroll
@@ -129,7 +195,7 @@ __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const C
           const int y = __shfl_up_sync(0xffffffffu, pre, o);
           if (lane >= o) pre += y;
         }
-        int j0 = 0, pbase = 0;
+        int j0 = c0 == 0 ? head_segs : 0, pbase = 0;
         for (int guard = 0; guard < 33; guard++) {
           const bool stop = lane >= j0 && (ep != e || m + (pre - pbase) >= SUMFN_LIMIT);
           const unsigned mask = __ballot_sync(0xffffffffu, stop);
@@ -171,7 +237,9 @@ __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const C
       }
       if (lane == 0) sc->s = u2f(sum_pack(e, m));
     }
+    if (sp) sp->mark(29);
     g.sync();
+    if (sp) sp->mark(30);
   }
   return sc->s;
 }
@@ -179,27 +247,40 @@ __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const C
 // ---- warp-per-row dot products, four lanes per 256-weight super-block -----------------
 __device__ __forceinline__ float half_to_float_hw(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
 
+__device__ __forceinline__ U4 lds128q(uint32_t a) {
+  U4 v;
+  asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32q(uint32_t a) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+
 // Lane (b = lane/4, c = lane%4) of a warp: quarter c of block b. Returns the two
-// integers of the whole block (summed over the four lanes) to all four lanes.
+// integers of the whole block (summed over the four lanes) to all four lanes, and the
+// block's d|dmin word.
 template <bool Q5>
-__device__ __forceinline__ void quarter_k4(const uint8_t* wb, const uint8_t* xb, int c, int& sumi, int& summ) {
-  U4 hdr = lds128(wb);
-  K4Scales s = k4_unpack(hdr.y, hdr.z, hdr.w);
-  const uint8_t* qs = wb + (Q5 ? 48 : 16) + 32 * c;
-  U4 wa = lds128(qs), wc = lds128(qs + 16);
-  U4 y0 = lds128(xb + 64 * c), y1 = lds128(xb + 64 * c + 16), y2 = lds128(xb + 64 * c + 32), y3 = lds128(xb + 64 * c + 48);
+__device__ __forceinline__ void quarter_k4(uint32_t wb, uint32_t xb, int c, int& sumi, int& summ, uint32_t& dd) {
+  const U4 hdr = lds128q(wb);
+  dd = hdr.x;
+  const K4Scales s = k4_unpack(hdr.y, hdr.z, hdr.w);
+  const uint32_t qs = wb + (Q5 ? 48 : 16) + 32 * c;
+  const U4 wa = lds128q(qs), wc = lds128q(qs + 16);
+  const U4 y0 = lds128q(xb + 64 * c), y1 = lds128q(xb + 64 * c + 16), y2 = lds128q(xb + 64 * c + 32), y3 = lds128q(xb + 64 * c + 48);
   U4 h0{0, 0, 0, 0}, h1{0, 0, 0, 0};
   if (Q5) {
-    h0 = lds128(wb + 16);
-    h1 = lds128(wb + 32);
+    h0 = lds128q(wb + 16);
+    h1 = lds128q(wb + 32);
   }
   int s_lo = 0, s_hi = 0;
 #pragma unroll
   for (int i = 0; i < 8; i++) {
-    uint32_t w = i < 4 ? u4_get(wa, i) : u4_get(wc, i - 4);
+    const uint32_t w = i < 4 ? u4_get(wa, i) : u4_get(wc, i - 4);
     uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
     if (Q5) {
-      uint32_t h = i < 4 ? u4_get(h0, i) : u4_get(h1, i - 4);
+      const uint32_t h = i < 4 ? u4_get(h0, i) : u4_get(h1, i - 4);
       lo |= ((h >> (2 * c)) & 0x01010101u) << 4;
       hi |= ((h >> (2 * c + 1)) & 0x01010101u) << 4;
     }
@@ -211,9 +292,9 @@ __device__ __forceinline__ void quarter_k4(const uint8_t* wb, const uint8_t* xb,
   const int sc0 = (scw >> sh) & 0xFF, sc1 = (scw >> (sh + 8)) & 0xFF;
   const int m0 = (mw >> sh) & 0xFF, m1 = (mw >> (sh + 8)) & 0xFF;
   // bsums[4c..4c+3]: pairs (4c,4c+1) for sub-block 2c and (4c+2,4c+3) for 2c+1
-  const int2 bs = *reinterpret_cast<const int2*>(xb + XK_BSUMS + 8 * c);
+  const uint32_t bx = lds32q(xb + XK_BSUMS + 8 * c), by = lds32q(xb + XK_BSUMS + 8 * c + 4);
   int si = sc0 * s_lo + sc1 * s_hi;
-  int sm = m0 * ((int)(short)(bs.x & 0xFFFF) + (bs.x >> 16)) + m1 * ((int)(short)(bs.y & 0xFFFF) + (bs.y >> 16));
+  int sm = m0 * ((int)(short)(bx & 0xFFFF) + ((int)bx >> 16)) + m1 * ((int)(short)(by & 0xFFFF) + ((int)by >> 16));
   si += __shfl_xor_sync(0xffffffffu, si, 1);
   sm += __shfl_xor_sync(0xffffffffu, sm, 1);
   si += __shfl_xor_sync(0xffffffffu, si, 2);
@@ -223,66 +304,69 @@ __device__ __forceinline__ void quarter_k4(const uint8_t* wb, const uint8_t* xb,
 }
 
 // Q6_K: lane c covers half n = c/2 of the block and elements l in [16*(c%2), +16) of
-// each of its four 32-element quarters.
-__device__ __forceinline__ int quarter_q6k(const uint8_t* wb, const uint8_t* xb, int c) {
-  const uint32_t sh = ((uint32_t)(uintptr_t)wb & 2u) * 8u;
-  const uint32_t* p = reinterpret_cast<const uint32_t*>((uintptr_t)wb & ~(uintptr_t)3);
-  auto wload = [&](int k) -> uint32_t { return funnel_r(p[k], p[k + 1], sh); };
+// each of its four 32-element quarters. Blocks are only 2-byte aligned: words come from
+// the aligned stream through a funnel shift.
+__device__ __forceinline__ int quarter_q6k(uint32_t wb, uint32_t xb, int c) {
+  const uint32_t sh = (wb & 2u) * 8u, p = wb & ~3u;
+  auto wload = [&](int k) -> uint32_t { return funnel_r(lds32q(p + 4 * k), lds32q(p + 4 * k + 4), sh); };
   const int n = c >> 1, half = c & 1;
-  U4 y1 = lds128(xb + 128 * n + 16 * half), y2 = lds128(xb + 128 * n + 32 + 16 * half),
-     y3 = lds128(xb + 128 * n + 64 + 16 * half), y4 = lds128(xb + 128 * n + 96 + 16 * half);
+  const U4 y1 = lds128q(xb + 128 * n + 16 * half), y2 = lds128q(xb + 128 * n + 32 + 16 * half),
+           y3 = lds128q(xb + 128 * n + 64 + 16 * half), y4 = lds128q(xb + 128 * n + 96 + 16 * half);
   int a1 = 0, a2 = 0, a3 = 0, a4 = 0;
 #pragma unroll
   for (int ii = 0; ii < 4; ii++) {
     const int i = 4 * half + ii;
-    uint32_t l0 = wload(16 * n + i), l32 = wload(16 * n + 8 + i), h = wload(32 + 8 * n + i);
-    uint32_t q1 = (l0 & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
-    uint32_t q2 = (l32 & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
-    uint32_t q3 = ((l0 >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
-    uint32_t q4 = ((l32 >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
+    const uint32_t l0 = wload(16 * n + i), l32 = wload(16 * n + 8 + i), h = wload(32 + 8 * n + i);
+    const uint32_t q1 = (l0 & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
+    const uint32_t q2 = (l32 & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
+    const uint32_t q3 = ((l0 >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
+    const uint32_t q4 = ((l32 >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
     a1 = __dp4a((int)q1, (int)u4_get(y1, ii), a1);
     a2 = __dp4a((int)q2, (int)u4_get(y2, ii), a2);
     a3 = __dp4a((int)q3, (int)u4_get(y3, ii), a3);
     a4 = __dp4a((int)q4, (int)u4_get(y4, ii), a4);
   }
-  // scales 8n..8n+7 are words 48+2n, 49+2n; this lane uses bytes half, half+2, half+4, half+6
   const uint32_t s01 = wload(48 + 2 * n), s23 = wload(49 + 2 * n);
   const int g = 8 * n + half;
   const int c1 = (int)(int8_t)((s01 >> (8 * half)) & 0xFF), c2 = (int)(int8_t)((s01 >> (8 * half + 16)) & 0xFF);
   const int c3 = (int)(int8_t)((s23 >> (8 * half)) & 0xFF), c4 = (int)(int8_t)((s23 >> (8 * half + 16)) & 0xFF);
-  const int16_t* bs = reinterpret_cast<const int16_t*>(xb + XK_BSUMS);
+  const uint32_t bsa = xb + XK_BSUMS + 2 * g;
+  auto bs16 = [&](uint32_t a) -> int {
+    int v;
+    asm("ld.shared.s16 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+  };
   int tot = c1 * a1 + c2 * a2 + c3 * a3 + c4 * a4;
-  tot -= 32 * (c1 * (int)bs[g] + c2 * (int)bs[g + 2] + c3 * (int)bs[g + 4] + c4 * (int)bs[g + 6]);
+  tot -= 32 * (c1 * bs16(bsa) + c2 * bs16(bsa + 4) + c3 * bs16(bsa + 8) + c4 * bs16(bsa + 12));
   tot += __shfl_xor_sync(0xffffffffu, tot, 1);
   tot += __shfl_xor_sync(0xffffffffu, tot, 2);
   return tot;
 }
 
 // Dot product of one K-quant row (in shared memory) with the Q8_K activation images,
-// computed by one warp; terms are added in block order. All lanes return the sum.
-__device__ __forceinline__ float warp_row_dot_kq(int kind, const uint8_t* row, const uint8_t* sx, int nb) {
+// computed by one warp, four lanes per block; terms are added in block order. All lanes
+// return the sum. `row` and `sx` are shared-space addresses.
+__device__ __forceinline__ float warp_row_dot_s(int kind, uint32_t row, uint32_t sx, int nb) {
   const int lane = threadIdx.x & 31, bl = lane >> 2, c = lane & 3;
   const int bs = kind_size(kind);
   float sum = 0.0f;
   for (int g0 = 0; g0 < nb; g0 += 8) {
     const int b = g0 + bl;
-    const bool active = b < nb;
     // Idle lanes recompute the last block so every lane reaches the shuffles.
-    const int bb = active ? b : nb - 1;
-    const uint8_t* wb = row + (size_t)bb * bs;
-    const uint8_t* xb = sx + bb * XK_STRIDE;
+    const int bb = b < nb ? b : nb - 1;
+    const uint32_t wb = row + (uint32_t)bb * bs, xb = sx + (uint32_t)bb * XK_STRIDE;
+    const float d_x = __uint_as_float(lds32q(xb + XK_D));
     float term;
     if (kind == Q6_K) {
-      int si = quarter_q6k(wb, xb, c);
-      const uint32_t sh = ((uint32_t)(uintptr_t)(wb + 208) & 2u) * 8u;
-      const uint32_t* p = reinterpret_cast<const uint32_t*>((uintptr_t)(wb + 208) & ~(uintptr_t)3);
-      float d_w = half_to_float_hw((p[0] >> sh) & 0xFFFFu);
-      term = q6k_term(d_w, *reinterpret_cast<const float*>(xb + XK_D), si);
+      const int si = quarter_q6k(wb, xb, c);
+      const uint32_t da = wb + 208;
+      const uint32_t dw = lds32q(da & ~3u) >> ((da & 2u) * 8u);
+      term = q6k_term(half_to_float_hw(dw & 0xFFFFu), d_x, si);
     } else {
       int si, sm;
-      if (kind == Q5_K) quarter_k4<true>(wb, xb, c, si, sm); else quarter_k4<false>(wb, xb, c, si, sm);
-      const uint32_t h = *reinterpret_cast<const uint32_t*>(wb);
-      term = k4_term(half_to_float_hw(h & 0xFFFFu), half_to_float_hw(h >> 16), *reinterpret_cast<const float*>(xb + XK_D), si, sm);
+      uint32_t dd;
+      if (kind == Q5_K) quarter_k4<true>(wb, xb, c, si, sm, dd); else quarter_k4<false>(wb, xb, c, si, sm, dd);
+      term = k4_term(half_to_float_hw(dd & 0xFFFFu), half_to_float_hw(dd >> 16), d_x, si, sm);
     }
     const int nbg = min(8, nb - g0);
     float t[8];
@@ -294,7 +378,6 @@ __device__ __forceinline__ float warp_row_dot_kq(int kind, const uint8_t* row, c
   }
   return sum;
 }
-
 
 // ---- lane-per-block dot products ---------------------------------------------------------
 // One lane decodes one whole 256-weight super-block; the L = 2^k >= blocks-per-row lanes
@@ -444,6 +527,60 @@ __device__ __forceinline__ float group_row_dot(uint32_t row, int kind, uint32_t 
   return sum;
 }
 
+// ---- tagged activation words ---------------------------------------------------------------
+// Activation vectors that cross CTAs inside the step travel as 64-bit words {f32 value,
+// 32-bit tag}. A writer stores value and tag with one 8-byte store; a reader polls the word
+// until it carries the tag of the phase it expects. Data and "ready" arrive together, so
+// no fence, counter or grid-wide barrier sits between a matrix product and its consumers.
+// Tags are unique per (launch, phase): (launch count << 10) | phase id, phase id >= 1;
+// a zeroed buffer therefore never matches.
+typedef unsigned long long LLWord;
+constexpr uint32_t LL_SPIN_LIMIT = 1u << 21;
+
+__device__ __forceinline__ void ll_store(LLWord* p, float v, uint32_t tag) {
+  const LLWord w = ((LLWord)tag << 32) | (LLWord)__float_as_uint(v);
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ LLWord ll_load(const LLWord* p) {
+  LLWord w;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return w;
+}
+__device__ __forceinline__ void ll_load2(const LLWord* p, LLWord& a, LLWord& b) {
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+// Value of a word whose tag may be ignored (this CTA wrote it in an earlier phase).
+__device__ __forceinline__ float ll_value(const LLWord* p) { return __uint_as_float((uint32_t)ll_load(p)); }
+
+// Spin (bounded) until the word carries `tag`. On expiry the CTA's abort flag and the
+// device error word are set; every later wait then returns at once, so the kernel drains.
+__device__ __forceinline__ float ll_settle(const LLWord* p, LLWord w, uint32_t tag, volatile int* abort, int* err) {
+  if ((uint32_t)(w >> 32) != tag) {
+    uint32_t it = 0;
+    for (; it < LL_SPIN_LIMIT; ++it) {
+      w = ll_load(p);
+      if ((uint32_t)(w >> 32) == tag) break;
+      if ((it & 31u) == 31u && *abort) break;
+    }
+    if ((uint32_t)(w >> 32) != tag && !*abort) {
+      *abort = 1;
+      if (err) atomicOr(err, DEVERR_GRID_TIMEOUT);
+    }
+  }
+  return __uint_as_float((uint32_t)w);
+}
+__device__ __forceinline__ float ll_wait(const LLWord* p, uint32_t tag, volatile int* abort, int* err) {
+  return ll_settle(p, ll_load(p), tag, abort, err);
+}
+
+// Rows [c0, c1) of a row space of `span` rows that belong to this CTA: an even split with
+// the remainder spread over the first CTAs, so every CTA owns a row when span >= gridDim.x.
+__device__ __forceinline__ void cta_rows(int span, int& c0, int& c1) {
+  const int base = span / (int)gridDim.x, rem = span - base * (int)gridDim.x, b = (int)blockIdx.x;
+  c0 = b * base + min(b, rem);
+  c1 = c0 + base + (b < rem ? 1 : 0);
+}
+
 // ---- step description (built once by the host, lives in global memory) ------------------
 // One matrix-product phase as both the producer and the consumers see it. The row
 // space (concatenated rows, or shared rows in pair mode) is split evenly over the
@@ -452,6 +589,7 @@ struct MegaOp {
   GemvSeg seg[3];
   uint32_t row_bytes[3];
   int nseg, pair, cols, span_rows, rows_per_cta, tile_rows, epilogue;
+  int ll;  // outputs are tagged words (seg[].out points at LLWord), not plain floats
 };
 
 struct StepLayer {
@@ -472,7 +610,10 @@ struct StepParams {
   const uint8_t* token_embd;
   int embd_kind;
   size_t embd_row_bytes;
-  float *x, *xb, *q, *k, *v, *hb, *hb2, *logits, *k_cache, *v_cache;
+  LLWord *xl, *ql, *kl, *vl, *attl, *hbl;  // tagged activation vectors (residual, q, k, v, attention out, hidden)
+  float *x;                                // plain copy of the final residual stream, for readers outside the kernel
+  float *logits, *k_cache, *v_cache;
+  unsigned* epoch;                         // launch count; bumped by CTA 0 when the kernel ends
   const float* rope_table;
   int* step;  // {token, pos, n_generated}
   int* history;
@@ -566,7 +707,8 @@ __device__ __forceinline__ int op_tile_parts(const MegaOp& op, int t0, int t1, T
 
 // Producer side (one thread): request every tile of this CTA's share of `op`.
 __device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, RingPos& pp) {
-  const int c0 = blockIdx.x * op.rows_per_cta, c1 = min(c0 + op.rows_per_cta, op.span_rows);
+  int c0, c1;
+  cta_rows(op.span_rows, c0, c1);
   for (int t0 = c0; t0 < c1; t0 += op.tile_rows) {
     if (!ring_wait(R, &R.empty[pp.st], pp.parity ^ 1u)) return;
     TilePart parts[3];
@@ -588,13 +730,18 @@ __device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, Ring
 // is applied in the epilogue. `sx` holds the Q8_K images of the activation vector;
 // `op` lives in shared memory.
 __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp,
-                                           int n_warps) {
-  const int rows_per_cta = op.rows_per_cta, span = op.span_rows, tile_rows = op.tile_rows, pair = op.pair;
-  const int epilogue = op.epilogue, nb = op.cols >> 8;
-  const int c0 = blockIdx.x * rows_per_cta, c1 = min(c0 + rows_per_cta, span);
+                                           int n_warps, uint32_t tag) {
+  const int rows_per_cta = op.rows_per_cta, tile_rows = op.tile_rows, pair = op.pair;
+  const int epilogue = op.epilogue, nb = op.cols >> 8, ll = op.ll;
+  int c0, c1;
+  cta_rows(op.span_rows, c0, c1);
   const int lane = threadIdx.x & 31;
+  // Small ops (a row or less per warp) use the short-latency four-lanes-per-block dot, one
+  // row per warp; large ones the cheaper lane-per-block form.
+  const bool narrow = rows_per_cta * (pair ? 2 : 1) <= n_warps;
   int L = 1;
   while (L < nb && L < 32) L <<= 1;
+  if (narrow) L = 32;
   const int G = 32 / L;                             // rows per warp pass
   const bool split = pair && G >= 2;                // gate | up halves of one warp
   const int rows_per_pass = split ? G / 2 : G;
@@ -624,17 +771,33 @@ __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, Ring
             const float up = __shfl_down_sync(0xffffffffu, v, 16);
             if (u < R_rows && which == 0 && (lane & (L - 1)) == 0) {
               const int r = t0 + u;
-              op.seg[0].out[r] = epilogue == EPI_SILU_MUL ? silu_mul_exact(v, up) : v;
-              op.seg[1].out[r] = up;
+              const float hv = epilogue == EPI_SILU_MUL ? silu_mul_exact(v, up) : v;
+              if (ll) {
+                ll_store(reinterpret_cast<LLWord*>(op.seg[0].out) + r, hv, tag);
+              } else {
+                op.seg[0].out[r] = hv;
+                op.seg[1].out[r] = up;
+              }
             }
           } else {
             const int u = ps;  // one row per pass: gate, then up
-            const float g = group_row_dot(base0 + (uint32_t)u * op.row_bytes[0], op.seg[0].kind, sxa, nb, L);
-            const float up = group_row_dot(base1 + (uint32_t)u * op.row_bytes[1], op.seg[1].kind, sxa, nb, L);
+            float g, up;
+            if (narrow) {
+              g = warp_row_dot_s(op.seg[0].kind, base0 + (uint32_t)u * op.row_bytes[0], sxa, nb);
+              up = warp_row_dot_s(op.seg[1].kind, base1 + (uint32_t)u * op.row_bytes[1], sxa, nb);
+            } else {
+              g = group_row_dot(base0 + (uint32_t)u * op.row_bytes[0], op.seg[0].kind, sxa, nb, L);
+              up = group_row_dot(base1 + (uint32_t)u * op.row_bytes[1], op.seg[1].kind, sxa, nb, L);
+            }
             if (lane == 0) {
               const int r = t0 + u;
-              op.seg[0].out[r] = epilogue == EPI_SILU_MUL ? silu_mul_exact(g, up) : g;
-              op.seg[1].out[r] = up;
+              const float hv = epilogue == EPI_SILU_MUL ? silu_mul_exact(g, up) : g;
+              if (ll) {
+                ll_store(reinterpret_cast<LLWord*>(op.seg[0].out) + r, hv, tag);
+              } else {
+                op.seg[0].out[r] = hv;
+                op.seg[1].out[r] = up;
+              }
             }
           }
         } else {
@@ -650,10 +813,17 @@ __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, Ring
             row = stage + tp.soff + ((uint32_t)(uintptr_t)tp.src & 15u) + (uint32_t)lr * op.row_bytes[tp.seg];
             kind = op.seg[tp.seg].kind;
           }
-          const float v = group_row_dot(row, kind, sxa, nb, L);
+          const float v = narrow ? (row ? warp_row_dot_s(kind, row, sxa, nb) : 0.0f) : group_row_dot(row, kind, sxa, nb, L);
           if (u < R_rows && (lane & (L - 1)) == 0) {
-            float* o = op.seg[parts[pi].seg].out + parts[pi].row0 + lr;
-            *o = epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
+            const int oi = parts[pi].row0 + lr;
+            if (ll) {
+              // a residual row is only ever written by its owner, so its old value needs no tag check
+              LLWord* o = reinterpret_cast<LLWord*>(op.seg[parts[pi].seg].out) + oi;
+              ll_store(o, epilogue == EPI_ACCUM ? fadd(ll_value(o), v) : v, tag);
+            } else {
+              float* o = op.seg[parts[pi].seg].out + oi;
+              *o = epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
+            }
           }
         }
       }
@@ -695,42 +865,52 @@ __device__ __forceinline__ bool grid_sync(const StepParams& P, const CtaGroup& g
   return !*abort;
 }
 
-// Optional sub-phase cycle counters (slots 16..31 of the profile array).
-struct SubProf {
-  unsigned long long* prof;
-  long long last;
-  __device__ __forceinline__ void mark(int slot) {
-    if (prof) {
-      long long now = clock64();
-      prof[slot] += (unsigned long long)(now - last);
-      last = now;
-    }
-  }
-};
-
 // ---- activation phases -----------------------------------------------------------------------
 struct MegaSmem {
   uint8_t* sx;          // Q8_K images of the current activation vector
   float* scr;           // f32 scratch
   SeqSumScratch* ss;
   float* red;           // 32 floats
+  volatile int* abort;  // this CTA gave up on a bounded wait
+  int* err;             // device error word
 };
 
 // x -> rmsnorm -> Q8_K images in shared memory (ops.rs:7-18 then quant.rs:248-283).
-// `src` is global (read past L1) or, for the embedding, already in scr[0..n).
-__device__ __forceinline__ void phase_norm_quant(const float* src, bool src_in_scr, const float* w, int n, float eps,
-                                                 const MegaSmem& M, const CtaGroup& g, SubProf sp = SubProf{nullptr, 0}) {
+// `src` holds tagged words other CTAs publish under `tag`; for the embedding the row is
+// already in scr[0..n). `mirror`, when given, receives a plain copy of the row.
+__device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag, bool src_in_scr, float* mirror, const float* w,
+                                                 int n, float eps, const MegaSmem& M, const CtaGroup& g,
+                                                 SubProf sp = SubProf{nullptr, 0}) {
   sp.last = clock64();
   float* row = M.scr;
   float* sq = M.scr + n;
-  for (int i = g.tid; i < n; i += g.nthreads) {
-    float v = src_in_scr ? row[i] : __ldcg(src + i);
-    row[i] = v;
-    sq[i] = fmul(v, v);
+  if (src_in_scr) {
+    for (int i = g.tid; i < n; i += g.nthreads) sq[i] = fmul(row[i], row[i]);
+  } else {
+    // all of a thread's words are requested before the first one is examined
+    constexpr int U = 4;
+    for (int base = g.tid; base < n; base += U * g.nthreads) {
+      LLWord wd[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int i = base + u * g.nthreads;
+        if (i < n) wd[u] = ll_load(src + i);
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int i = base + u * g.nthreads;
+        if (i < n) {
+          const float v = ll_settle(src + i, wd[u], tag, M.abort, M.err);
+          row[i] = v;
+          sq[i] = fmul(v, v);
+          if (mirror) mirror[i] = v;
+        }
+      }
+    }
   }
   g.sync();
   sp.mark(16);
-  float ss = group_seq_sum(sq, n, M.ss, g);
+  float ss = group_seq_sum(sq, n, M.ss, g, &sp);
   sp.mark(17);
   float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
   g.sync();
@@ -743,17 +923,26 @@ __device__ __forceinline__ void phase_norm_quant(const float* src, bool src_in_s
   sp.mark(19);
 }
 
-// A vector another CTA produced -> Q8_K images.
-__device__ __forceinline__ void phase_quant(const float* src, int n, const MegaSmem& M, const CtaGroup& g) {
-  const int warp = g.tid >> 5, nw = g.nthreads >> 5;
-  for (int b = warp; b < n / 256; b += nw) warp_quantize_q8k<true>(src + b * 256, M.sx + b * XK_STRIDE, 1);
+// A vector other CTAs publish under `tag` -> Q8_K images.
+__device__ __forceinline__ void phase_quant(const LLWord* src, uint32_t tag, int n, const MegaSmem& M, const CtaGroup& g) {
+  const int warp = g.tid >> 5, nw = g.nthreads >> 5, lane = g.tid & 31;
+  for (int b = warp; b < n / 256; b += nw) {
+    const LLWord* p = src + b * 256 + 8 * lane;
+    LLWord wd[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) ll_load2(p + 2 * i, wd[2 * i], wd[2 * i + 1]);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = ll_settle(p + i, wd[i], tag, M.abort, M.err);
+    warp_quantize_q8k_vals(v, M.sx + b * XK_STRIDE, 1);
+  }
   g.sync();
 }
 
 // Per-head q/k norm, RoPE, KV store and attention for head `h` (ops.rs:74-87, 40-70,
 // 152-157, 185-218), by the consumer warps of one CTA.
-__device__ void phase_attention(const StepParams& P, int li, int h, int pos, const MegaSmem& M, const CtaGroup& g,
-                                SubProf pf = SubProf{nullptr, 0}) {
+__device__ void phase_attention(const StepParams& P, int li, int h, int pos, uint32_t tag_in, uint32_t tag_out,
+                                const MegaSmem& M, const CtaGroup& g, SubProf pf = SubProf{nullptr, 0}) {
   pf.last = clock64();
   const int hd = P.head_dim, kvd = P.n_kv_head * hd, gqa = P.n_head / P.n_kv_head, kvh = h / gqa;
   const int n = pos + 1, tid = g.tid, T = g.nthreads;
@@ -767,10 +956,20 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
   const float* const k_norm_w = P.layers[li].k_norm;
   float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd;
   float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd;
-  for (int i = tid; i < hd; i += T) {
-    sq[i] = __ldcg(P.q + h * hd + i);
-    sk[i] = __ldcg(P.k + kvh * hd + i);
-    sv[i] = __ldcg(P.v + kvh * hd + i);
+  // RoPE factors of this thread's pair, requested before the wait below
+  const int rope_half = P.rot_dim / 2;
+  float rope_c = 0.0f, rope_s = 0.0f;
+  if (tid < 2 * rope_half) {
+    const float* cs = P.rope_table + (size_t)pos * P.rot_dim;
+    const int i = tid < rope_half ? tid : tid - rope_half;
+    rope_c = cs[2 * i];
+    rope_s = cs[2 * i + 1];
+  }
+  // this head's q and its group's k, v rows as the q/k/v products publish them
+  for (int j = tid; j < 3 * hd; j += T) {
+    const int which = j / hd, i = j - which * hd;
+    const LLWord* src = which == 0 ? P.ql + h * hd + i : (which == 1 ? P.kl : P.vl) + kvh * hd + i;
+    sq[j] = ll_wait(src, tag_in, M.abort, M.err);  // sq, sk, sv are consecutive
   }
   g.sync();
   if (P.qk_norm) {
@@ -785,18 +984,13 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
       g.sync();
     }
   }
-  {
-    const float* cs = P.rope_table + (size_t)pos * P.rot_dim;
-    const int half = P.rot_dim / 2;
-    for (int j = tid; j < 2 * half; j += T) {
-      float* v = j < half ? sq : sk;
-      const int i = j < half ? j : j - half;
-      const int i0 = P.neox ? i : 2 * i, i1 = P.neox ? i + half : 2 * i + 1;
-      const float c = cs[2 * i], s = cs[2 * i + 1];
-      const float x0 = v[i0], x1 = v[i1];
-      v[i0] = fsub(fmul(x0, c), fmul(x1, s));
-      v[i1] = fadd(fmul(x0, s), fmul(x1, c));
-    }
+  if (tid < 2 * rope_half) {  // rot_dim <= head_dim <= the group's thread count
+    float* v = tid < rope_half ? sq : sk;
+    const int i = tid < rope_half ? tid : tid - rope_half;
+    const int i0 = P.neox ? i : 2 * i, i1 = P.neox ? i + rope_half : 2 * i + 1;
+    const float x0 = v[i0], x1 = v[i1];
+    v[i0] = fsub(fmul(x0, rope_c), fmul(x1, rope_s));
+    v[i1] = fadd(fmul(x0, rope_s), fmul(x1, rope_c));
   }
   g.sync();
   if (h % gqa == 0) {
@@ -806,27 +1000,47 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
     }
   }
   pf.mark(20);
-  // scores
+  // scores: cached K rows are staged through shared memory in chunks (one round of
+  // coalesced loads), padded by one float4 per row to spread the banks
   const float scale = 1.0f / sqrtf((float)hd);
+  const int hd4 = hd >> 2, kstride = hd + 4;
+  const int k_chunk = (P.v_chunk * hd) / kstride;
   float lmax = -INFINITY;
-  for (int t = tid; t < n; t += T) {
-    float s = 0.0f;
-    if (t == pos) {
-      for (int i = 0; i < hd; i++) s = fadd(s, fmul(sq[i], sk[i]));
-    } else {
-      const float4* kt = reinterpret_cast<const float4*>(kc + (size_t)t * kvd + kvh * hd);
+  for (int c0 = 0; c0 < n; c0 += k_chunk) {
+    const int cn = min(k_chunk, n - c0);
+    g.sync();
+    // two rows per thread are requested before the first is stored
+    for (int t = tid / hd4, i4 = tid % hd4; t < cn; t += 2 * (T / hd4)) {
+      float4 kk[2];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int tu = t + u * (T / hd4), tt = c0 + tu;
+        if (tu < cn)
+          kk[u] = tt == pos ? reinterpret_cast<const float4*>(sk)[i4]
+                            : __ldcg(reinterpret_cast<const float4*>(kc + (size_t)tt * kvd + kvh * hd) + i4);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int tu = t + u * (T / hd4);
+        if (tu < cn) *reinterpret_cast<float4*>(vbuf + tu * kstride + 4 * i4) = kk[u];
+      }
+    }
+    g.sync();
+    for (int t = tid; t < cn; t += T) {
+      const float4* kt = reinterpret_cast<const float4*>(vbuf + t * kstride);
+      float s = 0.0f;
 #pragma unroll 4
-      for (int i = 0; i < hd / 4; i++) {
-        float4 kk = kt[i];
+      for (int i = 0; i < hd4; i++) {
+        const float4 kk = kt[i];
         s = fadd(s, fmul(sq[4 * i], kk.x));
         s = fadd(s, fmul(sq[4 * i + 1], kk.y));
         s = fadd(s, fmul(sq[4 * i + 2], kk.z));
         s = fadd(s, fmul(sq[4 * i + 3], kk.w));
       }
+      s = fmul(s, scale);
+      sc[c0 + t] = s;
+      lmax = fmaxf(lmax, s);
     }
-    s = fmul(s, scale);
-    sc[t] = s;
-    lmax = fmaxf(lmax, s);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
@@ -848,12 +1062,20 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
   for (int c0 = 0; c0 < n; c0 += P.v_chunk) {
     const int cn = min(P.v_chunk, n - c0);
     g.sync();
-    for (int j = tid; j < cn * (hd / 4); j += T) {
-      const int t = c0 + j / (hd / 4), i4 = j % (hd / 4);
-      float4 vv;
-      if (t == pos) vv = reinterpret_cast<const float4*>(sv)[i4];
-      else vv = reinterpret_cast<const float4*>(vc + (size_t)t * kvd + kvh * hd)[i4];
-      reinterpret_cast<float4*>(vbuf)[j] = vv;
+    for (int t = tid / hd4, i4 = tid % hd4; t < cn; t += 2 * (T / hd4)) {
+      float4 vv[2];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int tu = t + u * (T / hd4), tt = c0 + tu;
+        if (tu < cn)
+          vv[u] = tt == pos ? reinterpret_cast<const float4*>(sv)[i4]
+                            : __ldcg(reinterpret_cast<const float4*>(vc + (size_t)tt * kvd + kvh * hd) + i4);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int tu = t + u * (T / hd4);
+        if (tu < cn) reinterpret_cast<float4*>(vbuf)[tu * hd4 + i4] = vv[u];
+      }
     }
     g.sync();
     if (tid < hd) {
@@ -861,7 +1083,7 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, con
       for (int t = 0; t < cn; t++) o = fadd(o, fmul(sc[c0 + t], vbuf[t * hd + tid]));
     }
   }
-  if (tid < hd) P.xb[h * hd + tid] = o;
+  if (tid < hd) ll_store(P.attl + h * hd + tid, o, tag_out);
   pf.mark(24);
 }
 
@@ -909,8 +1131,11 @@ __device__ void phase_argmax(const StepParams& P, const MegaSmem& M, const CtaGr
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
-constexpr int MEGA_THREADS = 1024;
-constexpr int MEGA_CONSUMER_WARPS = 31;
+#ifndef MEGA_THREADS_N
+#define MEGA_THREADS_N 768
+#endif
+constexpr int MEGA_THREADS = MEGA_THREADS_N;
+constexpr int MEGA_CONSUMER_WARPS = MEGA_THREADS / 32 - 1;
 constexpr int MEGA_BAR_BYTES = 128;     // up to 8 stages x (full, empty)
 constexpr int MEGA_SEQSUM_BYTES = 2064;  // sizeof(SeqSumScratch) rounded up to 16
 static_assert(sizeof(SeqSumScratch) <= MEGA_SEQSUM_BYTES, "SeqSumScratch layout");
@@ -982,81 +1207,90 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
 
   // ---- consumer warps ----
   CtaGroup g{(int)threadIdx.x, MEGA_CONSUMER_WARPS * 32, 1};
-  MegaSmem M{sx, scr, ssc, red};
+  MegaSmem M{sx, scr, ssc, red, abort, P.err};
   RingPos cp{0, 0u};
   unsigned bar_target = 0;
   const int token = P.step[0], pos = P.step[1];
+  // Tags of this launch: phase k (1..5) of layer li is tag_base + 5 * li + k.
+  const uint32_t tag_base = *P.epoch << 10;
   const bool prof_on = P.prof && (int)blockIdx.x == P.prof_cta && g.tid == 0;
   long long prof_last = clock64();
 #define MEGA_PROF(slot)                                 \
   do {                                                  \
     if (prof_on) {                                      \
       long long now_ = clock64();                       \
-      P.prof[slot] += (unsigned long long)(now_ - prof_last); \
+      atomicAdd(&P.prof[slot], (unsigned long long)(now_ - prof_last)); \
       prof_last = now_;                                 \
     }                                                   \
   } while (0)
 
-  // embedding row (quant.rs:300-443 via emit.rs:469): every CTA keeps a copy, CTA 0 publishes it
+  // embedding row (quant.rs:300-443 via emit.rs:469): every CTA keeps a copy and publishes
+  // the residual rows it owns (the rows of wo / down it computes)
   {
     const uint8_t* row = P.token_embd + (size_t)token * P.embd_row_bytes;
+    int r0, r1;
+    cta_rows(P.dim, r0, r1);
     for (int e = g.tid; e < P.dim; e += g.nthreads) {
       float v = dequant_elem(P.embd_kind, row, (size_t)e);
       scr[e] = v;
-      if (blockIdx.x == 0) P.x[e] = v;
+      if (e >= r0 && e < r1) ll_store(P.xl + e, v, 0u);
     }
     g.sync();
   }
   MEGA_PROF(0);
 
-  bool ok = true;
-  for (int li = 0; li < P.n_layer; li++) {
+  // One loop over the step's matrix products (four per layer, then the output head), so
+  // that each phase's code exists once. Phases hand their vectors on as tagged words;
+  // the only grid-wide barrier left is the one in front of the argmax.
+  const int n_stage = 4 * P.n_layer + (P.want_logits ? 1 : 0);
+#pragma unroll 1
+  for (int st = 0; st < n_stage; st++) {
+    const int li = st >> 2, ph = st & 3;
+    const bool head = li == P.n_layer;
     const StepLayer& L = table[li];
-    // A: attn norm + q/k/v
-    phase_norm_quant(P.x, li == 0, L.attn_norm, P.dim, P.eps, M, g, SubProf{prof_on ? P.prof : nullptr, 0});
-    MEGA_PROF(1);
-    consume_op(L.qkv, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
-    MEGA_PROF(2);
-    ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
-    MEGA_PROF(3);
-    // B: attention, one head per CTA
-    for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
-      if (ok) phase_attention(P, li, h, pos, M, g, SubProf{prof_on ? P.prof : nullptr, 0});
-      g.sync();
+    const MegaOp& op = (&L.qkv)[ph];  // qkv, wo, gu, down are consecutive members
+    const int slot = ph == 0 ? 1 : 3 * ph + 3;
+    const uint32_t tl = tag_base + 5u * (uint32_t)li;  // + k: phase k of this layer
+    if ((ph & 1) == 0) {
+      // attention norm -> q/k/v, ffn norm -> gate/up + SiLU, output norm -> logits
+      const float* w = head ? P.output_norm : (ph == 0 ? L.attn_norm : L.ffn_norm);
+      const uint32_t tin = ph == 0 ? tl : tl + 3u;  // residual after the previous layer's down / this layer's wo
+      phase_norm_quant(P.xl, tin, st == 0, head && blockIdx.x == 0 ? P.x : nullptr, w, P.dim, P.eps, M, g,
+                       SubProf{prof_on && ph == 0 && !head ? P.prof : nullptr, 0});
+    } else {
+      // attention output -> wo, activated hidden -> down; both join the residual stream
+      if (ph == 1) phase_quant(P.attl, tl + 2u, qd, M, g);
+      else phase_quant(P.hbl, tl + 4u, P.hidden, M, g);
     }
-    MEGA_PROF(4);
-    ok = grid_sync(P, g, bar_target, abort);
-    MEGA_PROF(5);
-    // C: wo, joined into the residual stream
-    phase_quant(P.xb, qd, M, g);
-    MEGA_PROF(6);
-    consume_op(L.wo, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
-    MEGA_PROF(7);
-    ok = grid_sync(P, g, bar_target, abort);
-    MEGA_PROF(8);
-    // D: ffn norm + gate/up + SiLU
-    phase_norm_quant(P.x, false, L.ffn_norm, P.dim, P.eps, M, g);
-    MEGA_PROF(9);
-    consume_op(L.gu, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
-    MEGA_PROF(10);
-    ok = grid_sync(P, g, bar_target, abort);
-    MEGA_PROF(11);
-    // E: down, joined into the residual stream
-    phase_quant(P.hb, P.hidden, M, g);
-    MEGA_PROF(12);
-    consume_op(L.down, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
-    MEGA_PROF(13);
-    ok = grid_sync(P, g, bar_target, abort);
-    MEGA_PROF(14);
-  }
-  if (P.want_logits) {
-    phase_norm_quant(P.x, false, P.output_norm, P.dim, P.eps, M, g);
-    consume_op(table[P.n_layer].qkv, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
-    if (P.with_argmax) {
-      ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
-      if (blockIdx.x == 0 && ok) phase_argmax(P, M, g);
+    if (!head) MEGA_PROF(slot);
+    // q/k/v: tl+1, wo: tl+3, gate/up: tl+4, down: tl+5 (the head writes plain floats)
+    consume_op(op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, tl + (ph == 0 ? 1u : (uint32_t)ph + 2u));
+    if (head) break;
+    // The next phase rewrites the activation images and the scratch rows; warps that are
+    // done must also not start polling while others still compute.
+    g.sync();
+    MEGA_PROF(slot + 1);
+    if (ph == 0) {
+      // attention, one head per CTA
+      for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
+        phase_attention(P, li, h, pos, tl + 1u, tl + 2u, M, g, SubProf{prof_on ? P.prof : nullptr, 0});
+        g.sync();
+      }
+      MEGA_PROF(4);
     }
   }
+  if (!P.want_logits && blockIdx.x == 0) {
+    // no output head: still leave a plain copy of the final residual stream
+    const uint32_t tin = tag_base + 5u * (uint32_t)P.n_layer;
+    for (int i = g.tid; i < P.dim; i += g.nthreads) P.x[i] = ll_wait(P.xl + i, tin, abort, P.err);
+  }
+  if (P.want_logits && P.with_argmax) {
+    const bool ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
+    if (blockIdx.x == 0 && ok) phase_argmax(P, M, g);
+  }
+  // Next launch, next tags. Every CTA read the count before it published anything, and
+  // CTA 0 gets here only after consuming words from every CTA.
+  if (blockIdx.x == 0 && g.tid == 0) *P.epoch = *P.epoch + 1u;
   MEGA_PROF(15);
 #undef MEGA_PROF
 }

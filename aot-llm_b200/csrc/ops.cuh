@@ -46,18 +46,9 @@ __device__ __forceinline__ float block_seq_sum(const float* p, int n, float* slo
 // quant.rs:248-283. `src` may be shared or global. The block is written either in
 // the reference's BlockQ8_K layout (image == 0) or as the 304-byte image the GEMV
 // kernels read (image == 1).
-template <bool CG = false>
-__device__ __forceinline__ void warp_quantize_q8k(const float* src, uint8_t* dst, int image) {
+// Core: lane holds elements 8*lane .. 8*lane+7 of the block in v[].
+__device__ __forceinline__ void warp_quantize_q8k_vals(const float (&v)[8], uint8_t* dst, int image) {
   const int lane = threadIdx.x & 31;
-  float v[8];
-  if (CG) {
-    // data written by other CTAs of the same launch: bypass L1
-    float4 a = __ldcg(reinterpret_cast<const float4*>(src) + 2 * lane), b = __ldcg(reinterpret_cast<const float4*>(src) + 2 * lane + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = src[8 * lane + i];
-  }
   // signed extreme: first element with strictly larger |v|
   float amax = 0.0f, mx = 0.0f;
   int idx = 0;
@@ -104,6 +95,21 @@ __device__ __forceinline__ void warp_quantize_q8k(const float* src, uint8_t* dst
   int s2 = s + __shfl_xor_sync(0xffffffffu, s, 1);
   if ((lane & 1) == 0) bs[lane >> 1] = (int16_t)s2;
   if (lane == 0) *dptr = d;
+}
+
+template <bool CG = false>
+__device__ __forceinline__ void warp_quantize_q8k(const float* src, uint8_t* dst, int image) {
+  const int lane = threadIdx.x & 31;
+  float v[8];
+  if (CG) {
+    // data written by other CTAs of the same launch: bypass L1
+    float4 a = __ldcg(reinterpret_cast<const float4*>(src) + 2 * lane), b = __ldcg(reinterpret_cast<const float4*>(src) + 2 * lane + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = src[8 * lane + i];
+  }
+  warp_quantize_q8k_vals(v, dst, image);
 }
 
 // quant.rs:231-245 for one 32-value block handled by one warp (lane = element).
