@@ -5,6 +5,8 @@ generated project; see INTEGRATION.md.
 """
 from __future__ import annotations
 
+import fcntl
+import hashlib
 import os
 import shutil
 import subprocess
@@ -34,26 +36,48 @@ def nvcc_path() -> str:
     return p
 
 
-def stale() -> bool:
-    if not LIB.exists():
-        return True
-    t = LIB.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.cpp")) + \
+STAMP = HERE / "libaot_cuda.so.srchash"
+
+
+def source_hash() -> str:
+    """Hash of everything the library is built from (contents, not timestamps: a copied
+    tree does not keep modification times in a useful order)."""
+    deps = sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.cpp"))) + \
         [HERE.parent / "include" / "aot_cuda.h"]
-    return any(d.stat().st_mtime > t for d in deps)
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for d in deps:
+        h.update(d.name.encode())
+        h.update(d.read_bytes())
+    return h.hexdigest()
+
+
+def stale() -> bool:
+    if not LIB.exists() or not STAMP.exists():
+        return True
+    return STAMP.read_text().strip() != source_hash()
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not stale():
         return LIB
-    cmd = [nvcc_path(), *NVCC_FLAGS, "-o", str(LIB), *map(str, SOURCES)]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose:
-        sys.stderr.write(r.stderr)
-    if r.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
+    # Several ranks of one job may get here together: one builds, the others wait and
+    # then find the library fresh. The new file replaces the old one atomically.
+    with open(HERE / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not stale():
+            return LIB
+        tmp = HERE / f".libaot_cuda.{os.getpid()}.so"
+        cmd = [nvcc_path(), *NVCC_FLAGS, "-o", str(tmp), *map(str, SOURCES)]
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose:
+            sys.stderr.write(r.stderr)
+        if r.returncode != 0:
+            tmp.unlink(missing_ok=True)
+            raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
+        os.replace(tmp, LIB)
+        STAMP.write_text(source_hash() + "\n")
     return LIB
 
 

@@ -157,25 +157,10 @@ def run_reference(args, rank: int, world: int):
 
 def run_ours(args, rank: int, world: int, local_rank: int):
     pkg = graft.import_package()
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist_mod
-        torch.cuda.set_device(local_rank)
-        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        dist = dist_mod
-
-    def barrier():
-        if dist:
-            dist.barrier()
-
-    def max_over_ranks(v: float) -> float:
-        if not dist:
-            return v
-        import torch
-        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    # N GPUs = N independent replicas of the decode path (no data-path collective); the
+    # process group only brackets the timed regions and takes the slowest rank's time.
+    ranks = pkg.ranks.Ranks(pkg.ranks.RankInfo(rank, world, local_rank), backend="nccl")
+    barrier, max_over_ranks = ranks.barrier, ranks.max_over_ranks
 
     spec = pkg.model.tinyllama()
     d = spec.head.dims
@@ -231,8 +216,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     gemv_gbs = sweep_bytes / (sweep_ms * 1e-3) / 1e9
 
     if rank != 0:
-        if dist:
-            dist.destroy_process_group()
+        ranks.close()
         return
 
     cpu = None
@@ -267,8 +251,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if cpu:
         out["cpu_baseline"] = cpu
     print(json.dumps(out))
-    if dist:
-        dist.destroy_process_group()
+    ranks.close()
 
 
 def main():
