@@ -15,6 +15,7 @@
 
 #include "../../include/aot_cuda.h"
 #include "gemv.cuh"
+#include "gemm.cuh"
 #include "mega.cuh"
 #include "ops.cuh"
 
@@ -110,6 +111,55 @@ static int check_weight_alignment(int kind, const void* w) {
   return 0;
 }
 
+// m = 8..64 activation rows against K-quant matrices: int8 tensor-core tiles (gemm.cuh).
+// Arguments were checked by launch_gemv.
+template <int NT, bool PAIR>
+static int launch_gemm_nt(aotcu_ctx* c, const GemmParams& P, int grid, size_t smem) {
+  static bool attr_set[64] = {};
+  int dev = c->device;
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    CU_TRY(cudaFuncSetAttribute(gemm_q8k_mma_kernel<NT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+    attr_set[dev] = true;
+  }
+  return launch(c, gemm_q8k_mma_kernel<NT, PAIR>, dim3(grid), dim3(GEMM_WARPS * 32), smem, P);
+}
+
+static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
+  GemmParams P = {};
+  int tiles = 0;
+  for (int s = 0; s < call.nseg; s++) {
+    P.seg[s] = call.seg[s];
+    P.tiles_before[s] = tiles;
+    if (!call.pair || s == 0) tiles += (call.seg[s].rows + 15) / 16;
+  }
+  if (call.pair) P.tiles_before[1] = 0;
+  P.nseg = call.nseg;
+  P.pair = call.pair;
+  P.cols = (int)call.cols;
+  P.m = (int)call.m;
+  P.m_pad = (P.m + 7) & ~7;
+  P.epilogue = call.epilogue;
+  P.x = reinterpret_cast<const uint8_t*>(call.x);
+  P.x_image = call.x_mode == 1;
+  // Token groups per warp: all of them when there are plenty of row tiles, fewer to put
+  // more warps to work on a small matrix.
+  const int groups8 = P.m_pad / 8;
+  int nt = 8;
+  while (nt > 2 && (size_t)tiles * ((groups8 + nt - 1) / nt) < (size_t)c->n_sm * GEMM_WARPS / 2) nt >>= 1;
+  if (call.pair && nt > 4) nt = 4;  // two matrices' accumulators per thread
+  P.n_groups = (groups8 + nt - 1) / nt;
+  P.m_pad = P.n_groups * nt * 8;  // every token slot a warp touches exists in the staged chunk
+  P.n_items = tiles * P.n_groups;
+  int grid = (P.n_items + GEMM_WARPS - 1) / GEMM_WARPS;
+  if (grid > c->n_sm * 2) grid = c->n_sm * 2;
+  const size_t smem = (size_t)2 * GEMM_KB * P.m_pad * XK_STRIDE;
+  ARG_CHECK(smem <= c->max_smem, "activation chunk does not fit in shared memory");
+  if (call.pair) return nt == 4 ? launch_gemm_nt<4, true>(c, P, grid, smem) : launch_gemm_nt<2, true>(c, P, grid, smem);
+  if (nt == 8) return launch_gemm_nt<8, false>(c, P, grid, smem);
+  if (nt == 4) return launch_gemm_nt<4, false>(c, P, grid, smem);
+  return launch_gemm_nt<2, false>(c, P, grid, smem);
+}
+
 static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
   ARG_CHECK(call.nseg >= 1 && call.nseg <= 3, "1..3 matrices per launch");
   const int act = kind_act(call.seg[0].kind);
@@ -156,6 +206,9 @@ static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
     return launch(c, gemv_float_kernel, dim3(grid), dim3(256), 0, P);
   }
   ARG_CHECK(((uintptr_t)call.x % (P.x_image ? 16 : 4)) == 0, "activation blocks are misaligned");
+
+  // Prompt chunks of K-quant matrices go to the tensor-core kernel.
+  if (act == ACT_Q8_K && call.m >= 8 && call.m <= (size_t)GEMM_MAX_M) return launch_gemm(c, call);
 
   const int mult = call.pair ? 2 : 1;
   int grid = c->n_sm;

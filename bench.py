@@ -137,10 +137,15 @@ def run_reference(args, rank: int, world: int):
     pkg = graft.import_package()
     spec = pkg.model.tinyllama()
     cores = os.cpu_count() or 1
-    threads = min(cores, 8)  # the reference's default (crates/aot-kernels/src/app.rs:214-216)
     steps = max(1, min(args.steps, 64))
     warmup = max(1, min(args.warmup, 4))
-    tps, dt = cpu_decode(spec, steps, warmup, threads)
+    # The reference defaults to min(cores, 8) threads (crates/aot-kernels/src/app.rs:214-216)
+    # and takes --threads; both settings are timed and the faster one is the line's value.
+    tried = {}
+    for threads in sorted({min(cores, 8), cores}):
+        tried[threads] = cpu_decode(spec, steps, warmup, threads)[0]
+    threads = max(tried, key=tried.get)
+    tps = tried[threads]
     cfg = workload_config(spec)
     sample = f"{steps} decode steps after the {PROMPT_LEN}-token prompt and {warmup} warm-up tokens"
     print(json.dumps({
@@ -149,7 +154,7 @@ def run_reference(args, rank: int, world: int):
         "dtype": "int8 block dot products with f32 accumulation (Q8 activations x Q4_K/Q6_K weights)",
         "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
-                         "host_cores": cores,
+                         "host_cores": cores, "tok_s_by_threads": {str(k): v for k, v in tried.items()},
                          "note": "C++ restatement of the reference's AVX2 kernel table and forward pass (oracle/); the Rust reference cannot be built here"},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -222,11 +227,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
-        threads = min(cores, 8)
         cpu_steps = 24
-        cpu_tps, cpu_dt = cpu_decode(spec, cpu_steps, 2, threads)
+        tried = {}
+        for threads in sorted({min(cores, 8), cores}):
+            tried[threads] = cpu_decode(spec, cpu_steps, 2, threads)
+        threads = max(tried, key=lambda k: tried[k][0])
+        cpu_tps, cpu_dt = tried[threads]
         cpu = {"value": cpu_tps, "unit": UNIT, "cores": threads, "kind": "port", "host_cores": cores,
-               "sample": f"{cpu_steps} decode steps of the same model after the prompt and 2 warm-up tokens ({cpu_dt:.1f} s)"}
+               "tok_s_by_threads": {str(k): v[0] for k, v in tried.items()},
+               "sample": f"{cpu_steps} decode steps of the same model after the prompt and 2 warm-up tokens ({cpu_dt:.1f} s), best of the reference's default thread count and all host threads"}
 
     out = {
         "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,

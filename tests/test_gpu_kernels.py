@@ -138,6 +138,26 @@ def test_matmul_bit_exact(pkg, ob, ctx, kind):
         assert_bits_equal(ctx.host_matmul(kind, w, xs, m, rows, cols), want, "host-buffer path")
 
 
+# Prompt chunks of 8..64 tokens on K-quant matrices run on int8 tensor-core tiles; results
+# must still equal the per-token products bit for bit (crates/aot-kernels/tests/dots.rs:205-266).
+@pytest.mark.parametrize("kind", [Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("rows,cols", [(37, 512), (160, 2048), (48, 5632)])
+def test_matmul_tensor_core_tiles_bit_exact(pkg, ob, ctx, kind, rows, cols):
+    pool, tab = ob.Pool(4), ob.detect_table()
+    w = make_weights(pkg, kind, rows, cols, 77 + kind)
+    dw = ctx.to_device(w)
+    for m in (8, 13, 16, 40, 64):
+        xs = _x(m * cols, 100 + m, 1.0)
+        q = ob.quantize_act(kind, xs)
+        want = ob.matmul(pool, tab, kind, w, q, m, rows, cols)
+        dout = ctx.alloc(m * rows * 4)
+        ctx.matmul(kind, dout, dw, ctx.to_device(q.view(np.uint8)), m, rows, cols)
+        got = dout.download(np.float32, m * rows).reshape(m, rows)
+        assert_bits_equal(got, want, f"matmul kind {kind} {rows}x{cols} m {m} (reference-layout blocks)")
+        assert_bits_equal(ctx.host_matmul(kind, w, xs, m, rows, cols), want, f"kind {kind} m {m} host-buffer path")
+    ctx.device_status()
+
+
 def test_matmul_large_tile_loop(pkg, ob, ctx):
     rows, cols, m = 1200, 2048, 5
     w = make_weights(pkg, Q4_K, rows, cols, 5)

@@ -165,3 +165,28 @@ def test_one_kernel_decode_step_bit_exact(pkg, ob, ctx, arch):
     assert ids.tolist() == want
     assert_bits_equal(g.logits(), om.logits(), "logits after the greedy run")
     ctx.device_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("arch", ["llama", "qwen3"])
+def test_prompt_chunks_on_tensor_core_tiles_bit_exact(pkg, ob, ctx, arch):
+    """Prompt chunks of 8..64 tokens (q/k/v, gate/up pair, accumulate epilogues on the
+    tensor-core kernel) against the oracle, then decode from the cache they left."""
+    spec = pkg.model.tiny(arch, n_layer=2, kinds=_kquant_kinds, dim=512, hidden=768, vocab=600)
+    n_ctx = 160
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 64)
+    om = ob.model_from_spec(spec, n_ctx, 64, n_threads=4)
+    rng = np.random.default_rng(11)
+    pos = 0
+    for n in (64, 21, 8, 40):
+        toks = rng.integers(0, 600, n).tolist()
+        g.forward_batch(toks, pos, True)
+        om.forward_batch(toks, pos, True)
+        assert_bits_equal(g.logits(), om.logits(), f"{arch} logits after a chunk of {n} at {pos}")
+        pos += n
+    for t in (3, 9):
+        g.forward(t, pos, True)
+        om.forward(t, pos, True)
+        assert_bits_equal(g.logits(), om.logits(), f"{arch} decode at {pos} after the prompt chunks")
+        pos += 1
+    ctx.device_status()
