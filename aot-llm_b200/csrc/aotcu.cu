@@ -114,14 +114,14 @@ static int check_weight_alignment(int kind, const void* w) {
 // m = 8..64 activation rows against K-quant matrices: int8 tensor-core tiles (gemm.cuh).
 // Arguments were checked by launch_gemv.
 template <int NT, bool PAIR>
-static int launch_gemm_nt(aotcu_ctx* c, const GemmParams& P, int grid, size_t smem) {
+static int launch_gemm_nt(aotcu_ctx* c, const GemmParams& P, int grid, int warps, size_t smem) {
   static bool attr_set[64] = {};
   int dev = c->device;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     CU_TRY(cudaFuncSetAttribute(gemm_q8k_mma_kernel<NT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
     attr_set[dev] = true;
   }
-  return launch(c, gemm_q8k_mma_kernel<NT, PAIR>, dim3(grid), dim3(GEMM_WARPS * 32), smem, P);
+  return launch(c, gemm_q8k_mma_kernel<NT, PAIR>, dim3(grid), dim3(warps * 32), smem, P);
 }
 
 static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
@@ -137,27 +137,31 @@ static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
   P.pair = call.pair;
   P.cols = (int)call.cols;
   P.m = (int)call.m;
-  P.m_pad = (P.m + 7) & ~7;
   P.epilogue = call.epilogue;
   P.x = reinterpret_cast<const uint8_t*>(call.x);
   P.x_image = call.x_mode == 1;
-  // Token groups per warp: all of them when there are plenty of row tiles, fewer to put
-  // more warps to work on a small matrix.
-  const int groups8 = P.m_pad / 8;
-  int nt = 8;
-  while (nt > 2 && (size_t)tiles * ((groups8 + nt - 1) / nt) < (size_t)c->n_sm * GEMM_WARPS / 2) nt >>= 1;
-  if (call.pair && nt > 4) nt = 4;  // two matrices' accumulators per thread
+  P.n_tiles = tiles;
+  // Token groups per warp: all of them when there are plenty of row tiles, fewer (more,
+  // smaller work items) on a small matrix. A CTA's warps share one token group, so a CTA
+  // stages only that group's activation images.
+  const int groups8 = (P.m + 7) / 8;
+  int nt = call.pair ? 2 : 8;  // pair mode keeps two matrices' accumulators per thread
+  while (nt > 2 && (size_t)tiles * ((groups8 + nt - 1) / nt) < (size_t)c->n_sm * 8) nt >>= 1;
   P.n_groups = (groups8 + nt - 1) / nt;
-  P.m_pad = P.n_groups * nt * 8;  // every token slot a warp touches exists in the staged chunk
-  P.n_items = tiles * P.n_groups;
-  int grid = (P.n_items + GEMM_WARPS - 1) / GEMM_WARPS;
-  if (grid > c->n_sm * 2) grid = c->n_sm * 2;
-  const size_t smem = (size_t)2 * GEMM_KB * P.m_pad * XK_STRIDE;
+  int warps = GEMM_WARPS;
+  while (warps > 2 && (size_t)tiles * P.n_groups < (size_t)c->n_sm * warps) warps >>= 1;
+  int ctas_per_group = (tiles + warps - 1) / warps;
+  const int cap = (c->n_sm * 2) / P.n_groups;
+  if (ctas_per_group > cap) ctas_per_group = cap < 1 ? 1 : cap;
+  const int grid = ctas_per_group * P.n_groups;
+  const int nb = (int)(call.cols / 256);
+  P.kb = nb < 4 ? nb : 4;
+  const size_t smem = (size_t)2 * P.kb * 8 * nt * XK_STRIDE;
   ARG_CHECK(smem <= c->max_smem, "activation chunk does not fit in shared memory");
-  if (call.pair) return nt == 4 ? launch_gemm_nt<4, true>(c, P, grid, smem) : launch_gemm_nt<2, true>(c, P, grid, smem);
-  if (nt == 8) return launch_gemm_nt<8, false>(c, P, grid, smem);
-  if (nt == 4) return launch_gemm_nt<4, false>(c, P, grid, smem);
-  return launch_gemm_nt<2, false>(c, P, grid, smem);
+  if (call.pair) return nt == 4 ? launch_gemm_nt<4, true>(c, P, grid, warps, smem) : launch_gemm_nt<2, true>(c, P, grid, warps, smem);
+  if (nt == 8) return launch_gemm_nt<8, false>(c, P, grid, warps, smem);
+  if (nt == 4) return launch_gemm_nt<4, false>(c, P, grid, warps, smem);
+  return launch_gemm_nt<2, false>(c, P, grid, warps, smem);
 }
 
 static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
@@ -509,6 +513,15 @@ static int gpu_qk_post(aotcu_gpu* g, size_t li, const int* pos_ptr, size_t pos0,
   return launch(g->c, qk_post_kernel, dim3(d.n_head + d.n_kv_head, (unsigned)m), dim3(128), 0, P);
 }
 
+// Shared memory of the attention kernel with the scores of rows up to `max_len` positions
+// kept on chip, and what a CTA may use.
+static size_t attn_smem_budget(const aotcu_ctx* c) { return c->max_smem - sizeof(SeqSumScratch) * 8 - 1024; }
+static size_t attn_smem_bytes(int n_head, int n_kv_head, int head_dim, size_t max_len) {
+  const int gqa = n_head / n_kv_head, hpc = gqa < 8 ? gqa : 8;
+  max_len = (max_len + 3) & ~(size_t)3;
+  return ((size_t)hpc * head_dim + (size_t)ATTN_CHUNK * (head_dim + 4) + (size_t)hpc * max_len) * sizeof(float);
+}
+
 static int launch_attention(aotcu_ctx* c, float* out, const float* q, const float* kc, const float* vc, float* scratch,
                             const int* pos_ptr, size_t pos0, size_t m, int n_head, int n_kv_head, int head_dim,
                             size_t n_ctx, size_t window, int smem_scores) {
@@ -523,12 +536,28 @@ static int launch_attention(aotcu_ctx* c, float* out, const float* q, const floa
   P.n_head = n_head;
   P.n_kv_head = n_kv_head;
   P.head_dim = head_dim;
-  P.ctx = (int)n_ctx;
+  P.ctx = (int)((n_ctx + 3) & ~(size_t)3);  // row stride of the score scratch, 16-byte aligned rows
   P.window = (int)window;
-  P.smem_scores = smem_scores;
   P.scale = 1.0f / sqrtf((float)head_dim);
-  size_t smem = ((size_t)head_dim + (size_t)smem_scores + 4) * sizeof(float);
-  return launch(c, attention_kernel, dim3(n_head, (unsigned)m), dim3(256), smem, P);
+  ARG_CHECK(head_dim % 4 == 0 && head_dim <= 256, "head_dim must be a multiple of 4, at most 256");
+  const int gqa = n_head / n_kv_head;
+  P.heads_per_cta = gqa < 8 ? gqa : 8;
+  const int splits = (gqa + P.heads_per_cta - 1) / P.heads_per_cta;
+  // Scores in shared memory when the longest row of this call fits, else in `scratch`.
+  size_t max_len = pos_ptr ? n_ctx : std::min(n_ctx, pos0 + m);
+  max_len = (max_len + 3) & ~(size_t)3;
+  const size_t fixed = ((size_t)P.heads_per_cta * head_dim + (size_t)ATTN_CHUNK * (head_dim + 4)) * sizeof(float);
+  const size_t with_scores = fixed + (size_t)P.heads_per_cta * max_len * sizeof(float);
+  const size_t budget = attn_smem_budget(c);
+  size_t smem = fixed;
+  if (smem_scores && with_scores <= budget) {
+    P.smem_scores = (int)max_len;
+    smem = with_scores;
+  } else {
+    ARG_CHECK(scratch, "attention needs a score scratch buffer for this context length");
+    P.smem_scores = 0;
+  }
+  return launch(c, attention_kernel, dim3((unsigned)(n_kv_head * splits), (unsigned)m), dim3(ATTN_THREADS), smem, P);
 }
 
 static int gpu_attention(aotcu_gpu* g, float* out, const float* q, size_t li, const int* pos_ptr, size_t pos0, size_t m,
@@ -838,8 +867,10 @@ int aotcu_init(int device, aotcu_ctx** out) {
   CU_TRY(cudaMemset(c->d_err, 0, sizeof(int)));
   CU_TRY(cudaFuncSetAttribute(gemv_q8k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
   CU_TRY(cudaFuncSetAttribute(gemv_q80_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
-  CU_TRY(cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
-  CU_TRY(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  // These two also hold the exact-sum scratch in static shared memory.
+  CU_TRY(cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)(c->max_smem - sizeof(SeqSumScratch) - 1024)));
+  CU_TRY(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_budget(c)));
   *out = c;
   return 0;
 }
@@ -1081,8 +1112,8 @@ int aotcu_attention(aotcu_ctx* c, float* out, const float* q, const float* k_cac
   ARG_CHECK(head_dim % 4 == 0 && head_dim <= 256, "head_dim %zu must be a multiple of 4, at most 256", head_dim);
   ARG_CHECK(pos0 + m <= ctx_len, "positions exceed the context");
   if (m == 0) return 0;
-  size_t cap = (c->max_smem / sizeof(float)) - head_dim - 64;
-  ARG_CHECK(ctx_len <= cap, "context %zu too long for the stand-alone attention entry point (max %zu)", ctx_len, cap);
+  ARG_CHECK(attn_smem_bytes((int)n_head, (int)n_kv_head, (int)head_dim, pos0 + m) <= attn_smem_budget(c),
+            "%zu positions are too many for the stand-alone attention entry point (scores are kept in shared memory)", pos0 + m);
   return launch_attention(c, out, q, k_cache, v_cache, nullptr, nullptr, pos0, m, (int)n_head, (int)n_kv_head,
                           (int)head_dim, ctx_len, window, (int)ctx_len);
 }
@@ -1218,12 +1249,11 @@ int aotcu_gpu_new(aotcu_ctx* c, const aotcu_model_head* head, const aotcu_layer*
   }
   // Attention scores: shared memory when the context fits, else a global scratch.
   {
-    size_t cap = c->max_smem / sizeof(float) - d.head_dim - 64;
-    if (n_ctx <= cap && n_ctx <= 32768) {
+    if (attn_smem_bytes(d.n_head, d.n_kv_head, d.head_dim, n_ctx) <= attn_smem_budget(c)) {
       g->smem_scores = (int)n_ctx;
     } else {
       g->smem_scores = 0;
-      G_TRY(cudaMalloc(&g->attn_scratch, g->max_batch * d.n_head * n_ctx * sizeof(float)));
+      G_TRY(cudaMalloc(&g->attn_scratch, g->max_batch * d.n_head * ((n_ctx + 3) & ~(size_t)3) * sizeof(float)));
     }
   }
   g->history_cap = n_ctx;

@@ -24,7 +24,7 @@
 namespace aot {
 
 constexpr int GEMM_WARPS = 8;   // warps per CTA
-constexpr int GEMM_KB = 2;      // super-blocks per staged activation chunk
+constexpr int GEMM_MAX_KB = 8;  // super-blocks per staged activation chunk, at most
 constexpr int GEMM_MAX_M = 64;
 
 struct GemmParams {
@@ -32,9 +32,9 @@ struct GemmParams {
   int nseg, pair, cols, m, epilogue;
   const uint8_t* x;   // [m][cols/256] Q8_K images (304 bytes) or reference-layout BlockQ8_K (292 bytes)
   int x_image;
-  int m_pad;          // token slots staged per chunk: n_groups * NT * 8 (>= m)
-  int n_groups;       // token groups of 8*NT per tile
-  int n_items;        // (row tile, token group) pairs
+  int n_groups;       // token groups of 8*NT tokens; CTA c works on group c % n_groups
+  int n_tiles;        // 16-row tiles over all matrices (pair mode: of one matrix)
+  int kb;             // super-blocks per staged activation chunk
   int tiles_before[4];  // first tile index of each matrix (pair mode: one list for both)
 };
 
@@ -81,28 +81,61 @@ __device__ __forceinline__ uint32_t ldg32_a2(const uint8_t* p) {
   return (uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16);
 }
 
-// One 16-row tile of one matrix against NT token groups: adds, per super-block and in
-// block order, the f32 terms into acc[t][i] (i: 0 = row g / token 2q, 1 = row g / token
-// 2q+1, 2 = row g+8 / token 2q, 3 = row g+8 / token 2q+1; g = lane/4, q = lane%4).
-// `xs` is the shared-space address of the chunk buffer, layout [kb][token][304].
+// The words of one super-block that a thread needs for its two rows (row g and row g+8 of
+// the tile; g = lane/4, q = lane%4), fetched one block ahead of their use.
+//   Q4_K / Q5_K: [0..3] d|dmin + packed scales, [4..11] nibble words (pair c: 4+2c low-k,
+//                5+2c high-k), [12..13] fifth-bit words (Q5_K)
+//   Q6_K:        [0..3] low nibbles l, [4..7] low nibbles l+32, [8..11] high bits
+//                (index 2n+hh), [12..15] scales, [16] d
+struct WFrag {
+  uint32_t w[2][17];
+};
+
+__device__ __forceinline__ void gemm_load_frag(int kind, const uint8_t* wa, const uint8_t* wb, WFrag& f) {
+  const int q = threadIdx.x & 3;
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    const uint8_t* p = r ? wb : wa;
+    if (kind == Q6_K) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {  // i = 2n + hh
+        const int lo = 64 * (i >> 1) + 16 * (i & 1) + 4 * q;
+        f.w[r][i] = ldg32_a2(p + lo);
+        f.w[r][4 + i] = ldg32_a2(p + lo + 32);
+        f.w[r][8 + i] = ldg32_a2(p + 128 + 32 * (i >> 1) + 16 * (i & 1) + 4 * q);
+        f.w[r][12 + i] = ldg32_a2(p + 192 + 4 * i);
+      }
+      f.w[r][16] = ldg32_a2(p + 206) >> 16;
+    } else {
+      const uint4 h = __ldg(reinterpret_cast<const uint4*>(p));
+      f.w[r][0] = h.x; f.w[r][1] = h.y; f.w[r][2] = h.z; f.w[r][3] = h.w;
+      const int qoff = kind == Q5_K ? 48 : 16;
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        f.w[r][4 + 2 * c] = __ldg(reinterpret_cast<const uint32_t*>(p + qoff + 32 * c) + q);
+        f.w[r][5 + 2 * c] = __ldg(reinterpret_cast<const uint32_t*>(p + qoff + 32 * c + 16) + q);
+      }
+      if (kind == Q5_K) {
+        f.w[r][12] = __ldg(reinterpret_cast<const uint32_t*>(p + 16) + q);
+        f.w[r][13] = __ldg(reinterpret_cast<const uint32_t*>(p + 32) + q);
+      }
+    }
+  }
+}
+
+// One 16-row tile of one matrix against NT token groups: adds the f32 term of one
+// super-block into acc.v[t][i] (i: 0 = row g / token 2q, 1 = row g / token 2q+1, 2 = row
+// g+8 / token 2q, 3 = row g+8 / token 2q+1). Called in block order.
+// `xs` is the shared-space address of the block's images, layout [token][304].
 template <int NT>
 struct TileAcc {
   float v[NT][4];
 };
 
 template <int NT, bool Q5>
-__device__ __forceinline__ void gemm_block_k4(const uint8_t* wa, const uint8_t* wb, uint32_t xs, int tok0, TileAcc<NT>& acc) {
+__device__ __forceinline__ void gemm_block_k4(const WFrag& f, uint32_t xs, int tok0, TileAcc<NT>& acc) {
   const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-  const uint4 ha = __ldg(reinterpret_cast<const uint4*>(wa)), hb = __ldg(reinterpret_cast<const uint4*>(wb));
-  const K4Scales sa = k4_unpack(ha.y, ha.z, ha.w), sb = k4_unpack(hb.y, hb.z, hb.w);
-  constexpr int QOFF = Q5 ? 48 : 16;
-  uint32_t hqa0 = 0, hqa1 = 0, hqb0 = 0, hqb1 = 0;
-  if (Q5) {
-    hqa0 = __ldg(reinterpret_cast<const uint32_t*>(wa + 16) + q);
-    hqa1 = __ldg(reinterpret_cast<const uint32_t*>(wa + 32) + q);
-    hqb0 = __ldg(reinterpret_cast<const uint32_t*>(wb + 16) + q);
-    hqb1 = __ldg(reinterpret_cast<const uint32_t*>(wb + 32) + q);
-  }
+  const K4Scales sa = k4_unpack(f.w[0][1], f.w[0][2], f.w[0][3]), sb = k4_unpack(f.w[1][1], f.w[1][2], f.w[1][3]);
   int sumi[NT][4];
 #pragma unroll
   for (int t = 0; t < NT; t++) {
@@ -111,20 +144,17 @@ __device__ __forceinline__ void gemm_block_k4(const uint8_t* wa, const uint8_t* 
   }
 #pragma unroll
   for (int c = 0; c < 4; c++) {
-    const uint32_t qa0 = __ldg(reinterpret_cast<const uint32_t*>(wa + QOFF + 32 * c) + q);
-    const uint32_t qa1 = __ldg(reinterpret_cast<const uint32_t*>(wa + QOFF + 32 * c + 16) + q);
-    const uint32_t qb0 = __ldg(reinterpret_cast<const uint32_t*>(wb + QOFF + 32 * c) + q);
-    const uint32_t qb1 = __ldg(reinterpret_cast<const uint32_t*>(wb + QOFF + 32 * c + 16) + q);
+    const uint32_t qa0 = f.w[0][4 + 2 * c], qa1 = f.w[0][5 + 2 * c], qb0 = f.w[1][4 + 2 * c], qb1 = f.w[1][5 + 2 * c];
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
       const int j = 2 * c + hi;  // sub-block
       uint32_t a0 = (hi ? qa0 >> 4 : qa0) & 0x0F0F0F0Fu, a2 = (hi ? qa1 >> 4 : qa1) & 0x0F0F0F0Fu;
       uint32_t a1 = (hi ? qb0 >> 4 : qb0) & 0x0F0F0F0Fu, a3 = (hi ? qb1 >> 4 : qb1) & 0x0F0F0F0Fu;
       if (Q5) {
-        a0 |= ((hqa0 >> j) & 0x01010101u) << 4;
-        a2 |= ((hqa1 >> j) & 0x01010101u) << 4;
-        a1 |= ((hqb0 >> j) & 0x01010101u) << 4;
-        a3 |= ((hqb1 >> j) & 0x01010101u) << 4;
+        a0 |= ((f.w[0][12] >> j) & 0x01010101u) << 4;
+        a2 |= ((f.w[0][13] >> j) & 0x01010101u) << 4;
+        a1 |= ((f.w[1][12] >> j) & 0x01010101u) << 4;
+        a3 |= ((f.w[1][13] >> j) & 0x01010101u) << 4;
       }
       const int sca = byte_of(j < 4 ? sa.sc_lo : sa.sc_hi, j & 3), scb = byte_of(j < 4 ? sb.sc_lo : sb.sc_hi, j & 3);
 #pragma unroll
@@ -144,8 +174,8 @@ __device__ __forceinline__ void gemm_block_k4(const uint8_t* wa, const uint8_t* 
   const uint32_t ma45 = __byte_perm(sa.m_hi, 0, 0x1100), ma67 = __byte_perm(sa.m_hi, 0, 0x3322);
   const uint32_t mb01 = __byte_perm(sb.m_lo, 0, 0x1100), mb23 = __byte_perm(sb.m_lo, 0, 0x3322);
   const uint32_t mb45 = __byte_perm(sb.m_hi, 0, 0x1100), mb67 = __byte_perm(sb.m_hi, 0, 0x3322);
-  const float da = half_bits_to_float((uint16_t)(ha.x & 0xFFFFu)), dmina = half_bits_to_float((uint16_t)(ha.x >> 16));
-  const float db = half_bits_to_float((uint16_t)(hb.x & 0xFFFFu)), dminb = half_bits_to_float((uint16_t)(hb.x >> 16));
+  const float da = half_bits_to_float((uint16_t)(f.w[0][0] & 0xFFFFu)), dmina = half_bits_to_float((uint16_t)(f.w[0][0] >> 16));
+  const float db = half_bits_to_float((uint16_t)(f.w[1][0] & 0xFFFFu)), dminb = half_bits_to_float((uint16_t)(f.w[1][0] >> 16));
 #pragma unroll
   for (int t = 0; t < NT; t++) {
 #pragma unroll
@@ -171,7 +201,7 @@ __device__ __forceinline__ void gemm_block_k4(const uint8_t* wa, const uint8_t* 
 // Q6_K: sixteen 16-weight sub-blocks with signed 8-bit scales. Weights are used as
 // 0..63 and the -32 offset goes through the activation sums (see blockmath.cuh).
 template <int NT>
-__device__ __forceinline__ void gemm_block_q6k(const uint8_t* wa, const uint8_t* wb, uint32_t xs, int tok0, TileAcc<NT>& acc) {
+__device__ __forceinline__ void gemm_block_q6k(const WFrag& f, uint32_t xs, int tok0, TileAcc<NT>& acc) {
   const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   int sumi[NT][4];
 #pragma unroll
@@ -179,26 +209,20 @@ __device__ __forceinline__ void gemm_block_q6k(const uint8_t* wa, const uint8_t*
 #pragma unroll
     for (int i = 0; i < 4; i++) sumi[t][i] = 0;
   }
-  uint32_t sca[4], scb[4];  // scales, four per word
-#pragma unroll
-  for (int k = 0; k < 4; k++) {
-    sca[k] = ldg32_a2(wa + 192 + 4 * k);
-    scb[k] = ldg32_a2(wb + 192 + 4 * k);
-  }
 #pragma unroll
   for (int n = 0; n < 2; n++) {
 #pragma unroll
     for (int hh = 0; hh < 2; hh++) {
-      const int lo = 64 * n + 16 * hh + 4 * q, ho = 128 + 32 * n + 16 * hh + 4 * q;
-      const uint32_t la0 = ldg32_a2(wa + lo), la32 = ldg32_a2(wa + lo + 32), hqa = ldg32_a2(wa + ho);
-      const uint32_t lb0 = ldg32_a2(wb + lo), lb32 = ldg32_a2(wb + lo + 32), hqb = ldg32_a2(wb + ho);
+      const int i4 = 2 * n + hh;
+      const uint32_t la0 = f.w[0][i4], la32 = f.w[0][4 + i4], hqa = f.w[0][8 + i4];
+      const uint32_t lb0 = f.w[1][i4], lb32 = f.w[1][4 + i4], hqb = f.w[1][8 + i4];
 #pragma unroll
       for (int qu = 0; qu < 4; qu++) {  // quarter of the 128-weight half
         const uint32_t la = (qu & 1) ? la32 : la0, lb = (qu & 1) ? lb32 : lb0;
-        const uint32_t a0 = ((qu & 2) ? la >> 4 : la) & 0x0F0F0F0Fu | (((hqa >> (2 * qu)) & 0x03030303u) << 4);
-        const uint32_t a1 = ((qu & 2) ? lb >> 4 : lb) & 0x0F0F0F0Fu | (((hqb >> (2 * qu)) & 0x03030303u) << 4);
+        const uint32_t a0 = (((qu & 2) ? la >> 4 : la) & 0x0F0F0F0Fu) | (((hqa >> (2 * qu)) & 0x03030303u) << 4);
+        const uint32_t a1 = (((qu & 2) ? lb >> 4 : lb) & 0x0F0F0F0Fu) | (((hqb >> (2 * qu)) & 0x03030303u) << 4);
         const int s = 8 * n + hh + 2 * qu;  // sub-block
-        const int ca = (int)(int8_t)byte_of(sca[s >> 2], s & 3), cb = (int)(int8_t)byte_of(scb[s >> 2], s & 3);
+        const int ca = (int)(int8_t)byte_of(f.w[0][12 + (s >> 2)], s & 3), cb = (int)(int8_t)byte_of(f.w[1][12 + (s >> 2)], s & 3);
         const int yoff = 128 * n + 32 * qu + 16 * hh + 4 * q;
 #pragma unroll
         for (int t = 0; t < NT; t++) {
@@ -213,8 +237,7 @@ __device__ __forceinline__ void gemm_block_q6k(const uint8_t* wa, const uint8_t*
       }
     }
   }
-  const float da = half_bits_to_float((uint16_t)(ldg32_a2(wa + 208 - 2) >> 16));
-  const float db = half_bits_to_float((uint16_t)(ldg32_a2(wb + 208 - 2) >> 16));
+  const float da = half_bits_to_float((uint16_t)f.w[0][16]), db = half_bits_to_float((uint16_t)f.w[1][16]);
 #pragma unroll
   for (int t = 0; t < NT; t++) {
 #pragma unroll
@@ -222,14 +245,14 @@ __device__ __forceinline__ void gemm_block_q6k(const uint8_t* wa, const uint8_t*
       const uint32_t xt = xs + (uint32_t)(tok0 + 8 * t + 2 * q + e) * XK_STRIDE;
       const U4 b0 = gm_lds128(xt + XK_BSUMS), b1 = gm_lds128(xt + XK_BSUMS + 16);
       int ba = 0, bb = 0;
-      ba = dp2a_lo(b0.x, sca[0], ba); ba = dp2a_hi(b0.y, sca[0], ba);
-      ba = dp2a_lo(b0.z, sca[1], ba); ba = dp2a_hi(b0.w, sca[1], ba);
-      ba = dp2a_lo(b1.x, sca[2], ba); ba = dp2a_hi(b1.y, sca[2], ba);
-      ba = dp2a_lo(b1.z, sca[3], ba); ba = dp2a_hi(b1.w, sca[3], ba);
-      bb = dp2a_lo(b0.x, scb[0], bb); bb = dp2a_hi(b0.y, scb[0], bb);
-      bb = dp2a_lo(b0.z, scb[1], bb); bb = dp2a_hi(b0.w, scb[1], bb);
-      bb = dp2a_lo(b1.x, scb[2], bb); bb = dp2a_hi(b1.y, scb[2], bb);
-      bb = dp2a_lo(b1.z, scb[3], bb); bb = dp2a_hi(b1.w, scb[3], bb);
+      ba = dp2a_lo(b0.x, f.w[0][12], ba); ba = dp2a_hi(b0.y, f.w[0][12], ba);
+      ba = dp2a_lo(b0.z, f.w[0][13], ba); ba = dp2a_hi(b0.w, f.w[0][13], ba);
+      ba = dp2a_lo(b1.x, f.w[0][14], ba); ba = dp2a_hi(b1.y, f.w[0][14], ba);
+      ba = dp2a_lo(b1.z, f.w[0][15], ba); ba = dp2a_hi(b1.w, f.w[0][15], ba);
+      bb = dp2a_lo(b0.x, f.w[1][12], bb); bb = dp2a_hi(b0.y, f.w[1][12], bb);
+      bb = dp2a_lo(b0.z, f.w[1][13], bb); bb = dp2a_hi(b0.w, f.w[1][13], bb);
+      bb = dp2a_lo(b1.x, f.w[1][14], bb); bb = dp2a_hi(b1.y, f.w[1][14], bb);
+      bb = dp2a_lo(b1.z, f.w[1][15], bb); bb = dp2a_hi(b1.w, f.w[1][15], bb);
       const float dx = __uint_as_float(gm_lds32(xt + XK_D));
       acc.v[t][e] = fadd(acc.v[t][e], q6k_term(da, dx, sumi[t][e] - 32 * ba));
       acc.v[t][2 + e] = fadd(acc.v[t][2 + e], q6k_term(db, dx, sumi[t][2 + e] - 32 * bb));
@@ -238,35 +261,35 @@ __device__ __forceinline__ void gemm_block_q6k(const uint8_t* wa, const uint8_t*
 }
 
 template <int NT>
-__device__ __forceinline__ void gemm_block(int kind, const uint8_t* wa, const uint8_t* wb, uint32_t xs, int tok0,
-                                           TileAcc<NT>& acc) {
-  if (kind == Q4_K) gemm_block_k4<NT, false>(wa, wb, xs, tok0, acc);
-  else if (kind == Q6_K) gemm_block_q6k<NT>(wa, wb, xs, tok0, acc);
-  else gemm_block_k4<NT, true>(wa, wb, xs, tok0, acc);
+__device__ __forceinline__ void gemm_block(int kind, const WFrag& f, uint32_t xs, int tok0, TileAcc<NT>& acc) {
+  if (kind == Q4_K) gemm_block_k4<NT, false>(f, xs, tok0, acc);
+  else if (kind == Q6_K) gemm_block_q6k<NT>(f, xs, tok0, acc);
+  else gemm_block_k4<NT, true>(f, xs, tok0, acc);
 }
 
-// Stage the activation images of super-blocks [b0, b0 + kb_n) for all m_pad tokens into
-// `dst` ([kb][token][304]); rows beyond m repeat the last token (their results are dropped).
-__device__ __forceinline__ void gemm_stage_x(uint32_t dst, const uint8_t* x, int x_image, int nb, int b0, int kb_n, int m,
-                                             int m_pad) {
+// Stage the activation images of super-blocks [b0, b0 + kb_n) for tokens [t0, t0 + nt8) into
+// `dst` ([kb][slot][304]); slots beyond token m-1 repeat the last token (their results are
+// dropped).
+__device__ __forceinline__ void gemm_stage_x(uint32_t dst, const uint8_t* x, int x_image, int nb, int b0, int kb_n, int t0,
+                                             int nt8, int m) {
   if (x_image) {
-    const int pieces = kb_n * m_pad * (XK_STRIDE / 16);
+    const int pieces = kb_n * nt8 * (XK_STRIDE / 16);
     for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
-      const int kb = i / (m_pad * (XK_STRIDE / 16)), r = i - kb * (m_pad * (XK_STRIDE / 16));
-      const int tok = r / (XK_STRIDE / 16), p = r - tok * (XK_STRIDE / 16);
-      const int ts = tok < m ? tok : m - 1;
-      cp_async16(dst + (uint32_t)((kb * m_pad + tok) * XK_STRIDE + 16 * p),
+      const int kb = i / (nt8 * (XK_STRIDE / 16)), r = i - kb * (nt8 * (XK_STRIDE / 16));
+      const int slot = r / (XK_STRIDE / 16), p = r - slot * (XK_STRIDE / 16);
+      const int ts = min(t0 + slot, m - 1);
+      cp_async16(dst + (uint32_t)((kb * nt8 + slot) * XK_STRIDE + 16 * p),
                  x + ((size_t)ts * nb + (size_t)(b0 + kb)) * XK_STRIDE + 16 * p);
     }
   } else {
     // BlockQ8_K {f32 d; i8 qs[256]; i16 bsums[16]} (quant.rs:8-14), word by word into the image layout
-    const int pieces = kb_n * m_pad * 73;
+    const int pieces = kb_n * nt8 * 73;
     for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
-      const int kb = i / (m_pad * 73), r = i - kb * (m_pad * 73);
-      const int tok = r / 73, w = r - tok * 73;
-      const int ts = tok < m ? tok : m - 1;
+      const int kb = i / (nt8 * 73), r = i - kb * (nt8 * 73);
+      const int slot = r / 73, w = r - slot * 73;
+      const int ts = min(t0 + slot, m - 1);
       const int off = w == 0 ? XK_D : (w <= 64 ? (w - 1) * 4 : XK_BSUMS + (w - 65) * 4);
-      cp_async4(dst + (uint32_t)((kb * m_pad + tok) * XK_STRIDE + off), x + ((size_t)ts * nb + (size_t)(b0 + kb)) * 292 + 4 * w);
+      cp_async4(dst + (uint32_t)((kb * nt8 + slot) * XK_STRIDE + off), x + ((size_t)ts * nb + (size_t)(b0 + kb)) * 292 + 4 * w);
     }
   }
 }
@@ -275,26 +298,31 @@ template <int NT, bool PAIR>
 __global__ void __launch_bounds__(GEMM_WARPS * 32) gemm_q8k_mma_kernel(const GemmParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int nb = P.cols >> 8;
+  const int n_warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-  const uint32_t buf_bytes = (uint32_t)(GEMM_KB * P.m_pad * XK_STRIDE);
+  constexpr int NT8 = 8 * NT;
+  const uint32_t buf_bytes = (uint32_t)(P.kb * NT8 * XK_STRIDE);
   const uint32_t sbase = smem_addr(smem);
-  const int n_chunks = (nb + GEMM_KB - 1) / GEMM_KB;
-  const int per_round = gridDim.x * GEMM_WARPS;
-  const int n_rounds = (P.n_items + per_round - 1) / per_round;
+  const int n_chunks = (nb + P.kb - 1) / P.kb;
+  // All warps of a CTA work on the same token group, so only its tokens are staged.
+  const int tg = (int)blockIdx.x % P.n_groups, cta_in_group = (int)blockIdx.x / P.n_groups;
+  const int ctas_per_group = (int)gridDim.x / P.n_groups;
+  const int tokg = tg * NT8;  // first token of the group
+  const int per_round = ctas_per_group * n_warps;
+  const int n_rounds = (P.n_tiles + per_round - 1) / per_round;
+  constexpr int n_mat = PAIR ? 2 : 1;
+  constexpr int tok0 = 0;     // token slots inside the staged chunk
   pdl_launch_dependents();
   pdl_wait();
   for (int round = 0; round < n_rounds; round++) {
-    // this warp's (row tile, token group)
-    const int item = (round * (int)gridDim.x + (int)blockIdx.x) * GEMM_WARPS + warp;
-    const bool active = item < P.n_items;
-    const int tile = active ? item / P.n_groups : 0;
-    const int tok0 = active ? (item - tile * P.n_groups) * 8 * NT : 0;
+    const int tile_raw = (round * ctas_per_group + cta_in_group) * n_warps + warp;
+    const bool active = tile_raw < P.n_tiles;
+    const int tile = active ? tile_raw : 0;
     int s = 0;
     if (!PAIR) {
       while (s < P.nseg - 1 && tile >= P.tiles_before[s + 1]) s++;
     }
     const int r0 = (tile - P.tiles_before[s]) * 16;
-    constexpr int n_mat = PAIR ? 2 : 1;
     TileAcc<NT> acc[n_mat];
 #pragma unroll
     for (int mt = 0; mt < n_mat; mt++) {
@@ -317,14 +345,18 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32) gemm_q8k_mma_kernel(const Gem
       wrow[mt][0] = sg.w + (size_t)min(r0 + g, sg.rows - 1) * row_bytes;
       wrow[mt][1] = sg.w + (size_t)min(r0 + g + 8, sg.rows - 1) * row_bytes;
     }
+    // Weights are fetched one (block, matrix) step ahead of their use; the sequence runs
+    // straight through the activation chunks.
+    WFrag cur, nxt;
+    if (active) gemm_load_frag(kind[0], wrow[0][0], wrow[0][1], cur);
     __syncthreads();  // the previous round is done with both chunk buffers
-    gemm_stage_x(sbase, P.x, P.x_image, nb, 0, min(GEMM_KB, nb), P.m, P.m_pad);
+    gemm_stage_x(sbase, P.x, P.x_image, nb, 0, min(P.kb, nb), tokg, NT8, P.m);
     cp_async_commit();
     for (int ch = 0; ch < n_chunks; ch++) {
-      const int b0 = ch * GEMM_KB, kb_n = min(GEMM_KB, nb - b0);
+      const int b0 = ch * P.kb, kb_n = min(P.kb, nb - b0);
       if (ch + 1 < n_chunks) {
-        gemm_stage_x(sbase + ((ch + 1) & 1) * buf_bytes, P.x, P.x_image, nb, b0 + GEMM_KB, min(GEMM_KB, nb - b0 - GEMM_KB), P.m,
-                     P.m_pad);
+        gemm_stage_x(sbase + ((ch + 1) & 1) * buf_bytes, P.x, P.x_image, nb, b0 + P.kb, min(P.kb, nb - b0 - P.kb), tokg, NT8,
+                     P.m);
         cp_async_commit();
         cp_async_wait<1>();
       } else {
@@ -335,11 +367,16 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32) gemm_q8k_mma_kernel(const Gem
         const uint32_t xs = sbase + (ch & 1) * buf_bytes;
         for (int kb = 0; kb < kb_n; kb++) {
           const int b = b0 + kb;
-          const uint32_t xb = xs + (uint32_t)(kb * P.m_pad) * XK_STRIDE;
-          gemm_block<NT>(kind[0], wrow[0][0] + (size_t)b * rbytes[0], wrow[0][1] + (size_t)b * rbytes[0], xb, tok0, acc[0]);
-          if (PAIR)
-            gemm_block<NT>(kind[n_mat - 1], wrow[n_mat - 1][0] + (size_t)b * rbytes[n_mat - 1],
-                           wrow[n_mat - 1][1] + (size_t)b * rbytes[n_mat - 1], xb, tok0, acc[n_mat - 1]);
+          const uint32_t xb = xs + (uint32_t)(kb * NT8) * XK_STRIDE;
+#pragma unroll
+          for (int mt = 0; mt < n_mat; mt++) {
+            // next step: the other matrix of this block, or the first matrix of the next block
+            const int nmt = mt + 1 < n_mat ? mt + 1 : 0, nbk = mt + 1 < n_mat ? b : b + 1;
+            if (nbk < nb)
+              gemm_load_frag(kind[nmt], wrow[nmt][0] + (size_t)nbk * rbytes[nmt], wrow[nmt][1] + (size_t)nbk * rbytes[nmt], nxt);
+            gemm_block<NT>(kind[mt], cur, xb, tok0, acc[mt]);
+            cur = nxt;
+          }
         }
       }
       __syncthreads();  // everyone is done with this buffer before it is refilled
@@ -349,7 +386,7 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32) gemm_q8k_mma_kernel(const Gem
       for (int t = 0; t < NT; t++) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-          const int row = r0 + g + (i >> 1) * 8, tok = tok0 + 8 * t + 2 * q + (i & 1);
+          const int row = r0 + g + (i >> 1) * 8, tok = tokg + 8 * t + 2 * q + (i & 1);
           const GemvSeg& sg = P.seg[PAIR ? 0 : s];
           if (row < sg.rows && tok < P.m) {
             const size_t o = (size_t)tok * sg.rows + row;

@@ -11,6 +11,7 @@
 #include "blockmath.cuh"
 #include "device_utils.cuh"
 #include "expf_exact.cuh"
+#include "groupsum.cuh"
 
 namespace aot {
 
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const RmsnormParams P) {
   extern __shared__ __align__(16) float sm_f[];
   float* row = sm_f;          // n
   float* sq = sm_f + P.n;     // n
-  float* slot = sq + P.n;     // 1
+  __shared__ SeqSumScratch ssc;
   pdl_launch_dependents();
   pdl_wait();
   const float* x = P.x + (size_t)blockIdx.x * P.x_stride;
@@ -191,7 +192,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const RmsnormParams P) {
     row[i] = v;
     sq[i] = fmul(v, v);
   }
-  float ss = block_seq_sum(sq, P.n, slot);
+  __syncthreads();
+  float ss = group_seq_sum(sq, P.n, &ssc, CtaGroup{(int)threadIdx.x, (int)blockDim.x, 0});
   float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)P.n), P.eps)));
   for (int i = threadIdx.x; i < P.n; i += blockDim.x) {
     float y = fmul(fmul(row[i], r), P.w[i]);
@@ -313,8 +315,12 @@ __global__ void __launch_bounds__(128) rmsnorm_heads_kernel(float* x, const floa
 }
 
 // ---- attention (ops.rs:185-218, 517-556) ------------------------------------------------------
-// One CTA per (head, query row). Scores and the softmax live in shared memory
-// (or in `scratch` for very long contexts).
+// One CTA per (group of up to 8 query heads that share a KV head, query row); one warp
+// per query head. Cached K and V rows are staged through shared memory once per CTA and
+// used by all its heads. Scores and the softmax live in shared memory (or in `scratch`
+// for contexts that do not fit). Order-sensitive reductions keep the reference's order:
+// each q.k dot is one sequential chain, the softmax denominator is the exact sequential
+// sum, the value mix runs over positions in order.
 struct AttnParams {
   float* out;         // m x q_dim
   const float* q;     // m x q_dim
@@ -324,77 +330,140 @@ struct AttnParams {
   const int* pos_ptr;
   int pos0;
   int n_head, n_kv_head, head_dim, ctx, window;
-  int smem_scores;    // capacity (floats) of the shared score buffer, 0 = use scratch
+  int smem_scores;    // capacity (floats per head) of the shared score buffer, 0 = use scratch
+  int heads_per_cta;  // query heads of one KV head handled by a CTA (<= 8)
   float scale;
 };
 
-__global__ void __launch_bounds__(256) attention_kernel(const AttnParams P) {
+constexpr int ATTN_THREADS = 256;
+constexpr int ATTN_CHUNK = 64;  // cached positions staged at a time
+
+__global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParams P) {
   extern __shared__ __align__(16) float sm_f[];
-  __shared__ float red[32];
-  __shared__ float slot;
+  __shared__ SeqSumScratch ssc[8];
   pdl_launch_dependents();
   pdl_wait();
-  const int h = blockIdx.x, row = blockIdx.y;
-  const int hd = P.head_dim, kv_dim = P.n_kv_head * hd, q_dim = P.n_head * hd;
+  const int hd = P.head_dim, hd4 = hd >> 2, kv_dim = P.n_kv_head * hd, q_dim = P.n_head * hd;
+  const int gqa = P.n_head / P.n_kv_head, hpc = P.heads_per_cta;
+  const int splits = (gqa + hpc - 1) / hpc;
+  const int kvh = blockIdx.x / splits, part = blockIdx.x - kvh * splits;
+  const int row = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h_local = part * hpc + warp;                      // head inside the KV group
+  const bool has_head = warp < hpc && h_local < gqa;
+  const int h = kvh * gqa + (has_head ? h_local : 0);
   const int pos = (P.pos_ptr ? *P.pos_ptr : P.pos0) + row;
   const int n = pos + 1;
   const int t0 = (P.window > 0 && pos + 1 > P.window) ? pos + 1 - P.window : 0;
   const int len = n - t0;
-  const int kvh = h / (P.n_head / P.n_kv_head);
-  float* qh = sm_f;  // hd floats
-  float* sc = P.smem_scores ? sm_f + hd : P.scratch + ((size_t)row * P.n_head + h) * P.ctx;
-  for (int i = threadIdx.x; i < hd; i += blockDim.x) qh[i] = P.q[(size_t)row * q_dim + h * hd + i];
-  __syncthreads();
+  const int kstride = hd + 4;
+  float* qs = sm_f;                                  // hpc x hd
+  float* kv = qs + hpc * hd;                         // ATTN_CHUNK x (hd + 4)
+  float* sc_all = kv + ATTN_CHUNK * kstride;         // hpc x smem_scores
+  float* sc = P.smem_scores ? sc_all + warp * P.smem_scores : P.scratch + ((size_t)row * P.n_head + h) * P.ctx;
+  for (int i = threadIdx.x; i < hpc * hd; i += ATTN_THREADS) {
+    const int w = i / hd, hl = part * hpc + w;
+    qs[i] = hl < gqa ? P.q[(size_t)row * q_dim + (kvh * gqa + hl) * hd + (i - w * hd)] : 0.0f;
+  }
   // scores: dot(q, k_t) * scale, each dot a sequential f32 loop (ops.rs:160-166)
   float lmax = -INFINITY;
-  for (int t = threadIdx.x; t < len; t += blockDim.x) {
-    const float4* kt = reinterpret_cast<const float4*>(P.k_cache + (size_t)(t0 + t) * kv_dim + kvh * hd);
-    float s = 0.0f;
-#pragma unroll 4
-    for (int i = 0; i < hd / 4; i++) {
-      float4 kk = kt[i];
-      s = fadd(s, fmul(qh[4 * i], kk.x));
-      s = fadd(s, fmul(qh[4 * i + 1], kk.y));
-      s = fadd(s, fmul(qh[4 * i + 2], kk.z));
-      s = fadd(s, fmul(qh[4 * i + 3], kk.w));
-    }
-    s = fmul(s, P.scale);
-    sc[t] = s;
-    lmax = fmaxf(lmax, s);
-  }
-  // block max (order-free)
+  const float* qh = qs + warp * hd;
+  for (int c0 = 0; c0 < len; c0 += ATTN_CHUNK) {
+    const int cn = min(ATTN_CHUNK, len - c0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < cn * hd4; i += 2 * ATTN_THREADS) {
+      float4 a[2];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = lmax;
-  __syncthreads();
-  float mx = red[0];
-  for (int w = 1; w < (int)(blockDim.x >> 5); w++) mx = fmaxf(mx, red[w]);
-  // exp, then the denominator in position order (ops.rs:103-107)
-  for (int t = threadIdx.x; t < len; t += blockDim.x) sc[t] = expf_exact(fsub(sc[t], mx));
-  float sum = block_seq_sum(sc, len, &slot);
-  float inv = fdiv(1.0f, sum);
-  for (int t = threadIdx.x; t < len; t += blockDim.x) sc[t] = fmul(sc[t], inv);
-  __syncthreads();
-  // out[i] = sum_t a_t * v_t[i], t in order (ops.rs:208-214)
-  if ((int)threadIdx.x < hd) {
-    const float* vb = P.v_cache + (size_t)t0 * kv_dim + kvh * hd + threadIdx.x;
-    float o = 0.0f;
-    int t = 0;
-    for (; t + 8 <= len; t += 8) {
-      float v0 = vb[(size_t)(t + 0) * kv_dim], v1 = vb[(size_t)(t + 1) * kv_dim], v2 = vb[(size_t)(t + 2) * kv_dim],
-            v3 = vb[(size_t)(t + 3) * kv_dim], v4 = vb[(size_t)(t + 4) * kv_dim], v5 = vb[(size_t)(t + 5) * kv_dim],
-            v6 = vb[(size_t)(t + 6) * kv_dim], v7 = vb[(size_t)(t + 7) * kv_dim];
-      o = fadd(o, fmul(sc[t + 0], v0));
-      o = fadd(o, fmul(sc[t + 1], v1));
-      o = fadd(o, fmul(sc[t + 2], v2));
-      o = fadd(o, fmul(sc[t + 3], v3));
-      o = fadd(o, fmul(sc[t + 4], v4));
-      o = fadd(o, fmul(sc[t + 5], v5));
-      o = fadd(o, fmul(sc[t + 6], v6));
-      o = fadd(o, fmul(sc[t + 7], v7));
+      for (int u = 0; u < 2; u++) {
+        const int j = i + u * ATTN_THREADS;
+        if (j < cn * hd4) {
+          const int t = j / hd4, i4 = j - t * hd4;
+          a[u] = reinterpret_cast<const float4*>(P.k_cache + (size_t)(t0 + c0 + t) * kv_dim + kvh * hd)[i4];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int j = i + u * ATTN_THREADS;
+        if (j < cn * hd4) {
+          const int t = j / hd4, i4 = j - t * hd4;
+          *reinterpret_cast<float4*>(kv + t * kstride + 4 * i4) = a[u];
+        }
+      }
     }
-    for (; t < len; t++) o = fadd(o, fmul(sc[t], vb[(size_t)t * kv_dim]));
-    P.out[(size_t)row * q_dim + h * hd + threadIdx.x] = o;
+    __syncthreads();
+    if (has_head) {
+      for (int t = lane; t < cn; t += 32) {
+        const float4* kt = reinterpret_cast<const float4*>(kv + t * kstride);
+        float s = 0.0f;
+#pragma unroll 4
+        for (int i = 0; i < hd4; i++) {
+          const float4 kk = kt[i];
+          const float4 qq = reinterpret_cast<const float4*>(qh)[i];
+          s = fadd(s, fmul(qq.x, kk.x));
+          s = fadd(s, fmul(qq.y, kk.y));
+          s = fadd(s, fmul(qq.z, kk.z));
+          s = fadd(s, fmul(qq.w, kk.w));
+        }
+        s = fmul(s, P.scale);
+        sc[c0 + t] = s;
+        lmax = fmaxf(lmax, s);
+      }
+    }
+  }
+  if (has_head) {
+    // this head's softmax, by its own warp: max (order-free), exp, the denominator in
+    // position order (ops.rs:103-107)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
+    __syncwarp();
+    for (int t = lane; t < len; t += 32) sc[t] = expf_exact(fsub(sc[t], lmax));
+    __syncwarp();
+    const float sum = group_seq_sum(sc, len, &ssc[warp], CtaGroup{lane, 32, 1 + warp});
+    const float inv = fdiv(1.0f, sum);
+    for (int t = lane; t < len; t += 32) sc[t] = fmul(sc[t], inv);
+    __syncwarp();
+  }
+  // out[i] = sum_t a_t * v_t[i], t in order (ops.rs:208-214); lane owns dims lane, lane+32, ...
+  float o[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) o[j] = 0.0f;
+  for (int c0 = 0; c0 < len; c0 += ATTN_CHUNK) {
+    const int cn = min(ATTN_CHUNK, len - c0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < cn * hd4; i += 2 * ATTN_THREADS) {
+      float4 a[2];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int j = i + u * ATTN_THREADS;
+        if (j < cn * hd4) {
+          const int t = j / hd4, i4 = j - t * hd4;
+          a[u] = reinterpret_cast<const float4*>(P.v_cache + (size_t)(t0 + c0 + t) * kv_dim + kvh * hd)[i4];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int j = i + u * ATTN_THREADS;
+        if (j < cn * hd4) {
+          const int t = j / hd4, i4 = j - t * hd4;
+          *reinterpret_cast<float4*>(kv + t * hd + 4 * i4) = a[u];
+        }
+      }
+    }
+    __syncthreads();
+    if (has_head) {
+#pragma unroll 4
+      for (int t = 0; t < cn; t++) {
+        const float a = sc[c0 + t];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+          if (lane + 32 * j < hd) o[j] = fadd(o[j], fmul(a, kv[t * hd + lane + 32 * j]));
+      }
+    }
+  }
+  if (has_head) {
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      if (lane + 32 * j < hd) P.out[(size_t)row * q_dim + h * hd + lane + 32 * j] = o[j];
   }
 }
 
