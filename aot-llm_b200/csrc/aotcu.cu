@@ -113,15 +113,15 @@ static int check_weight_alignment(int kind, const void* w) {
 
 // m = 8..64 activation rows against K-quant matrices: int8 tensor-core tiles (gemm.cuh).
 // Arguments were checked by launch_gemv.
-template <int NT, bool PAIR>
-static int launch_gemm_nt(aotcu_ctx* c, const GemmParams& P, int grid, int warps, size_t smem) {
+template <bool PAIR>
+static int launch_gemm_t(aotcu_ctx* c, const GemmParams& P, int grid, size_t smem) {
   static bool attr_set[64] = {};
   int dev = c->device;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    CU_TRY(cudaFuncSetAttribute(gemm_q8k_mma_kernel<NT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+    CU_TRY(cudaFuncSetAttribute(gemm_q8k_mma_kernel<PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
     attr_set[dev] = true;
   }
-  return launch(c, gemm_q8k_mma_kernel<NT, PAIR>, dim3(grid), dim3(warps * 32), smem, P);
+  return launch(c, gemm_q8k_mma_kernel<PAIR>, dim3(grid), dim3(GEMM_WARPS * 32), smem, P);
 }
 
 static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
@@ -141,27 +141,26 @@ static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
   P.x = reinterpret_cast<const uint8_t*>(call.x);
   P.x_image = call.x_mode == 1;
   P.n_tiles = tiles;
-  // Token groups per warp: all of them when there are plenty of row tiles, fewer (more,
-  // smaller work items) on a small matrix. A CTA's warps share one token group, so a CTA
-  // stages only that group's activation images.
-  const int groups8 = (P.m + 7) / 8;
-  int nt = call.pair ? 2 : 8;  // pair mode keeps two matrices' accumulators per thread
-  while (nt > 2 && (size_t)tiles * ((groups8 + nt - 1) / nt) < (size_t)c->n_sm * 8) nt >>= 1;
-  P.n_groups = (groups8 + nt - 1) / nt;
-  int warps = GEMM_WARPS;
-  while (warps > 2 && (size_t)tiles * P.n_groups < (size_t)c->n_sm * warps) warps >>= 1;
-  int ctas_per_group = (tiles + warps - 1) / warps;
+  P.n_groups = (P.m + GEMM_TOK - 1) / GEMM_TOK;
+  const int nb = (int)(call.cols / 256), n_mat = call.pair ? 2 : 1;
+  // The warps of a tile split its super-blocks four ways when there are enough of them.
+  P.ks = nb >= 4 ? 4 : (nb >= 2 ? 2 : 1);
+  const int tpc = GEMM_WARPS / P.ks;
+  // Super-blocks staged at a time: all of them if images + terms fit, else as many as fit
+  // beside a second resident CTA.
+  const size_t per_block = (size_t)GEMM_TOK * XK_STRIDE + (size_t)tpc * n_mat * 32 * GEMM_NT * 4 * sizeof(float);
+  const size_t budget = c->max_smem / 2 - 2048;
+  int kc = nb;
+  if ((size_t)kc * per_block > budget) kc = (int)(budget / per_block);
+  ARG_CHECK(kc >= 1, "one super-block column does not fit in shared memory");
+  kc = (kc / P.ks) * P.ks > 0 ? (kc / P.ks) * P.ks : kc;  // whole strides of the k-split
+  P.kc = kc;
+  const size_t smem = (size_t)kc * per_block;
+  int ctas_per_group = (tiles + tpc - 1) / tpc;
   const int cap = (c->n_sm * 2) / P.n_groups;
   if (ctas_per_group > cap) ctas_per_group = cap < 1 ? 1 : cap;
   const int grid = ctas_per_group * P.n_groups;
-  const int nb = (int)(call.cols / 256);
-  P.kb = nb < 4 ? nb : 4;
-  const size_t smem = (size_t)2 * P.kb * 8 * nt * XK_STRIDE;
-  ARG_CHECK(smem <= c->max_smem, "activation chunk does not fit in shared memory");
-  if (call.pair) return nt == 4 ? launch_gemm_nt<4, true>(c, P, grid, warps, smem) : launch_gemm_nt<2, true>(c, P, grid, warps, smem);
-  if (nt == 8) return launch_gemm_nt<8, false>(c, P, grid, warps, smem);
-  if (nt == 4) return launch_gemm_nt<4, false>(c, P, grid, warps, smem);
-  return launch_gemm_nt<2, false>(c, P, grid, warps, smem);
+  return call.pair ? launch_gemm_t<true>(c, P, grid, smem) : launch_gemm_t<false>(c, P, grid, smem);
 }
 
 static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {

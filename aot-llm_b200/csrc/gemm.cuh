@@ -6,14 +6,16 @@
 // everything is integer arithmetic (exact in any order), and the f32 block terms are added in
 // block order per (row, token) by the one thread that owns that output element.
 //
-// A warp owns a tile of 16 weight rows and NT groups of 8 tokens. For every 32-weight
-// sub-block (16-weight for Q6_K) it issues one mma.sync m16n8k32 (m16n8k16) u8 x s8 -> s32
-// per token group, starting from zero: the per-sub-block scale differs per row, so the
-// accumulator has to be read out after every K = 32 and is folded into the block's integer
-// sum with one integer multiply-add per output element. Weight nibbles are unpacked in
-// registers straight from global memory (each 32-byte sector is used completely by the
-// quad that reads it); the activation images of the current K chunk sit in shared memory,
-// double buffered with cp.async.
+// A CTA works on one group of 16 tokens (two MMA column groups) whose Q8_K images it stages
+// in shared memory once, and on TPC row tiles of 16 weight rows at a time; the KS warps of a
+// tile split the tile's super-blocks between them. For every 32-weight sub-block (16-weight
+// for Q6_K) a warp issues one mma.sync m16n8k32 (m16n8k16) u8 x s8 -> s32 per column group,
+// starting from zero: the per-sub-block scale differs per row, so the accumulator has to be
+// read out after every K = 32 and is folded into the block's integer sum with one integer
+// multiply-add per output element. Each warp leaves the f32 term of each of its blocks in
+// shared memory; after a barrier the terms of an output element are added in block order.
+// Weight nibbles are unpacked in registers straight from global memory, fetched one block
+// ahead (each 32-byte sector is used completely by the quad that reads it).
 #pragma once
 #include <cuda_fp16.h>
 
@@ -32,9 +34,10 @@ struct GemmParams {
   int nseg, pair, cols, m, epilogue;
   const uint8_t* x;   // [m][cols/256] Q8_K images (304 bytes) or reference-layout BlockQ8_K (292 bytes)
   int x_image;
-  int n_groups;       // token groups of 8*NT tokens; CTA c works on group c % n_groups
+  int n_groups;       // token groups of 16 tokens; CTA c works on group c % n_groups
   int n_tiles;        // 16-row tiles over all matrices (pair mode: of one matrix)
-  int kb;             // super-blocks per staged activation chunk
+  int ks;             // warps that split one tile's super-blocks (a divisor of the CTA's warps)
+  int kc;             // super-blocks staged at a time (all of them when they fit)
   int tiles_before[4];  // first tile index of each matrix (pair mode: one list for both)
 };
 
@@ -69,6 +72,9 @@ __device__ __forceinline__ uint32_t gm_lds32(uint32_t a) {
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
   return v;
 }
+__device__ __forceinline__ void gm_lds64(uint32_t a, uint32_t& x, uint32_t& y) {
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(x), "=r"(y) : "r"(a));
+}
 __device__ __forceinline__ U4 gm_lds128(uint32_t a) {
   U4 v;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
@@ -77,14 +83,15 @@ __device__ __forceinline__ U4 gm_lds128(uint32_t a) {
 
 // A 32-bit word at a 2-byte aligned global address.
 __device__ __forceinline__ uint32_t ldg32_a2(const uint8_t* p) {
+  if (((uintptr_t)p & 2u) == 0) return __ldg(reinterpret_cast<const uint32_t*>(p));
   const unsigned short* q = reinterpret_cast<const unsigned short*>(p);
   return (uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16);
 }
 
 // The words of one super-block that a thread needs for its two rows (row g and row g+8 of
 // the tile; g = lane/4, q = lane%4), fetched one block ahead of their use.
-//   Q4_K / Q5_K: [0..3] d|dmin + packed scales, [4..11] nibble words (pair c: 4+2c low-k,
-//                5+2c high-k), [12..13] fifth-bit words (Q5_K)
+//   Q4_K / Q5_K: [0..3] d|dmin + packed scales, [4..11] nibble words (pair c: 4+2c holds
+//                weights k = 8q..8q+3, 5+2c k = 8q+4..8q+7), [12..13] fifth-bit words (Q5_K)
 //   Q6_K:        [0..3] low nibbles l, [4..7] low nibbles l+32, [8..11] high bits
 //                (index 2n+hh), [12..15] scales, [16] d
 struct WFrag {
@@ -110,14 +117,18 @@ __device__ __forceinline__ void gemm_load_frag(int kind, const uint8_t* wa, cons
       const uint4 h = __ldg(reinterpret_cast<const uint4*>(p));
       f.w[r][0] = h.x; f.w[r][1] = h.y; f.w[r][2] = h.z; f.w[r][3] = h.w;
       const int qoff = kind == Q5_K ? 48 : 16;
+      // lane q takes bytes 8q..8q+7 of every 32-byte nibble run: weights k = 8q..8q+7 of both
+      // sub-blocks of the pair (the activation fragment uses the same k order)
 #pragma unroll
       for (int c = 0; c < 4; c++) {
-        f.w[r][4 + 2 * c] = __ldg(reinterpret_cast<const uint32_t*>(p + qoff + 32 * c) + q);
-        f.w[r][5 + 2 * c] = __ldg(reinterpret_cast<const uint32_t*>(p + qoff + 32 * c + 16) + q);
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(p + qoff + 32 * c) + q);
+        f.w[r][4 + 2 * c] = v.x;
+        f.w[r][5 + 2 * c] = v.y;
       }
       if (kind == Q5_K) {
-        f.w[r][12] = __ldg(reinterpret_cast<const uint32_t*>(p + 16) + q);
-        f.w[r][13] = __ldg(reinterpret_cast<const uint32_t*>(p + 32) + q);
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(p + 16) + q);
+        f.w[r][12] = v.x;
+        f.w[r][13] = v.y;
       }
     }
   }
@@ -159,9 +170,11 @@ __device__ __forceinline__ void gemm_block_k4(const WFrag& f, uint32_t xs, int t
       const int sca = byte_of(j < 4 ? sa.sc_lo : sa.sc_hi, j & 3), scb = byte_of(j < 4 ? sb.sc_lo : sb.sc_hi, j & 3);
 #pragma unroll
       for (int t = 0; t < NT; t++) {
-        const uint32_t xa = xs + (uint32_t)(tok0 + 8 * t + g) * XK_STRIDE + 32 * j + 4 * q;
+        const uint32_t xa = xs + (uint32_t)(tok0 + 8 * t + g) * XK_STRIDE + 32 * j + 8 * q;
+        uint32_t y0, y1;
+        gm_lds64(xa, y0, y1);  // activations k = 8q..8q+3 and 8q+4..8q+7, matching the weight words
         int cc[4];
-        mma_u8s8_k32(cc, a0, a1, a2, a3, gm_lds32(xa), gm_lds32(xa + 16));
+        mma_u8s8_k32(cc, a0, a1, a2, a3, y0, y1);
         sumi[t][0] += sca * cc[0];
         sumi[t][1] += sca * cc[1];
         sumi[t][2] += scb * cc[2];
@@ -282,40 +295,58 @@ __device__ __forceinline__ void gemm_stage_x(uint32_t dst, const uint8_t* x, int
                  x + ((size_t)ts * nb + (size_t)(b0 + kb)) * XK_STRIDE + 16 * p);
     }
   } else {
-    // BlockQ8_K {f32 d; i8 qs[256]; i16 bsums[16]} (quant.rs:8-14), word by word into the image layout
+    // BlockQ8_K {f32 d; i8 qs[256]; i16 bsums[16]} (quant.rs:8-14), word by word into the image
+    // layout, with plain loads (four in flight per thread)
     const int pieces = kb_n * nt8 * 73;
-    for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
-      const int kb = i / (nt8 * 73), r = i - kb * (nt8 * 73);
-      const int slot = r / 73, w = r - slot * 73;
-      const int ts = min(t0 + slot, m - 1);
-      const int off = w == 0 ? XK_D : (w <= 64 ? (w - 1) * 4 : XK_BSUMS + (w - 65) * 4);
-      cp_async4(dst + (uint32_t)((kb * nt8 + slot) * XK_STRIDE + off), x + ((size_t)ts * nb + (size_t)(b0 + kb)) * 292 + 4 * w);
+    for (int i0 = threadIdx.x; i0 < pieces; i0 += 4 * blockDim.x) {
+      uint32_t v[4];
+      uint32_t da[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int i = i0 + u * blockDim.x;
+        if (i < pieces) {
+          const int kb = i / (nt8 * 73), r = i - kb * (nt8 * 73);
+          const int slot = r / 73, w = r - slot * 73;
+          const int ts = min(t0 + slot, m - 1);
+          const int off = w == 0 ? XK_D : (w <= 64 ? (w - 1) * 4 : XK_BSUMS + (w - 65) * 4);
+          da[u] = dst + (uint32_t)((kb * nt8 + slot) * XK_STRIDE + off);
+          v[u] = __ldg(reinterpret_cast<const uint32_t*>(x + ((size_t)ts * nb + (size_t)(b0 + kb)) * 292) + w);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        if (i0 + u * (int)blockDim.x < pieces) asm volatile("st.shared.u32 [%0], %1;" ::"r"(da[u]), "r"(v[u]) : "memory");
+      }
     }
   }
 }
 
-template <int NT, bool PAIR>
-__global__ void __launch_bounds__(GEMM_WARPS * 32) gemm_q8k_mma_kernel(const GemmParams P) {
+constexpr int GEMM_NT = 2;             // MMA column groups (of 8 tokens) per CTA
+constexpr int GEMM_TOK = 8 * GEMM_NT;  // tokens per CTA
+
+template <bool PAIR>
+__global__ void __launch_bounds__(GEMM_WARPS * 32, 2) gemm_q8k_mma_kernel(const GemmParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int nb = P.cols >> 8;
+  constexpr int NT = GEMM_NT, NT8 = GEMM_TOK, n_mat = PAIR ? 2 : 1, EPL = NT * 4;  // EPL: outputs per lane
+  const int nb = P.cols >> 8, kc = P.kc;
+  const int n_chunks = (nb + kc - 1) / kc;
   const int n_warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-  constexpr int NT8 = 8 * NT;
-  const uint32_t buf_bytes = (uint32_t)(P.kb * NT8 * XK_STRIDE);
-  const uint32_t sbase = smem_addr(smem);
-  const int n_chunks = (nb + P.kb - 1) / P.kb;
-  // All warps of a CTA work on the same token group, so only its tokens are staged.
+  const int ks = P.ks, tpc = n_warps / ks;   // k-parts per tile, tiles per CTA
+  const int tile_i = warp / ks, part = warp - tile_i * ks;
+  // [images: kc x 16 tokens x 304][terms: tpc x n_mat x kc x 256 floats]
+  const uint32_t ximg = smem_addr(smem);
+  float* terms = reinterpret_cast<float*>(smem + (size_t)kc * NT8 * XK_STRIDE);
   const int tg = (int)blockIdx.x % P.n_groups, cta_in_group = (int)blockIdx.x / P.n_groups;
   const int ctas_per_group = (int)gridDim.x / P.n_groups;
   const int tokg = tg * NT8;  // first token of the group
-  const int per_round = ctas_per_group * n_warps;
+  const int per_round = ctas_per_group * tpc;
   const int n_rounds = (P.n_tiles + per_round - 1) / per_round;
-  constexpr int n_mat = PAIR ? 2 : 1;
-  constexpr int tok0 = 0;     // token slots inside the staged chunk
+  const int per_part = EPL / ks > 0 ? EPL / ks : 1;  // outputs per lane this warp sums
   pdl_launch_dependents();
   pdl_wait();
   for (int round = 0; round < n_rounds; round++) {
-    const int tile_raw = (round * ctas_per_group + cta_in_group) * n_warps + warp;
+    const int tile_raw = (round * ctas_per_group + cta_in_group) * tpc + tile_i;
     const bool active = tile_raw < P.n_tiles;
     const int tile = active ? tile_raw : 0;
     int s = 0;
@@ -323,15 +354,6 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32) gemm_q8k_mma_kernel(const Gem
       while (s < P.nseg - 1 && tile >= P.tiles_before[s + 1]) s++;
     }
     const int r0 = (tile - P.tiles_before[s]) * 16;
-    TileAcc<NT> acc[n_mat];
-#pragma unroll
-    for (int mt = 0; mt < n_mat; mt++) {
-#pragma unroll
-      for (int t = 0; t < NT; t++) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) acc[mt].v[t][i] = 0.0f;
-      }
-    }
     // rows of this thread (clamped: a ragged last tile recomputes the last row)
     const uint8_t* wrow[n_mat][2];
     int kind[n_mat];
@@ -345,58 +367,79 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32) gemm_q8k_mma_kernel(const Gem
       wrow[mt][0] = sg.w + (size_t)min(r0 + g, sg.rows - 1) * row_bytes;
       wrow[mt][1] = sg.w + (size_t)min(r0 + g + 8, sg.rows - 1) * row_bytes;
     }
-    // Weights are fetched one (block, matrix) step ahead of their use; the sequence runs
-    // straight through the activation chunks.
+    // Within a chunk of kc super-blocks this warp takes blocks part, part + ks, ...;
+    // weights are fetched one (block, matrix) step ahead of their use, across chunks too.
     WFrag cur, nxt;
-    if (active) gemm_load_frag(kind[0], wrow[0][0], wrow[0][1], cur);
-    __syncthreads();  // the previous round is done with both chunk buffers
-    gemm_stage_x(sbase, P.x, P.x_image, nb, 0, min(P.kb, nb), tokg, NT8, P.m);
-    cp_async_commit();
+    if (active && part < nb) gemm_load_frag(kind[0], wrow[0][0] + (size_t)part * rbytes[0], wrow[0][1] + (size_t)part * rbytes[0], cur);
+    float sum0[EPL], sum1[EPL];  // running sums of this thread's outputs (first / second matrix)
+#pragma unroll
+    for (int e = 0; e < EPL; e++) sum0[e] = sum1[e] = 0.0f;
     for (int ch = 0; ch < n_chunks; ch++) {
-      const int b0 = ch * P.kb, kb_n = min(P.kb, nb - b0);
-      if (ch + 1 < n_chunks) {
-        gemm_stage_x(sbase + ((ch + 1) & 1) * buf_bytes, P.x, P.x_image, nb, b0 + P.kb, min(P.kb, nb - b0 - P.kb), tokg, NT8,
-                     P.m);
+      const int b0 = ch * kc, b1 = min(b0 + kc, nb);
+      if (n_chunks > 1 || round == 0) {
+        // (with one chunk the images of the token group stay for all rounds)
+        gemm_stage_x(ximg, P.x, P.x_image, nb, b0, b1 - b0, tokg, NT8, P.m);
         cp_async_commit();
-        cp_async_wait<1>();
-      } else {
         cp_async_wait<0>();
       }
-      __syncthreads();
+      __syncthreads();  // images are in place; the terms of the previous chunk have been consumed
       if (active) {
-        const uint32_t xs = sbase + (ch & 1) * buf_bytes;
-        for (int kb = 0; kb < kb_n; kb++) {
-          const int b = b0 + kb;
-          const uint32_t xb = xs + (uint32_t)(kb * NT8) * XK_STRIDE;
+        for (int b = b0 + part; b < b1; b += ks) {
+          const uint32_t xb = ximg + (uint32_t)((b - b0) * NT8) * XK_STRIDE;
 #pragma unroll
           for (int mt = 0; mt < n_mat; mt++) {
-            // next step: the other matrix of this block, or the first matrix of the next block
-            const int nmt = mt + 1 < n_mat ? mt + 1 : 0, nbk = mt + 1 < n_mat ? b : b + 1;
+            int nbk = b;
+            if (mt + 1 == n_mat) {
+              nbk = b + ks;
+              if (nbk >= b1) nbk = b1 + part;  // first block of this warp in the next chunk
+            }
+            const int nmt = mt + 1 < n_mat ? mt + 1 : 0;
             if (nbk < nb)
               gemm_load_frag(kind[nmt], wrow[nmt][0] + (size_t)nbk * rbytes[nmt], wrow[nmt][1] + (size_t)nbk * rbytes[nmt], nxt);
-            gemm_block<NT>(kind[mt], cur, xb, tok0, acc[mt]);
+            TileAcc<NT> term;
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+#pragma unroll
+              for (int i = 0; i < 4; i++) term.v[t][i] = 0.0f;
+            }
+            gemm_block<NT>(kind[mt], cur, xb, 0, term);
+            float4* dst = reinterpret_cast<float4*>(terms + ((size_t)(tile_i * n_mat + mt) * kc + (b - b0)) * (32 * EPL) + lane * EPL);
+#pragma unroll
+            for (int t = 0; t < NT; t++) dst[t] = make_float4(term.v[t][0], term.v[t][1], term.v[t][2], term.v[t][3]);
             cur = nxt;
           }
         }
       }
-      __syncthreads();  // everyone is done with this buffer before it is refilled
+      __syncthreads();  // all terms of the chunk are written; the images may be replaced
+      if (active) {
+        // The terms of an output element are added in block order by one thread; the ks
+        // warps of a tile share the tile's outputs.
+#pragma unroll
+        for (int e = 0; e < EPL; e++) {
+          if (e >= part * per_part && e < (part + 1) * per_part) {
+            const float* tp = terms + (size_t)(tile_i * n_mat) * kc * (32 * EPL) + lane * EPL + e;
+            for (int b = 0; b < b1 - b0; b++) {
+              sum0[e] = fadd(sum0[e], tp[(size_t)b * (32 * EPL)]);
+              if (PAIR) sum1[e] = fadd(sum1[e], tp[(size_t)(kc + b) * (32 * EPL)]);
+            }
+          }
+        }
+      }
     }
     if (active) {
 #pragma unroll
-      for (int t = 0; t < NT; t++) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
+      for (int e = 0; e < EPL; e++) {
+        if (e >= part * per_part && e < (part + 1) * per_part) {
+          const int t = e >> 2, i = e & 3;
           const int row = r0 + g + (i >> 1) * 8, tok = tokg + 8 * t + 2 * q + (i & 1);
           const GemvSeg& sg = P.seg[PAIR ? 0 : s];
           if (row < sg.rows && tok < P.m) {
             const size_t o = (size_t)tok * sg.rows + row;
             if (PAIR) {
-              const float gate = acc[0].v[t][i], up = acc[n_mat - 1].v[t][i];
-              P.seg[0].out[o] = P.epilogue == EPI_SILU_MUL ? silu_mul_exact(gate, up) : gate;
-              P.seg[1].out[o] = up;
+              P.seg[0].out[o] = P.epilogue == EPI_SILU_MUL ? silu_mul_exact(sum0[e], sum1[e]) : sum0[e];
+              P.seg[1].out[o] = sum1[e];
             } else {
-              const float v = acc[0].v[t][i];
-              sg.out[o] = P.epilogue == EPI_ACCUM ? fadd(sg.out[o], v) : v;
+              sg.out[o] = P.epilogue == EPI_ACCUM ? fadd(sg.out[o], sum0[e]) : sum0[e];
             }
           }
         }
