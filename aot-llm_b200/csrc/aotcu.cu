@@ -163,6 +163,45 @@ static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
   return call.pair ? launch_gemm_t<true>(c, P, grid, smem) : launch_gemm_t<false>(c, P, grid, smem);
 }
 
+// One K-quant product for a single activation row on the ring producer/consumer kernel.
+constexpr size_t STREAM_STAGE_BYTES = 32768;
+static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
+  StreamGemvParams P = {};
+  MegaOp& op = P.op;
+  size_t max_rb = 1;
+  for (int s = 0; s < call.nseg; s++) {
+    op.seg[s] = call.seg[s];
+    op.row_bytes[s] = (uint32_t)kind_row_bytes(call.seg[s].kind, call.cols);
+    max_rb = std::max(max_rb, (size_t)op.row_bytes[s]);
+  }
+  op.nseg = call.nseg;
+  op.pair = call.pair;
+  op.cols = (int)call.cols;
+  op.span_rows = (int)span;
+  op.rows_per_cta = (int)((span + c->n_sm - 1) / c->n_sm);
+  const int tr = (int)((STREAM_STAGE_BYTES - 192) / (max_rb * (call.pair ? 2 : 1)));
+  op.tile_rows = tr < 1 ? 1 : tr;
+  op.epilogue = call.epilogue;
+  op.ll = 0;
+  P.x = call.x;
+  P.x_image = call.x_mode == 1;
+  P.err = c->d_err;
+  P.stage_bytes = (int)STREAM_STAGE_BYTES;
+  const size_t fixed = (call.cols / 256) * XK_STRIDE + MEGA_BAR_BYTES + 16;
+  ARG_CHECK(fixed + 2 * STREAM_STAGE_BYTES <= c->max_smem, "activation vector too long for shared memory");
+  int n_stages = (int)((c->max_smem - fixed) / STREAM_STAGE_BYTES);
+  if (n_stages > 6) n_stages = 6;
+  P.n_stages = n_stages;
+  const size_t smem = (size_t)n_stages * STREAM_STAGE_BYTES + fixed;
+  static bool attr_set[64] = {};
+  if (c->device >= 0 && c->device < 64 && !attr_set[c->device]) {
+    CU_TRY(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+    attr_set[c->device] = true;
+  }
+  const int grid = span < (size_t)c->n_sm ? (int)span : c->n_sm;
+  return launch(c, gemv_stream_kernel, dim3(grid), dim3(MEGA_THREADS), smem, P);
+}
+
 static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
   ARG_CHECK(call.nseg >= 1 && call.nseg <= 3, "1..3 matrices per launch");
   const int act = kind_act(call.seg[0].kind);
@@ -210,8 +249,10 @@ static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
   }
   ARG_CHECK(((uintptr_t)call.x % (P.x_image ? 16 : 4)) == 0, "activation blocks are misaligned");
 
-  // Prompt chunks of K-quant matrices go to the tensor-core kernel.
+  // Prompt chunks of K-quant matrices go to the tensor-core kernel, single rows to the
+  // streaming kernel (whole rows per warp, no barrier per tile).
   if (act == ACT_Q8_K && call.m >= 8 && call.m <= (size_t)GEMM_MAX_M) return launch_gemm(c, call);
+  if (act == ACT_Q8_K && call.m == 1 && 2 * max_rb + 192 <= STREAM_STAGE_BYTES) return launch_gemv_stream(c, call, span);
 
   const int mult = call.pair ? 2 : 1;
   int grid = c->n_sm;

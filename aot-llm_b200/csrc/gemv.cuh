@@ -268,7 +268,10 @@ __device__ __forceinline__ float silu_mul_exact(float g, float u) {
 // batches, matmul_* of matvec.rs:479-546) the resident weight tile is applied to
 // the m activation vectors one after the other; per token the arithmetic is the
 // same code path as m == 1, so batched == single bit for bit.
-constexpr int GEMV_THREADS = 256;
+#ifndef GEMV_THREADS_N
+#define GEMV_THREADS_N 256
+#endif
+constexpr int GEMV_THREADS = GEMV_THREADS_N;
 constexpr int GEMV_TRP = 64;  // max rows (over all parts) of one tile
 
 struct TileCtx {

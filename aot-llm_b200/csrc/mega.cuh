@@ -1071,4 +1071,71 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
 #undef MEGA_PROF
 }
 
+// ---- one matrix product with the same machinery ------------------------------------------
+// A single K-quant product (up to three matrices, or a gate/up pair) against one Q8_K
+// activation vector: the producer warp streams this CTA's rows through the ring while the
+// consumer warps take whole rows, with no CTA-wide barrier per tile. Used for single-row
+// products outside the one-kernel step (the operator API, models the step does not cover).
+struct StreamGemvParams {
+  MegaOp op;
+  const void* x;  // Q8_K images (x_image) or reference-layout BlockQ8_K
+  int x_image;
+  int n_stages, stage_bytes;
+  int* err;
+};
+
+__global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const StreamGemvParams P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  // [stages][sx images][barriers 128 B][abort]
+  const int nb = P.op.cols >> 8;
+  uint8_t* stages = smem;
+  uint8_t* sx = stages + (size_t)P.n_stages * P.stage_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sx + (size_t)nb * XK_STRIDE);
+  volatile int* abort = reinterpret_cast<volatile int*>(bars + MEGA_BAR_BYTES / 8);
+  Ring R;
+  R.stages = stages;
+  R.full = bars;
+  R.empty = bars + P.n_stages;
+  R.n_stages = P.n_stages;
+  R.stage_bytes = P.stage_bytes;
+  R.abort = abort;
+  R.err = P.err;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P.n_stages; s++) {
+      mbar_init(&R.full[s], 1);
+      mbar_init(&R.empty[s], MEGA_CONSUMER_WARPS);
+    }
+    *abort = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  pdl_launch_dependents();
+  if (warp == MEGA_CONSUMER_WARPS) {
+    // weights do not depend on the previous kernel: stream them right away
+    if ((threadIdx.x & 31) == 0) {
+      RingPos pp{0, 0u};
+      produce_op(P.op, R, pp);
+    }
+    return;
+  }
+  pdl_wait();
+  CtaGroup g{(int)threadIdx.x, MEGA_CONSUMER_WARPS * 32, 1};
+  if (P.x_image) {
+    const uint4* src4 = reinterpret_cast<const uint4*>(P.x);
+    for (int i = g.tid; i < nb * (XK_STRIDE / 16); i += g.nthreads) reinterpret_cast<uint4*>(sx)[i] = src4[i];
+  } else {
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(P.x);
+    for (int i = g.tid; i < nb * 73; i += g.nthreads) {
+      const int b = i / 73, w = i - b * 73;
+      const int off = w == 0 ? XK_D : (w <= 64 ? (w - 1) * 4 : XK_BSUMS + (w - 65) * 4);
+      *reinterpret_cast<uint32_t*>(sx + b * XK_STRIDE + off) = src[i];
+    }
+  }
+  g.sync();
+  RingPos cp{0, 0u};
+  consume_op(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, 0u);
+}
+
+
 }  // namespace aot
