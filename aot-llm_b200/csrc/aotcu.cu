@@ -185,9 +185,10 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   op.ll = 0;
   P.x = call.x;
   P.x_image = call.x_mode == 1;
+  P.q80 = kind_act(call.seg[0].kind) == ACT_Q8_0;
   P.err = c->d_err;
   P.stage_bytes = (int)STREAM_STAGE_BYTES;
-  const size_t fixed = (call.cols / 256) * XK_STRIDE + MEGA_BAR_BYTES + 16;
+  const size_t fixed = (P.q80 ? (call.cols / 32) * X0_STRIDE : (call.cols / 256) * XK_STRIDE) + MEGA_BAR_BYTES + 16;
   ARG_CHECK(fixed + 2 * STREAM_STAGE_BYTES <= c->max_smem, "activation vector too long for shared memory");
   int n_stages = (int)((c->max_smem - fixed) / STREAM_STAGE_BYTES);
   if (n_stages > 6) n_stages = 6;
@@ -252,7 +253,7 @@ static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
   // Prompt chunks of K-quant matrices go to the tensor-core kernel, single rows to the
   // streaming kernel (whole rows per warp, no barrier per tile).
   if (act == ACT_Q8_K && call.m >= 8 && call.m <= (size_t)GEMM_MAX_M) return launch_gemm(c, call);
-  if (act == ACT_Q8_K && call.m == 1 && 2 * max_rb + 192 <= STREAM_STAGE_BYTES) return launch_gemv_stream(c, call, span);
+  if (call.m == 1 && 2 * max_rb + 192 <= STREAM_STAGE_BYTES) return launch_gemv_stream(c, call, span);
 
   const int mult = call.pair ? 2 : 1;
   int grid = c->n_sm;
@@ -1588,6 +1589,35 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
 // layer, then the output head), back to back in one CUDA graph, `iters` replays. The
 // layers' weights are distinct and together far larger than L2, so every launch
 // streams from HBM. Used by the benchmark to quote the GEMV kernel's bandwidth.
+int aotcu_bench_matmul(aotcu_ctx* c, int kind, float* out, const uint8_t* w, size_t copy_stride, size_t n_copies,
+                       const void* xs, size_t m, size_t rows, size_t cols, int iters, float* ms_per_launch) {
+  ARG_CHECK(c && out && w && xs && ms_per_launch, "NULL argument");
+  ARG_CHECK(iters >= 1 && n_copies >= 1 && m >= 1, "iters, n_copies and m must be at least 1");
+  if (int rc = ctx_set_device(c)) return rc;
+  auto one = [&](int i) -> int {
+    const uint8_t* wi = w + (size_t)(i % (int)n_copies) * copy_stride;
+    return m == 1 ? aotcu_matvec(c, kind, out, wi, xs, rows, cols) : aotcu_matmul(c, kind, out, wi, xs, m, rows, cols);
+  };
+  for (int i = 0; i < 3; i++)
+    if (int rc = one(i)) return rc;
+  cudaEvent_t e0, e1;
+  CU_TRY(cudaEventCreate(&e0));
+  CU_TRY(cudaEventCreate(&e1));
+  CU_TRY(cudaEventRecord(e0, c->stream));
+  int rc = 0;
+  for (int i = 0; i < iters && !rc; i++) rc = one(i);
+  cudaEventRecord(e1, c->stream);
+  cudaError_t e = cudaEventSynchronize(e1);
+  float ms = 0.0f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (rc) return rc;
+  if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "bench_matmul: %s", cudaGetErrorString(e));
+  *ms_per_launch = ms / (float)iters;
+  return check_device_errors(c);
+}
+
 int aotcu_bench_gemv_sweep(aotcu_gpu* g, int iters, float* ms_per_sweep, uint64_t* launches_per_sweep,
                            uint64_t* bytes_per_sweep) {
   ARG_CHECK(g && iters >= 1 && ms_per_sweep, "bad argument");

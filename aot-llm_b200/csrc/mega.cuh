@@ -1071,6 +1071,104 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
 #undef MEGA_PROF
 }
 
+// ---- Q4_0 / Q5_0 / Q8_0 rows from the ring --------------------------------------------------
+// The reference's AVX2 kernels keep eight f32 lane accumulators per row; lane k adds
+// fma(d_w*d_x, float(p_k), acc_k) per 32-weight block, in block order, and the row ends
+// with a fixed 8-lane tree (simd_avx2.rs:29-34, 61-72). Here eight threads own the eight
+// lane chains of a row (four rows per warp pass).
+__device__ __forceinline__ uint32_t lds32_a2s(uint32_t a) {  // 32-bit word at a 2-byte aligned shared address
+  uint32_t lo, hi;
+  asm("ld.shared.u16 %0, [%1];" : "=r"(lo) : "r"(a));
+  asm("ld.shared.u16 %0, [%1];" : "=r"(hi) : "r"(a + 2));
+  return lo | (hi << 16);
+}
+
+template <int KIND>
+__device__ __forceinline__ float row_chain_q80(uint32_t row, uint32_t sx, int nb, int k) {
+  constexpr int BS = KIND == Q4_0 ? 18 : (KIND == Q5_0 ? 22 : 34);
+  float acc = 0.0f;
+#pragma unroll 4
+  for (int b = 0; b < nb; b++) {
+    const uint32_t wb = row + (uint32_t)b * BS, xb = sx + (uint32_t)b * X0_STRIDE;
+    uint32_t hd;
+    asm("ld.shared.u16 %0, [%1];" : "=r"(hd) : "r"(wb));
+    const float d = fmul(half_to_float_hw(hd), __uint_as_float(lds32q(xb + X0_D)));
+    const uint32_t y = lds32q(xb + 4 * k);
+    int p;
+    if (KIND == Q8_0) p = q8_0_lane(lds32_a2s(wb + 2 + 4 * k), y);
+    else if (KIND == Q4_0) p = q4_0_lane(lds32_a2s(wb + 2 + 4 * (k & 3)), k, y);
+    else p = q5_0_lane(lds32_a2s(wb + 6 + 4 * (k & 3)), lds32_a2s(wb + 2), k, y);
+    acc = ffma(d, i2f(p), acc);
+  }
+  return acc;
+}
+
+// Consumer side for matrices of the Q8_0 family; `sx` holds the 48-byte Q8_0 images.
+__device__ __forceinline__ void consume_op_q80(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp,
+                                               int n_warps) {
+  const int tile_rows = op.tile_rows, pair = op.pair, epilogue = op.epilogue, nb = op.cols >> 5;
+  int c0, c1;
+  cta_rows(op.span_rows, c0, c1);
+  const int lane = threadIdx.x & 31, k = lane & 7, gi = lane >> 3;
+  const uint32_t sxa = smem_addr(sx);
+  int rot = 0;
+  for (int t0 = c0; t0 < c1; t0 += tile_rows) {
+    if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
+    const int t1 = min(t0 + tile_rows, c1);
+    const uint32_t stage = smem_addr(R.stages + (size_t)cp.st * R.stage_bytes);
+    const int R_rows = t1 - t0;
+    const int n_pass = (R_rows + 3) / 4;  // four rows per warp pass
+    int ps = warp - rot;
+    if (ps < 0) ps += n_warps;
+    if (ps < n_pass) {
+      TilePart parts[3];
+      const int np = op_tile_parts(op, t0, t1, parts);
+      for (; ps < n_pass; ps += n_warps) {
+        const int u = ps * 4 + gi;
+        float v[2] = {0.0f, 0.0f};
+        int pi = 0, lr = u;
+        if (!pair && u < R_rows) {
+          while (pi < np - 1 && lr >= parts[pi].rows) {
+            lr -= parts[pi].rows;
+            pi++;
+          }
+        }
+        const int n_mat = pair ? 2 : 1;
+        for (int mt = 0; mt < n_mat; mt++) {
+          const TilePart& tp = parts[pair ? mt : pi];
+          const int kind = op.seg[tp.seg].kind;
+          const uint32_t row = stage + tp.soff + ((uint32_t)(uintptr_t)tp.src & 15u) + (uint32_t)(pair ? u : lr) * op.row_bytes[tp.seg];
+          float a = 0.0f;
+          if (u < R_rows) {
+            if (kind == Q4_0) a = row_chain_q80<Q4_0>(row, sxa, nb, k);
+            else if (kind == Q5_0) a = row_chain_q80<Q5_0>(row, sxa, nb, k);
+            else a = row_chain_q80<Q8_0>(row, sxa, nb, k);
+          }
+          // ((a0+a4)+(a2+a6)) + ((a1+a5)+(a3+a7)) over the row's eight lanes
+          a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 4));
+          a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 2));
+          a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 1));
+          v[mt] = a;
+        }
+        if (u < R_rows && k == 0) {
+          if (pair) {
+            const int r = t0 + u;
+            op.seg[0].out[r] = epilogue == EPI_SILU_MUL ? silu_mul_exact(v[0], v[1]) : v[0];
+            op.seg[1].out[r] = v[1];
+          } else {
+            float* o = op.seg[parts[pi].seg].out + parts[pi].row0 + lr;
+            *o = epilogue == EPI_ACCUM ? fadd(__ldcg(o), v[0]) : v[0];
+          }
+        }
+      }
+    }
+    rot = (rot + n_pass) % n_warps;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&R.empty[cp.st]);
+    cp.advance(R.n_stages);
+  }
+}
+
 // ---- one matrix product with the same machinery ------------------------------------------
 // A single K-quant product (up to three matrices, or a gate/up pair) against one Q8_K
 // activation vector: the producer warp streams this CTA's rows through the ring while the
@@ -1078,8 +1176,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
 // products outside the one-kernel step (the operator API, models the step does not cover).
 struct StreamGemvParams {
   MegaOp op;
-  const void* x;  // Q8_K images (x_image) or reference-layout BlockQ8_K
+  const void* x;  // activation images (x_image) or reference-layout blocks
   int x_image;
+  int q80;        // matrices of the Q8_0 family (Q8_0 activations) instead of K-quants
   int n_stages, stage_bytes;
   int* err;
 };
@@ -1087,10 +1186,11 @@ struct StreamGemvParams {
 __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const StreamGemvParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   // [stages][sx images][barriers 128 B][abort]
-  const int nb = P.op.cols >> 8;
+  const int nb = P.q80 ? P.op.cols >> 5 : P.op.cols >> 8;
+  const int xstride = P.q80 ? X0_STRIDE : XK_STRIDE;
   uint8_t* stages = smem;
   uint8_t* sx = stages + (size_t)P.n_stages * P.stage_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sx + (size_t)nb * XK_STRIDE);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sx + (size_t)nb * xstride);
   volatile int* abort = reinterpret_cast<volatile int*>(bars + MEGA_BAR_BYTES / 8);
   Ring R;
   R.stages = stages;
@@ -1123,7 +1223,14 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   CtaGroup g{(int)threadIdx.x, MEGA_CONSUMER_WARPS * 32, 1};
   if (P.x_image) {
     const uint4* src4 = reinterpret_cast<const uint4*>(P.x);
-    for (int i = g.tid; i < nb * (XK_STRIDE / 16); i += g.nthreads) reinterpret_cast<uint4*>(sx)[i] = src4[i];
+    for (int i = g.tid; i < nb * (xstride / 16); i += g.nthreads) reinterpret_cast<uint4*>(sx)[i] = src4[i];
+  } else if (P.q80) {
+    // BlockQ8_0 {f32 d; i8 qs[32]} (quant.rs:16-20) -> image {qs; d}
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(P.x);
+    for (int i = g.tid; i < nb * 9; i += g.nthreads) {
+      const int b = i / 9, w = i - b * 9;
+      *reinterpret_cast<uint32_t*>(sx + b * X0_STRIDE + (w == 0 ? X0_D : (w - 1) * 4)) = src[i];
+    }
   } else {
     const uint32_t* src = reinterpret_cast<const uint32_t*>(P.x);
     for (int i = g.tid; i < nb * 73; i += g.nthreads) {
@@ -1134,7 +1241,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   }
   g.sync();
   RingPos cp{0, 0u};
-  consume_op(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, 0u);
+  if (P.q80) consume_op_q80(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
+  else consume_op(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, 0u);
 }
 
 

@@ -124,6 +124,15 @@ class Context:
     def matmul(self, kind: int, out, w, xs, m: int, rows: int, cols: int):
         check(L.load().aotcu_matmul(self.h, kind, _dp(out), _dp(w), _dp(xs), m, rows, cols))
 
+    def bench_matmul(self, kind: int, out, w, copy_stride: int, n_copies: int, xs, m: int, rows: int, cols: int,
+                     iters: int) -> float:
+        """Average milliseconds per launch of the (m x cols) by (rows x cols) product, timed on the
+        device over `iters` back-to-back launches that rotate through `n_copies` copies of `w`."""
+        ms = C.c_float(0.0)
+        check(L.load().aotcu_bench_matmul(self.h, kind, _dp(out), _dp(w), copy_stride, n_copies, _dp(xs), m, rows, cols,
+                                          iters, C.byref(ms)))
+        return float(ms.value)
+
     def matvec_k_static(self, kind: int, out, w, x_f32, rows: int, cols: int):
         """K-quant product of an f32 device vector through the library's built-in activation
         area: no device allocation anywhere on this call path (see include/aot_cuda.h)."""

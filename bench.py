@@ -100,6 +100,93 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
+L2_BYTES = 126 * 1024 * 1024
+KINDS = {"f32": 0, "f16": 1, "bf16": 2, "q4_0": 3, "q5_0": 4, "q8_0": 5, "q4_k": 6, "q5_k": 7, "q6_k": 8}
+
+
+def _synth_matrix(pkg, kind: int, rows: int, cols: int, seed: int) -> np.ndarray:
+    """Seeded random blocks of one quant type, fields uniform as in BASELINE.json configs[0]."""
+    rb = pkg.lib.row_bytes(kind, cols)
+    w = np.zeros(rows * rb, dtype=np.uint8)
+    pkg.lib.check(pkg.lib.load().aotcu_synth_tensor(kind, rows, cols, 1e-3, 1e-2, seed, w.ctypes.data))
+    return w
+
+
+def time_product(pkg, ctx, kind: int, rows: int, cols: int, m: int, iters: int, host_w=None):
+    """Device time per launch of the (m x cols)·(rows x cols)^T product with the weights streamed
+    from HBM: the launches rotate through enough copies of the matrix to exceed the L2 size.
+    Returns (microseconds per launch, weight bytes, copies)."""
+    w = host_w if host_w is not None else _synth_matrix(pkg, kind, rows, cols, 7)
+    copies = max(1, -(-int(1.25 * L2_BYTES) // w.nbytes))
+    stride = (w.nbytes + 255) & ~255
+    dw = ctx.alloc(stride * copies)
+    for i in range(copies):
+        dw.upload(w, i * stride)
+    x = np.random.default_rng(5).standard_normal(m * cols).astype(np.float32)
+    dxf = ctx.to_device(x)
+    if kind >= KINDS["q4_k"]:      # K-quants take Q8_K activation blocks (292 bytes per 256 values)
+        dx = ctx.alloc(m * cols // 256 * 292)
+        ctx.quantize_q8_k(dxf, m * cols, dx)
+    elif kind >= KINDS["q4_0"]:    # Q4_0 / Q5_0 / Q8_0 take Q8_0 blocks (36 bytes per 32 values)
+        dx = ctx.alloc(m * cols // 32 * 36)
+        ctx.quantize_q8_0(dxf, m * cols, dx)
+    else:                          # float kinds take f32
+        dx = dxf
+    dout = ctx.alloc(m * rows * 4)
+    ms = ctx.bench_matmul(kind, dout, dw, stride, copies, dx, m, rows, cols, iters)
+    dw.free(); dx.free(); dout.free()
+    if dxf is not dx:
+        dxf.free()
+    return ms * 1e3, w.nbytes, copies
+
+
+def cpu_matvec_gbs(pkg, kind: int, rows: int, cols: int, threads: int, seconds: float = 2.0):
+    """The oracle's matvec on the host cores (weights larger than the CPU caches are not
+    arranged for: a 6.5 MB matrix is cache resident there, as it is in the reference's own
+    micro-benchmarks)."""
+    from oracle import binding as ob
+    w = _synth_matrix(pkg, kind, rows, cols, 7)
+    x = np.random.default_rng(5).standard_normal(cols).astype(np.float32)
+    q = ob.quantize_act(kind, x)
+    pool, tab = ob.Pool(threads), ob.detect_table()
+    ob.matvec(pool, tab, kind, w, q, rows, cols)
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
+        ob.matvec(pool, tab, kind, w, q, rows, cols)
+        n += 1
+    dt = time.perf_counter() - t0
+    return w.nbytes * n / dt / 1e9, n
+
+
+def prompt_tokens_n(vocab: int, n: int):
+    return np.random.default_rng(PROMPT_SEED + 1).integers(0, vocab, n).tolist()
+
+
+def run_sweep(args):
+    """BASELINE.json configs[4]: every quant type at four matrix shapes, M = 1 and M = 64."""
+    pkg = graft.import_package()
+    ctx = pkg.Context(0)
+    peak, peak_src = measured_peak_gbs()
+    shapes = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]
+    if args.sweep_small:
+        shapes = shapes[:2]
+    rows_out = []
+    for name in ("q4_0", "q5_0", "q8_0", "q4_k", "q5_k", "q6_k", "f16", "bf16"):
+        kind = KINDS[name]
+        for rows, cols in shapes:
+            w = _synth_matrix(pkg, kind, rows, cols, 7)
+            for m in (1, 64):
+                iters = 20 if m == 1 else 5
+                us, nbytes, copies = time_product(pkg, ctx, kind, rows, cols, m, iters, host_w=w)
+                rows_out.append({"kind": name, "rows": rows, "cols": cols, "m": m, "us_per_launch": round(us, 2),
+                                 "weight_gbs": round(nbytes / us / 1e3, 1), "frac_of_hbm_peak": round(nbytes / us / 1e3 / peak, 4),
+                                 "tera_ops": round(2.0 * rows * cols * m / us / 1e6, 2), "copies": copies})
+            del w
+    print(json.dumps({"metric": "quant_kernel_sweep", "unit": "GB/s of weight bytes per launch", "peak": peak,
+                      "peak_source": peak_src, "l2_policy": "launches rotate through copies of the matrix that together exceed L2",
+                      "rows": rows_out}))
+
+
 def prompt_tokens(vocab: int):
     return np.random.default_rng(PROMPT_SEED).integers(0, vocab, PROMPT_LEN).tolist()
 
@@ -220,6 +307,26 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     sweep_ms, sweep_launches, sweep_bytes = g.gemv_sweep(20)
     gemv_gbs = sweep_bytes / (sweep_ms * 1e-3) / 1e9
 
+    # ---- configs[0]: one Q4_K matvec, 5632 x 2048, weights streamed from HBM ----------------
+    mv_us, mv_bytes, mv_copies = time_product(pkg, ctx, KINDS["q4_k"], 5632, 2048, 1, 200)
+
+    # ---- configs[2]: a 512-token prompt in chunks of 64 --------------------------------------
+    p_tokens = prompt_tokens_n(d.vocab, 512)
+    gp = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 1024, 64)
+
+    def prompt_pass():
+        for c0 in range(0, 512, 64):
+            gp.forward_batch(p_tokens[c0:c0 + 64], c0, c0 + 64 == 512)
+
+    prompt_pass()
+    ctx.sync()
+    barrier()
+    ctx.timer_start()
+    prompt_pass()
+    prompt_ms = max_over_ranks(ctx.timer_stop())
+    barrier()
+    gp.close()
+
     if rank != 0:
         ranks.close()
         return
@@ -236,6 +343,23 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         cpu = {"value": cpu_tps, "unit": UNIT, "cores": threads, "kind": "port", "host_cores": cores,
                "tok_s_by_threads": {str(k): v[0] for k, v in tried.items()},
                "sample": f"{cpu_steps} decode steps of the same model after the prompt and 2 warm-up tokens ({cpu_dt:.1f} s), best of the reference's default thread count and all host threads"}
+
+    extra_cpu = {}
+    if cpu:
+        from oracle import binding as ob
+        cpu_threads = cpu["cores"]
+        gbs, n_calls = cpu_matvec_gbs(pkg, KINDS["q4_k"], 5632, 2048, cpu_threads)
+        extra_cpu["matvec"] = {"value": gbs, "unit": "GB/s", "cores": cpu_threads, "kind": "port",
+                               "sample": f"{n_calls} calls of the oracle's matvec_q4_k, 5632x2048 (cache resident on the host)"}
+        om = ob.model_from_spec(spec, 1024, 64, n_threads=cpu_threads)
+        om.forward_batch(p_tokens[:64], 0, False)
+        t0 = time.perf_counter()
+        om.forward_batch(p_tokens[64:128], 64, False)
+        om.forward_batch(p_tokens[128:192], 128, True)
+        dt = time.perf_counter() - t0
+        om.close()
+        extra_cpu["prompt"] = {"value": 128 / dt, "unit": "tok/s", "cores": cpu_threads, "kind": "port",
+                               "sample": f"chunks 2 and 3 (128 tokens) of the same prompt ({dt:.1f} s)"}
 
     out = {
         "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
@@ -255,6 +379,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "gemv_kernel_sweep": {"kernel": "gemv_q8k_kernel", "achieved": gemv_gbs, "unit": "GB/s", "frac": gemv_gbs / peak,
                               "launches": int(sweep_launches), "algorithmic_bytes": int(sweep_bytes),
                               "avg_launch_us": sweep_ms * 1e3 / sweep_launches},
+        "matvec_q4_k": {"workload": "configs[0]: Q4_K matvec, W 5632x2048, x f32 quantized to Q8_K", "value": mv_bytes / mv_us / 1e3,
+                        "unit": "GB/s", "frac": mv_bytes / mv_us / 1e3 / peak, "us_per_launch": mv_us,
+                        "weight_bytes": int(mv_bytes), "copies_rotated": int(mv_copies),
+                        "cpu_baseline": extra_cpu.get("matvec")},
+        "prompt": {"workload": "configs[2]: 512-token prompt in chunks of 64 on the same model", "value": world * 512 / (prompt_ms * 1e-3),
+                   "unit": "tok/s", "ms": prompt_ms, "cpu_baseline": extra_cpu.get("prompt")},
         "generated_head": [int(x) for x in ids[:8]],
     }
     if cpu:
@@ -271,11 +401,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--pdl", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="quant-type kernel sweep (configs[4]) instead of the decode benchmark")
+    ap.add_argument("--sweep-small", action="store_true", help="with --sweep: only the two smaller shapes")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     graft.build()
+    if args.sweep:
+        if rank == 0:
+            run_sweep(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
     else:

@@ -271,6 +271,15 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value);
 int aotcu_bench_gemv_sweep(aotcu_gpu* g, int iters, float* ms_per_sweep, uint64_t* launches_per_sweep,
                            uint64_t* bytes_per_sweep);
 
+/* Benchmark helper (the role of the per-kind `bench_ops` table of the reference,
+ * crates/aot-kernels/tests/metal.rs:456-641): launches the product of `m` activation rows
+ * (m = 1: aotcu_matvec, m > 1: aotcu_matmul) `iters` times back to back inside one pair of
+ * CUDA events and returns the average milliseconds per launch. `w` holds `n_copies` copies
+ * of the matrix, `copy_stride` bytes apart; launch i uses copy i % n_copies, so that with
+ * n_copies * matrix bytes above the L2 size every launch streams its weights from HBM. */
+int aotcu_bench_matmul(aotcu_ctx* ctx, int kind, float* out, const uint8_t* w, size_t copy_stride, size_t n_copies,
+                       const void* xs, size_t m, size_t rows, size_t cols, int iters, float* ms_per_launch);
+
 /* Tuning aid for the one-kernel decode step (no counterpart in the reference): runs
  * one step and returns the SM cycles CTA `cta` spent in each of its 16 phases
  * (slots 16..31: sub-phases of the first norm and of attention). */
