@@ -12,6 +12,7 @@
 // (integers exact, mul/sub unfused); one thread per row then adds the terms in
 // block order, which is the reference's `sumf += ...` loop.
 #pragma once
+#include <cuda_fp16.h>
 #include "blockmath.cuh"
 #include "device_utils.cuh"
 #include "expf_exact.cuh"
@@ -514,9 +515,27 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_q80_kernel(const GemvParams
 // (simd_avx2.rs:433-493), the 8-lane tree, then the unfused scalar tail. Weights
 // are read straight from global memory.
 __device__ __forceinline__ float load_wf(int kind, const uint8_t* wrow, int j) {
-  if (kind == F32) return reinterpret_cast<const float*>(wrow)[j];
-  uint32_t h = reinterpret_cast<const uint16_t*>(wrow)[j];
-  return kind == F16 ? half_bits_to_float(h) : bf16_bits_to_float(h);
+  if (kind == F32) return __ldg(reinterpret_cast<const float*>(wrow) + j);
+  const unsigned short h = __ldg(reinterpret_cast<const unsigned short*>(wrow) + j);
+  // both conversions are exact (every f16 / bf16 value is an f32 value)
+  return kind == F16 ? __half2float(__ushort_as_half(h)) : __uint_as_float((uint32_t)h << 16);
+}
+
+// One AVX2 lane chain of a row: acc = fma(w[j], x[j], acc) for j = k, k+8, ... below n8.
+// Weights are requested 32 steps ahead of the adds so that enough bytes are in flight.
+template <int KIND>
+__device__ __forceinline__ float float_lane_chain(const uint8_t* wrow, const float* x, int k, int n8) {
+  float acc = 0.0f;
+  int j = k;
+  for (; j + 8 * 31 < n8; j += 8 * 32) {
+    float w[32];
+#pragma unroll
+    for (int u = 0; u < 32; u++) w[u] = load_wf(KIND, wrow, j + 8 * u);
+#pragma unroll
+    for (int u = 0; u < 32; u++) acc = ffma(w[u], x[j + 8 * u], acc);
+  }
+  for (; j < n8; j += 8) acc = ffma(load_wf(KIND, wrow, j), x[j], acc);
+  return acc;
 }
 
 __global__ void __launch_bounds__(256) gemv_float_kernel(const GemvParams P) {
@@ -547,8 +566,9 @@ __global__ void __launch_bounds__(256) gemv_float_kernel(const GemvParams P) {
         const uint8_t* wrow = P.seg[sg].w + (size_t)(live ? r : 0) * kind_row_bytes(kind, P.cols);
         float acc = 0.0f;
         if (live) {
-#pragma unroll 8
-          for (int j = k; j < n8; j += 8) acc = ffma(load_wf(kind, wrow, j), x[j], acc);
+          if (kind == F16) acc = float_lane_chain<F16>(wrow, x, k, n8);
+          else if (kind == BF16) acc = float_lane_chain<BF16>(wrow, x, k, n8);
+          else acc = float_lane_chain<F32>(wrow, x, k, n8);
         }
         float s1 = fadd(acc, __shfl_xor_sync(0xffffffffu, acc, 4));  // a_k + a_{k+4}
         float t1 = fadd(s1, __shfl_xor_sync(0xffffffffu, s1, 2));
