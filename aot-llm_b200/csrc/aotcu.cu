@@ -13,6 +13,8 @@
 #include <string>
 #include <vector>
 
+#include <dlfcn.h>
+
 #include "../../include/aot_cuda.h"
 #include "gemv.cuh"
 #include "gemm.cuh"
@@ -335,6 +337,39 @@ __global__ void block_sums_kernel(int kind, const uint8_t* w, const uint8_t* x, 
 }
 
 // ---- device State + model (the `Gpu` of metal.rs) ------------------------------------------------
+// ---- tensor parallel exchange (NCCL, loaded at run time) ----------------------------------
+// Row-sharded models sum the partial outputs of attn_output and ffn_down over the ranks.
+// NCCL is not linked: the host names the shared library (the one its process already
+// uses), and the five entry points needed are looked up with dlsym.
+struct TpState {
+  void* lib = nullptr;
+  void* comm = nullptr;   // ncclComm_t
+  int rank = 0, world = 1;
+  // ncclResult_t (0 = success) f(...)
+  int (*get_unique_id)(void*) = nullptr;
+  int (*comm_init_rank)(void**, int, /* ncclUniqueId by value: 128 bytes */ struct NcclId, int) = nullptr;
+  int (*all_reduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*comm_destroy)(void*) = nullptr;
+  const char* (*get_error_string)(int) = nullptr;
+};
+struct NcclId {
+  char bytes[128];
+};
+constexpr int NCCL_FLOAT32 = 7, NCCL_SUM = 0;  // ncclFloat32, ncclSum of nccl.h
+
+static int tp_load(TpState* t, const char* path) {
+  t->lib = dlopen(path && *path ? path : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!t->lib) return fail(AOTCU_ERR_UNSUPPORTED, "cannot load NCCL (%s): %s", path ? path : "libnccl.so.2", dlerror());
+  t->get_unique_id = reinterpret_cast<decltype(t->get_unique_id)>(dlsym(t->lib, "ncclGetUniqueId"));
+  t->comm_init_rank = reinterpret_cast<decltype(t->comm_init_rank)>(dlsym(t->lib, "ncclCommInitRank"));
+  t->all_reduce = reinterpret_cast<decltype(t->all_reduce)>(dlsym(t->lib, "ncclAllReduce"));
+  t->comm_destroy = reinterpret_cast<decltype(t->comm_destroy)>(dlsym(t->lib, "ncclCommDestroy"));
+  t->get_error_string = reinterpret_cast<decltype(t->get_error_string)>(dlsym(t->lib, "ncclGetErrorString"));
+  if (!t->get_unique_id || !t->comm_init_rank || !t->all_reduce || !t->comm_destroy || !t->get_error_string)
+    return fail(AOTCU_ERR_UNSUPPORTED, "the NCCL library lacks a required entry point");
+  return 0;
+}
+
 struct aotcu_gpu {
   aotcu_ctx* c = nullptr;
   aotcu_model_head head;
@@ -365,6 +400,7 @@ struct aotcu_gpu {
   bool use_graph = true;
   // Persistent one-kernel decode step (mega.cuh), when the model qualifies.
   bool mega_ok = false, use_mega = true;
+  TpState* tp = nullptr;              // set by aotcu_tp_attach: this Gpu holds one shard of the model
   StepLayer* d_step_layers = nullptr;
   unsigned* d_grid_bar = nullptr;     // [0] barrier arrivals of one launch, [1] launch count
   LLWord* d_ll = nullptr;             // tagged activation vectors of the one-kernel step
@@ -614,6 +650,19 @@ static int gpu_attention(aotcu_gpu* g, float* out, const float* q, size_t li, co
 // ---- the generated forward pass, interpreted (emit.rs) -----------------------------------------------
 // One transformer block for m tokens. `pos_ptr` (device) is used by decode steps so a
 // captured graph can be replayed for any position; batches pass pos0 by value.
+static int tp_all_reduce(aotcu_gpu* g, float* buf, size_t n) {
+  TpState* t = g->tp;
+  const int r = t->all_reduce(buf, buf, n, NCCL_FLOAT32, NCCL_SUM, t->comm, g->c->stream);
+  if (r != 0) return fail(AOTCU_ERR_CUDA, "ncclAllReduce: %s", t->get_error_string(r));
+  note_write(g, buf);
+  return 0;
+}
+
+static int gpu_add(aotcu_gpu* g, float* x, const float* y, size_t n) {
+  note_write(g, x);
+  return launch(g->c, add_inplace_kernel, dim3(grid_for(g->c, n, 256)), dim3(256), 0, x, y, n);
+}
+
 static int layer_forward(aotcu_gpu* g, size_t li, const int* pos_ptr, size_t pos0, size_t m, bool batch) {
   const aotcu_dims& d = g->head.dims;
   const aotcu_layer& l = g->layers[li];
@@ -644,9 +693,17 @@ static int layer_forward(aotcu_gpu* g, size_t li, const int* pos_ptr, size_t pos
   // emit.rs:287
   if (int rc = gpu_attention(g, xb, q, li, pos_ptr, pos0, m, window)) return rc;
   // emit.rs:288-295
+  const bool tp = g->tp && g->tp->world > 1;
   if (d.post_norms) {
     if (int rc = gpu_matmul(g, xb2, l.wo, xb, m, 0)) return rc;
+    if (tp)
+      if (int rc = tp_all_reduce(g, xb2, m * dim)) return rc;
     if (int rc = gpu_rmsnorm(g, x, dim, xb2, dim, wf32(g, l.attn_post_norm), dim, m, d.eps, 1, false)) return rc;
+  } else if (tp) {
+    // this rank's heads give a partial attn_output; the ranks' partials are summed, then joined
+    if (int rc = gpu_matmul(g, xb2, l.wo, xb, m, 0)) return rc;
+    if (int rc = tp_all_reduce(g, xb2, m * dim)) return rc;
+    if (int rc = gpu_add(g, x, xb2, m * dim)) return rc;
   } else {
     if (int rc = gpu_matmul(g, x, l.wo, xb, m, 1)) return rc;
   }
@@ -655,7 +712,13 @@ static int layer_forward(aotcu_gpu* g, size_t li, const int* pos_ptr, size_t pos
   if (int rc = gpu_gate_up(g, hb, hb2, l.gate, l.up, xb, m)) return rc;
   if (d.post_norms) {
     if (int rc = gpu_matmul(g, xb2, l.down, hb, m, 0)) return rc;
+    if (tp)
+      if (int rc = tp_all_reduce(g, xb2, m * dim)) return rc;
     if (int rc = gpu_rmsnorm(g, x, dim, xb2, dim, wf32(g, l.ffn_post_norm), dim, m, d.eps, 1, false)) return rc;
+  } else if (tp) {
+    if (int rc = gpu_matmul(g, xb2, l.down, hb, m, 0)) return rc;
+    if (int rc = tp_all_reduce(g, xb2, m * dim)) return rc;
+    if (int rc = gpu_add(g, x, xb2, m * dim)) return rc;
   } else {
     if (int rc = gpu_matmul(g, x, l.down, hb, m, 1)) return rc;
   }
@@ -1332,6 +1395,10 @@ void aotcu_gpu_free(aotcu_gpu* g) {
   cudaFree(g->d_step_layers);
   cudaFree(g->d_grid_bar);
   cudaFree(g->d_ll);
+  if (g->tp) {
+    if (g->tp->comm) g->tp->comm_destroy(g->tp->comm);
+    delete g->tp;
+  }
   if (g->h_pinned) cudaFreeHost(g->h_pinned);
   delete g;
 }
@@ -1536,6 +1603,55 @@ int aotcu_generate(aotcu_gpu* g, uint32_t token, size_t pos, size_t n_steps, uin
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   return check_device_errors(c);
+}
+
+int aotcu_tp_unique_id(const char* nccl_library, uint8_t out_id[128]) {
+  ARG_CHECK(out_id, "NULL argument");
+  TpState t;
+  if (int rc = tp_load(&t, nccl_library)) return rc;
+  NcclId id;
+  const int r = t.get_unique_id(&id);
+  if (r != 0) return fail(AOTCU_ERR_CUDA, "ncclGetUniqueId: %s", t.get_error_string(r));
+  memcpy(out_id, id.bytes, 128);
+  return 0;  // the library stays loaded
+}
+
+int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world, const uint8_t id[128]) {
+  ARG_CHECK(g && id, "NULL argument");
+  ARG_CHECK(world >= 1 && rank >= 0 && rank < world, "bad rank %d of %d", rank, world);
+  ARG_CHECK(!g->tp, "this Gpu already belongs to a tensor-parallel group");
+  if (int rc = ctx_set_device(g->c)) return rc;
+  TpState* t = new TpState();
+  t->rank = rank;
+  t->world = world;
+  if (world > 1) {
+    if (int rc = tp_load(t, nccl_library)) {
+      delete t;
+      return rc;
+    }
+    NcclId nid;
+    memcpy(nid.bytes, id, 128);
+    const int r = t->comm_init_rank(&t->comm, world, nid, rank);
+    if (r != 0) {
+      int rc = fail(AOTCU_ERR_CUDA, "ncclCommInitRank: %s", t->get_error_string(r));
+      delete t;
+      return rc;
+    }
+  }
+  // The one-kernel step has no exchange between ranks: sharded models take the per-operator path.
+  CU_TRY(cudaStreamSynchronize(g->c->stream));
+  for (int i = 0; i < 2; i++)
+    if (g->decode_graph[i]) {
+      cudaGraphExecDestroy(g->decode_graph[i]);
+      g->decode_graph[i] = nullptr;
+    }
+  if (g->gen_graph) {
+    cudaGraphExecDestroy(g->gen_graph);
+    g->gen_graph = nullptr;
+  }
+  g->tp = t;
+  if (world > 1) g->mega_ok = false;
+  return 0;
 }
 
 uint64_t aotcu_gpu_dispatches(aotcu_gpu* g) { return g ? g->c->launches : 0; }

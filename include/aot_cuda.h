@@ -264,6 +264,19 @@ uint64_t aotcu_gpu_dispatches(aotcu_gpu* g);
  * launch between kernels, default 0). */
 int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value);
 
+/* Tensor parallel decode (no counterpart in the reference, which runs on one device): each
+ * rank creates an aotcu_gpu from its shard of the model (query/KV heads and FFN rows split
+ * across ranks; attn_output and ffn_down split by columns on 256-weight boundaries) and
+ * joins a group. Inside the forward pass the ranks' partial attn_output and ffn_down rows
+ * are summed with an NCCL all-reduce on the context's stream before they join the residual
+ * stream. `nccl_library` names the NCCL shared object to load (NULL: "libnccl.so.2" from
+ * the loader path). One rank calls aotcu_tp_unique_id and hands the 128 bytes to all
+ * ranks by its own means; every rank then calls aotcu_tp_attach (collective). Sums across
+ * ranks change the order of f32 additions: results match the single-device path to
+ * rounding (1e-3 relative at the logits), not bit for bit. */
+int aotcu_tp_unique_id(const char* nccl_library, uint8_t out_id[128]);
+int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world, const uint8_t id[128]);
+
 /* Benchmark helper (no counterpart in the reference; its per-op figures come from
  * `bench_ops`, crates/aot-kernels/tests/metal.rs:456-641): times only the matrix
  * products of one decode step, back to back, and reports milliseconds per sweep,
