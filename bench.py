@@ -393,6 +393,73 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ranks.close()
 
 
+def run_tp(args, rank: int, world: int, local_rank: int):
+    """BASELINE.json configs[3]: Qwen3-8B-shaped decode, row-sharded over the ranks, one token
+    stream (strong scaling). Every rank builds the synthetic model from the same seed and
+    keeps its shard."""
+    pkg = graft.import_package()
+    ranks = pkg.ranks.Ranks(pkg.ranks.RankInfo(rank, world, local_rank), backend="nccl")
+    t_build = time.perf_counter()
+    full = pkg.model.qwen3_8b(n_layer=args.tp_layers)
+    full_bytes = full.weight_bytes_per_token()
+    spec = pkg.tp.shard_spec(full, rank, world)
+    del full
+    t_build = time.perf_counter() - t_build
+    d = spec.head.dims
+    ctx = pkg.Context(local_rank)
+    n_prompt, steps, warmup = 512, args.steps, max(args.warmup, 3)
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_prompt + warmup + steps + 8, 64)
+    pkg.tp.attach(g, rank, world, pkg.tp.exchange_id(ranks, pkg.tp.unique_id))
+    toks = prompt_tokens_n(d.vocab, n_prompt)
+
+    def prompt_pass():
+        for c0 in range(0, n_prompt, 64):
+            g.forward_batch(toks[c0:c0 + 64], c0, c0 + 64 == n_prompt)
+
+    prompt_pass()
+    ctx.sync()
+    ranks.barrier()
+    ctx.timer_start()
+    prompt_pass()
+    prompt_ms = ranks.max_over_ranks(ctx.timer_stop())
+    first = int(np.argmax(g.logits()))
+    warm_ids, _ = g.generate(first, n_prompt, warmup)
+    ctx.sync()
+    ranks.barrier()
+    launches0 = g.dispatches()
+    with ClockSampler(local_rank) as clk:
+        ids, ms = g.generate(int(warm_ids[-1]), n_prompt + warmup, steps)
+        ctx.sync()
+    ranks.barrier()
+    launches = g.dispatches() - launches0
+    ms = ranks.max_over_ranks(ms)
+    tps = steps / (ms * 1e-3)
+    peak, peak_src = measured_peak_gbs()
+    mid_pos = n_prompt + warmup + steps // 2
+    step_bytes = spec.weight_bytes_per_token() + spec.kv_bytes_per_position() * (mid_pos + 1)
+    gbs = step_bytes / (ms * 1e-3 / steps) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 block dot products with f32 accumulation (Q8 activations x Q4_K/Q6_K weights)", "data": "synthetic",
+            "config": {"workload": "configs[3]: Qwen3-8B-shaped decode, Q4_K_M mix, random-init weights, 512-token prompt then greedy decode; "
+                                   "query/KV heads and FFN rows sharded over the ranks, all-reduce after attn_output and ffn_down",
+                       "dim": d.dim, "hidden_per_rank": d.hidden, "n_layer": d.n_layer, "n_head_per_rank": d.n_head,
+                       "n_kv_head_per_rank": d.n_kv_head, "head_dim": d.head_dim, "vocab": d.vocab, "parallelism": f"tp{world}",
+                       "weight_bytes_per_token_whole_model": int(full_bytes),
+                       "weight_bytes_per_token_per_rank": int(spec.weight_bytes_per_token()),
+                       "l2_policy": "inputs_larger_than_l2"},
+            "clocks": clk.summary(), "gpu_launches": int(launches),
+            "prompt": {"value": n_prompt / (prompt_ms * 1e-3), "unit": "tok/s", "ms": prompt_ms},
+            "roofline": {"bound": "hbm", "kernel": "whole decode step of one rank", "achieved": gbs, "peak": peak, "unit": "GB/s",
+                         "frac": gbs / peak, "peak_source": peak_src, "traffic": None,
+                         "algorithmic_bytes_per_launch": int(step_bytes), "roofline_tok_s": peak * 1e9 / step_bytes},
+            "host_build_s": t_build, "generated_head": [int(x) for x in ids[:8]],
+        }))
+    ranks.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -401,6 +468,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--pdl", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp", action="store_true", help="configs[3]: Qwen3-8B-shaped decode sharded over the ranks")
+    ap.add_argument("--tp-layers", type=int, default=36)
     ap.add_argument("--sweep", action="store_true", help="quant-type kernel sweep (configs[4]) instead of the decode benchmark")
     ap.add_argument("--sweep-small", action="store_true", help="with --sweep: only the two smaller shapes")
     args = ap.parse_args()
@@ -411,6 +480,9 @@ def main():
     if args.sweep:
         if rank == 0:
             run_sweep(args)
+        return
+    if args.tp:
+        run_tp(args, rank, world, local_rank)
         return
     if args.impl == "reference":
         run_reference(args, rank, world)
