@@ -401,6 +401,8 @@ struct aotcu_gpu {
   // Persistent one-kernel decode step (mega.cuh), when the model qualifies.
   bool mega_ok = false, use_mega = true;
   TpState* tp = nullptr;              // set by aotcu_tp_attach: this Gpu holds one shard of the model
+  LLWord* tp_inbox = nullptr;         // partial rows from every rank (aotcu_tp_inbox_handle)
+  void* tp_peer_map[8] = {};          // peers' inboxes mapped into this process
   StepLayer* d_step_layers = nullptr;
   unsigned* d_grid_bar = nullptr;     // [0] barrier arrivals of one launch, [1] launch count
   LLWord* d_ll = nullptr;             // tagged activation vectors of the one-kernel step
@@ -1399,6 +1401,9 @@ void aotcu_gpu_free(aotcu_gpu* g) {
     if (g->tp->comm) g->tp->comm_destroy(g->tp->comm);
     delete g->tp;
   }
+  for (void* p : g->tp_peer_map)
+    if (p) cudaIpcCloseMemHandle(p);
+  cudaFree(g->tp_inbox);
   if (g->h_pinned) cudaFreeHost(g->h_pinned);
   delete g;
 }
@@ -1616,11 +1621,56 @@ int aotcu_tp_unique_id(const char* nccl_library, uint8_t out_id[128]) {
   return 0;  // the library stays loaded
 }
 
-int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world, const uint8_t id[128]) {
+constexpr int TP_MAX_WORLD = 8;
+
+int aotcu_tp_inbox_handle(aotcu_gpu* g, uint8_t out_handle[64]) {
+  ARG_CHECK(g && out_handle, "NULL argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (int rc = ctx_set_device(g->c)) return rc;
+  if (!g->tp_inbox) {
+    const size_t words = (size_t)2 * TP_MAX_WORLD * g->head.dims.dim;
+    CU_TRY(cudaMalloc(&g->tp_inbox, words * sizeof(LLWord)));
+    CU_TRY(cudaMemset(g->tp_inbox, 0, words * sizeof(LLWord)));
+  }
+  cudaIpcMemHandle_t h;
+  CU_TRY(cudaIpcGetMemHandle(&h, g->tp_inbox));
+  memcpy(out_handle, &h, 64);
+  return 0;
+}
+
+int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world, const uint8_t id[128],
+                    const uint8_t* peer_handles) {
   ARG_CHECK(g && id, "NULL argument");
-  ARG_CHECK(world >= 1 && rank >= 0 && rank < world, "bad rank %d of %d", rank, world);
+  ARG_CHECK(world >= 1 && world <= TP_MAX_WORLD && rank >= 0 && rank < world, "bad rank %d of %d (at most %d ranks)", rank,
+            world, TP_MAX_WORLD);
   ARG_CHECK(!g->tp, "this Gpu already belongs to a tensor-parallel group");
   if (int rc = ctx_set_device(g->c)) return rc;
+  CU_TRY(cudaStreamSynchronize(g->c->stream));
+  // Peers' inboxes first, the (blocking, collective) communicator second: once any rank is
+  // back from this call, every rank has mapped every inbox.
+  const bool fused = world > 1 && peer_handles && g->tp_inbox && g->mega_ok;
+  if (fused) {
+    TpExchange& x = g->step_params.tp;
+    x.world = world;
+    x.rank = rank;
+    x.dim = g->head.dims.dim;
+    for (int r = 0; r < world; r++) {
+      if (r == rank) {
+        x.inbox[r] = g->tp_inbox;
+        continue;
+      }
+      cudaIpcMemHandle_t h;
+      memcpy(&h, peer_handles + (size_t)r * 64, 64);
+      void* p = nullptr;
+      cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d): %s", r, cudaGetErrorString(e));
+      g->tp_peer_map[r] = p;
+      x.inbox[r] = reinterpret_cast<LLWord*>(p);
+    }
+    // every rank counts launches from the same value, so tags agree across GPUs
+    const unsigned one = 1;
+    CU_TRY(cudaMemcpy(g->d_grid_bar + 1, &one, sizeof(unsigned), cudaMemcpyHostToDevice));
+  }
   TpState* t = new TpState();
   t->rank = rank;
   t->world = world;
@@ -1638,8 +1688,6 @@ int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world,
       return rc;
     }
   }
-  // The one-kernel step has no exchange between ranks: sharded models take the per-operator path.
-  CU_TRY(cudaStreamSynchronize(g->c->stream));
   for (int i = 0; i < 2; i++)
     if (g->decode_graph[i]) {
       cudaGraphExecDestroy(g->decode_graph[i]);
@@ -1650,7 +1698,9 @@ int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world,
     g->gen_graph = nullptr;
   }
   g->tp = t;
-  if (world > 1) g->mega_ok = false;
+  // Without mapped inboxes the one-kernel step has no exchange between ranks: the sharded
+  // model then takes the per-operator path with NCCL all-reduces.
+  if (world > 1 && !fused) g->mega_ok = false;
   return 0;
 }
 

@@ -357,6 +357,38 @@ __device__ __forceinline__ void cta_rows(int span, int& c0, int& c1) {
   c1 = c0 + base + (b < rem ? 1 : 0);
 }
 
+// ---- tagged words across GPUs -----------------------------------------------------------------
+// Row-sharded models (each GPU holds some heads and some FFN rows) produce partial rows of
+// attn_output and ffn_down. A rank stores its partial of row i as a tagged word into slot
+// [product][its rank][i] of every rank's inbox (plain 8-byte stores to peer memory over
+// NVLink); the CTA that owns row i on each rank waits for the world's words, adds them in
+// rank order (so every rank gets the same bits) and publishes the new residual row locally.
+struct TpExchange {
+  int world, rank, dim;
+  LLWord* inbox[8];  // inbox of rank d (peer mapping), layout [2 products][world][dim]
+};
+
+__device__ __forceinline__ void ll_store_sys(LLWord* p, float v, uint32_t tag) {
+  const LLWord w = ((LLWord)tag << 32) | (LLWord)__float_as_uint(v);
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ float ll_wait_sys(const LLWord* p, uint32_t tag, volatile int* abort, int* err) {
+  LLWord w;
+  uint32_t it = 0;
+  for (;;) {
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    if ((uint32_t)(w >> 32) == tag) break;
+    if (++it >= LL_SPIN_LIMIT || ((it & 31u) == 31u && *abort)) {
+      if (!*abort) {
+        *abort = 1;
+        if (err) atomicOr(err, DEVERR_GRID_TIMEOUT);
+      }
+      break;
+    }
+  }
+  return __uint_as_float((uint32_t)w);
+}
+
 // ---- step description (built once by the host, lives in global memory) ------------------
 // One matrix-product phase as both the producer and the consumers see it. The row
 // space (concatenated rows, or shared rows in pair mode) is split evenly over the
@@ -390,6 +422,7 @@ struct StepParams {
   float *x;                                // plain copy of the final residual stream, for readers outside the kernel
   float *logits, *k_cache, *v_cache;
   unsigned* epoch;                         // launch count; bumped by CTA 0 when the kernel ends
+  TpExchange tp;                           // world > 1: this GPU holds one shard of the model
   const float* rope_table;
   int* step;  // {token, pos, n_generated}
   int* history;
@@ -506,7 +539,7 @@ __device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, Ring
 // is applied in the epilogue. `sx` holds the Q8_K images of the activation vector;
 // `op` lives in shared memory.
 __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp,
-                                           int n_warps, uint32_t tag) {
+                                           int n_warps, uint32_t tag, const TpExchange* tpx = nullptr, int which = 0) {
   const int rows_per_cta = op.rows_per_cta, tile_rows = op.tile_rows, pair = op.pair;
   const int epilogue = op.epilogue, nb = op.cols >> 8, ll = op.ll;
   int c0, c1;
@@ -592,7 +625,11 @@ __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, Ring
           const float v = narrow ? (row ? warp_row_dot_s(kind, row, sxa, nb) : 0.0f) : group_row_dot(row, kind, sxa, nb, L);
           if (u < R_rows && (lane & (L - 1)) == 0) {
             const int oi = parts[pi].row0 + lr;
-            if (ll) {
+            if (ll && tpx && epilogue == EPI_ACCUM) {
+              // a partial row of a sharded product: hand it to every rank (this one included)
+              for (int dst = 0; dst < tpx->world; dst++)
+                ll_store_sys(tpx->inbox[dst] + ((size_t)which * tpx->world + tpx->rank) * tpx->dim + oi, v, tag);
+            } else if (ll) {
               // a residual row is only ever written by its owner, so its old value needs no tag check
               LLWord* o = reinterpret_cast<LLWord*>(op.seg[parts[pi].seg].out) + oi;
               ll_store(o, epilogue == EPI_ACCUM ? fadd(ll_value(o), v) : v, tag);
@@ -1040,11 +1077,25 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     }
     if (!head) MEGA_PROF(slot);
     // q/k/v: tl+1, wo: tl+3, gate/up: tl+4, down: tl+5 (the head writes plain floats)
-    consume_op(op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, tl + (ph == 0 ? 1u : (uint32_t)ph + 2u));
+    const uint32_t tag_out = tl + (ph == 0 ? 1u : (uint32_t)ph + 2u);
+    const bool exchange = P.tp.world > 1 && (ph & 1) && !head;
+    consume_op(op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, tag_out, exchange ? &P.tp : nullptr, ph >> 1);
     if (head) break;
     // The next phase rewrites the activation images and the scratch rows; warps that are
     // done must also not start polling while others still compute.
     g.sync();
+    if (exchange) {
+      // The rows this CTA owns: wait for every rank's partial, add them in rank order, join
+      // the residual stream and publish the row for this GPU's CTAs.
+      int r0, r1;
+      cta_rows(P.dim, r0, r1);
+      for (int i = r0 + g.tid; i < r1; i += g.nthreads) {
+        const LLWord* in = P.tp.inbox[P.tp.rank] + (size_t)(ph >> 1) * P.tp.world * P.dim + i;
+        float sum = ll_wait_sys(in, tag_out, abort, P.err);
+        for (int src = 1; src < P.tp.world; src++) sum = fadd(sum, ll_wait_sys(in + (size_t)src * P.dim, tag_out, abort, P.err));
+        ll_store(P.xl + i, fadd(ll_value(P.xl + i), sum), tag_out);
+      }
+    }
     MEGA_PROF(slot + 1);
     if (ph == 0) {
       // attention, one head per CTA

@@ -331,5 +331,6 @@ class Gpu:
     def dispatches(self) -> int:
         return L.load().aotcu_gpu_dispatches(self.h)
 
-    def set_option(self, name: str, value: int):
-        check(L.load().aotcu_gpu_set_option(self.h, name.encode(), value))
+    def set_option(self, name: str, value: int) -> int:
+        """Sets a tuning switch; query names ("mega_available") return their value."""
+        return check(L.load().aotcu_gpu_set_option(self.h, name.encode(), value))

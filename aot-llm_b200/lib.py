@@ -137,7 +137,8 @@ SYMBOLS = {
     "aotcu_gpu_set_option": (_i, [_vp, C.c_char_p, _i]),
     "aotcu_bench_gemv_sweep": (_i, [_vp, _i, C.POINTER(_f), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "aotcu_tp_unique_id": (_i, [C.c_char_p, _vp]),
-    "aotcu_tp_attach": (_i, [_vp, C.c_char_p, _i, _i, _vp]),
+    "aotcu_tp_inbox_handle": (_i, [_vp, _vp]),
+    "aotcu_tp_attach": (_i, [_vp, C.c_char_p, _i, _i, _vp, _vp]),
     "aotcu_bench_matmul": (_i, [_vp, _i, _vp, _vp, _sz, _sz, _vp, _sz, _sz, _sz, _i, C.POINTER(_f)]),
     "aotcu_gpu_profile_step": (_i, [_vp, _u32, _sz, _i, _vp]),
     "aotcu_synth_quantize_row": (_i, [_i, _vp, _sz, _vp]),

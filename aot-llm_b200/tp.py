@@ -165,12 +165,47 @@ def unique_id(nccl_library: str | None = None) -> bytes:
     return bytes(buf)
 
 
-def attach(gpu, rank: int, world: int, uid: bytes, nccl_library: str | None = None) -> None:
-    """Collective: every rank calls it with the same 128-byte id (from `unique_id` on one rank)."""
+def inbox_handle(gpu) -> bytes:
+    """This rank's inbox for the other ranks' partial rows, as a 64-byte CUDA IPC handle."""
+    buf = (C.c_uint8 * 64)()
+    check(L.load().aotcu_tp_inbox_handle(gpu.h, buf))
+    return bytes(buf)
+
+
+def attach(gpu, rank: int, world: int, uid: bytes, nccl_library: str | None = None, peer_handles: bytes | None = None) -> None:
+    """Collective: every rank calls it with the same 128-byte id (from `unique_id` on one rank).
+    `peer_handles` = the ranks' inbox handles in rank order (world x 64 bytes) keeps the decode
+    step's exchange inside the one-kernel step; None sends every exchange through NCCL."""
     if len(uid) != 128:
         raise ValueError("the id is 128 bytes")
     buf = (C.c_uint8 * 128).from_buffer_copy(uid)
-    check(L.load().aotcu_tp_attach(gpu.h, (nccl_library or nccl_library_path()).encode(), rank, world, buf))
+    ph = None
+    if peer_handles is not None:
+        if len(peer_handles) != 64 * world:
+            raise ValueError("peer_handles holds 64 bytes per rank")
+        ph = (C.c_uint8 * len(peer_handles)).from_buffer_copy(peer_handles)
+    check(L.load().aotcu_tp_attach(gpu.h, (nccl_library or nccl_library_path()).encode(), rank, world, buf, ph))
+
+
+def gather_handles(ranks, mine: bytes) -> bytes:
+    """All ranks' 64-byte handles in rank order, through the process group."""
+    if ranks.info.world == 1:
+        return mine
+    import torch
+    import torch.distributed as dist
+    dev = ranks._device
+    t = torch.tensor(list(mine), dtype=torch.uint8, device=dev)
+    outs = [torch.zeros(64, dtype=torch.uint8, device=dev) for _ in range(ranks.info.world)]
+    dist.all_gather(outs, t)
+    return b"".join(bytes(o.cpu().tolist()) for o in outs)
+
+
+def join(gpu, ranks, fused: bool = True, nccl_library: str | None = None) -> None:
+    """The whole hand-shake for one rank: id from rank 0, inbox handles from everyone, attach."""
+    info = ranks.info
+    uid = exchange_id(ranks, lambda: unique_id(nccl_library))
+    handles = gather_handles(ranks, inbox_handle(gpu)) if fused and info.world > 1 else None
+    attach(gpu, info.rank, info.world, uid, nccl_library, handles)
 
 
 def exchange_id(ranks, make_id) -> bytes:

@@ -409,7 +409,8 @@ def run_tp(args, rank: int, world: int, local_rank: int):
     ctx = pkg.Context(local_rank)
     n_prompt, steps, warmup = 512, args.steps, max(args.warmup, 3)
     g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_prompt + warmup + steps + 8, 64)
-    pkg.tp.attach(g, rank, world, pkg.tp.exchange_id(ranks, pkg.tp.unique_id))
+    pkg.tp.join(g, ranks, fused=not args.tp_nccl)
+    one_kernel = bool(g.set_option("mega_available", 0))
     toks = prompt_tokens_n(d.vocab, n_prompt)
 
     def prompt_pass():
@@ -447,6 +448,8 @@ def run_tp(args, rank: int, world: int, local_rank: int):
                                    "query/KV heads and FFN rows sharded over the ranks, all-reduce after attn_output and ffn_down",
                        "dim": d.dim, "hidden_per_rank": d.hidden, "n_layer": d.n_layer, "n_head_per_rank": d.n_head,
                        "n_kv_head_per_rank": d.n_kv_head, "head_dim": d.head_dim, "vocab": d.vocab, "parallelism": f"tp{world}",
+                       "exchange": ("tagged words over peer memory inside the one-kernel step" if one_kernel and world > 1 else
+                                    "none" if world == 1 else "NCCL all-reduce between per-operator kernels"),
                        "weight_bytes_per_token_whole_model": int(full_bytes),
                        "weight_bytes_per_token_per_rank": int(spec.weight_bytes_per_token()),
                        "l2_policy": "inputs_larger_than_l2"},
@@ -470,6 +473,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp", action="store_true", help="configs[3]: Qwen3-8B-shaped decode sharded over the ranks")
     ap.add_argument("--tp-layers", type=int, default=36)
+    ap.add_argument("--tp-nccl", action="store_true", help="with --tp: exchange through NCCL all-reduces (per-operator path)")
     ap.add_argument("--sweep", action="store_true", help="quant-type kernel sweep (configs[4]) instead of the decode benchmark")
     ap.add_argument("--sweep-small", action="store_true", help="with --sweep: only the two smaller shapes")
     args = ap.parse_args()

@@ -273,9 +273,19 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value);
  * the loader path). One rank calls aotcu_tp_unique_id and hands the 128 bytes to all
  * ranks by its own means; every rank then calls aotcu_tp_attach (collective). Sums across
  * ranks change the order of f32 additions: results match the single-device path to
- * rounding (1e-3 relative at the logits), not bit for bit. */
+ * rounding (1e-3 relative at the logits), not bit for bit.
+ *
+ * Decode steps of models the one-kernel step covers can keep the exchange inside that kernel:
+ * every rank first calls aotcu_tp_inbox_handle (allocates its inbox for the other ranks'
+ * partial rows and returns its 64-byte CUDA IPC handle), the host gathers the handles of all
+ * ranks in rank order (world x 64 bytes) and passes them to aotcu_tp_attach as
+ * `peer_handles`. Each GPU then writes its partial rows straight into the peers' inboxes over
+ * NVLink and adds the world's partials in rank order. With peer_handles == NULL every
+ * exchange goes through NCCL. At most 8 ranks, one process per GPU, all on one box. */
 int aotcu_tp_unique_id(const char* nccl_library, uint8_t out_id[128]);
-int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world, const uint8_t id[128]);
+int aotcu_tp_inbox_handle(aotcu_gpu* g, uint8_t out_handle[64]);
+int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world, const uint8_t id[128],
+                    const uint8_t* peer_handles);
 
 /* Benchmark helper (no counterpart in the reference; its per-op figures come from
  * `bench_ops`, crates/aot-kernels/tests/metal.rs:456-641): times only the matrix

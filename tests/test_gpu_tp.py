@@ -24,7 +24,7 @@ WORKER = textwrap.dedent("""
     Q4_K, Q5_K, Q6_K = pkg.lib.Q4_K, pkg.lib.Q5_K, pkg.lib.Q6_K
     kinds = lambda l, t: {{"wv": Q6_K, "down": Q6_K if l % 2 == 0 else Q4_K, "output": Q6_K, "wo": Q5_K}}.get(t, Q4_K)
     out = {{}}
-    for arch in ("llama", "qwen3"):
+    for arch, fused in (("llama", True), ("qwen3", True), ("llama", False)):
         kw = dict(dim=512, hidden=2048, n_layer=3, n_head=8, n_kv_head=4, head_dim=128, vocab=600, seed=5, kinds=kinds, n_ctx_train=256)
         if arch == "qwen3":
             kw.update(qk_norm=True, rope_neox=True, rope_base=1e6, eps=1e-6)
@@ -32,8 +32,9 @@ WORKER = textwrap.dedent("""
         ctx = pkg.Context(info.local_rank)
         sh = pkg.tp.shard_spec(spec, info.rank, info.world)
         g = pkg.Gpu(ctx, sh.head, sh.layers, sh.weights, 128, 16)
-        uid = pkg.tp.exchange_id(ranks, pkg.tp.unique_id)
-        pkg.tp.attach(g, info.rank, info.world, uid)
+        # fused: partial rows cross NVLink inside the one-kernel step; else NCCL all-reduces
+        pkg.tp.join(g, ranks, fused=fused)
+        one_kernel = bool(g.set_option("mega_available", 0))
         full = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 128, 16) if ranks.is_root else None
         prompt = [5, 17, 300, 42, 7, 7, 1, 599, 0, 12, 13]
         worst, agree, total = 0.0, 0, 0
@@ -56,7 +57,8 @@ WORKER = textwrap.dedent("""
             tok, pos = int(np.argmax(lg)), pos + 1
         ids, ms = g.generate(tok, pos, 16)         # the device-side greedy loop, all ranks in step
         ctx.device_status()
-        out[arch] = {{"worst_rel": worst, "agree": agree, "total": total, "ids": [int(i) for i in ids]}}
+        out[arch + ("-fused" if fused else "-nccl")] = {{"worst_rel": worst, "agree": agree, "total": total,
+                                                         "ids": [int(i) for i in ids], "one_kernel": one_kernel, "fused": fused}}
         ranks.barrier()
     if ranks.is_root:
         print(json.dumps(out))
@@ -84,3 +86,4 @@ def test_two_ranks_match_single_device(tmp_path):
         assert res["worst_rel"] < 1e-3, (arch, res)      # north-star tolerance for f32 outputs
         assert res["agree"] == res["total"], (arch, res)  # same greedy choice at every compared step
         assert len(res["ids"]) == 16
+        assert res["one_kernel"] == res["fused"], (arch, res)  # the fused exchange keeps the one-kernel step
