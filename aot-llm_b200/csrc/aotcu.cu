@@ -783,10 +783,11 @@ static int mega_setup(aotcu_gpu* g) {
   int n_stages = (int)((c->max_smem - fixed) / stage_bytes);
   if (n_stages > 8) n_stages = 8;
   // One CTA per SM must be resident for the grid barriers.
-  CU_TRY(cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  CU_TRY(cudaFuncSetAttribute(decode_step_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  CU_TRY(cudaFuncSetAttribute(decode_step_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
   g->mega_smem = (size_t)n_stages * stage_bytes + fixed;
   int per_sm = 0;
-  CU_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, MEGA_THREADS, g->mega_smem));
+  CU_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel<true>, MEGA_THREADS, g->mega_smem));
   if (per_sm < 1) return 0;
 
   auto seg = [&](const aotcu_tensor& t, float* out) { return GemvSeg{wptr(g, t), out, (int)t.rows, t.kind}; };
@@ -884,7 +885,8 @@ static int enqueue_mega(aotcu_gpu* g, int want_logits, bool with_argmax, unsigne
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_step_kernel, P);
+  cudaError_t e = P.tp.world > 1 ? cudaLaunchKernelEx(&cfg, decode_step_kernel<true>, P)
+                                 : cudaLaunchKernelEx(&cfg, decode_step_kernel<false>, P);
   if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "decode_step_kernel launch: %s", cudaGetErrorString(e));
   c->launches++;
   g->qsrc = aotcu_gpu::QSrc();

@@ -538,6 +538,7 @@ __device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, Ring
 // the warp takes gate rows and the upper half the matching up rows, and the SiLU gate
 // is applied in the epilogue. `sx` holds the Q8_K images of the activation vector;
 // `op` lives in shared memory.
+template <bool TP = false>
 __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp,
                                            int n_warps, uint32_t tag, const TpExchange* tpx = nullptr, int which = 0) {
   const int rows_per_cta = op.rows_per_cta, tile_rows = op.tile_rows, pair = op.pair;
@@ -625,7 +626,7 @@ __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, Ring
           const float v = narrow ? (row ? warp_row_dot_s(kind, row, sxa, nb) : 0.0f) : group_row_dot(row, kind, sxa, nb, L);
           if (u < R_rows && (lane & (L - 1)) == 0) {
             const int oi = parts[pi].row0 + lr;
-            if (ll && tpx && epilogue == EPI_ACCUM) {
+            if (TP && ll && tpx && epilogue == EPI_ACCUM) {
               // a partial row of a sharded product: hand it to every rank (this one included)
               for (int dst = 0; dst < tpx->world; dst++)
                 ll_store_sys(tpx->inbox[dst] + ((size_t)which * tpx->world + tpx->rank) * tpx->dim + oi, v, tag);
@@ -955,6 +956,8 @@ static_assert(sizeof(SeqSumScratch) <= MEGA_SEQSUM_BYTES, "SeqSumScratch layout"
 // Bytes of shared memory besides the ring stages, the activation images and the scratch.
 constexpr int MEGA_TAIL_BYTES = MEGA_BAR_BYTES + MEGA_SEQSUM_BYTES + 64 * 4 + 16;
 
+// TP: this GPU holds one shard of a row-sharded model and exchanges partial rows with its peers.
+template <bool TP>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const StepParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   // [stages][sx images][scratch][barriers 128 B][SeqSumScratch][red 64 floats][abort]
@@ -1078,13 +1081,13 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     if (!head) MEGA_PROF(slot);
     // q/k/v: tl+1, wo: tl+3, gate/up: tl+4, down: tl+5 (the head writes plain floats)
     const uint32_t tag_out = tl + (ph == 0 ? 1u : (uint32_t)ph + 2u);
-    const bool exchange = P.tp.world > 1 && (ph & 1) && !head;
-    consume_op(op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, tag_out, exchange ? &P.tp : nullptr, ph >> 1);
+    const bool exchange = TP && (ph & 1) && !head;
+    consume_op<TP>(op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, tag_out, exchange ? &P.tp : nullptr, ph >> 1);
     if (head) break;
     // The next phase rewrites the activation images and the scratch rows; warps that are
     // done must also not start polling while others still compute.
     g.sync();
-    if (exchange) {
+    if (TP && exchange) {
       // The rows this CTA owns: wait for every rank's partial, add them in rank order, join
       // the residual stream and publish the row for this GPU's CTAs.
       int r0, r1;
