@@ -165,7 +165,9 @@ static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
   return call.pair ? launch_gemm_t<true>(c, P, grid, smem) : launch_gemm_t<false>(c, P, grid, smem);
 }
 
-// One K-quant product for a single activation row on the ring producer/consumer kernel.
+// One product on the ring producer/consumer kernel: a single activation row for K-quants,
+// one or more rows for the Q8_0 family (as many at a time as their images fit in shared
+// memory; the matrix is streamed once per such group).
 constexpr size_t STREAM_STAGE_BYTES = 32768;
 static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   StreamGemvParams P = {};
@@ -185,24 +187,37 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   op.tile_rows = tr < 1 ? 1 : tr;
   op.epilogue = call.epilogue;
   op.ll = 0;
-  P.x = call.x;
   P.x_image = call.x_mode == 1;
   P.q80 = kind_act(call.seg[0].kind) == ACT_Q8_0;
   P.err = c->d_err;
   P.stage_bytes = (int)STREAM_STAGE_BYTES;
-  const size_t fixed = (P.q80 ? (call.cols / 32) * X0_STRIDE : (call.cols / 256) * XK_STRIDE) + MEGA_BAR_BYTES + 16;
-  ARG_CHECK(fixed + 2 * STREAM_STAGE_BYTES <= c->max_smem, "activation vector too long for shared memory");
-  int n_stages = (int)((c->max_smem - fixed) / STREAM_STAGE_BYTES);
-  if (n_stages > 6) n_stages = 6;
-  P.n_stages = n_stages;
-  const size_t smem = (size_t)n_stages * STREAM_STAGE_BYTES + fixed;
+  const size_t x_image_bytes = P.q80 ? (call.cols / 32) * X0_STRIDE : (call.cols / 256) * XK_STRIDE;
+  const size_t x_src_bytes = P.x_image ? x_image_bytes : (P.q80 ? (call.cols / 32) * 36 : (call.cols / 256) * 292);
+  const size_t tail = MEGA_BAR_BYTES + 16;
+  ARG_CHECK(x_image_bytes + tail + 2 * STREAM_STAGE_BYTES <= c->max_smem, "activation vector too long for shared memory");
+  // activation rows per launch: leave room for at least three stages
+  size_t group = (c->max_smem - tail - 3 * STREAM_STAGE_BYTES) / x_image_bytes;
+  if (group < 1) group = 1;
+  if (group > call.m) group = call.m;
   static bool attr_set[64] = {};
   if (c->device >= 0 && c->device < 64 && !attr_set[c->device]) {
     CU_TRY(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
     attr_set[c->device] = true;
   }
   const int grid = span < (size_t)c->n_sm ? (int)span : c->n_sm;
-  return launch(c, gemv_stream_kernel, dim3(grid), dim3(MEGA_THREADS), smem, P);
+  for (size_t t0 = 0; t0 < call.m; t0 += group) {
+    const size_t mg = std::min(group, call.m - t0);
+    P.m = (int)mg;
+    P.x = reinterpret_cast<const uint8_t*>(call.x) + t0 * x_src_bytes;
+    for (int s = 0; s < call.nseg; s++) op.seg[s].out = call.seg[s].out + t0 * (size_t)call.seg[s].rows;
+    const size_t fixed = mg * x_image_bytes + tail;
+    int n_stages = (int)((c->max_smem - fixed) / STREAM_STAGE_BYTES);
+    if (n_stages > 6) n_stages = 6;
+    P.n_stages = n_stages;
+    const size_t smem = (size_t)n_stages * STREAM_STAGE_BYTES + fixed;
+    if (int rc = launch(c, gemv_stream_kernel, dim3(grid), dim3(MEGA_THREADS), smem, P)) return rc;
+  }
+  return 0;
 }
 
 static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
@@ -255,7 +270,7 @@ static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
   // Prompt chunks of K-quant matrices go to the tensor-core kernel, single rows to the
   // streaming kernel (whole rows per warp, no barrier per tile).
   if (act == ACT_Q8_K && call.m >= 8 && call.m <= (size_t)GEMM_MAX_M) return launch_gemm(c, call);
-  if (call.m == 1 && 2 * max_rb + 192 <= STREAM_STAGE_BYTES) return launch_gemv_stream(c, call, span);
+  if ((call.m == 1 || act == ACT_Q8_0) && 2 * max_rb + 192 <= STREAM_STAGE_BYTES) return launch_gemv_stream(c, call, span);
 
   const int mult = call.pair ? 2 : 1;
   int grid = c->n_sm;

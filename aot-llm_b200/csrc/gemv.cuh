@@ -538,6 +538,37 @@ __device__ __forceinline__ float float_lane_chain(const uint8_t* wrow, const flo
   return acc;
 }
 
+// The same lane chain for TG activation rows at once: the weights of 16 steps are loaded
+// once and applied to every row's own accumulator, each in the order of the single-row chain.
+template <int KIND, int TG>
+__device__ __forceinline__ void float_lane_chain_multi(const uint8_t* wrow, const float* x, int cols, int k, int n8, int ntok,
+                                                       float (&acc)[TG]) {
+#pragma unroll
+  for (int t = 0; t < TG; t++) acc[t] = 0.0f;
+  int j = k;
+  for (; j + 8 * 15 < n8; j += 8 * 16) {
+    float w[16];
+#pragma unroll
+    for (int u = 0; u < 16; u++) w[u] = load_wf(KIND, wrow, j + 8 * u);
+#pragma unroll
+    for (int t = 0; t < TG; t++) {
+      if (t < ntok) {
+        const float* xt = x + (size_t)t * cols + j;
+#pragma unroll
+        for (int u = 0; u < 16; u++) acc[t] = ffma(w[u], xt[8 * u], acc[t]);
+      }
+    }
+  }
+  for (; j < n8; j += 8) {
+    const float w = load_wf(KIND, wrow, j);
+#pragma unroll
+    for (int t = 0; t < TG; t++)
+      if (t < ntok) acc[t] = ffma(w, x[(size_t)t * cols + j], acc[t]);
+  }
+}
+
+constexpr int FLOAT_TG = 8;  // activation rows handled per pass over a weight row
+
 __global__ void __launch_bounds__(256) gemv_float_kernel(const GemvParams P) {
   pdl_launch_dependents();
   pdl_wait();
@@ -556,8 +587,8 @@ __global__ void __launch_bounds__(256) gemv_float_kernel(const GemvParams P) {
         s++;
       }
     }
-    for (int tok = 0; tok < P.m; tok++) {
-      const float* x = reinterpret_cast<const float*>(P.x) + (size_t)tok * P.cols;
+    if (P.m == 1) {
+      const float* x = reinterpret_cast<const float*>(P.x);
       float res[2] = {0.0f, 0.0f};
       const int nmat = P.pair ? 2 : 1;
       for (int mi = 0; mi < nmat; mi++) {
@@ -580,12 +611,58 @@ __global__ void __launch_bounds__(256) gemv_float_kernel(const GemvParams P) {
       }
       if (live && k == 0) {
         if (P.pair) {
-          const size_t o = (size_t)tok * P.seg[0].rows + r;
-          P.seg[0].out[o] = P.epilogue == EPI_SILU_MUL ? silu_mul_exact(res[0], res[1]) : res[0];
-          P.seg[1].out[o] = res[1];
+          P.seg[0].out[r] = P.epilogue == EPI_SILU_MUL ? silu_mul_exact(res[0], res[1]) : res[0];
+          P.seg[1].out[r] = res[1];
         } else {
-          float* o = P.seg[s].out + (size_t)tok * P.seg[s].rows + r;
+          float* o = P.seg[s].out + r;
           *o = P.epilogue == EPI_ACCUM ? fadd(*o, res[0]) : res[0];
+        }
+      }
+      continue;
+    }
+    // several activation rows: groups of FLOAT_TG rows share one pass over the weight row
+    for (int tok0 = 0; tok0 < P.m; tok0 += FLOAT_TG) {
+      const int ntok = min(FLOAT_TG, P.m - tok0);
+      const float* x = reinterpret_cast<const float*>(P.x) + (size_t)tok0 * P.cols;
+      float res[2][FLOAT_TG];
+      const int nmat = P.pair ? 2 : 1;
+      for (int mi = 0; mi < nmat; mi++) {
+        const int sg = P.pair ? mi : s;
+        const int kind = P.seg[sg].kind;
+        const uint8_t* wrow = P.seg[sg].w + (size_t)(live ? r : 0) * kind_row_bytes(kind, P.cols);
+        float acc[FLOAT_TG];
+#pragma unroll
+        for (int t = 0; t < FLOAT_TG; t++) acc[t] = 0.0f;
+        if (live) {
+          if (kind == F16) float_lane_chain_multi<F16, FLOAT_TG>(wrow, x, P.cols, k, n8, ntok, acc);
+          else if (kind == BF16) float_lane_chain_multi<BF16, FLOAT_TG>(wrow, x, P.cols, k, n8, ntok, acc);
+          else float_lane_chain_multi<F32, FLOAT_TG>(wrow, x, P.cols, k, n8, ntok, acc);
+        }
+#pragma unroll
+        for (int t = 0; t < FLOAT_TG; t++) {
+          float s1 = fadd(acc[t], __shfl_xor_sync(0xffffffffu, acc[t], 4));  // a_k + a_{k+4}
+          float t1 = fadd(s1, __shfl_xor_sync(0xffffffffu, s1, 2));
+          float sum = fadd(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+          if (live && k == 0 && t < ntok) {
+            for (int j = n8; j < P.cols; j++) sum = fadd(sum, fmul(load_wf(kind, wrow, j), x[(size_t)t * P.cols + j]));
+          }
+          res[mi][t] = sum;
+        }
+      }
+      if (live && k == 0) {
+#pragma unroll
+        for (int t = 0; t < FLOAT_TG; t++) {
+          if (t < ntok) {
+            const int tok = tok0 + t;
+            if (P.pair) {
+              const size_t o = (size_t)tok * P.seg[0].rows + r;
+              P.seg[0].out[o] = P.epilogue == EPI_SILU_MUL ? silu_mul_exact(res[0][t], res[1][t]) : res[0][t];
+              P.seg[1].out[o] = res[1][t];
+            } else {
+              float* o = P.seg[s].out + (size_t)tok * P.seg[s].rows + r;
+              *o = P.epilogue == EPI_ACCUM ? fadd(*o, res[0][t]) : res[0][t];
+            }
+          }
         }
       }
     }

@@ -1158,8 +1158,10 @@ __device__ __forceinline__ float row_chain_q80(uint32_t row, uint32_t sx, int nb
 }
 
 // Consumer side for matrices of the Q8_0 family; `sx` holds the 48-byte Q8_0 images.
+// `m` activation rows (their images back to back in `sx`) are applied to every resident row;
+// output element (token, row) goes to out[token * rows + row].
 __device__ __forceinline__ void consume_op_q80(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp,
-                                               int n_warps) {
+                                               int n_warps, int m) {
   const int tile_rows = op.tile_rows, pair = op.pair, epilogue = op.epilogue, nb = op.cols >> 5;
   int c0, c1;
   cta_rows(op.span_rows, c0, c1);
@@ -1188,30 +1190,33 @@ __device__ __forceinline__ void consume_op_q80(const MegaOp& op, const Ring& R, 
           }
         }
         const int n_mat = pair ? 2 : 1;
-        for (int mt = 0; mt < n_mat; mt++) {
-          const TilePart& tp = parts[pair ? mt : pi];
-          const int kind = op.seg[tp.seg].kind;
-          const uint32_t row = stage + tp.soff + ((uint32_t)(uintptr_t)tp.src & 15u) + (uint32_t)(pair ? u : lr) * op.row_bytes[tp.seg];
-          float a = 0.0f;
-          if (u < R_rows) {
-            if (kind == Q4_0) a = row_chain_q80<Q4_0>(row, sxa, nb, k);
-            else if (kind == Q5_0) a = row_chain_q80<Q5_0>(row, sxa, nb, k);
-            else a = row_chain_q80<Q8_0>(row, sxa, nb, k);
+        for (int tok = 0; tok < m; tok++) {
+          const uint32_t sxt = sxa + (uint32_t)tok * (uint32_t)nb * X0_STRIDE;
+          for (int mt = 0; mt < n_mat; mt++) {
+            const TilePart& tp = parts[pair ? mt : pi];
+            const int kind = op.seg[tp.seg].kind;
+            const uint32_t row = stage + tp.soff + ((uint32_t)(uintptr_t)tp.src & 15u) + (uint32_t)(pair ? u : lr) * op.row_bytes[tp.seg];
+            float a = 0.0f;
+            if (u < R_rows) {
+              if (kind == Q4_0) a = row_chain_q80<Q4_0>(row, sxt, nb, k);
+              else if (kind == Q5_0) a = row_chain_q80<Q5_0>(row, sxt, nb, k);
+              else a = row_chain_q80<Q8_0>(row, sxt, nb, k);
+            }
+            // ((a0+a4)+(a2+a6)) + ((a1+a5)+(a3+a7)) over the row's eight lanes
+            a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 4));
+            a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 2));
+            a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 1));
+            v[mt] = a;
           }
-          // ((a0+a4)+(a2+a6)) + ((a1+a5)+(a3+a7)) over the row's eight lanes
-          a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 4));
-          a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 2));
-          a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 1));
-          v[mt] = a;
-        }
-        if (u < R_rows && k == 0) {
-          if (pair) {
-            const int r = t0 + u;
-            op.seg[0].out[r] = epilogue == EPI_SILU_MUL ? silu_mul_exact(v[0], v[1]) : v[0];
-            op.seg[1].out[r] = v[1];
-          } else {
-            float* o = op.seg[parts[pi].seg].out + parts[pi].row0 + lr;
-            *o = epilogue == EPI_ACCUM ? fadd(__ldcg(o), v[0]) : v[0];
+          if (u < R_rows && k == 0) {
+            if (pair) {
+              const size_t r = (size_t)tok * op.seg[0].rows + t0 + u;
+              op.seg[0].out[r] = epilogue == EPI_SILU_MUL ? silu_mul_exact(v[0], v[1]) : v[0];
+              op.seg[1].out[r] = v[1];
+            } else {
+              float* o = op.seg[parts[pi].seg].out + (size_t)tok * op.seg[parts[pi].seg].rows + parts[pi].row0 + lr;
+              *o = epilogue == EPI_ACCUM ? fadd(__ldcg(o), v[0]) : v[0];
+            }
           }
         }
       }
@@ -1233,6 +1238,7 @@ struct StreamGemvParams {
   const void* x;  // activation images (x_image) or reference-layout blocks
   int x_image;
   int q80;        // matrices of the Q8_0 family (Q8_0 activations) instead of K-quants
+  int m;          // activation rows (more than one only for the Q8_0 family)
   int n_stages, stage_bytes;
   int* err;
 };
@@ -1244,7 +1250,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   const int xstride = P.q80 ? X0_STRIDE : XK_STRIDE;
   uint8_t* stages = smem;
   uint8_t* sx = stages + (size_t)P.n_stages * P.stage_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sx + (size_t)nb * xstride);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sx + (size_t)P.m * nb * xstride);
   volatile int* abort = reinterpret_cast<volatile int*>(bars + MEGA_BAR_BYTES / 8);
   Ring R;
   R.stages = stages;
@@ -1275,13 +1281,14 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   }
   pdl_wait();
   CtaGroup g{(int)threadIdx.x, MEGA_CONSUMER_WARPS * 32, 1};
+  const int nbm = nb * P.m;  // blocks of all activation rows, back to back
   if (P.x_image) {
     const uint4* src4 = reinterpret_cast<const uint4*>(P.x);
-    for (int i = g.tid; i < nb * (xstride / 16); i += g.nthreads) reinterpret_cast<uint4*>(sx)[i] = src4[i];
+    for (int i = g.tid; i < nbm * (xstride / 16); i += g.nthreads) reinterpret_cast<uint4*>(sx)[i] = src4[i];
   } else if (P.q80) {
     // BlockQ8_0 {f32 d; i8 qs[32]} (quant.rs:16-20) -> image {qs; d}
     const uint32_t* src = reinterpret_cast<const uint32_t*>(P.x);
-    for (int i = g.tid; i < nb * 9; i += g.nthreads) {
+    for (int i = g.tid; i < nbm * 9; i += g.nthreads) {
       const int b = i / 9, w = i - b * 9;
       *reinterpret_cast<uint32_t*>(sx + b * X0_STRIDE + (w == 0 ? X0_D : (w - 1) * 4)) = src[i];
     }
@@ -1295,7 +1302,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   }
   g.sync();
   RingPos cp{0, 0u};
-  if (P.q80) consume_op_q80(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
+  if (P.q80) consume_op_q80(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, P.m);
   else consume_op(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, 0u);
 }
 

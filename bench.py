@@ -303,7 +303,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     step_bytes = spec.weight_bytes_per_token() + spec.kv_bytes_per_position() * (mid_pos + 1)
     step_gbs = step_bytes / (ms * 1e-3 / steps) / 1e9
     one_kernel = launches == steps
-    # The per-operator GEMV kernel alone (used by prompt batches and the operator API).
+    # The single-row product kernel alone (operator API, models the one-kernel step does not cover):
+    # every matrix product of one decode step, back to back.
     sweep_ms, sweep_launches, sweep_bytes = g.gemv_sweep(20)
     gemv_gbs = sweep_bytes / (sweep_ms * 1e-3) / 1e9
 
@@ -376,7 +377,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                      "algorithmic_bytes_per_launch": int(step_bytes), "avg_launch_us": ms * 1e3 / steps,
                      "roofline_tok_s": peak * 1e9 / step_bytes,
                      "how": "weights + KV bytes of one token / (device time of the timed loop / steps), CUDA events on the launching stream; traffic = dram read+write of one launch from ncu (profiles/)"},
-        "gemv_kernel_sweep": {"kernel": "gemv_q8k_kernel", "achieved": gemv_gbs, "unit": "GB/s", "frac": gemv_gbs / peak,
+        "gemv_kernel_sweep": {"kernel": "gemv_stream_kernel", "achieved": gemv_gbs, "unit": "GB/s", "frac": gemv_gbs / peak,
                               "launches": int(sweep_launches), "algorithmic_bytes": int(sweep_bytes),
                               "avg_launch_us": sweep_ms * 1e3 / sweep_launches},
         "matvec_q4_k": {"workload": "configs[0]: Q4_K matvec, W 5632x2048, x f32 quantized to Q8_K", "value": mv_bytes / mv_us / 1e3,
