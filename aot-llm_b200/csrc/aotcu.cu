@@ -768,7 +768,7 @@ static int mega_setup(aotcu_gpu* g) {
   const aotcu_tensor& out_t = g->head.output.present ? g->head.output : g->head.token_embd;
   const size_t qd = (size_t)d.n_head * d.head_dim;
   bool ok = !d.qkv_bias && !d.post_norms && !d.gelu && !d.embd_scale && d.swa_window == 0 && d.dim % 256 == 0 &&
-            d.hidden % 256 == 0 && qd % 256 == 0 && d.head_dim % 4 == 0 && kind_act(out_t.kind) == ACT_Q8_K;
+            d.hidden % 256 == 0 && qd % 256 == 0 && d.head_dim % 16 == 0 && kind_act(out_t.kind) == ACT_Q8_K;
   for (const auto& l : g->layers) {
     const aotcu_tensor* ts[7] = {&l.wq, &l.wk, &l.wv, &l.wo, &l.gate, &l.up, &l.down};
     for (auto t : ts) ok = ok && kind_act(t->kind) == ACT_Q8_K;
@@ -780,9 +780,10 @@ static int mega_setup(aotcu_gpu* g) {
   ok = ok && d.n_layer <= 200 && (size_t)d.dim >= (size_t)c->n_sm && (size_t)d.hidden >= (size_t)c->n_sm;
   if (!ok) return 0;
   const int stage_bytes = 32768;
-  const int v_chunk = 8192 / d.head_dim;
+  const int v_chunk = 6144 / d.head_dim;  // positions per staged chunk (two buffers of 24 KB + padding)
   size_t nb_max = std::max(std::max((size_t)d.dim, (size_t)d.hidden), qd) / 256;
-  size_t scratch = std::max((size_t)2 * d.dim, (size_t)4 * d.head_dim + ((g->n_ctx + 3) & ~(size_t)3) + (size_t)v_chunk * d.head_dim) * sizeof(float);
+  // norm rows (2 x dim) or the attention scratch: q, k, v, squares, scores, two staged chunks of padded rows
+  size_t scratch = std::max((size_t)2 * d.dim, (size_t)4 * d.head_dim + ((g->n_ctx + 3) & ~(size_t)3) + (size_t)2 * v_chunk * (d.head_dim + 4)) * sizeof(float);
   scratch = (scratch + 127) & ~(size_t)127;
   const size_t table_bytes = (((size_t)d.n_layer + 1) * sizeof(StepLayer) + 15) & ~(size_t)15;
   size_t fixed = nb_max * XK_STRIDE + scratch + MEGA_TAIL_BYTES + table_bytes;

@@ -753,6 +753,21 @@ __device__ __forceinline__ void phase_quant(const LLWord* src, uint32_t tag, int
   g.sync();
 }
 
+// Stage rows [c0, c0 + cn) of one KV head (row `pos` comes from `cur`, the row of the token
+// being decoded, which is not in the cache yet) into `buf` with row stride `stride` floats.
+// Cached rows travel with cp.async (no registers, completion by cp.async.wait_group), so
+// the next chunk loads while the current one is consumed.
+__device__ __forceinline__ void stage_kv_rows(float* buf, int stride, const float* cache, size_t kvd, int head_off, int hd4,
+                                              int c0, int cn, int pos, const float* cur, int tid, int T) {
+  for (int j = tid; j < cn * hd4; j += T) {
+    const int t = j / hd4, i4 = j - t * hd4, tt = c0 + t;
+    float* dst = buf + t * stride + 4 * i4;
+    if (tt == pos) *reinterpret_cast<float4*>(dst) = reinterpret_cast<const float4*>(cur)[i4];
+    else asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(cache + (size_t)tt * kvd + head_off + 4 * i4) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
 // Per-head q/k norm, RoPE, KV store and attention for head `h` (ops.rs:74-87, 40-70,
 // 152-157, 185-218), by the consumer warps of one CTA.
 __device__ void phase_attention(const StepParams& P, int li, int h, int pos, uint32_t tag_in, uint32_t tag_out,
@@ -765,7 +780,7 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, uin
   float* sv = sk + hd;          // hd
   float* sp = sv + hd;          // hd (squares)
   float* sc = sp + hd;          // n_ctx scores
-  float* vbuf = sc + ((P.n_ctx + 3) & ~3);  // v_chunk x hd, 16-byte aligned
+  float* vbuf = sc + ((P.n_ctx + 3) & ~3);  // two chunk buffers of v_chunk x (hd + 4) floats, 16-byte aligned
   const float* const q_norm_w = P.layers[li].q_norm;
   const float* const k_norm_w = P.layers[li].k_norm;
   float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd;
@@ -814,48 +829,50 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, uin
     }
   }
   pf.mark(20);
-  // scores: cached K rows are staged through shared memory in chunks (one round of
-  // coalesced loads), padded by one float4 per row to spread the banks
+  // scores: cached K rows are staged through shared memory in chunks, double buffered; rows
+  // are padded by one float4 to spread the banks
   const float scale = 1.0f / sqrtf((float)hd);
-  const int hd4 = hd >> 2, kstride = hd + 4;
-  const int k_chunk = (P.v_chunk * hd) / kstride;
+  const int hd4 = hd >> 2, kstride = hd + 4, chunk = P.v_chunk;
+  const int buf_floats = chunk * kstride;
   float lmax = -INFINITY;
-  for (int c0 = 0; c0 < n; c0 += k_chunk) {
-    const int cn = min(k_chunk, n - c0);
-    g.sync();
-    // two rows per thread are requested before the first is stored
-    for (int t = tid / hd4, i4 = tid % hd4; t < cn; t += 2 * (T / hd4)) {
-      float4 kk[2];
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int tu = t + u * (T / hd4), tt = c0 + tu;
-        if (tu < cn)
-          kk[u] = tt == pos ? reinterpret_cast<const float4*>(sk)[i4]
-                            : __ldcg(reinterpret_cast<const float4*>(kc + (size_t)tt * kvd + kvh * hd) + i4);
-      }
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int tu = t + u * (T / hd4);
-        if (tu < cn) *reinterpret_cast<float4*>(vbuf + tu * kstride + 4 * i4) = kk[u];
-      }
+  stage_kv_rows(vbuf, kstride, kc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sk, tid, T);
+  for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
+    const int cn = min(chunk, n - c0);
+    float* cur_buf = vbuf + (ci & 1) * buf_floats;
+    if (c0 + chunk < n) {
+      stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, kstride, kc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sk,
+                    tid, T);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     g.sync();
     for (int t = tid; t < cn; t += T) {
-      const float4* kt = reinterpret_cast<const float4*>(vbuf + t * kstride);
+      const float4* kt = reinterpret_cast<const float4*>(cur_buf + t * kstride);
+      const float4* qt = reinterpret_cast<const float4*>(sq);
       float s = 0.0f;
-#pragma unroll 4
-      for (int i = 0; i < hd4; i++) {
-        const float4 kk = kt[i];
-        s = fadd(s, fmul(sq[4 * i], kk.x));
-        s = fadd(s, fmul(sq[4 * i + 1], kk.y));
-        s = fadd(s, fmul(sq[4 * i + 2], kk.z));
-        s = fadd(s, fmul(sq[4 * i + 3], kk.w));
+      for (int i0 = 0; i0 < hd4; i0 += 4) {
+        // products first (independent), then the chain of adds in element order
+        float pr[16];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          const float4 kk = kt[i0 + u], qq = qt[i0 + u];
+          pr[4 * u] = fmul(qq.x, kk.x);
+          pr[4 * u + 1] = fmul(qq.y, kk.y);
+          pr[4 * u + 2] = fmul(qq.z, kk.z);
+          pr[4 * u + 3] = fmul(qq.w, kk.w);
+        }
+#pragma unroll
+        for (int u = 0; u < 16; u++) s = fadd(s, pr[u]);
       }
       s = fmul(s, scale);
       sc[c0 + t] = s;
       lmax = fmaxf(lmax, s);
     }
+    g.sync();  // this buffer is refilled two chunks later
   }
+  // the first chunk of V rows loads while the softmax runs
+  stage_kv_rows(vbuf, hd, vc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sv, tid, T);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
   if ((tid & 31) == 0) M.red[tid >> 5] = lmax;
@@ -871,31 +888,30 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, uin
   float inv = fdiv(1.0f, sum);
   g.sync();
   for (int t = tid; t < n; t += T) sc[t] = fmul(sc[t], inv);
-  // value mix, positions in order; cached rows are staged through shared memory in chunks
+  // value mix, positions in order (ops.rs:208-214); cached rows staged as above
   float o = 0.0f;
-  for (int c0 = 0; c0 < n; c0 += P.v_chunk) {
-    const int cn = min(P.v_chunk, n - c0);
-    g.sync();
-    for (int t = tid / hd4, i4 = tid % hd4; t < cn; t += 2 * (T / hd4)) {
-      float4 vv[2];
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int tu = t + u * (T / hd4), tt = c0 + tu;
-        if (tu < cn)
-          vv[u] = tt == pos ? reinterpret_cast<const float4*>(sv)[i4]
-                            : __ldcg(reinterpret_cast<const float4*>(vc + (size_t)tt * kvd + kvh * hd) + i4);
-      }
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int tu = t + u * (T / hd4);
-        if (tu < cn) reinterpret_cast<float4*>(vbuf)[tu * hd4 + i4] = vv[u];
-      }
+  for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
+    const int cn = min(chunk, n - c0);
+    const float* cur_buf = vbuf + (ci & 1) * buf_floats;
+    if (c0 + chunk < n) {
+      stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, hd, vc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sv, tid, T);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     g.sync();
     if (tid < hd) {
-#pragma unroll 8
-      for (int t = 0; t < cn; t++) o = fadd(o, fmul(sc[c0 + t], vbuf[t * hd + tid]));
+      int t = 0;
+      for (; t + 8 <= cn; t += 8) {
+        float pr[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) pr[u] = fmul(sc[c0 + t + u], cur_buf[(t + u) * hd + tid]);
+#pragma unroll
+        for (int u = 0; u < 8; u++) o = fadd(o, pr[u]);
+      }
+      for (; t < cn; t++) o = fadd(o, fmul(sc[c0 + t], cur_buf[t * hd + tid]));
     }
+    g.sync();
   }
   if (tid < hd) ll_store(P.attl + h * hd + tid, o, tag_out);
   pf.mark(24);
@@ -1067,6 +1083,21 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     const MegaOp& op = (&L.qkv)[ph];  // qkv, wo, gu, down are consecutive members
     const int slot = ph == 0 ? 1 : 3 * ph + 3;
     const uint32_t tl = tag_base + 5u * (uint32_t)li;  // + k: phase k of this layer
+    if (ph == 0 && !head) {
+      // The cached K and V rows this CTA's heads will read were evicted from L2 by the weight
+      // stream; ask for them now, two phases ahead of their use.
+      for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
+        const int kvd = P.n_kv_head * P.head_dim, kvh = h / (P.n_head / P.n_kv_head);
+        const int lines = (P.head_dim * 4 + 127) / 128;  // 128-byte lines per cached row of one head
+        const float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd + kvh * P.head_dim;
+        const float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd + kvh * P.head_dim;
+        for (int j = g.tid; j < pos * lines; j += g.nthreads) {
+          const int t = j / lines, ln = j - t * lines;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(kc + (size_t)t * kvd + 32 * ln));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(vc + (size_t)t * kvd + 32 * ln));
+        }
+      }
+    }
     if ((ph & 1) == 0) {
       // attention norm -> q/k/v, ffn norm -> gate/up + SiLU, output norm -> logits
       const float* w = head ? P.output_norm : (ph == 0 ? L.attn_norm : L.ffn_norm);
