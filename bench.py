@@ -373,7 +373,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": "decode_step_kernel" if one_kernel else "per-operator kernels (whole step)",
                      "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
-                     "peak_source": peak_src, "traffic": 641164800 if one_kernel else None,
+                     "peak_source": peak_src, "traffic": 639746560 if one_kernel else None,
                      "algorithmic_bytes_per_launch": int(step_bytes), "avg_launch_us": ms * 1e3 / steps,
                      "roofline_tok_s": peak * 1e9 / step_bytes,
                      "how": "weights + KV bytes of one token / (device time of the timed loop / steps), CUDA events on the launching stream; traffic = dram read+write of one launch from ncu (profiles/)"},
