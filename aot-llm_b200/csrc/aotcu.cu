@@ -1145,6 +1145,22 @@ int aotcu_matvec2(aotcu_ctx* c, int kind, float* out_a, float* out_b, const uint
   return launch_gemv(c, call);
 }
 
+int aotcu_matmul2(aotcu_ctx* c, int kind, float* out_a, float* out_b, const uint8_t* w_a, const uint8_t* w_b, const void* xs,
+                  size_t m, size_t rows, size_t cols) {
+  ARG_CHECK(c, "ctx is NULL");
+  ARG_CHECK(kind >= 0 && kind < N_KINDS, "unknown kind %d", kind);
+  if (rows == 0 || m == 0) return 0;
+  GemvCall call;
+  call.seg[0] = GemvSeg{w_a, out_a, (int)rows, kind};
+  call.seg[1] = GemvSeg{w_b, out_b, (int)rows, kind};
+  call.nseg = 2;
+  call.pair = 1;
+  call.cols = cols;
+  call.x = xs;
+  call.m = m;
+  return launch_gemv(c, call);
+}
+
 int aotcu_matvec3(aotcu_ctx* c, const int kinds[3], float* const outs[3], const uint8_t* const ws[3], const void* x,
                   const size_t rows[3], size_t cols) {
   ARG_CHECK(c && kinds && outs && ws && rows, "NULL argument");
@@ -1685,6 +1701,9 @@ int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world,
       g->tp_peer_map[r] = p;
       x.inbox[r] = reinterpret_cast<LLWord*>(p);
     }
+    // ranks step together: bound the waits at about half a minute instead of two seconds
+    const uint32_t limit = 1u << 25;
+    CU_TRY(cudaMemcpyToSymbol(c_ll_spin_limit, &limit, sizeof(limit)));
     // every rank counts launches from the same value, so tags agree across GPUs
     const unsigned one = 1;
     CU_TRY(cudaMemcpy(g->d_grid_bar + 1, &one, sizeof(unsigned), cudaMemcpyHostToDevice));

@@ -43,6 +43,7 @@ struct SeqSumScratch {
   int csum[SEQSUM_SEGS];      // integer mantissa increment of the segment in its predicted binade
   int epred[SEQSUM_SEGS];     // predicted exponent field, or -1 when the segment needs term-by-term adds
   float s;
+  float head_s;               // sum of the first 128 terms when an idle warp computed it ahead of the walk
 };
 
 // Every thread of the group calls it and receives the result.
@@ -70,6 +71,23 @@ __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const C
     return sc->s;
   }
   if (tid == 0) sc->s = 0.0f;
+  // The plain add chain over the first 128 terms (see the walk) can run beside steps 1-3
+  // when the group's last warp has no segments of its own there.
+  const int S_first = (min(n, SEQSUM_SEGS * 32) + 31) >> 5;
+  const bool head_ahead = nwarps >= 2 && (nwarps - 1) * 4 >= S_first;
+  if (head_ahead && warp == nwarps - 1) {
+    float s = 0.0f;
+    const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll 4
+    for (int k = 0; k < 32; k++) {
+      const float4 a = q[k];
+      s = fadd(s, a.x);
+      s = fadd(s, a.y);
+      s = fadd(s, a.z);
+      s = fadd(s, a.w);
+    }
+    if (lane == 0) sc->head_s = s;
+  }
   for (int base = 0; base < n; base += SEQSUM_SEGS * 32) {
     const int len = min(n - base, SEQSUM_SEGS * 32), S = (len + 31) >> 5;
     // 1. inexact per-segment sums; a warp takes four segments at a time so that their
@@ -156,15 +174,19 @@ __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const C
       // ties at every step. They go through one plain add chain (every lane the same).
       int head_segs = 0;
       if (base == 0 && len >= 128) {
-        float s = sc->s;
-        const float4* q = reinterpret_cast<const float4*>(p);
+        float s = sc->s;  // 0
+        if (head_ahead) {
+          s = sc->head_s;
+        } else {
+          const float4* q = reinterpret_cast<const float4*>(p);
 #pragma unroll 4
-        for (int k = 0; k < 32; k++) {
-          const float4 a = q[k];
-          s = fadd(s, a.x);
-          s = fadd(s, a.y);
-          s = fadd(s, a.z);
-          s = fadd(s, a.w);
+          for (int k = 0; k < 32; k++) {
+            const float4 a = q[k];
+            s = fadd(s, a.x);
+            s = fadd(s, a.y);
+            s = fadd(s, a.z);
+            s = fadd(s, a.w);
+          }
         }
         sum_decompose(f2u(s), e, m);
         head_segs = 4;

@@ -311,7 +311,9 @@ __device__ __forceinline__ float group_row_dot(uint32_t row, int kind, uint32_t 
 // Tags are unique per (launch, phase): (launch count << 10) | phase id, phase id >= 1;
 // a zeroed buffer therefore never matches.
 typedef unsigned long long LLWord;
-constexpr uint32_t LL_SPIN_LIMIT = 1u << 21;
+// Polls before a wait gives up (about a microsecond each). The host raises it when several
+// GPUs step together: a rank whose host thread is late must not make its peers give up.
+__constant__ uint32_t c_ll_spin_limit = 1u << 21;
 
 __device__ __forceinline__ void ll_store(LLWord* p, float v, uint32_t tag) {
   const LLWord w = ((LLWord)tag << 32) | (LLWord)__float_as_uint(v);
@@ -333,7 +335,8 @@ __device__ __forceinline__ float ll_value(const LLWord* p) { return __uint_as_fl
 __device__ __forceinline__ float ll_settle(const LLWord* p, LLWord w, uint32_t tag, volatile int* abort, int* err) {
   if ((uint32_t)(w >> 32) != tag) {
     uint32_t it = 0;
-    for (; it < LL_SPIN_LIMIT; ++it) {
+    const uint32_t limit = c_ll_spin_limit;
+    for (; it < limit; ++it) {
       w = ll_load(p);
       if ((uint32_t)(w >> 32) == tag) break;
       if ((it & 31u) == 31u && *abort) break;
@@ -378,7 +381,7 @@ __device__ __forceinline__ float ll_wait_sys(const LLWord* p, uint32_t tag, vola
   for (;;) {
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
     if ((uint32_t)(w >> 32) == tag) break;
-    if (++it >= LL_SPIN_LIMIT || ((it & 31u) == 31u && *abort)) {
+    if (++it >= c_ll_spin_limit || ((it & 31u) == 31u && *abort)) {
       if (!*abort) {
         *abort = 1;
         if (err) atomicOr(err, DEVERR_GRID_TIMEOUT);
@@ -698,6 +701,17 @@ __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag
   sp.last = clock64();
   float* row = M.scr;
   float* sq = M.scr + n;
+  // this thread's norm weights, requested before the wait for the row
+  constexpr int WMAX = 8;
+  float wv[WMAX];
+  const bool w_in_regs = n <= WMAX * g.nthreads;
+  if (w_in_regs) {
+#pragma unroll
+    for (int u = 0; u < WMAX; u++) {
+      const int i = g.tid + u * g.nthreads;
+      wv[u] = i < n ? w[i] : 0.0f;
+    }
+  }
   if (src_in_scr) {
     for (int i = g.tid; i < n; i += g.nthreads) sq[i] = fmul(row[i], row[i]);
   } else {
@@ -728,7 +742,15 @@ __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag
   sp.mark(17);
   float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
   g.sync();
-  for (int i = g.tid; i < n; i += g.nthreads) row[i] = fmul(fmul(row[i], r), w[i]);
+  if (w_in_regs) {
+#pragma unroll
+    for (int u = 0; u < WMAX; u++) {
+      const int i = g.tid + u * g.nthreads;
+      if (i < n) row[i] = fmul(fmul(row[i], r), wv[u]);
+    }
+  } else {
+    for (int i = g.tid; i < n; i += g.nthreads) row[i] = fmul(fmul(row[i], r), w[i]);
+  }
   g.sync();
   sp.mark(18);
   const int warp = g.tid >> 5, nw = g.nthreads >> 5;

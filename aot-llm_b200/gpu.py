@@ -124,6 +124,9 @@ class Context:
     def matmul(self, kind: int, out, w, xs, m: int, rows: int, cols: int):
         check(L.load().aotcu_matmul(self.h, kind, _dp(out), _dp(w), _dp(xs), m, rows, cols))
 
+    def matmul2(self, kind: int, out_a, out_b, w_a, w_b, xs, m: int, rows: int, cols: int):
+        check(L.load().aotcu_matmul2(self.h, kind, _dp(out_a), _dp(out_b), _dp(w_a), _dp(w_b), _dp(xs), m, rows, cols))
+
     def bench_matmul(self, kind: int, out, w, copy_stride: int, n_copies: int, xs, m: int, rows: int, cols: int,
                      iters: int) -> float:
         """Average milliseconds per launch of the (m x cols) by (rows x cols) product, timed on the

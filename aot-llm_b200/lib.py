@@ -105,6 +105,7 @@ SYMBOLS = {
     "aotcu_matvec2": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _sz]),
     "aotcu_matvec3": (_i, [_vp, C.POINTER(_i), _pp, _pp, _vp, C.POINTER(_sz), _sz]),
     "aotcu_matmul": (_i, [_vp, _i, _vp, _vp, _vp, _sz, _sz, _sz]),
+    "aotcu_matmul2": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "aotcu_matvec_k_static": (_i, [_vp, _i, _vp, _vp, _vp, _sz, _sz]),
     "aotcu_block_sums": (_i, [_vp, _i, _vp, _vp, _sz, _sz, _vp, _vp]),
     "aotcu_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _f]),

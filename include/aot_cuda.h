@@ -122,6 +122,11 @@ int aotcu_matvec3(aotcu_ctx* ctx, const int kinds[3], float* const outs[3], cons
  * to m calls of aotcu_matvec. */
 int aotcu_matmul(aotcu_ctx* ctx, int kind, float* out, const uint8_t* w, const void* xs, size_t m, size_t rows,
                  size_t cols);
+/* matmul2_q8_k_input / matmul2_q8_0_input (matvec.rs:571-583): two matrices of equal shape
+ * and kind against the same m activation vectors (ffn_gate and ffn_up of a prompt chunk);
+ * out_x[i*rows + r] as aotcu_matmul. */
+int aotcu_matmul2(aotcu_ctx* ctx, int kind, float* out_a, float* out_b, const uint8_t* w_a, const uint8_t* w_b,
+                  const void* xs, size_t m, size_t rows, size_t cols);
 /* No counterpart in the reference (its CPU kernels borrow `State.aqk`, which the caller
  * owns). out[r] = dot(W[r], quantize_q8_k(x)) for a K-quant matrix (kind Q4_K, Q5_K or
  * Q6_K) and an f32 device vector x, bit-identical to aotcu_quantize_q8_k followed by

@@ -158,6 +158,23 @@ def test_matmul_tensor_core_tiles_bit_exact(pkg, ob, ctx, kind, rows, cols):
     ctx.device_status()
 
 
+# matmul2 (crates/aot-kernels/src/matvec.rs:571-583): gate and up of a prompt chunk in one call
+@pytest.mark.parametrize("kind", [Q8_0, Q4_K, Q6_K, F16])
+def test_matmul2_bit_exact(pkg, ob, ctx, kind):
+    rows, cols = 40, 512
+    pool, tab = ob.Pool(3), ob.detect_table()
+    wa, wb = make_weights(pkg, kind, rows, cols, 201 + kind), make_weights(pkg, kind, rows, cols, 301 + kind)
+    dwa, dwb = ctx.to_device(wa), ctx.to_device(wb)
+    for m in (1, 5, 8, 33):
+        xs = _x(m * cols, 40 + m, 1.0)
+        q = ob.quantize_act(kind, xs)
+        da, db = ctx.alloc(m * rows * 4), ctx.alloc(m * rows * 4)
+        ctx.matmul2(kind, da, db, dwa, dwb, ctx.to_device(q.view(np.uint8)), m, rows, cols)
+        assert_bits_equal(da.download(np.float32, m * rows).reshape(m, rows), ob.matmul(pool, tab, kind, wa, q, m, rows, cols), f"matmul2 a kind {kind} m {m}")
+        assert_bits_equal(db.download(np.float32, m * rows).reshape(m, rows), ob.matmul(pool, tab, kind, wb, q, m, rows, cols), f"matmul2 b kind {kind} m {m}")
+    ctx.device_status()
+
+
 def test_matmul_large_tile_loop(pkg, ob, ctx):
     rows, cols, m = 1200, 2048, 5
     w = make_weights(pkg, Q4_K, rows, cols, 5)
