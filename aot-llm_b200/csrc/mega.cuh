@@ -701,16 +701,13 @@ __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag
   sp.last = clock64();
   float* row = M.scr;
   float* sq = M.scr + n;
-  // this thread's norm weights, requested before the wait for the row
-  constexpr int WMAX = 8;
-  float wv[WMAX];
-  const bool w_in_regs = n <= WMAX * g.nthreads;
-  if (w_in_regs) {
-#pragma unroll
-    for (int u = 0; u < WMAX; u++) {
-      const int i = g.tid + u * g.nthreads;
-      wv[u] = i < n ? w[i] : 0.0f;
-    }
+  // Scaling and quantization are one pass: warp b takes super-block b, lane l its elements
+  // 8l..8l+7. The norm weights of the warp's first block are requested before the wait.
+  const int warp = g.tid >> 5, nw = g.nthreads >> 5, lane = g.tid & 31, nblk = n >> 8;
+  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+  if (warp < nblk) {
+    w0 = __ldg(reinterpret_cast<const float4*>(w + warp * 256 + 8 * lane));
+    w1 = __ldg(reinterpret_cast<const float4*>(w + warp * 256 + 8 * lane) + 1);
   }
   if (src_in_scr) {
     for (int i = g.tid; i < n; i += g.nthreads) sq[i] = fmul(row[i], row[i]);
@@ -741,20 +738,21 @@ __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag
   float ss = group_seq_sum(sq, n, M.ss, g, &sp);
   sp.mark(17);
   float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
-  g.sync();
-  if (w_in_regs) {
-#pragma unroll
-    for (int u = 0; u < WMAX; u++) {
-      const int i = g.tid + u * g.nthreads;
-      if (i < n) row[i] = fmul(fmul(row[i], r), wv[u]);
-    }
-  } else {
-    for (int i = g.tid; i < n; i += g.nthreads) row[i] = fmul(fmul(row[i], r), w[i]);
-  }
-  g.sync();
   sp.mark(18);
-  const int warp = g.tid >> 5, nw = g.nthreads >> 5;
-  for (int b = warp; b < n / 256; b += nw) warp_quantize_q8k<false>(row + b * 256, M.sx + b * XK_STRIDE, 1);
+  for (int b = warp; b < nblk; b += nw) {
+    if (b != warp) {
+      w0 = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane));
+      w1 = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane) + 1);
+    }
+    const float4 x0 = *reinterpret_cast<const float4*>(row + b * 256 + 8 * lane);
+    const float4 x1 = *(reinterpret_cast<const float4*>(row + b * 256 + 8 * lane) + 1);
+    float v[8];
+    v[0] = fmul(fmul(x0.x, r), w0.x); v[1] = fmul(fmul(x0.y, r), w0.y);
+    v[2] = fmul(fmul(x0.z, r), w0.z); v[3] = fmul(fmul(x0.w, r), w0.w);
+    v[4] = fmul(fmul(x1.x, r), w1.x); v[5] = fmul(fmul(x1.y, r), w1.y);
+    v[6] = fmul(fmul(x1.z, r), w1.z); v[7] = fmul(fmul(x1.w, r), w1.w);
+    warp_quantize_q8k_vals(v, M.sx + b * XK_STRIDE, 1);
+  }
   g.sync();
   sp.mark(19);
 }
