@@ -151,3 +151,14 @@ def test_parallel_sequential_sum_is_exact(hostcheck):
         for T, head in ((992, 48), (32, 0), (256, 8), (7, 3)):
             got = np.float32(hostcheck.hc_seqsum(p.ctypes.data_as(C.c_void_p), p.size, T, head, None))
             assert got.view(np.uint32) == want.view(np.uint32) or (np.isnan(got) and np.isnan(want)), (p.size, T)
+
+
+def test_bench_kind_table_matches_the_library(pkg):
+    """bench.py names kinds by the ids of include/aot_cuda.h."""
+    import importlib.util
+    from pathlib import Path
+    spec = importlib.util.spec_from_file_location("bench_mod", Path(__file__).resolve().parent.parent / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert [k for k, _ in sorted(bench.KINDS.items(), key=lambda kv: kv[1])] == pkg.lib.KIND_NAMES
+    assert bench.METRIC == "decode_tokens_per_s"
