@@ -175,6 +175,22 @@ def test_matmul2_bit_exact(pkg, ob, ctx, kind):
     ctx.device_status()
 
 
+# Wide rows: the activation images of all rows do not fit in shared memory at once, so the
+# streaming kernel (Q8_0 family) and the float kernel work through them in groups.
+@pytest.mark.parametrize("kind", [Q4_0, Q8_0, BF16])
+def test_matmul_wide_rows_in_groups_bit_exact(pkg, ob, ctx, kind):
+    rows, cols, m = 24, 8192, 61
+    pool, tab = ob.Pool(4), ob.detect_table()
+    w = make_weights(pkg, kind, rows, cols, 400 + kind)
+    xs = _x(m * cols, 77, 1.0)
+    q = ob.quantize_act(kind, xs)
+    want = ob.matmul(pool, tab, kind, w, q, m, rows, cols)
+    dout = ctx.alloc(m * rows * 4)
+    ctx.matmul(kind, dout, ctx.to_device(w), ctx.to_device(q.view(np.uint8)), m, rows, cols)
+    assert_bits_equal(dout.download(np.float32, m * rows).reshape(m, rows), want, f"matmul kind {kind} {rows}x{cols} m {m}")
+    ctx.device_status()
+
+
 def test_matmul_large_tile_loop(pkg, ob, ctx):
     rows, cols, m = 1200, 2048, 5
     w = make_weights(pkg, Q4_K, rows, cols, 5)
