@@ -1,7 +1,7 @@
 """Builds libaot_cuda.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
 The same command is what a Rust ``build.rs`` would run for the reference's
-generated project; see INTEGRATION.md.
+generated project.
 """
 from __future__ import annotations
 

@@ -1,5 +1,5 @@
 """Benchmark of the hot path: batch-1 greedy decode of the synthetic
-TinyLlama-shaped Q4_K_M model (BASELINE.json configs[1]).
+TinyLlama-shaped Q4_K_M model (benchmark configuration 1).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -105,7 +105,7 @@ KINDS = {"f32": 0, "f16": 1, "bf16": 2, "q4_0": 3, "q5_0": 4, "q8_0": 5, "q4_k":
 
 
 def _synth_matrix(pkg, kind: int, rows: int, cols: int, seed: int) -> np.ndarray:
-    """Seeded random blocks of one quant type, fields uniform as in BASELINE.json configs[0]."""
+    """Seeded random blocks of one quant type, every field of the layout filled uniformly (benchmark configuration 0)."""
     rb = pkg.lib.row_bytes(kind, cols)
     w = np.zeros(rows * rb, dtype=np.uint8)
     pkg.lib.check(pkg.lib.load().aotcu_synth_tensor(kind, rows, cols, 1e-3, 1e-2, seed, w.ctypes.data))
@@ -163,7 +163,7 @@ def prompt_tokens_n(vocab: int, n: int):
 
 
 def run_sweep(args):
-    """BASELINE.json configs[4]: every quant type at four matrix shapes, M = 1 and M = 64."""
+    """Benchmark configuration 4: every quant type at four matrix shapes, M = 1 and M = 64."""
     pkg = graft.import_package()
     ctx = pkg.Context(0)
     peak, peak_src = measured_peak_gbs()
@@ -395,7 +395,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
 
 def run_tp(args, rank: int, world: int, local_rank: int):
-    """BASELINE.json configs[3]: Qwen3-8B-shaped decode, row-sharded over the ranks, one token
+    """Benchmark configuration 3: Qwen3-8B-shaped decode, row-sharded over the ranks, one token
     stream (strong scaling). Every rank builds the synthetic model from the same seed and
     keeps its shard."""
     pkg = graft.import_package()

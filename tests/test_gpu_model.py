@@ -102,7 +102,7 @@ def test_forward_bounds_match_generated_asserts(pkg, ctx):
 
 
 def test_tinyllama_shape_greedy_128_identical(pkg, ob, ctx):
-    """BASELINE config 1: TinyLlama-shaped Q4_K_M model, 6-token prompt, 128 greedy tokens."""
+    """Benchmark configuration 1: TinyLlama-shaped Q4_K_M model, 6-token prompt, 128 greedy tokens."""
     spec = pkg.model.tinyllama()
     prompt = np.random.default_rng(7).integers(0, 32000, 6).tolist()
     n_ctx, n_gen = 160, 128
