@@ -1,4 +1,6 @@
 """Whole-step parity: the interpreted forward pass on the GPU against the oracle's."""
+import os
+
 import numpy as np
 import pytest
 
@@ -189,4 +191,33 @@ def test_prompt_chunks_on_tensor_core_tiles_bit_exact(pkg, ob, ctx, arch):
         om.forward(t, pos, True)
         assert_bits_equal(g.logits(), om.logits(), f"{arch} decode at {pos} after the prompt chunks")
         pos += 1
+    ctx.device_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.timeout(600)
+def test_long_context_decode_bit_exact(pkg, ob, ctx):
+    """Near the end of a 2048-position context: prompt chunks of 64 fill the cache, then the
+    one-kernel step decodes with ~2000 cached positions per head (many staged K/V chunks, the
+    exact softmax sum over two thousand terms). Four layers of the TinyLlama shape keep the
+    CPU side of the comparison short."""
+    spec = pkg.model.tinyllama(n_layer=4)
+    n_ctx, n_prompt, n_gen = 2048, 1984, 6
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 64)
+    om = ob.model_from_spec(spec, n_ctx, 64, n_threads=min(16, os.cpu_count() or 1))
+    toks = np.random.default_rng(21).integers(0, 32000, n_prompt).tolist()
+    for c0 in range(0, n_prompt, 64):
+        last = c0 + 64 == n_prompt
+        g.forward_batch(toks[c0:c0 + 64], c0, last)
+        om.forward_batch(toks[c0:c0 + 64], c0, last)
+    assert_bits_equal(g.logits(), om.logits(), "logits after the 1984-token prompt")
+    first = ob.argmax(om.logits())
+    ids, _ = g.generate(first, n_prompt, n_gen)
+    want, tok = [], first
+    for i in range(n_gen):
+        om.forward(tok, n_prompt + i, True)
+        tok = ob.argmax(om.logits())
+        want.append(tok)
+    assert ids.tolist() == want
+    assert_bits_equal(g.logits(), om.logits(), "logits at position 1989")
     ctx.device_status()
