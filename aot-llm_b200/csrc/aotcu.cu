@@ -309,6 +309,8 @@ static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
 // ---- parity export: integer block sums -------------------------------------------------------
 __global__ void block_sums_kernel(int kind, const uint8_t* w, const uint8_t* x, int rows, int nb, int32_t* sumi,
                                   int32_t* summ) {
+  pdl_launch_dependents();
+  pdl_wait();  // a launch with programmatic stream serialization must not run ahead of its predecessor
   // One thread per (row, block), straight from global memory with byte reads; this
   // is a checker for the integer arithmetic, not a fast path.
   for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < (size_t)rows * nb;

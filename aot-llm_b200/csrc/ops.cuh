@@ -149,6 +149,8 @@ __global__ void quantize_q80_kernel(const float* __restrict__ x, uint8_t* __rest
 
 // Reference-layout blocks -> images (for callers that hand in BlockQ8_K / BlockQ8_0 arrays).
 __global__ void q8k_to_image_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int n_blocks) {
+  pdl_launch_dependents();
+  pdl_wait();  // a launch with programmatic stream serialization must not run ahead of its predecessor
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks * 73; i += gridDim.x * blockDim.x) {
     int b = i / 73, w = i - b * 73;
     int off = w == 0 ? 288 : (w <= 64 ? (w - 1) * 4 : 256 + (w - 65) * 4);
@@ -156,6 +158,8 @@ __global__ void q8k_to_image_kernel(const uint8_t* __restrict__ in, uint8_t* __r
   }
 }
 __global__ void q80_to_image_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int n_blocks) {
+  pdl_launch_dependents();
+  pdl_wait();  // a launch with programmatic stream serialization must not run ahead of its predecessor
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks * 9; i += gridDim.x * blockDim.x) {
     int b = i / 9, w = i - b * 9;
     int off = w == 0 ? 32 : (w - 1) * 4;
@@ -283,6 +287,8 @@ __global__ void __launch_bounds__(128) qk_post_kernel(const QkPostParams P) {
 // Stand-alone pieces of the same, for the operator-level API.
 __global__ void rope_kernel(float* x, int m, int n_heads, int head_dim, int rot_dim, const float* cs, int cs_stride,
                             int neox) {
+  pdl_launch_dependents();
+  pdl_wait();  // a launch with programmatic stream serialization must not run ahead of its predecessor
   const int half = rot_dim / 2;
   const size_t total = (size_t)m * n_heads * half;
   for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
@@ -300,6 +306,8 @@ __global__ void rope_kernel(float* x, int m, int n_heads, int head_dim, int rot_
 }
 
 __global__ void __launch_bounds__(128) rmsnorm_heads_kernel(float* x, const float* w, int head_dim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();  // a launch with programmatic stream serialization must not run ahead of its predecessor
   __shared__ float h[256];
   __shared__ float sq[256];
   __shared__ float slot;
@@ -483,15 +491,21 @@ __global__ void add_inplace_kernel(float* x, const float* y, size_t n) {
     x[i] = fadd(x[i], y[i]);
 }
 __global__ void add_bias_rows_kernel(float* x, const float* b, size_t n, size_t m) {
+  pdl_launch_dependents();
+  pdl_wait();  // a launch with programmatic stream serialization must not run ahead of its predecessor
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n * m; i += (size_t)gridDim.x * blockDim.x)
     x[i] = fadd(x[i], b[i % n]);
 }
 __global__ void scale_inplace_kernel(float* x, float s, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();  // a launch with programmatic stream serialization must not run ahead of its predecessor
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     x[i] = fmul(x[i], s);
 }
 __global__ void store_kv_kernel(float* k_cache, float* v_cache, const float* k, const float* v, size_t n,
                                 const int* pos_ptr, int pos0, int kv_dim) {
+  pdl_launch_dependents();
+  pdl_wait();  // a launch with programmatic stream serialization must not run ahead of its predecessor
   size_t at = (size_t)(pos_ptr ? *pos_ptr : pos0) * kv_dim;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     k_cache[at + i] = k[i];

@@ -221,3 +221,32 @@ def test_long_context_decode_bit_exact(pkg, ob, ctx):
     assert ids.tolist() == want
     assert_bits_equal(g.logits(), om.logits(), "logits at position 1989")
     ctx.device_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("arch", ["llama", "qwen2", "qwen3"])
+def test_dependent_launch_switch_keeps_results(pkg, ob, ctx, arch):
+    """The "pdl" switch lets every kernel of the per-operator path start while its predecessor
+    drains; each kernel waits for the predecessor's results before it touches them, so the
+    output is unchanged bit for bit (prompt chunk, per-token steps, with and without graphs)."""
+    spec = pkg.model.tiny(arch, n_layer=3)
+    n_ctx = 96
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 16)
+    om = ob.model_from_spec(spec, n_ctx, 16, n_threads=4)
+    g.set_option("pdl", 1)
+    if g.set_option("mega_available", 0):
+        g.set_option("mega", 0)
+    prompt = [5, 17, 300, 42, 7, 7, 1, 250, 0, 33, 91, 2]
+    g.forward_batch(prompt, 0, True)
+    om.forward_batch(prompt, 0, True)
+    assert_bits_equal(g.logits(), om.logits(), f"{arch} prompt logits with dependent launches")
+    tok, pos = ob.argmax(om.logits()), len(prompt)
+    for graph in (0, 1):
+        g.set_option("graph", graph)
+        for _ in range(6):
+            g.forward(tok, pos, True)
+            om.forward(tok, pos, True)
+            assert_bits_equal(g.logits(), om.logits(), f"{arch} logits at {pos} graph {graph} with dependent launches")
+            tok, pos = ob.argmax(om.logits()), pos + 1
+    g.set_option("pdl", 0)
+    ctx.device_status()
