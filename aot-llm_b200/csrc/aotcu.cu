@@ -56,7 +56,7 @@ struct aotcu_ctx {
   size_t max_smem = 0;
   cudaStream_t stream = nullptr;
   int* d_err = nullptr;
-  bool pdl = false;
+  bool pdl = true;  // programmatic dependent launch between the kernels of a stream
   uint64_t launches = 0;
   cudaEvent_t t0 = nullptr, t1 = nullptr;
 };

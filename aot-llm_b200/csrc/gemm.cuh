@@ -341,7 +341,6 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32, 2) gemm_q8k_mma_kernel(const 
   const int n_rounds = (P.n_tiles + per_round - 1) / per_round;
   const int per_part = EPL / ks > 0 ? EPL / ks : 1;  // outputs per lane this warp sums
   pdl_launch_dependents();
-  pdl_wait();
   for (int round = 0; round < n_rounds; round++) {
     const int tile_raw = (round * ctas_per_group + cta_in_group) * tpc + tile_i;
     const bool active = tile_raw < P.n_tiles;
@@ -373,6 +372,8 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32, 2) gemm_q8k_mma_kernel(const 
     for (int e = 0; e < EPL; e++) sum0[e] = sum1[e] = 0.0f;
     for (int ch = 0; ch < n_chunks; ch++) {
       const int b0 = ch * kc, b1 = min(b0 + kc, nb);
+      // Weights do not depend on the previous kernel; activations and outputs do.
+      if (round == 0 && ch == 0) pdl_wait();
       if (n_chunks > 1 || round == 0) {
         // (with one chunk the images of the token group stay for all rounds)
         gemm_stage_x(ximg, P.x, P.x_image, nb, b0, b1 - b0, tokg, NT8, P.m);

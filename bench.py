@@ -258,8 +258,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     d = spec.head.dims
     ctx = pkg.Context(local_rank)
     g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, N_CTX, 8)
-    if args.pdl:
-        g.set_option("pdl", 1)
+    if args.pdl >= 0:
+        g.set_option("pdl", args.pdl)   # default: the library's own default (on)
     prompt = prompt_tokens(d.vocab)
     steps, warmup = args.steps, max(args.warmup, 3)
 
@@ -470,7 +470,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--pdl", type=int, default=0)
+    ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch: 0 off, 1 on, -1 library default")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp", action="store_true", help="configs[3]: Qwen3-8B-shaped decode sharded over the ranks")
     ap.add_argument("--tp-layers", type=int, default=36)

@@ -266,7 +266,7 @@ int aotcu_generate(aotcu_gpu* g, uint32_t token, size_t pos, size_t n_steps, uin
 uint64_t aotcu_gpu_dispatches(aotcu_gpu* g);
 /* Tuning switches (the role of AOT_GPU_MV_ROWS, metal.rs:368): name = "graph"
  * (replay decode steps as a CUDA graph, default 1), "pdl" (programmatic dependent
- * launch between kernels, default 0), "mega" (run decode steps as the one-kernel step
+ * launch between kernels, default 1), "mega" (run decode steps as the one-kernel step
  * when the model allows it, default 1). Query: "mega_available" returns 1 when the model
  * can use the one-kernel step, else 0 (the value argument is ignored). */
 int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value);
