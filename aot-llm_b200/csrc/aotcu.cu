@@ -615,7 +615,7 @@ static size_t attn_smem_budget(const aotcu_ctx* c) { return c->max_smem - sizeof
 static size_t attn_smem_bytes(int n_head, int n_kv_head, int head_dim, size_t max_len) {
   const int gqa = n_head / n_kv_head, hpc = gqa < 8 ? gqa : 8;
   max_len = (max_len + 3) & ~(size_t)3;
-  return ((size_t)hpc * head_dim + (size_t)ATTN_CHUNK * (head_dim + 4) + (size_t)hpc * max_len) * sizeof(float);
+  return ((size_t)hpc * head_dim + (size_t)2 * ATTN_CHUNK * (head_dim + 4) + (size_t)hpc * max_len) * sizeof(float);
 }
 
 static int launch_attention(aotcu_ctx* c, float* out, const float* q, const float* kc, const float* vc, float* scratch,
@@ -642,7 +642,7 @@ static int launch_attention(aotcu_ctx* c, float* out, const float* q, const floa
   // Scores in shared memory when the longest row of this call fits, else in `scratch`.
   size_t max_len = pos_ptr ? n_ctx : std::min(n_ctx, pos0 + m);
   max_len = (max_len + 3) & ~(size_t)3;
-  const size_t fixed = ((size_t)P.heads_per_cta * head_dim + (size_t)ATTN_CHUNK * (head_dim + 4)) * sizeof(float);
+  const size_t fixed = ((size_t)P.heads_per_cta * head_dim + (size_t)2 * ATTN_CHUNK * (head_dim + 4)) * sizeof(float);
   const size_t with_scores = fixed + (size_t)P.heads_per_cta * max_len * sizeof(float);
   const size_t budget = attn_smem_budget(c);
   size_t smem = fixed;

@@ -366,42 +366,42 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParam
   const int len = n - t0;
   const int kstride = hd + 4;
   float* qs = sm_f;                                  // hpc x hd
-  float* kv = qs + hpc * hd;                         // ATTN_CHUNK x (hd + 4)
-  float* sc_all = kv + ATTN_CHUNK * kstride;         // hpc x smem_scores
+  float* kv = qs + hpc * hd;                         // two buffers of ATTN_CHUNK x (hd + 4)
+  const int buf_floats = ATTN_CHUNK * kstride;
+  float* sc_all = kv + 2 * buf_floats;               // hpc x smem_scores
   float* sc = P.smem_scores ? sc_all + warp * P.smem_scores : P.scratch + ((size_t)row * P.n_head + h) * P.ctx;
   for (int i = threadIdx.x; i < hpc * hd; i += ATTN_THREADS) {
     const int w = i / hd, hl = part * hpc + w;
     qs[i] = hl < gqa ? P.q[(size_t)row * q_dim + (kvh * gqa + hl) * hd + (i - w * hd)] : 0.0f;
   }
+  // Cached rows [c0, c0 + cn) of this KV head into a chunk buffer with cp.async: the next
+  // chunk loads while the current one is consumed.
+  auto stage = [&](float* buf, const float* cache, int stride, int c0, int cn) {
+    for (int j = threadIdx.x; j < cn * hd4; j += ATTN_THREADS) {
+      const int t = j / hd4, i4 = j - t * hd4;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(buf + t * stride + 4 * i4)),
+                   "l"(cache + (size_t)(t0 + c0 + t) * kv_dim + kvh * hd + 4 * i4)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
   // scores: dot(q, k_t) * scale, each dot a sequential f32 loop (ops.rs:160-166)
   float lmax = -INFINITY;
   const float* qh = qs + warp * hd;
-  for (int c0 = 0; c0 < len; c0 += ATTN_CHUNK) {
+  stage(kv, P.k_cache, kstride, 0, min(ATTN_CHUNK, len));
+  for (int c0 = 0, ci = 0; c0 < len; c0 += ATTN_CHUNK, ci++) {
     const int cn = min(ATTN_CHUNK, len - c0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < cn * hd4; i += 2 * ATTN_THREADS) {
-      float4 a[2];
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int j = i + u * ATTN_THREADS;
-        if (j < cn * hd4) {
-          const int t = j / hd4, i4 = j - t * hd4;
-          a[u] = reinterpret_cast<const float4*>(P.k_cache + (size_t)(t0 + c0 + t) * kv_dim + kvh * hd)[i4];
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int j = i + u * ATTN_THREADS;
-        if (j < cn * hd4) {
-          const int t = j / hd4, i4 = j - t * hd4;
-          *reinterpret_cast<float4*>(kv + t * kstride + 4 * i4) = a[u];
-        }
-      }
+    const float* cur = kv + (ci & 1) * buf_floats;
+    if (c0 + ATTN_CHUNK < len) {
+      stage(kv + ((ci + 1) & 1) * buf_floats, P.k_cache, kstride, c0 + ATTN_CHUNK, min(ATTN_CHUNK, len - c0 - ATTN_CHUNK));
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     if (has_head) {
       for (int t = lane; t < cn; t += 32) {
-        const float4* kt = reinterpret_cast<const float4*>(kv + t * kstride);
+        const float4* kt = reinterpret_cast<const float4*>(cur + t * kstride);
         float s = 0.0f;
 #pragma unroll 4
         for (int i = 0; i < hd4; i++) {
@@ -417,7 +417,10 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParam
         lmax = fmaxf(lmax, s);
       }
     }
+    __syncthreads();  // this buffer is refilled two chunks later
   }
+  // the first chunk of V rows loads while the softmax runs
+  stage(kv, P.v_cache, hd, 0, min(ATTN_CHUNK, len));
   if (has_head) {
     // this head's softmax, by its own warp: max (order-free), exp, the denominator in
     // position order (ops.rs:103-107)
@@ -435,27 +438,14 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParam
   float o[8];
 #pragma unroll
   for (int j = 0; j < 8; j++) o[j] = 0.0f;
-  for (int c0 = 0; c0 < len; c0 += ATTN_CHUNK) {
+  for (int c0 = 0, ci = 0; c0 < len; c0 += ATTN_CHUNK, ci++) {
     const int cn = min(ATTN_CHUNK, len - c0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < cn * hd4; i += 2 * ATTN_THREADS) {
-      float4 a[2];
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int j = i + u * ATTN_THREADS;
-        if (j < cn * hd4) {
-          const int t = j / hd4, i4 = j - t * hd4;
-          a[u] = reinterpret_cast<const float4*>(P.v_cache + (size_t)(t0 + c0 + t) * kv_dim + kvh * hd)[i4];
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int j = i + u * ATTN_THREADS;
-        if (j < cn * hd4) {
-          const int t = j / hd4, i4 = j - t * hd4;
-          *reinterpret_cast<float4*>(kv + t * hd + 4 * i4) = a[u];
-        }
-      }
+    const float* cur = kv + (ci & 1) * buf_floats;
+    if (c0 + ATTN_CHUNK < len) {
+      stage(kv + ((ci + 1) & 1) * buf_floats, P.v_cache, hd, c0 + ATTN_CHUNK, min(ATTN_CHUNK, len - c0 - ATTN_CHUNK));
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     if (has_head) {
@@ -464,9 +454,10 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParam
         const float a = sc[c0 + t];
 #pragma unroll
         for (int j = 0; j < 8; j++)
-          if (lane + 32 * j < hd) o[j] = fadd(o[j], fmul(a, kv[t * hd + lane + 32 * j]));
+          if (lane + 32 * j < hd) o[j] = fadd(o[j], fmul(a, cur[t * hd + lane + 32 * j]));
       }
     }
+    __syncthreads();
   }
   if (has_head) {
 #pragma unroll
