@@ -503,7 +503,7 @@ static int gpu_rmsnorm(aotcu_gpu* g, float* dst, size_t dst_stride, const float*
   size_t smem = (2 * n + 4) * sizeof(float);
   ARG_CHECK(smem <= c->max_smem, "rmsnorm row of %zu floats does not fit shared memory", n);
   note_write(g, dst);
-  if (int rc = launch(c, rmsnorm_kernel, dim3((unsigned)m), dim3(256), smem, P)) return rc;
+  if (int rc = launch(c, rmsnorm_kernel, dim3((unsigned)m), dim3(512), smem, P)) return rc;
   if (q) {
     g->qsrc = aotcu_gpu::QSrc();
     g->qsrc.ptr = dst;
@@ -1202,7 +1202,7 @@ int aotcu_rmsnorm(aotcu_ctx* c, float* out, const float* x, const float* w, size
   P.eps = eps;
   size_t smem = (2 * n + 4) * sizeof(float);
   ARG_CHECK(smem <= c->max_smem, "row of %zu floats does not fit shared memory", n);
-  return launch(c, rmsnorm_kernel, dim3((unsigned)m), dim3(256), smem, P);
+  return launch(c, rmsnorm_kernel, dim3((unsigned)m), dim3(512), smem, P);
 }
 
 int aotcu_rmsnorm_heads(aotcu_ctx* c, float* x, const float* w, size_t n_heads, size_t head_dim, float eps) {

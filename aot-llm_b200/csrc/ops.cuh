@@ -182,7 +182,7 @@ struct RmsnormParams {
   uint8_t* q80_out;  // images, n/32 per row
 };
 
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const RmsnormParams P) {
+__global__ void __launch_bounds__(512) rmsnorm_kernel(const RmsnormParams P) {
   extern __shared__ __align__(16) float sm_f[];
   float* row = sm_f;          // n
   float* sq = sm_f + P.n;     // n
