@@ -193,7 +193,7 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   P.stage_bytes = (int)STREAM_STAGE_BYTES;
   const size_t x_image_bytes = P.q80 ? (call.cols / 32) * X0_STRIDE : (call.cols / 256) * XK_STRIDE;
   const size_t x_src_bytes = P.x_image ? x_image_bytes : (P.q80 ? (call.cols / 32) * 36 : (call.cols / 256) * 292);
-  const size_t tail = MEGA_BAR_BYTES + 16;
+  const size_t tail = MEGA_BAR_BYTES + 16 + MEGA_TERMS_BYTES;
   ARG_CHECK(x_image_bytes + tail + 2 * STREAM_STAGE_BYTES <= c->max_smem, "activation vector too long for shared memory");
   // activation rows per launch: leave room for at least three stages
   size_t group = (c->max_smem - tail - 3 * STREAM_STAGE_BYTES) / x_image_bytes;
@@ -781,25 +781,45 @@ static int mega_setup(aotcu_gpu* g) {
   const size_t kvd = (size_t)d.n_kv_head * d.head_dim;
   ok = ok && d.n_layer <= 200 && (size_t)d.dim >= (size_t)c->n_sm && (size_t)d.hidden >= (size_t)c->n_sm;
   if (!ok) return 0;
-  const int stage_bytes = 32768;
-  const int v_chunk = 6144 / d.head_dim;  // positions per staged chunk (two buffers of 24 KB + padding)
   size_t nb_max = std::max(std::max((size_t)d.dim, (size_t)d.hidden), qd) / 256;
-  // norm rows (2 x dim) or the attention scratch: q, k, v, squares, scores, two staged chunks of padded rows
-  size_t scratch = std::max((size_t)2 * d.dim, (size_t)4 * d.head_dim + ((g->n_ctx + 3) & ~(size_t)3) + (size_t)2 * v_chunk * (d.head_dim + 4)) * sizeof(float);
-  scratch = (scratch + 127) & ~(size_t)127;
-  const size_t table_bytes = (((size_t)d.n_layer + 1) * sizeof(StepLayer) + 15) & ~(size_t)15;
-  size_t fixed = nb_max * XK_STRIDE + scratch + MEGA_TAIL_BYTES + table_bytes;
-  if (fixed + 2 * (size_t)stage_bytes > c->max_smem) return 0;
-  // The largest row of any matrix must fit one stage.
+  // Block-term strips hold two rows of a gate/up pair, norm rows stay in registers (two
+  // super-blocks per warp).
+  if (((nb_max | 1) * 2 > (size_t)WARP_TERMS_FLOATS) || (size_t)d.dim > (size_t)512 * MEGA_CONSUMER_WARPS) return 0;
+  // The largest row of any matrix must fit a ring stage twice (a gate/up pair).
   size_t max_rb = 0;
   for (const auto& l : g->layers) {
     const aotcu_tensor* ts[7] = {&l.wq, &l.wk, &l.wv, &l.wo, &l.gate, &l.up, &l.down};
     for (auto t : ts) max_rb = std::max(max_rb, (size_t)kind_row_bytes(t->kind, t->cols));
   }
   max_rb = std::max(max_rb, (size_t)kind_row_bytes(out_t.kind, out_t.cols));
-  if (2 * max_rb + 192 > (size_t)stage_bytes) return 0;
-  int n_stages = (int)((c->max_smem - fixed) / stage_bytes);
-  if (n_stages > 8) n_stages = 8;
+  // Scratch: a head of norm rows (2 x dim) or attention vectors (q, k, v, squares, scores),
+  // then the area that stages cached K and V rows. 72 KB of staging hold every cached row of
+  // one head up to 140 positions at head_dim 64; longer contexts go through two chunk buffers.
+  const size_t small_floats = (std::max((size_t)2 * d.dim, (size_t)4 * d.head_dim + ((g->n_ctx + 3) & ~(size_t)3)) + 31) & ~(size_t)31;
+  size_t stage_floats = 18432;
+  const size_t table_bytes = (((size_t)d.n_layer + 1) * sizeof(StepLayer) + 15) & ~(size_t)15;
+  size_t scratch = 0, fixed = 0;
+  int stage_bytes = 0, n_stages = 0;
+  for (;;) {
+    scratch = ((small_floats + stage_floats) * sizeof(float) + 127) & ~(size_t)127;
+    fixed = nb_max * XK_STRIDE + scratch + MEGA_TAIL_BYTES + table_bytes;
+    // ring: the stage size that leaves the least shared memory unused
+    size_t best = 0;
+    for (int sb : {16384, 24576, 32768, 12288}) {
+      if (2 * max_rb + 192 > (size_t)sb || fixed + 2 * (size_t)sb > c->max_smem) continue;
+      int ns = (int)std::min<size_t>(8, (c->max_smem - fixed) / sb);
+      if ((size_t)ns * sb > best) {
+        best = (size_t)ns * sb;
+        stage_bytes = sb;
+        n_stages = ns;
+      }
+    }
+    if (best >= 96 * 1024 || stage_floats <= 6144) break;
+    stage_floats -= 2048;  // a small ring starves the products: give staging space back
+  }
+  if (n_stages < 2) return 0;
+  const int v_chunk = (int)(stage_floats / 2 / (d.head_dim + 4));  // positions per chunk buffer
+  if (v_chunk < 8) return 0;
   // One CTA per SM must be resident for the grid barriers.
   CU_TRY(cudaFuncSetAttribute(decode_step_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
   CU_TRY(cudaFuncSetAttribute(decode_step_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
@@ -880,6 +900,9 @@ static int mega_setup(aotcu_gpu* g) {
   P.step = g->d_step; P.history = g->d_history; P.history_cap = (int)g->history_cap; P.out_token = g->d_out_token;
   P.grid_bar = g->d_grid_bar; P.err = c->d_err;
   P.n_stages = n_stages; P.stage_bytes = stage_bytes; P.scratch_bytes = (int)scratch; P.v_chunk = v_chunk; P.table_bytes = (int)table_bytes;
+  P.small_floats = (int)small_floats; P.stage_floats = (int)stage_floats;
+  P.fast = 0;
+  P.spin_limit = 1 << 21;  // about two seconds of polling
   g->mega_ok = true;
   return 0;
 }
@@ -957,7 +980,8 @@ static int check_device_errors(aotcu_ctx* c) {
   CU_TRY(cudaStreamSynchronize(c->stream));
   if (h) {
     CU_TRY(cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream));
-    if (h & DEVERR_MBAR_TIMEOUT) return fail(AOTCU_ERR_TIMEOUT, "a bounded device-side wait expired (error word %d)", h);
+    if (h & (DEVERR_MBAR_TIMEOUT | DEVERR_GRID_TIMEOUT))
+      return fail(AOTCU_ERR_TIMEOUT, "a bounded device-side wait expired (error word %d)", h);
     return fail(AOTCU_ERR_CUDA, "device error word %d", h);
   }
   return 0;
@@ -1704,8 +1728,7 @@ int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world,
       x.inbox[r] = reinterpret_cast<LLWord*>(p);
     }
     // ranks step together: bound the waits at about half a minute instead of two seconds
-    const uint32_t limit = 1u << 25;
-    CU_TRY(cudaMemcpyToSymbol(c_ll_spin_limit, &limit, sizeof(limit)));
+    g->step_params.spin_limit = 1 << 25;
     // every rank counts launches from the same value, so tags agree across GPUs
     const unsigned one = 1;
     CU_TRY(cudaMemcpy(g->d_grid_bar + 1, &one, sizeof(unsigned), cudaMemcpyHostToDevice));
@@ -1769,6 +1792,29 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
     return 0;
   }
   if (!strcmp(name, "mega_available")) return g->mega_ok ? 1 : 0;
+  if (!strcmp(name, "fast") || !strcmp(name, "exact") || !strcmp(name, "spin_limit")) {
+    // Parameters of the one-kernel step are baked into the captured graphs: drop them.
+    CU_TRY(cudaStreamSynchronize(g->c->stream));
+    for (int i = 0; i < 2; i++)
+      if (g->decode_graph[i]) {
+        cudaGraphExecDestroy(g->decode_graph[i]);
+        g->decode_graph[i] = nullptr;
+      }
+    if (g->gen_graph) {
+      cudaGraphExecDestroy(g->gen_graph);
+      g->gen_graph = nullptr;
+    }
+    if (!strcmp(name, "spin_limit")) {
+      ARG_CHECK(value >= 1, "spin_limit must be at least 1");
+      g->step_params.spin_limit = value;
+    } else if (!strcmp(name, "fast")) {
+      ARG_CHECK(value >= 0 && value <= 15, "fast is a mask of bits 1, 2, 4, 8");
+      g->step_params.fast = value;
+    } else {
+      g->step_params.fast = value ? 0 : 15;
+    }
+    return 0;
+  }
   if (!strcmp(name, "pdl")) {
     if (g->c->pdl != (value != 0)) {
       // Captured graphs bake the launch attributes in; drop them.

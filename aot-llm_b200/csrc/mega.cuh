@@ -16,292 +16,10 @@
 #include "gemv.cuh"
 #include "groupsum.cuh"
 #include "ops.cuh"
+#include "rowdot.cuh"
 #include "seqsum.cuh"
 
 namespace aot {
-
-// ---- warp-per-row dot products, four lanes per 256-weight super-block -----------------
-__device__ __forceinline__ float half_to_float_hw(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
-
-__device__ __forceinline__ U4 lds128q(uint32_t a) {
-  U4 v;
-  asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds32q(uint32_t a) {
-  uint32_t v;
-  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-
-// Lane (b = lane/4, c = lane%4) of a warp: quarter c of block b. Returns the two
-// integers of the whole block (summed over the four lanes) to all four lanes, and the
-// block's d|dmin word.
-template <bool Q5>
-__device__ __forceinline__ void quarter_k4(uint32_t wb, uint32_t xb, int c, int& sumi, int& summ, uint32_t& dd) {
-  const U4 hdr = lds128q(wb);
-  dd = hdr.x;
-  const K4Scales s = k4_unpack(hdr.y, hdr.z, hdr.w);
-  const uint32_t qs = wb + (Q5 ? 48 : 16) + 32 * c;
-  const U4 wa = lds128q(qs), wc = lds128q(qs + 16);
-  const U4 y0 = lds128q(xb + 64 * c), y1 = lds128q(xb + 64 * c + 16), y2 = lds128q(xb + 64 * c + 32), y3 = lds128q(xb + 64 * c + 48);
-  U4 h0{0, 0, 0, 0}, h1{0, 0, 0, 0};
-  if (Q5) {
-    h0 = lds128q(wb + 16);
-    h1 = lds128q(wb + 32);
-  }
-  int s_lo = 0, s_hi = 0;
-#pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const uint32_t w = i < 4 ? u4_get(wa, i) : u4_get(wc, i - 4);
-    uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
-    if (Q5) {
-      const uint32_t h = i < 4 ? u4_get(h0, i) : u4_get(h1, i - 4);
-      lo |= ((h >> (2 * c)) & 0x01010101u) << 4;
-      hi |= ((h >> (2 * c + 1)) & 0x01010101u) << 4;
-    }
-    s_lo = __dp4a((int)lo, (int)(i < 4 ? u4_get(y0, i) : u4_get(y1, i - 4)), s_lo);
-    s_hi = __dp4a((int)hi, (int)(i < 4 ? u4_get(y2, i) : u4_get(y3, i - 4)), s_hi);
-  }
-  const uint32_t scw = c < 2 ? s.sc_lo : s.sc_hi, mw = c < 2 ? s.m_lo : s.m_hi;
-  const int sh = (c & 1) * 16;
-  const int sc0 = (scw >> sh) & 0xFF, sc1 = (scw >> (sh + 8)) & 0xFF;
-  const int m0 = (mw >> sh) & 0xFF, m1 = (mw >> (sh + 8)) & 0xFF;
-  // bsums[4c..4c+3]: pairs (4c,4c+1) for sub-block 2c and (4c+2,4c+3) for 2c+1
-  const uint32_t bx = lds32q(xb + XK_BSUMS + 8 * c), by = lds32q(xb + XK_BSUMS + 8 * c + 4);
-  int si = sc0 * s_lo + sc1 * s_hi;
-  int sm = m0 * ((int)(short)(bx & 0xFFFF) + ((int)bx >> 16)) + m1 * ((int)(short)(by & 0xFFFF) + ((int)by >> 16));
-  si += __shfl_xor_sync(0xffffffffu, si, 1);
-  sm += __shfl_xor_sync(0xffffffffu, sm, 1);
-  si += __shfl_xor_sync(0xffffffffu, si, 2);
-  sm += __shfl_xor_sync(0xffffffffu, sm, 2);
-  sumi = si;
-  summ = sm;
-}
-
-// Q6_K: lane c covers half n = c/2 of the block and elements l in [16*(c%2), +16) of
-// each of its four 32-element quarters. Blocks are only 2-byte aligned: words come from
-// the aligned stream through a funnel shift.
-__device__ __forceinline__ int quarter_q6k(uint32_t wb, uint32_t xb, int c) {
-  const uint32_t sh = (wb & 2u) * 8u, p = wb & ~3u;
-  auto wload = [&](int k) -> uint32_t { return funnel_r(lds32q(p + 4 * k), lds32q(p + 4 * k + 4), sh); };
-  const int n = c >> 1, half = c & 1;
-  const U4 y1 = lds128q(xb + 128 * n + 16 * half), y2 = lds128q(xb + 128 * n + 32 + 16 * half),
-           y3 = lds128q(xb + 128 * n + 64 + 16 * half), y4 = lds128q(xb + 128 * n + 96 + 16 * half);
-  int a1 = 0, a2 = 0, a3 = 0, a4 = 0;
-#pragma unroll
-  for (int ii = 0; ii < 4; ii++) {
-    const int i = 4 * half + ii;
-    const uint32_t l0 = wload(16 * n + i), l32 = wload(16 * n + 8 + i), h = wload(32 + 8 * n + i);
-    const uint32_t q1 = (l0 & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
-    const uint32_t q2 = (l32 & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
-    const uint32_t q3 = ((l0 >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
-    const uint32_t q4 = ((l32 >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
-    a1 = __dp4a((int)q1, (int)u4_get(y1, ii), a1);
-    a2 = __dp4a((int)q2, (int)u4_get(y2, ii), a2);
-    a3 = __dp4a((int)q3, (int)u4_get(y3, ii), a3);
-    a4 = __dp4a((int)q4, (int)u4_get(y4, ii), a4);
-  }
-  const uint32_t s01 = wload(48 + 2 * n), s23 = wload(49 + 2 * n);
-  const int g = 8 * n + half;
-  const int c1 = (int)(int8_t)((s01 >> (8 * half)) & 0xFF), c2 = (int)(int8_t)((s01 >> (8 * half + 16)) & 0xFF);
-  const int c3 = (int)(int8_t)((s23 >> (8 * half)) & 0xFF), c4 = (int)(int8_t)((s23 >> (8 * half + 16)) & 0xFF);
-  const uint32_t bsa = xb + XK_BSUMS + 2 * g;
-  auto bs16 = [&](uint32_t a) -> int {
-    int v;
-    asm("ld.shared.s16 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-  };
-  int tot = c1 * a1 + c2 * a2 + c3 * a3 + c4 * a4;
-  tot -= 32 * (c1 * bs16(bsa) + c2 * bs16(bsa + 4) + c3 * bs16(bsa + 8) + c4 * bs16(bsa + 12));
-  tot += __shfl_xor_sync(0xffffffffu, tot, 1);
-  tot += __shfl_xor_sync(0xffffffffu, tot, 2);
-  return tot;
-}
-
-// Dot product of one K-quant row (in shared memory) with the Q8_K activation images,
-// computed by one warp, four lanes per block; terms are added in block order. All lanes
-// return the sum. `row` and `sx` are shared-space addresses.
-__device__ __forceinline__ float warp_row_dot_s(int kind, uint32_t row, uint32_t sx, int nb) {
-  const int lane = threadIdx.x & 31, bl = lane >> 2, c = lane & 3;
-  const int bs = kind_size(kind);
-  float sum = 0.0f;
-  for (int g0 = 0; g0 < nb; g0 += 8) {
-    const int b = g0 + bl;
-    // Idle lanes recompute the last block so every lane reaches the shuffles.
-    const int bb = b < nb ? b : nb - 1;
-    const uint32_t wb = row + (uint32_t)bb * bs, xb = sx + (uint32_t)bb * XK_STRIDE;
-    const float d_x = __uint_as_float(lds32q(xb + XK_D));
-    float term;
-    if (kind == Q6_K) {
-      const int si = quarter_q6k(wb, xb, c);
-      const uint32_t da = wb + 208;
-      const uint32_t dw = lds32q(da & ~3u) >> ((da & 2u) * 8u);
-      term = q6k_term(half_to_float_hw(dw & 0xFFFFu), d_x, si);
-    } else {
-      int si, sm;
-      uint32_t dd;
-      if (kind == Q5_K) quarter_k4<true>(wb, xb, c, si, sm, dd); else quarter_k4<false>(wb, xb, c, si, sm, dd);
-      term = k4_term(half_to_float_hw(dd & 0xFFFFu), half_to_float_hw(dd >> 16), d_x, si, sm);
-    }
-    const int nbg = min(8, nb - g0);
-    float t[8];
-#pragma unroll
-    for (int j = 0; j < 8; j++) t[j] = __shfl_sync(0xffffffffu, term, 4 * j);
-#pragma unroll
-    for (int j = 0; j < 8; j++)
-      if (j < nbg) sum = fadd(sum, t[j]);
-  }
-  return sum;
-}
-
-// ---- lane-per-block dot products ---------------------------------------------------------
-// One lane decodes one whole 256-weight super-block; the L = 2^k >= blocks-per-row lanes
-// of a group cover one row, a warp covers 32/L rows at once. Fewer instructions per
-// weight byte than the four-lane split above, which matters because these phases are
-// bound by instruction issue, not by HBM.
-__device__ __forceinline__ U4 lds128s(uint32_t a) {
-  U4 v;
-  asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds32s(uint32_t a) {
-  uint32_t v;
-  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-
-template <bool Q5>
-__device__ __forceinline__ float block_term_k4(uint32_t wb, uint32_t xb) {
-  const U4 hdr = lds128s(wb);
-  const K4Scales s = k4_unpack(hdr.y, hdr.z, hdr.w);
-  U4 h0{0, 0, 0, 0}, h1{0, 0, 0, 0};
-  uint32_t qs = wb + 16;
-  if (Q5) {
-    h0 = lds128s(wb + 16);
-    h1 = lds128s(wb + 32);
-    qs = wb + 48;
-  }
-  int sumi = 0;
-#pragma unroll
-  for (int c = 0; c < 4; c++) {
-    const U4 wa = lds128s(qs + 32 * c), wc = lds128s(qs + 32 * c + 16);
-    const U4 y0 = lds128s(xb + 64 * c), y1 = lds128s(xb + 64 * c + 16), y2 = lds128s(xb + 64 * c + 32),
-             y3 = lds128s(xb + 64 * c + 48);
-    int s_lo = 0, s_hi = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const uint32_t w = i < 4 ? u4_get(wa, i) : u4_get(wc, i - 4);
-      uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
-      if (Q5) {
-        const uint32_t h = i < 4 ? u4_get(h0, i) : u4_get(h1, i - 4);
-        lo |= ((h >> (2 * c)) & 0x01010101u) << 4;
-        hi |= ((h >> (2 * c + 1)) & 0x01010101u) << 4;
-      }
-      s_lo = __dp4a((int)lo, (int)(i < 4 ? u4_get(y0, i) : u4_get(y1, i - 4)), s_lo);
-      s_hi = __dp4a((int)hi, (int)(i < 4 ? u4_get(y2, i) : u4_get(y3, i - 4)), s_hi);
-    }
-    const uint32_t scw = c < 2 ? s.sc_lo : s.sc_hi;
-    sumi += byte_of(scw, (2 * c) & 3) * s_lo + byte_of(scw, (2 * c + 1) & 3) * s_hi;
-  }
-  const U4 b0 = lds128s(xb + XK_BSUMS), b1 = lds128s(xb + XK_BSUMS + 16);
-  const uint32_t m01 = __byte_perm(s.m_lo, 0, 0x1100), m23 = __byte_perm(s.m_lo, 0, 0x3322);
-  const uint32_t m45 = __byte_perm(s.m_hi, 0, 0x1100), m67 = __byte_perm(s.m_hi, 0, 0x3322);
-  int summ = 0;
-  summ = dp2a_lo(b0.x, m01, summ);
-  summ = dp2a_hi(b0.y, m01, summ);
-  summ = dp2a_lo(b0.z, m23, summ);
-  summ = dp2a_hi(b0.w, m23, summ);
-  summ = dp2a_lo(b1.x, m45, summ);
-  summ = dp2a_hi(b1.y, m45, summ);
-  summ = dp2a_lo(b1.z, m67, summ);
-  summ = dp2a_hi(b1.w, m67, summ);
-  const float d_x = __uint_as_float(lds32s(xb + XK_D));
-  return k4_term(half_to_float_hw(hdr.x & 0xFFFFu), half_to_float_hw(hdr.x >> 16), d_x, sumi, summ);
-}
-
-__device__ __forceinline__ float block_term_q6k(uint32_t wb, uint32_t xb) {
-  // Blocks are 2-byte aligned: four consecutive words come from five aligned ones.
-  const uint32_t sh = (wb & 2u) * 8u, p = wb & ~3u;
-  auto load4 = [&](int k, uint32_t w[4]) {
-    uint32_t a0 = lds32s(p + 4 * k), a1 = lds32s(p + 4 * k + 4), a2 = lds32s(p + 4 * k + 8), a3 = lds32s(p + 4 * k + 12),
-             a4 = lds32s(p + 4 * k + 16);
-    w[0] = funnel_r(a0, a1, sh);
-    w[1] = funnel_r(a1, a2, sh);
-    w[2] = funnel_r(a2, a3, sh);
-    w[3] = funnel_r(a3, a4, sh);
-  };
-  uint32_t scw[4];
-  load4(48, scw);
-  int total = 0;
-#pragma unroll
-  for (int n = 0; n < 2; n++) {
-#pragma unroll
-    for (int half = 0; half < 2; half++) {
-      uint32_t l0[4], l32[4], h[4];
-      load4(16 * n + 4 * half, l0);
-      load4(16 * n + 8 + 4 * half, l32);
-      load4(32 + 8 * n + 4 * half, h);
-      const U4 y1 = lds128s(xb + 128 * n + 16 * half), y2 = lds128s(xb + 128 * n + 32 + 16 * half),
-               y3 = lds128s(xb + 128 * n + 64 + 16 * half), y4 = lds128s(xb + 128 * n + 96 + 16 * half);
-      int a1 = 0, a2 = 0, a3 = 0, a4 = 0;
-#pragma unroll
-      for (int ii = 0; ii < 4; ii++) {
-        const uint32_t q1 = (l0[ii] & 0x0F0F0F0Fu) | ((h[ii] << 4) & 0x30303030u);
-        const uint32_t q2 = (l32[ii] & 0x0F0F0F0Fu) | ((h[ii] << 2) & 0x30303030u);
-        const uint32_t q3 = ((l0[ii] >> 4) & 0x0F0F0F0Fu) | (h[ii] & 0x30303030u);
-        const uint32_t q4 = ((l32[ii] >> 4) & 0x0F0F0F0Fu) | ((h[ii] >> 2) & 0x30303030u);
-        a1 = __dp4a((int)q1, (int)u4_get(y1, ii), a1);
-        a2 = __dp4a((int)q2, (int)u4_get(y2, ii), a2);
-        a3 = __dp4a((int)q3, (int)u4_get(y3, ii), a3);
-        a4 = __dp4a((int)q4, (int)u4_get(y4, ii), a4);
-      }
-      const int g = 8 * n + half;
-      total += (int)(int8_t)byte_of(scw[g >> 2], g & 3) * a1;
-      total += (int)(int8_t)byte_of(scw[(g + 2) >> 2], (g + 2) & 3) * a2;
-      total += (int)(int8_t)byte_of(scw[(g + 4) >> 2], (g + 4) & 3) * a3;
-      total += (int)(int8_t)byte_of(scw[(g + 6) >> 2], (g + 6) & 3) * a4;
-    }
-  }
-  const U4 b0 = lds128s(xb + XK_BSUMS), b1 = lds128s(xb + XK_BSUMS + 16);
-  int bias = 0;
-  bias = dp2a_lo(b0.x, scw[0], bias);
-  bias = dp2a_hi(b0.y, scw[0], bias);
-  bias = dp2a_lo(b0.z, scw[1], bias);
-  bias = dp2a_hi(b0.w, scw[1], bias);
-  bias = dp2a_lo(b1.x, scw[2], bias);
-  bias = dp2a_hi(b1.y, scw[2], bias);
-  bias = dp2a_lo(b1.z, scw[3], bias);
-  bias = dp2a_hi(b1.w, scw[3], bias);
-  const uint32_t da = wb + 208;
-  const uint32_t dw = lds32s(da & ~3u) >> ((da & 2u) * 8u);
-  const float d_x = __uint_as_float(lds32s(xb + XK_D));
-  return q6k_term(half_to_float_hw(dw & 0xFFFFu), d_x, total - 32 * bias);
-}
-
-// Dot products of the rows a warp owns in one pass: lane = (group gi = lane / L, block
-// slot bl = lane % L). `row` is this lane's row in shared memory (0 when the group has
-// no row), `kind` its weight kind. Returns the row's sum to every lane of its group,
-// block terms added in block order (matvec.rs:84-106).
-__device__ __forceinline__ float group_row_dot(uint32_t row, int kind, uint32_t sx, int nb, int L) {
-  const int lane = threadIdx.x & 31, bl = lane & (L - 1), gbase = lane & ~(L - 1);
-  const int bs = kind_size(kind);
-  float sum = 0.0f;
-  for (int g0 = 0; g0 < nb; g0 += L) {
-    const int b = g0 + bl;
-    float term = 0.0f;
-    if (row != 0 && b < nb) {
-      const uint32_t wb = row + (uint32_t)b * bs, xb = sx + (uint32_t)b * XK_STRIDE;
-      if (kind == Q4_K) term = block_term_k4<false>(wb, xb);
-      else if (kind == Q6_K) term = block_term_q6k(wb, xb);
-      else term = block_term_k4<true>(wb, xb);
-    }
-    __syncwarp();
-    const int cnt = min(L, nb - g0);
-    for (int j = 0; j < cnt; j++) sum = fadd(sum, __shfl_sync(0xffffffffu, term, gbase + j));
-  }
-  return sum;
-}
 
 // ---- tagged activation words ---------------------------------------------------------------
 // Activation vectors that cross CTAs inside the step travel as 64-bit words {f32 value,
@@ -311,9 +29,10 @@ __device__ __forceinline__ float group_row_dot(uint32_t row, int kind, uint32_t 
 // Tags are unique per (launch, phase): (launch count << 10) | phase id, phase id >= 1;
 // a zeroed buffer therefore never matches.
 typedef unsigned long long LLWord;
-// Polls before a wait gives up (about a microsecond each). The host raises it when several
-// GPUs step together: a rank whose host thread is late must not make its peers give up.
-__constant__ uint32_t c_ll_spin_limit = 1u << 21;
+// Every wait below is bounded: `abort` points at two shared words of the CTA, [0] = a wait
+// of this CTA has given up, [1] = polls (about a microsecond each) before a wait gives up.
+// The host raises the limit when several GPUs step together: a rank whose host thread is
+// late must not make its peers give up.
 
 __device__ __forceinline__ void ll_store(LLWord* p, float v, uint32_t tag) {
   const LLWord w = ((LLWord)tag << 32) | (LLWord)__float_as_uint(v);
@@ -332,20 +51,23 @@ __device__ __forceinline__ float ll_value(const LLWord* p) { return __uint_as_fl
 
 // Spin (bounded) until the word carries `tag`. On expiry the CTA's abort flag and the
 // device error word are set; every later wait then returns at once, so the kernel drains.
-__device__ __forceinline__ float ll_settle(const LLWord* p, LLWord w, uint32_t tag, volatile int* abort, int* err) {
-  if ((uint32_t)(w >> 32) != tag) {
-    uint32_t it = 0;
-    const uint32_t limit = c_ll_spin_limit;
-    for (; it < limit; ++it) {
-      w = ll_load(p);
-      if ((uint32_t)(w >> 32) == tag) break;
-      if ((it & 31u) == 31u && *abort) break;
-    }
-    if ((uint32_t)(w >> 32) != tag && !*abort) {
-      *abort = 1;
-      if (err) atomicOr(err, DEVERR_GRID_TIMEOUT);
-    }
+__device__ __noinline__ LLWord ll_spin(const LLWord* p, uint32_t tag, volatile int* abort, int* err) {
+  LLWord w = 0;
+  uint32_t it = 0;
+  const uint32_t limit = (uint32_t)abort[1];
+  for (; it < limit; ++it) {
+    w = ll_load(p);
+    if ((uint32_t)(w >> 32) == tag) break;
+    if ((it & 31u) == 31u && *abort) break;
   }
+  if ((uint32_t)(w >> 32) != tag && !*abort) {
+    *abort = 1;
+    if (err) atomicOr(err, DEVERR_GRID_TIMEOUT);
+  }
+  return w;
+}
+__device__ __forceinline__ float ll_settle(const LLWord* p, LLWord w, uint32_t tag, volatile int* abort, int* err) {
+  if ((uint32_t)(w >> 32) != tag) w = ll_spin(p, tag, abort, err);
   return __uint_as_float((uint32_t)w);
 }
 __device__ __forceinline__ float ll_wait(const LLWord* p, uint32_t tag, volatile int* abort, int* err) {
@@ -378,10 +100,11 @@ __device__ __forceinline__ void ll_store_sys(LLWord* p, float v, uint32_t tag) {
 __device__ __forceinline__ float ll_wait_sys(const LLWord* p, uint32_t tag, volatile int* abort, int* err) {
   LLWord w;
   uint32_t it = 0;
+  const uint32_t limit = (uint32_t)abort[1];
   for (;;) {
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
     if ((uint32_t)(w >> 32) == tag) break;
-    if (++it >= c_ll_spin_limit || ((it & 31u) == 31u && *abort)) {
+    if (++it >= limit || ((it & 31u) == 31u && *abort)) {
       if (!*abort) {
         *abort = 1;
         if (err) atomicOr(err, DEVERR_GRID_TIMEOUT);
@@ -391,6 +114,18 @@ __device__ __forceinline__ float ll_wait_sys(const LLWord* p, uint32_t tag, vola
   }
   return __uint_as_float((uint32_t)w);
 }
+
+// The one-kernel step walks all of its code once per layer, so the code has to stay inside
+// the SM's instruction cache: everything large that is used from more than one place is
+// kept out of line.
+__device__ __noinline__ float expf_exact_call(float x) { return expf_exact(x); }
+__device__ __noinline__ float silu_mul_call(float g, float u) { return fmul(fdiv(g, fadd(1.0f, expf_exact(-g))), u); }
+__device__ __noinline__ float group_seq_sum_call(const float* p, int n, SeqSumScratch* sc, int tid, int nthreads, int bar_id,
+                                                 unsigned long long* prof) {
+  SubProf sp{prof, clock64()};
+  return group_seq_sum(p, n, sc, CtaGroup{tid, nthreads, bar_id}, prof ? &sp : nullptr);
+}
+__device__ __noinline__ float dequant_elem_call(int kind, const uint8_t* row, size_t e) { return dequant_elem(kind, row, e); }
 
 // ---- step description (built once by the host, lives in global memory) ------------------
 // One matrix-product phase as both the producer and the consumers see it. The row
@@ -436,7 +171,11 @@ struct StepParams {
   int* err;
   int n_stages, stage_bytes;
   int scratch_bytes;   // f32 scratch region (norm rows, attention)
-  int v_chunk;         // positions per staged V chunk
+  int small_floats;    // floats of the scratch region's head (norm rows; q, k, v, squares, scores); the rest stages K and V rows
+  int stage_floats;    // floats of the K/V staging area
+  int v_chunk;         // positions per staged K or V chunk when a head's rows do not fit the staging area
+  int fast;            // FastBits: which sequential f32 loops may be reordered
+  int spin_limit;      // polls before a tagged-word wait gives up
   int table_bytes;     // bytes of the StepLayer table staged in shared memory (n_layer + 1 entries)
   unsigned long long* prof;  // optional: cycles per phase, accumulated by one CTA
   int prof_cta;
@@ -479,7 +218,7 @@ __device__ __forceinline__ bool ring_wait(const Ring& R, uint64_t* bar, uint32_t
 }
 
 // Byte ranges of the tile covering rows [t0, t1) of the op's row space.
-__device__ __forceinline__ int op_tile_parts(const MegaOp& op, int t0, int t1, TilePart parts[3]) {
+__device__ __noinline__ int op_tile_parts(const MegaOp& op, int t0, int t1, TilePart parts[3]) {
   if (op.pair || op.nseg == 1) {
     const int np = op.pair ? 2 : 1;
     uint32_t soff = 0;
@@ -518,7 +257,7 @@ __device__ __forceinline__ int op_tile_parts(const MegaOp& op, int t0, int t1, T
 }
 
 // Producer side (one thread): request every tile of this CTA's share of `op`.
-__device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, RingPos& pp) {
+__device__ __noinline__ void produce_op(const MegaOp& op, const Ring& R, RingPos& pp) {
   int c0, c1;
   cta_rows(op.span_rows, c0, c1);
   for (int t0 = c0; t0 < c1; t0 += op.tile_rows) {
@@ -535,121 +274,121 @@ __device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, Ring
   }
 }
 
-// Consumer side (every consumer warp). A warp pass covers 32/L rows (L lanes per row);
-// passes are dealt to warps round robin, continuing across tiles (`rot`), so that
-// consecutive small tiles keep all warps busy at once. In pair mode the lower half of
-// the warp takes gate rows and the upper half the matching up rows, and the SiLU gate
-// is applied in the epilogue. `sx` holds the Q8_K images of the activation vector;
-// `op` lives in shared memory.
+// Consumer side (every consumer warp). The rows (gate/up row pairs in pair mode) of this
+// CTA's share are dealt to the warps round robin, continuing across tiles, and a warp takes
+// a whole row: four lanes per super-block with the activation slices in registers
+// (rowdot.cuh). Block terms are parked in the warp's strip `wterms`; when the strip is
+// full or the product ends, lane i adds the terms of parked row i in block order and runs
+// the epilogue (residual add, SiLU gate, exchange with the other ranks). `sx` holds the
+// Q8_K images of the activation vector; `op` lives in shared memory.
+constexpr int WARP_TERMS_FLOATS = 128;  // strip per consumer warp
+
+template <bool TP>
+__device__ __noinline__ void warp_flush(const MegaOp& op, const float* wterms, int pend, int u0, int n_warps, int c0, int nb,
+                                           int tstride, uint32_t tag, const TpExchange* tpx, int which, float old_pref,
+                                           bool have_pref) {
+  __syncwarp();
+  const int lane = threadIdx.x & 31;
+  if (op.pair) {
+    // lanes 0..15 add the gate rows, lanes 16..31 the matching up rows
+    const int i = lane & 15, mt = lane >> 4;
+    float v = 0.0f;
+    if (i < pend) v = terms_seq_sum(wterms + (2 * i + mt) * tstride, nb);
+    const float up = __shfl_down_sync(0xffffffffu, v, 16);
+    if (lane < pend) {
+      const int r = c0 + u0 + lane * n_warps;
+      const float hv = op.epilogue == EPI_SILU_MUL ? silu_mul_call(v, up) : v;
+      if (op.ll) {
+        ll_store(reinterpret_cast<LLWord*>(op.seg[0].out) + r, hv, tag);
+      } else {
+        op.seg[0].out[r] = hv;
+        op.seg[1].out[r] = up;
+      }
+    }
+  } else if (lane < pend) {
+    const float v = terms_seq_sum(wterms + lane * tstride, nb);
+    int sg = 0, oi = c0 + u0 + lane * n_warps;
+    while (sg < op.nseg - 1 && oi >= op.seg[sg].rows) {
+      oi -= op.seg[sg].rows;
+      sg++;
+    }
+    if (TP && op.ll && tpx && op.epilogue == EPI_ACCUM) {
+      // a partial row of a sharded product: hand it to every rank (this one included)
+      for (int dst = 0; dst < tpx->world; dst++)
+        ll_store_sys(tpx->inbox[dst] + ((size_t)which * tpx->world + tpx->rank) * tpx->dim + oi, v, tag);
+    } else if (op.ll) {
+      // a residual row is only ever written by its owner, so its old value needs no tag check
+      LLWord* o = reinterpret_cast<LLWord*>(op.seg[sg].out) + oi;
+      ll_store(o, op.epilogue == EPI_ACCUM ? fadd(have_pref ? old_pref : ll_value(o), v) : v, tag);
+    } else {
+      float* o = op.seg[sg].out + oi;
+      *o = op.epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
+    }
+  }
+  __syncwarp();
+}
+
 template <bool TP = false>
-__device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp,
+__device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, float* wterms, int warp,
                                            int n_warps, uint32_t tag, const TpExchange* tpx = nullptr, int which = 0) {
-  const int rows_per_cta = op.rows_per_cta, tile_rows = op.tile_rows, pair = op.pair;
-  const int epilogue = op.epilogue, nb = op.cols >> 8, ll = op.ll;
+  const int tile_rows = op.tile_rows, pair = op.pair, nb = op.cols >> 8;
   int c0, c1;
   cta_rows(op.span_rows, c0, c1);
   const int lane = threadIdx.x & 31;
-  // Small ops (a row or less per warp) use the short-latency four-lanes-per-block dot, one
-  // row per warp; large ones the cheaper lane-per-block form.
-  const bool narrow = rows_per_cta * (pair ? 2 : 1) <= n_warps;
-  int L = 1;
-  while (L < nb && L < 32) L <<= 1;
-  if (narrow) L = 32;
-  const int G = 32 / L;                             // rows per warp pass
-  const bool split = pair && G >= 2;                // gate | up halves of one warp
-  const int rows_per_pass = split ? G / 2 : G;
-  const int gi = lane / L;
+  const int mats = pair ? 2 : 1;
+  const int tstride = nb | 1;  // odd, so the lane-parallel reads of the flush spread over the banks
+  int cap = WARP_TERMS_FLOATS / (tstride * mats);
+  cap = cap > (pair ? 16 : 32) ? (pair ? 16 : 32) : cap;
   const uint32_t sxa = smem_addr(sx);
-  int rot = 0;
+  YCache yc;
+  yc.lay = YL_NONE;
+  yc.g0 = -1;
+  // Old residual values of the first batch of rows, asked for before the first tile arrives.
+  float old_pref = 0.0f;
+  const bool pref = !pair && op.ll && op.epilogue == EPI_ACCUM && !(TP && tpx) && op.nseg == 1;
+  if (pref) {
+    const int r = c0 + warp + lane * n_warps;
+    if (lane < cap && r < c1) old_pref = ll_value(reinterpret_cast<const LLWord*>(op.seg[0].out) + r);
+  }
+  int pend = 0, pend_u0 = 0, batch = 0;
   for (int t0 = c0; t0 < c1; t0 += tile_rows) {
     if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
     const int t1 = min(t0 + tile_rows, c1);
     const uint32_t stage = smem_addr(R.stages + (size_t)cp.st * R.stage_bytes);
-    const int R_rows = t1 - t0;
-    const int n_pass = (R_rows + rows_per_pass - 1) / rows_per_pass;
-    int ps = warp - rot;
-    if (ps < 0) ps += n_warps;
-    if (ps < n_pass) {
+    const int lo = t0 - c0, hi = t1 - c0;  // this tile's units, CTA-relative
+    int u = lo + (warp - lo % n_warps + n_warps) % n_warps;
+    if (u < hi) {
       TilePart parts[3];
       const int np = op_tile_parts(op, t0, t1, parts);
-      for (; ps < n_pass; ps += n_warps) {
-        if (pair) {
-          const uint32_t base0 = stage + parts[0].soff + ((uint32_t)(uintptr_t)parts[0].src & 15u);
-          const uint32_t base1 = stage + parts[1].soff + ((uint32_t)(uintptr_t)parts[1].src & 15u);
-          if (split) {
-            const int which = gi >= rows_per_pass ? 1 : 0;
-            const int u = ps * rows_per_pass + (gi - which * rows_per_pass);
-            const uint32_t row = u < R_rows ? (which ? base1 : base0) + (uint32_t)u * op.row_bytes[which] : 0u;
-            const float v = group_row_dot(row, op.seg[which].kind, sxa, nb, L);
-            const float up = __shfl_down_sync(0xffffffffu, v, 16);
-            if (u < R_rows && which == 0 && (lane & (L - 1)) == 0) {
-              const int r = t0 + u;
-              const float hv = epilogue == EPI_SILU_MUL ? silu_mul_exact(v, up) : v;
-              if (ll) {
-                ll_store(reinterpret_cast<LLWord*>(op.seg[0].out) + r, hv, tag);
-              } else {
-                op.seg[0].out[r] = hv;
-                op.seg[1].out[r] = up;
-              }
-            }
-          } else {
-            const int u = ps;  // one row per pass: gate, then up
-            float g, up;
-            if (narrow) {
-              g = warp_row_dot_s(op.seg[0].kind, base0 + (uint32_t)u * op.row_bytes[0], sxa, nb);
-              up = warp_row_dot_s(op.seg[1].kind, base1 + (uint32_t)u * op.row_bytes[1], sxa, nb);
-            } else {
-              g = group_row_dot(base0 + (uint32_t)u * op.row_bytes[0], op.seg[0].kind, sxa, nb, L);
-              up = group_row_dot(base1 + (uint32_t)u * op.row_bytes[1], op.seg[1].kind, sxa, nb, L);
-            }
-            if (lane == 0) {
-              const int r = t0 + u;
-              const float hv = epilogue == EPI_SILU_MUL ? silu_mul_exact(g, up) : g;
-              if (ll) {
-                ll_store(reinterpret_cast<LLWord*>(op.seg[0].out) + r, hv, tag);
-              } else {
-                op.seg[0].out[r] = hv;
-                op.seg[1].out[r] = up;
-              }
-            }
+      for (; u < hi; u += n_warps) {
+        if (pend == 0) pend_u0 = u;
+        const int lr0 = u - lo;  // row inside the tile
+        float* tdst = wterms + pend * mats * tstride;
+        int pi = 0, lr = lr0;
+        if (!pair) {
+          while (pi < np - 1 && lr >= parts[pi].rows) {
+            lr -= parts[pi].rows;
+            pi++;
           }
-        } else {
-          const int u = ps * G + gi;
-          uint32_t row = 0;
-          int kind = Q4_K, pi = 0, lr = u;
-          if (u < R_rows) {
-            while (pi < np - 1 && lr >= parts[pi].rows) {
-              lr -= parts[pi].rows;
-              pi++;
-            }
-            const TilePart& tp = parts[pi];
-            row = stage + tp.soff + ((uint32_t)(uintptr_t)tp.src & 15u) + (uint32_t)lr * op.row_bytes[tp.seg];
-            kind = op.seg[tp.seg].kind;
-          }
-          const float v = narrow ? (row ? warp_row_dot_s(kind, row, sxa, nb) : 0.0f) : group_row_dot(row, kind, sxa, nb, L);
-          if (u < R_rows && (lane & (L - 1)) == 0) {
-            const int oi = parts[pi].row0 + lr;
-            if (TP && ll && tpx && epilogue == EPI_ACCUM) {
-              // a partial row of a sharded product: hand it to every rank (this one included)
-              for (int dst = 0; dst < tpx->world; dst++)
-                ll_store_sys(tpx->inbox[dst] + ((size_t)which * tpx->world + tpx->rank) * tpx->dim + oi, v, tag);
-            } else if (ll) {
-              // a residual row is only ever written by its owner, so its old value needs no tag check
-              LLWord* o = reinterpret_cast<LLWord*>(op.seg[parts[pi].seg].out) + oi;
-              ll_store(o, epilogue == EPI_ACCUM ? fadd(ll_value(o), v) : v, tag);
-            } else {
-              float* o = op.seg[parts[pi].seg].out + oi;
-              *o = epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
-            }
-          }
+        }
+#pragma unroll 1
+        for (int mt = 0; mt < mats; mt++) {
+          const TilePart& tp = parts[pair ? mt : pi];
+          const uint32_t row = stage + tp.soff + ((uint32_t)(uintptr_t)tp.src & 15u) + (uint32_t)lr * op.row_bytes[tp.seg];
+          warp_row_terms(op.seg[tp.seg].kind, row, sxa, nb, yc, tdst + mt * tstride);
+        }
+        if (++pend == cap) {
+          warp_flush<TP>(op, wterms, pend, pend_u0, n_warps, c0, nb, tstride, tag, tpx, which, old_pref, pref && batch == 0);
+          pend = 0;
+          batch++;
         }
       }
     }
-    rot = (rot + n_pass) % n_warps;
     __syncwarp();
     if (lane == 0) mbar_arrive(&R.empty[cp.st]);
     cp.advance(R.n_stages);
   }
+  if (pend) warp_flush<TP>(op, wterms, pend, pend_u0, n_warps, c0, nb, tstride, tag, tpx, which, old_pref, pref && batch == 0);
 }
 
 // ---- grid-wide barrier for the consumer warps ---------------------------------------------
@@ -692,73 +431,114 @@ struct MegaSmem {
   int* err;             // device error word
 };
 
+// Which of the reference's sequential f32 loops may be evaluated in another order
+// (StepParams::fast). 0 reproduces every loop bit for bit; each bit trades one loop for a
+// tree or split form whose result differs in the last bits only.
+enum FastBits : int {
+  FAST_NORM_SUM = 1,     // sum of squares of rmsnorm (ops.rs:10-13)
+  FAST_SOFTMAX_SUM = 2,  // softmax denominator (ops.rs:103-107)
+  FAST_VALUE_MIX = 4,    // attention value mix over positions (ops.rs:208-214)
+  FAST_QK_DOT = 8,       // q.k dot products (ops.rs:160-166)
+};
+
+// Sum of the `nw` per-warp partials in red[0..nw), the same order in every thread.
+__device__ __forceinline__ float red_sum(const float* red, int nw) {
+  float s = 0.0f;
+  for (int w = 0; w < nw; w++) s = fadd(s, red[w]);
+  return s;
+}
+
 // x -> rmsnorm -> Q8_K images in shared memory (ops.rs:7-18 then quant.rs:248-283).
 // `src` holds tagged words other CTAs publish under `tag`; for the embedding the row is
-// already in scr[0..n). `mirror`, when given, receives a plain copy of the row.
+// already in scr[0..n). `mirror`, when given, receives a plain copy of the row. The warp
+// that owns a super-block keeps its 256 values in registers from the load to the quantized
+// image (at most two super-blocks per warp: n <= 512 * warps).
 __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag, bool src_in_scr, float* mirror, const float* w,
-                                                 int n, float eps, const MegaSmem& M, const CtaGroup& g,
+                                                 int n, float eps, int fast, const MegaSmem& M, const CtaGroup& g,
                                                  SubProf sp = SubProf{nullptr, 0}) {
   sp.last = clock64();
   float* row = M.scr;
   float* sq = M.scr + n;
-  // Scaling and quantization are one pass: warp b takes super-block b, lane l its elements
-  // 8l..8l+7. The norm weights of the warp's first block are requested before the wait.
   const int warp = g.tid >> 5, nw = g.nthreads >> 5, lane = g.tid & 31, nblk = n >> 8;
-  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
-  if (warp < nblk) {
-    w0 = __ldg(reinterpret_cast<const float4*>(w + warp * 256 + 8 * lane));
-    w1 = __ldg(reinterpret_cast<const float4*>(w + warp * 256 + 8 * lane) + 1);
+  float v[2][8];
+  float part = 0.0f;
+  // the norm weights are requested before the wait on the row
+  float4 nwt[2][2];
+#pragma unroll
+  for (int k = 0; k < 2; k++) {
+    const int b = warp + k * nw;
+    if (b < nblk) {
+      nwt[k][0] = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane));
+      nwt[k][1] = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane) + 1);
+    }
   }
-  if (src_in_scr) {
-    for (int i = g.tid; i < n; i += g.nthreads) sq[i] = fmul(row[i], row[i]);
-  } else {
-    // all of a thread's words are requested before the first one is examined
-    constexpr int U = 4;
-    for (int base = g.tid; base < n; base += U * g.nthreads) {
-      LLWord wd[U];
 #pragma unroll
-      for (int u = 0; u < U; u++) {
-        const int i = base + u * g.nthreads;
-        if (i < n) wd[u] = ll_load(src + i);
+  for (int k = 0; k < 2; k++) {
+    const int b = warp + k * nw;
+    if (b < nblk) {
+      const int e0 = b * 256 + 8 * lane;
+      if (src_in_scr) {
+        const float4 a0 = *reinterpret_cast<const float4*>(row + e0), a1 = *reinterpret_cast<const float4*>(row + e0 + 4);
+        v[k][0] = a0.x; v[k][1] = a0.y; v[k][2] = a0.z; v[k][3] = a0.w;
+        v[k][4] = a1.x; v[k][5] = a1.y; v[k][6] = a1.z; v[k][7] = a1.w;
+      } else {
+        // all eight words are requested before the first one is examined
+        const LLWord* p = src + e0;
+        LLWord wd[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) ll_load2(p + 2 * i, wd[2 * i], wd[2 * i + 1]);
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[k][i] = ll_settle(p + i, wd[i], tag, M.abort, M.err);
       }
+      if (mirror) {
+        *reinterpret_cast<float4*>(mirror + e0) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+        *reinterpret_cast<float4*>(mirror + e0 + 4) = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
+      }
+      if (fast & FAST_NORM_SUM) {
 #pragma unroll
-      for (int u = 0; u < U; u++) {
-        const int i = base + u * g.nthreads;
-        if (i < n) {
-          const float v = ll_settle(src + i, wd[u], tag, M.abort, M.err);
-          row[i] = v;
-          sq[i] = fmul(v, v);
-          if (mirror) mirror[i] = v;
-        }
+        for (int i = 0; i < 8; i++) part = fadd(part, fmul(v[k][i], v[k][i]));
+      } else {
+        *reinterpret_cast<float4*>(sq + e0) =
+            make_float4(fmul(v[k][0], v[k][0]), fmul(v[k][1], v[k][1]), fmul(v[k][2], v[k][2]), fmul(v[k][3], v[k][3]));
+        *reinterpret_cast<float4*>(sq + e0 + 4) =
+            make_float4(fmul(v[k][4], v[k][4]), fmul(v[k][5], v[k][5]), fmul(v[k][6], v[k][6]), fmul(v[k][7], v[k][7]));
       }
     }
   }
-  g.sync();
   sp.mark(16);
-  float ss = group_seq_sum(sq, n, M.ss, g, &sp);
+  float ss;
+  if (fast & FAST_NORM_SUM) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part = fadd(part, __shfl_xor_sync(0xffffffffu, part, o));
+    if (lane == 0) M.red[warp] = part;
+    g.sync();
+    ss = red_sum(M.red, nw);
+  } else {
+    g.sync();
+    ss = group_seq_sum_call(sq, n, M.ss, g.tid, g.nthreads, g.bar_id, sp.prof);
+    sp.last = clock64();
+  }
   sp.mark(17);
-  float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
-  sp.mark(18);
-  for (int b = warp; b < nblk; b += nw) {
-    if (b != warp) {
-      w0 = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane));
-      w1 = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane) + 1);
+  const float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
+#pragma unroll
+  for (int k = 0; k < 2; k++) {
+    const int b = warp + k * nw;
+    if (b < nblk) {
+      const float4 w0 = nwt[k][0], w1 = nwt[k][1];
+      float y[8];
+      y[0] = fmul(fmul(v[k][0], r), w0.x); y[1] = fmul(fmul(v[k][1], r), w0.y);
+      y[2] = fmul(fmul(v[k][2], r), w0.z); y[3] = fmul(fmul(v[k][3], r), w0.w);
+      y[4] = fmul(fmul(v[k][4], r), w1.x); y[5] = fmul(fmul(v[k][5], r), w1.y);
+      y[6] = fmul(fmul(v[k][6], r), w1.z); y[7] = fmul(fmul(v[k][7], r), w1.w);
+      warp_quantize_q8k_vals(y, M.sx + b * XK_STRIDE, 1);
     }
-    const float4 x0 = *reinterpret_cast<const float4*>(row + b * 256 + 8 * lane);
-    const float4 x1 = *(reinterpret_cast<const float4*>(row + b * 256 + 8 * lane) + 1);
-    float v[8];
-    v[0] = fmul(fmul(x0.x, r), w0.x); v[1] = fmul(fmul(x0.y, r), w0.y);
-    v[2] = fmul(fmul(x0.z, r), w0.z); v[3] = fmul(fmul(x0.w, r), w0.w);
-    v[4] = fmul(fmul(x1.x, r), w1.x); v[5] = fmul(fmul(x1.y, r), w1.y);
-    v[6] = fmul(fmul(x1.z, r), w1.z); v[7] = fmul(fmul(x1.w, r), w1.w);
-    warp_quantize_q8k_vals(v, M.sx + b * XK_STRIDE, 1);
   }
   g.sync();
   sp.mark(19);
 }
 
 // A vector other CTAs publish under `tag` -> Q8_K images.
-__device__ __forceinline__ void phase_quant(const LLWord* src, uint32_t tag, int n, const MegaSmem& M, const CtaGroup& g) {
+__device__ __noinline__ void phase_quant(const LLWord* src, uint32_t tag, int n, const MegaSmem& M, const CtaGroup& g) {
   const int warp = g.tid >> 5, nw = g.nthreads >> 5, lane = g.tid & 31;
   for (int b = warp; b < n / 256; b += nw) {
     const LLWord* p = src + b * 256 + 8 * lane;
@@ -788,9 +568,101 @@ __device__ __forceinline__ void stage_kv_rows(float* buf, int stride, const floa
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// Sum of p[0..n) (shared memory, written by any thread of the group) returned to every
+// thread: in the reference's sequential order, or as a tree when `tree` is set. Longer
+// sequential sums go through the segment algorithm of groupsum.cuh; up to SEQ_CHAIN_MAX
+// terms one thread's plain add chain (4 cycles per term) is quicker than its set-up.
+constexpr int SEQ_CHAIN_MAX = 1536;
+__device__ __noinline__ float cta_sum(const float* p, int n, bool tree, const MegaSmem& M, const CtaGroup& g) {
+  if (!tree && n > SEQ_CHAIN_MAX) return group_seq_sum_call(p, n, M.ss, g.tid, g.nthreads, g.bar_id, nullptr);
+  g.sync();
+  if (tree) {
+    float a = 0.0f;
+    for (int i = g.tid; i < n; i += g.nthreads) a = fadd(a, p[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fadd(a, __shfl_xor_sync(0xffffffffu, a, o));
+    if ((g.tid & 31) == 0) M.red[g.tid >> 5] = a;
+    g.sync();
+    return red_sum(M.red, g.nthreads >> 5);
+  }
+  if (g.tid == 0) {
+    float s = 0.0f;
+    int i = 0;
+    for (; i + 8 <= n; i += 8) {
+      const float4 a = *reinterpret_cast<const float4*>(p + i), b = *reinterpret_cast<const float4*>(p + i + 4);
+      s = fadd(s, a.x); s = fadd(s, a.y); s = fadd(s, a.z); s = fadd(s, a.w);
+      s = fadd(s, b.x); s = fadd(s, b.y); s = fadd(s, b.z); s = fadd(s, b.w);
+    }
+    for (; i < n; i++) s = fadd(s, p[i]);
+    M.red[40] = s;
+  }
+  g.sync();
+  return M.red[40];
+}
+
+// q.k over one head (ops.rs:160-166): products first (independent), then the adds in
+// element order; with `split`, four interleaved partial chains joined as (a0+a1)+(a2+a3).
+// `kchunk(j)` returns float4 chunk j of the cached row.
+template <class KChunk>
+__device__ __forceinline__ float qk_dot(const float4* qt, KChunk kchunk, int hd4, bool split) {
+  if (split) {
+    float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int i0 = 0; i0 < hd4; i0 += 4) {
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const float4 kk = kchunk(i0 + u), qq = qt[i0 + u];
+        a[u] = fadd(a[u], fadd(fadd(fmul(qq.x, kk.x), fmul(qq.y, kk.y)), fadd(fmul(qq.z, kk.z), fmul(qq.w, kk.w))));
+      }
+    }
+    return fadd(fadd(a[0], a[1]), fadd(a[2], a[3]));
+  }
+  float s = 0.0f;
+  for (int i0 = 0; i0 < hd4; i0 += 4) {
+    float pr[16];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const float4 kk = kchunk(i0 + u), qq = qt[i0 + u];
+      pr[4 * u] = fmul(qq.x, kk.x);
+      pr[4 * u + 1] = fmul(qq.y, kk.y);
+      pr[4 * u + 2] = fmul(qq.z, kk.z);
+      pr[4 * u + 3] = fmul(qq.w, kk.w);
+    }
+#pragma unroll
+    for (int u = 0; u < 16; u++) s = fadd(s, pr[u]);
+  }
+  return s;
+}
+
+// The cached K and V rows of positions [0, pos) of head h's KV head, requested into the
+// staging area long before the attention phase needs them (they do not depend on the token
+// being decoded): K rows first, then V rows, hd floats each; the 16-byte chunks of K row t
+// are stored at chunk index j ^ (t & 7) so that threads reading different rows hit
+// different banks. Returns false, and stages nothing, when the rows do not fit.
+__device__ __forceinline__ bool attn_stage_early(const StepParams& P, int li, int h, int pos, float* stg, const CtaGroup& g) {
+  const int hd = P.head_dim, n = pos + 1;
+  if ((size_t)2 * n * hd > (size_t)P.stage_floats) return false;
+  const int kvd = P.n_kv_head * hd, kvh = h / (P.n_head / P.n_kv_head), hd4 = hd >> 2;
+  const int mask = (hd & 31) == 0 ? 7 : 0;
+  const float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd + kvh * hd;
+  const float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd + kvh * hd;
+  float* kbuf = stg;
+  float* vbuf = stg + (size_t)n * hd;
+  for (int j = g.tid; j < pos * hd4; j += g.nthreads) {
+    const int t = j / hd4, i4 = j - t * hd4;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(kbuf + t * hd + 4 * (i4 ^ (t & mask)))),
+                 "l"(kc + (size_t)t * kvd + 4 * i4)
+                 : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(vbuf + t * hd + 4 * i4)), "l"(vc + (size_t)t * kvd + 4 * i4)
+                 : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  return true;
+}
+
 // Per-head q/k norm, RoPE, KV store and attention for head `h` (ops.rs:74-87, 40-70,
-// 152-157, 185-218), by the consumer warps of one CTA.
-__device__ void phase_attention(const StepParams& P, int li, int h, int pos, uint32_t tag_in, uint32_t tag_out,
+// 152-157, 185-218), by the consumer warps of one CTA. `staged`: attn_stage_early has put
+// the cached rows of this head into the staging area.
+__device__ __noinline__ void phase_attention(const StepParams& P, int li, int h, int pos, uint32_t tag_in, uint32_t tag_out, bool staged,
                                 const MegaSmem& M, const CtaGroup& g, SubProf pf = SubProf{nullptr, 0}) {
   pf.last = clock64();
   const int hd = P.head_dim, kvd = P.n_kv_head * hd, gqa = P.n_head / P.n_kv_head, kvh = h / gqa;
@@ -800,7 +672,7 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, uin
   float* sv = sk + hd;          // hd
   float* sp = sv + hd;          // hd (squares)
   float* sc = sp + hd;          // n_ctx scores
-  float* vbuf = sc + ((P.n_ctx + 3) & ~3);  // two chunk buffers of v_chunk x (hd + 4) floats, 16-byte aligned
+  float* stg = M.scr + P.small_floats;  // staging area, 16-byte aligned
   const float* const q_norm_w = P.layers[li].q_norm;
   const float* const k_norm_w = P.layers[li].k_norm;
   float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd;
@@ -826,8 +698,8 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, uin
       float* v = which ? sk : sq;
       const float* nw = which ? k_norm_w : q_norm_w;
       for (int i = tid; i < hd; i += T) sp[i] = fmul(v[i], v[i]);
-      float ss = group_seq_sum(sp, hd, M.ss, g);
-      float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)hd), P.eps)));
+      const float ss = (P.fast & FAST_NORM_SUM) ? cta_sum(sp, hd, true, M, g) : group_seq_sum_call(sp, hd, M.ss, g.tid, g.nthreads, g.bar_id, nullptr);
+      const float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)hd), P.eps)));
       g.sync();
       for (int i = tid; i < hd; i += T) v[i] = fmul(fmul(v[i], r), nw[i]);
       g.sync();
@@ -849,50 +721,61 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, uin
     }
   }
   pf.mark(20);
-  // scores: cached K rows are staged through shared memory in chunks, double buffered; rows
-  // are padded by one float4 to spread the banks
   const float scale = 1.0f / sqrtf((float)hd);
-  const int hd4 = hd >> 2, kstride = hd + 4, chunk = P.v_chunk;
-  const int buf_floats = chunk * kstride;
+  const int hd4 = hd >> 2;
+  const bool qk_split = (P.fast & FAST_QK_DOT) != 0;
   float lmax = -INFINITY;
-  stage_kv_rows(vbuf, kstride, kc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sk, tid, T);
-  for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
-    const int cn = min(chunk, n - c0);
-    float* cur_buf = vbuf + (ci & 1) * buf_floats;
-    if (c0 + chunk < n) {
-      stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, kstride, kc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sk,
-                    tid, T);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
+  const float4* qt = reinterpret_cast<const float4*>(sq);
+  float* vbuf;  // generic path: two chunk buffers; staged path: all rows
+  if (staged) {
+    // the row of the token being decoded joins the staged rows
+    const int mask = (hd & 31) == 0 ? 7 : 0;
+    float* kbuf = stg;
+    vbuf = stg + (size_t)n * hd;
+    for (int i4 = tid; i4 < 2 * hd4; i4 += T) {
+      if (i4 < hd4) reinterpret_cast<float4*>(kbuf + pos * hd)[i4 ^ (pos & mask)] = reinterpret_cast<const float4*>(sk)[i4];
+      else reinterpret_cast<float4*>(vbuf + pos * hd)[i4 - hd4] = reinterpret_cast<const float4*>(sv)[i4 - hd4];
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     g.sync();
-    for (int t = tid; t < cn; t += T) {
-      const float4* kt = reinterpret_cast<const float4*>(cur_buf + t * kstride);
-      const float4* qt = reinterpret_cast<const float4*>(sq);
-      float s = 0.0f;
-      for (int i0 = 0; i0 < hd4; i0 += 4) {
-        // products first (independent), then the chain of adds in element order
-        float pr[16];
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-          const float4 kk = kt[i0 + u], qq = qt[i0 + u];
-          pr[4 * u] = fmul(qq.x, kk.x);
-          pr[4 * u + 1] = fmul(qq.y, kk.y);
-          pr[4 * u + 2] = fmul(qq.z, kk.z);
-          pr[4 * u + 3] = fmul(qq.w, kk.w);
-        }
-#pragma unroll
-        for (int u = 0; u < 16; u++) s = fadd(s, pr[u]);
-      }
+    for (int t = tid; t < n; t += T) {
+      const float4* kt = reinterpret_cast<const float4*>(kbuf + t * hd);
+      const int sw = t & mask;
+      float s = qk_dot(qt, [&](int j) { return kt[j ^ sw]; }, hd4, qk_split);
       s = fmul(s, scale);
-      sc[c0 + t] = s;
+      sc[t] = s;
       lmax = fmaxf(lmax, s);
     }
-    g.sync();  // this buffer is refilled two chunks later
+  } else {
+    // cached K rows are staged through shared memory in chunks, double buffered; rows are
+    // padded by one float4 to spread the banks
+    vbuf = stg;
+    const int kstride = hd + 4, chunk = P.v_chunk;
+    const int buf_floats = chunk * kstride;
+    stage_kv_rows(vbuf, kstride, kc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sk, tid, T);
+    for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
+      const int cn = min(chunk, n - c0);
+      float* cur_buf = vbuf + (ci & 1) * buf_floats;
+      if (c0 + chunk < n) {
+        stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, kstride, kc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sk,
+                      tid, T);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
+      g.sync();
+      for (int t = tid; t < cn; t += T) {
+        const float4* kt = reinterpret_cast<const float4*>(cur_buf + t * kstride);
+        float s = qk_dot(qt, [&](int j) { return kt[j]; }, hd4, qk_split);
+        s = fmul(s, scale);
+        sc[c0 + t] = s;
+        lmax = fmaxf(lmax, s);
+      }
+      g.sync();  // this buffer is refilled two chunks later
+    }
+    // the first chunk of V rows loads while the softmax runs
+    stage_kv_rows(vbuf, hd, vc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sv, tid, T);
   }
-  // the first chunk of V rows loads while the softmax runs
-  stage_kv_rows(vbuf, hd, vc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sv, tid, T);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
   if ((tid & 31) == 0) M.red[tid >> 5] = lmax;
@@ -900,40 +783,74 @@ __device__ void phase_attention(const StepParams& P, int li, int h, int pos, uin
   pf.mark(21);
   float mx = M.red[0];
   for (int w = 1; w < (T >> 5); w++) mx = fmaxf(mx, M.red[w]);
-  for (int t = tid; t < n; t += T) sc[t] = expf_exact(fsub(sc[t], mx));
-  g.sync();
+  for (int t = tid; t < n; t += T) sc[t] = expf_exact_call(fsub(sc[t], mx));
   pf.mark(22);
-  float sum = group_seq_sum(sc, n, M.ss, g);
+  const float sum = cta_sum(sc, n, (P.fast & FAST_SOFTMAX_SUM) != 0, M, g);  // opens with a barrier
   pf.mark(23);
-  float inv = fdiv(1.0f, sum);
+  const float inv = fdiv(1.0f, sum);
   g.sync();
   for (int t = tid; t < n; t += T) sc[t] = fmul(sc[t], inv);
-  // value mix, positions in order (ops.rs:208-214); cached rows staged as above
-  float o = 0.0f;
-  for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
-    const int cn = min(chunk, n - c0);
-    const float* cur_buf = vbuf + (ci & 1) * buf_floats;
-    if (c0 + chunk < n) {
-      stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, hd, vc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sv, tid, T);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
+  // value mix, positions in order (ops.rs:208-214)
+  if (staged) {
     g.sync();
-    if (tid < hd) {
+    if (P.fast & FAST_VALUE_MIX) {
+      // positions split over up to four thread groups, partial sums joined in group order
+      int G = T / hd;
+      G = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
+      const int grp = tid / hd, d = tid - grp * hd, per = (n + G - 1) / G;
+      if (grp < G) {
+        float o = 0.0f;
+        const int t1 = min(n, (grp + 1) * per);
+        for (int t = grp * per; t < t1; t++) o = fadd(o, fmul(sc[t], vbuf[t * hd + d]));
+        sq[grp * hd + d] = o;  // q, k, v and the squares are no longer needed: 4 x hd floats
+      }
+      g.sync();
+      if (tid < hd) {
+        float o = sq[tid];
+        for (int k = 1; k < G; k++) o = fadd(o, sq[k * hd + tid]);
+        ll_store(P.attl + h * hd + tid, o, tag_out);
+      }
+    } else if (tid < hd) {
+      float o = 0.0f;
       int t = 0;
-      for (; t + 8 <= cn; t += 8) {
+      for (; t + 8 <= n; t += 8) {
         float pr[8];
 #pragma unroll
-        for (int u = 0; u < 8; u++) pr[u] = fmul(sc[c0 + t + u], cur_buf[(t + u) * hd + tid]);
+        for (int u = 0; u < 8; u++) pr[u] = fmul(sc[t + u], vbuf[(t + u) * hd + tid]);
 #pragma unroll
         for (int u = 0; u < 8; u++) o = fadd(o, pr[u]);
       }
-      for (; t < cn; t++) o = fadd(o, fmul(sc[c0 + t], cur_buf[t * hd + tid]));
+      for (; t < n; t++) o = fadd(o, fmul(sc[t], vbuf[t * hd + tid]));
+      ll_store(P.attl + h * hd + tid, o, tag_out);
     }
-    g.sync();
+  } else {
+    const int chunk = P.v_chunk, buf_floats = chunk * (hd + 4);
+    float o = 0.0f;
+    for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
+      const int cn = min(chunk, n - c0);
+      const float* cur_buf = vbuf + (ci & 1) * buf_floats;
+      if (c0 + chunk < n) {
+        stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, hd, vc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sv, tid, T);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
+      g.sync();
+      if (tid < hd) {
+        int t = 0;
+        for (; t + 8 <= cn; t += 8) {
+          float pr[8];
+#pragma unroll
+          for (int u = 0; u < 8; u++) pr[u] = fmul(sc[c0 + t + u], cur_buf[(t + u) * hd + tid]);
+#pragma unroll
+          for (int u = 0; u < 8; u++) o = fadd(o, pr[u]);
+        }
+        for (; t < cn; t++) o = fadd(o, fmul(sc[c0 + t], cur_buf[t * hd + tid]));
+      }
+      g.sync();
+    }
+    if (tid < hd) ll_store(P.attl + h * hd + tid, o, tag_out);
   }
-  if (tid < hd) ll_store(P.attl + h * hd + tid, o, tag_out);
   pf.mark(24);
 }
 
@@ -990,13 +907,14 @@ constexpr int MEGA_BAR_BYTES = 128;     // up to 8 stages x (full, empty)
 constexpr int MEGA_SEQSUM_BYTES = 2064;  // sizeof(SeqSumScratch) rounded up to 16
 static_assert(sizeof(SeqSumScratch) <= MEGA_SEQSUM_BYTES, "SeqSumScratch layout");
 // Bytes of shared memory besides the ring stages, the activation images and the scratch.
-constexpr int MEGA_TAIL_BYTES = MEGA_BAR_BYTES + MEGA_SEQSUM_BYTES + 64 * 4 + 16;
+constexpr int MEGA_TERMS_BYTES = MEGA_CONSUMER_WARPS * WARP_TERMS_FLOATS * 4;  // block-term strips of the consumer warps
+constexpr int MEGA_TAIL_BYTES = MEGA_BAR_BYTES + MEGA_SEQSUM_BYTES + 64 * 4 + 16 + MEGA_TERMS_BYTES;
 
 // TP: this GPU holds one shard of a row-sharded model and exchanges partial rows with its peers.
 template <bool TP>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const StepParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  // [stages][sx images][scratch][barriers 128 B][SeqSumScratch][red 64 floats][abort]
+  // [stages][sx images][scratch][barriers 128 B][SeqSumScratch][red 64 floats][abort][term strips][table]
   const int nb_max = (max(max(P.dim, P.hidden), P.n_head * P.head_dim)) / 256;
   uint8_t* stages = smem;
   uint8_t* sx = stages + (size_t)P.n_stages * P.stage_bytes;
@@ -1011,6 +929,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   cur += 64 * sizeof(float);
   volatile int* abort = reinterpret_cast<volatile int*>(cur);
   cur += 16;
+  float* const wterms_all = reinterpret_cast<float*>(cur);
+  cur += MEGA_TERMS_BYTES;
   // The step's tensor table (one StepLayer per layer + the output head), copied from
   // global memory once so that no phase waits on a descriptor load.
   StepLayer* const table = reinterpret_cast<StepLayer*>(cur);
@@ -1033,13 +953,22 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
       mbar_init(&R.full[s], 1);
       mbar_init(&R.empty[s], MEGA_CONSUMER_WARPS);
     }
-    *abort = 0;
+    // A launch that finds the device error word set (an earlier step's wait gave up: a
+    // peer is gone, say) does no work: steps already queued behind a failed one drain in
+    // microseconds instead of each waiting out its own limits.
+    abort[0] = *reinterpret_cast<volatile int*>(P.err) != 0 ? 1 : 0;
+    abort[1] = P.spin_limit;
     mbar_fence_init();
   }
   __syncthreads();
 
   const int warp = threadIdx.x >> 5;
   const int qd = P.n_head * P.head_dim;
+  if (*abort) {
+    // keep the launch count in step with the other ranks, whose tags follow it
+    if (blockIdx.x == 0 && threadIdx.x == 0) *P.epoch = *P.epoch + 1u;
+    return;
+  }
 
   if (warp == MEGA_CONSUMER_WARPS) {
     // ---- producer warp: one thread walks every matrix product of the step ----
@@ -1047,10 +976,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
       RingPos pp{0, 0u};
       for (int li = 0; li < P.n_layer && !*abort; li++) {
         const StepLayer& L = table[li];
-        produce_op(L.qkv, R, pp);
-        produce_op(L.wo, R, pp);
-        produce_op(L.gu, R, pp);
-        produce_op(L.down, R, pp);
+#pragma unroll 1
+        for (int ph = 0; ph < 4; ph++) produce_op((&L.qkv)[ph], R, pp);  // qkv, wo, gu, down are consecutive members
       }
       if (P.want_logits && !*abort) produce_op(table[P.n_layer].qkv, R, pp);
     }
@@ -1060,8 +987,10 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   // ---- consumer warps ----
   CtaGroup g{(int)threadIdx.x, MEGA_CONSUMER_WARPS * 32, 1};
   MegaSmem M{sx, scr, ssc, red, abort, P.err};
+  float* const wterms = wterms_all + warp * WARP_TERMS_FLOATS;
   RingPos cp{0, 0u};
   unsigned bar_target = 0;
+  bool staged = false;
   const int token = P.step[0], pos = P.step[1];
   // Tags of this launch: phase k (1..5) of layer li is tag_base + 5 * li + k.
   const uint32_t tag_base = *P.epoch << 10;
@@ -1083,7 +1012,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     int r0, r1;
     cta_rows(P.dim, r0, r1);
     for (int e = g.tid; e < P.dim; e += g.nthreads) {
-      float v = dequant_elem(P.embd_kind, row, (size_t)e);
+      float v = dequant_elem_call(P.embd_kind, row, (size_t)e);
       scr[e] = v;
       if (e >= r0 && e < r1) ll_store(P.xl + e, v, 0u);
     }
@@ -1103,10 +1032,13 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     const MegaOp& op = (&L.qkv)[ph];  // qkv, wo, gu, down are consecutive members
     const int slot = ph == 0 ? 1 : 3 * ph + 3;
     const uint32_t tl = tag_base + 5u * (uint32_t)li;  // + k: phase k of this layer
-    if (ph == 0 && !head) {
-      // The cached K and V rows this CTA's heads will read were evicted from L2 by the weight
-      // stream; ask for them now, two phases ahead of their use.
-      for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
+    if (ph == 0 && !head && (int)blockIdx.x < P.n_head) {
+      // The cached K and V rows this CTA's head will read do not depend on the token being
+      // decoded: request them into shared memory now, two phases ahead of their use. When
+      // they do not fit, at least ask for them into L2 (the weight stream evicts the cache
+      // between tokens).
+      staged = attn_stage_early(P, li, blockIdx.x, pos, scr + P.small_floats, g);
+      for (int h = blockIdx.x + (staged ? gridDim.x : 0); h < P.n_head; h += gridDim.x) {
         const int kvd = P.n_kv_head * P.head_dim, kvh = h / (P.n_head / P.n_kv_head);
         const int lines = (P.head_dim * 4 + 127) / 128;  // 128-byte lines per cached row of one head
         const float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd + kvh * P.head_dim;
@@ -1122,7 +1054,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
       // attention norm -> q/k/v, ffn norm -> gate/up + SiLU, output norm -> logits
       const float* w = head ? P.output_norm : (ph == 0 ? L.attn_norm : L.ffn_norm);
       const uint32_t tin = ph == 0 ? tl : tl + 3u;  // residual after the previous layer's down / this layer's wo
-      phase_norm_quant(P.xl, tin, st == 0, head && blockIdx.x == 0 ? P.x : nullptr, w, P.dim, P.eps, M, g,
+      phase_norm_quant(P.xl, tin, st == 0, head && blockIdx.x == 0 ? P.x : nullptr, w, P.dim, P.eps, P.fast, M, g,
                        SubProf{prof_on && ph == 0 && !head ? P.prof : nullptr, 0});
     } else {
       // attention output -> wo, activated hidden -> down; both join the residual stream
@@ -1133,7 +1065,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     // q/k/v: tl+1, wo: tl+3, gate/up: tl+4, down: tl+5 (the head writes plain floats)
     const uint32_t tag_out = tl + (ph == 0 ? 1u : (uint32_t)ph + 2u);
     const bool exchange = TP && (ph & 1) && !head;
-    consume_op<TP>(op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, tag_out, exchange ? &P.tp : nullptr, ph >> 1);
+    consume_op<TP>(op, R, cp, sx, wterms, warp, MEGA_CONSUMER_WARPS, tag_out, exchange ? &P.tp : nullptr, ph >> 1);
     if (head) break;
     // The next phase rewrites the activation images and the scratch rows; warps that are
     // done must also not start polling while others still compute.
@@ -1154,7 +1086,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     if (ph == 0) {
       // attention, one head per CTA
       for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
-        phase_attention(P, li, h, pos, tl + 1u, tl + 2u, M, g, SubProf{prof_on ? P.prof : nullptr, 0});
+        phase_attention(P, li, h, pos, tl + 1u, tl + 2u, staged && h == (int)blockIdx.x, M, g, SubProf{prof_on ? P.prof : nullptr, 0});
         g.sync();
       }
       MEGA_PROF(4);
@@ -1197,8 +1129,8 @@ __device__ __forceinline__ float row_chain_q80(uint32_t row, uint32_t sx, int nb
     const uint32_t wb = row + (uint32_t)b * BS, xb = sx + (uint32_t)b * X0_STRIDE;
     uint32_t hd;
     asm("ld.shared.u16 %0, [%1];" : "=r"(hd) : "r"(wb));
-    const float d = fmul(half_to_float_hw(hd), __uint_as_float(lds32q(xb + X0_D)));
-    const uint32_t y = lds32q(xb + 4 * k);
+    const float d = fmul(half_bits_hw(hd), __uint_as_float(rd_lds32(xb + X0_D)));
+    const uint32_t y = rd_lds32(xb + 4 * k);
     int p;
     if (KIND == Q8_0) p = q8_0_lane(lds32_a2s(wb + 2 + 4 * k), y);
     else if (KIND == Q4_0) p = q4_0_lane(lds32_a2s(wb + 2 + 4 * (k & 3)), k, y);
@@ -1296,13 +1228,14 @@ struct StreamGemvParams {
 
 __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const StreamGemvParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  // [stages][sx images][barriers 128 B][abort]
+  // [stages][sx images][barriers 128 B][abort][term strips]
   const int nb = P.q80 ? P.op.cols >> 5 : P.op.cols >> 8;
   const int xstride = P.q80 ? X0_STRIDE : XK_STRIDE;
   uint8_t* stages = smem;
   uint8_t* sx = stages + (size_t)P.n_stages * P.stage_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sx + (size_t)P.m * nb * xstride);
   volatile int* abort = reinterpret_cast<volatile int*>(bars + MEGA_BAR_BYTES / 8);
+  float* const wterms_all = reinterpret_cast<float*>(const_cast<int*>(abort) + 4);
   Ring R;
   R.stages = stages;
   R.full = bars;
@@ -1354,7 +1287,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   g.sync();
   RingPos cp{0, 0u};
   if (P.q80) consume_op_q80(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, P.m);
-  else consume_op(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, 0u);
+  else consume_op(P.op, R, cp, sx, wterms_all + warp * WARP_TERMS_FLOATS, warp, MEGA_CONSUMER_WARPS, 0u);
 }
 
 
