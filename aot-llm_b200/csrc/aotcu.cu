@@ -782,9 +782,9 @@ static int mega_setup(aotcu_gpu* g) {
   ok = ok && d.n_layer <= 200 && (size_t)d.dim >= (size_t)c->n_sm && (size_t)d.hidden >= (size_t)c->n_sm;
   if (!ok) return 0;
   size_t nb_max = std::max(std::max((size_t)d.dim, (size_t)d.hidden), qd) / 256;
-  // Block-term strips hold two rows of a gate/up pair, norm rows stay in registers (two
-  // super-blocks per warp).
-  if (((nb_max | 1) * 2 > (size_t)WARP_TERMS_FLOATS) || (size_t)d.dim > (size_t)512 * MEGA_CONSUMER_WARPS) return 0;
+  // Block-term strips hold two rows of a gate/up pair, norm rows stay in registers (one
+  // super-block per warp).
+  if (((nb_max | 1) * 2 > (size_t)WARP_TERMS_FLOATS) || (size_t)d.dim > (size_t)256 * MEGA_CONSUMER_WARPS) return 0;
   // The largest row of any matrix must fit a ring stage twice (a gate/up pair).
   size_t max_rb = 0;
   for (const auto& l : g->layers) {
@@ -1808,10 +1808,10 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
       ARG_CHECK(value >= 1, "spin_limit must be at least 1");
       g->step_params.spin_limit = value;
     } else if (!strcmp(name, "fast")) {
-      ARG_CHECK(value >= 0 && value <= 15, "fast is a mask of bits 1, 2, 4, 8");
+      ARG_CHECK(value >= 0 && value <= 3, "fast is a mask of bits 1 and 2");
       g->step_params.fast = value;
     } else {
-      g->step_params.fast = value ? 0 : 15;
+      g->step_params.fast = value ? 0 : 3;
     }
     return 0;
   }

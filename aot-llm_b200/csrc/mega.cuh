@@ -118,7 +118,6 @@ __device__ __forceinline__ float ll_wait_sys(const LLWord* p, uint32_t tag, vola
 // The one-kernel step walks all of its code once per layer, so the code has to stay inside
 // the SM's instruction cache: everything large that is used from more than one place is
 // kept out of line.
-__device__ __noinline__ float expf_exact_call(float x) { return expf_exact(x); }
 __device__ __noinline__ float silu_mul_call(float g, float u) { return fmul(fdiv(g, fadd(1.0f, expf_exact(-g))), u); }
 __device__ __noinline__ float group_seq_sum_call(const float* p, int n, SeqSumScratch* sc, int tid, int nthreads, int bar_id,
                                                  unsigned long long* prof) {
@@ -437,8 +436,6 @@ struct MegaSmem {
 enum FastBits : int {
   FAST_NORM_SUM = 1,     // sum of squares of rmsnorm (ops.rs:10-13)
   FAST_SOFTMAX_SUM = 2,  // softmax denominator (ops.rs:103-107)
-  FAST_VALUE_MIX = 4,    // attention value mix over positions (ops.rs:208-214)
-  FAST_QK_DOT = 8,       // q.k dot products (ops.rs:160-166)
 };
 
 // Sum of the `nw` per-warp partials in red[0..nw), the same order in every thread.
@@ -448,11 +445,19 @@ __device__ __forceinline__ float red_sum(const float* red, int nw) {
   return s;
 }
 
+// quant.rs:248-283 for the 256 values a warp holds (lane l: elements 8l..8l+7), written as
+// a block image. Out of line: the step uses it from three places.
+__device__ __noinline__ void quantize_block_call(float v0, float v1, float v2, float v3, float v4, float v5, float v6, float v7,
+                                                 uint8_t* dst) {
+  const float v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
+  warp_quantize_q8k_vals(v, dst, 1);
+}
+
 // x -> rmsnorm -> Q8_K images in shared memory (ops.rs:7-18 then quant.rs:248-283).
 // `src` holds tagged words other CTAs publish under `tag`; for the embedding the row is
 // already in scr[0..n). `mirror`, when given, receives a plain copy of the row. The warp
 // that owns a super-block keeps its 256 values in registers from the load to the quantized
-// image (at most two super-blocks per warp: n <= 512 * warps).
+// image (n <= 256 * warps).
 __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag, bool src_in_scr, float* mirror, const float* w,
                                                  int n, float eps, int fast, const MegaSmem& M, const CtaGroup& g,
                                                  SubProf sp = SubProf{nullptr, 0}) {
@@ -460,49 +465,38 @@ __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag
   float* row = M.scr;
   float* sq = M.scr + n;
   const int warp = g.tid >> 5, nw = g.nthreads >> 5, lane = g.tid & 31, nblk = n >> 8;
-  float v[2][8];
+  const bool mine = warp < nblk;
+  const int e0 = warp * 256 + 8 * lane;
+  float v[8];
   float part = 0.0f;
-  // the norm weights are requested before the wait on the row
-  float4 nwt[2][2];
+  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+  if (mine) {
+    // the norm weights are requested before the wait on the row
+    w0 = __ldg(reinterpret_cast<const float4*>(w + e0));
+    w1 = __ldg(reinterpret_cast<const float4*>(w + e0) + 1);
+    if (src_in_scr) {
+      const float4 a0 = *reinterpret_cast<const float4*>(row + e0), a1 = *reinterpret_cast<const float4*>(row + e0 + 4);
+      v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w;
+      v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+    } else {
+      // all eight words are requested before the first one is examined
+      const LLWord* p = src + e0;
+      LLWord wd[8];
 #pragma unroll
-  for (int k = 0; k < 2; k++) {
-    const int b = warp + k * nw;
-    if (b < nblk) {
-      nwt[k][0] = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane));
-      nwt[k][1] = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane) + 1);
+      for (int i = 0; i < 4; i++) ll_load2(p + 2 * i, wd[2 * i], wd[2 * i + 1]);
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = ll_settle(p + i, wd[i], tag, M.abort, M.err);
     }
-  }
+    if (mirror) {
+      *reinterpret_cast<float4*>(mirror + e0) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(mirror + e0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    if (fast & FAST_NORM_SUM) {
 #pragma unroll
-  for (int k = 0; k < 2; k++) {
-    const int b = warp + k * nw;
-    if (b < nblk) {
-      const int e0 = b * 256 + 8 * lane;
-      if (src_in_scr) {
-        const float4 a0 = *reinterpret_cast<const float4*>(row + e0), a1 = *reinterpret_cast<const float4*>(row + e0 + 4);
-        v[k][0] = a0.x; v[k][1] = a0.y; v[k][2] = a0.z; v[k][3] = a0.w;
-        v[k][4] = a1.x; v[k][5] = a1.y; v[k][6] = a1.z; v[k][7] = a1.w;
-      } else {
-        // all eight words are requested before the first one is examined
-        const LLWord* p = src + e0;
-        LLWord wd[8];
-#pragma unroll
-        for (int i = 0; i < 4; i++) ll_load2(p + 2 * i, wd[2 * i], wd[2 * i + 1]);
-#pragma unroll
-        for (int i = 0; i < 8; i++) v[k][i] = ll_settle(p + i, wd[i], tag, M.abort, M.err);
-      }
-      if (mirror) {
-        *reinterpret_cast<float4*>(mirror + e0) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
-        *reinterpret_cast<float4*>(mirror + e0 + 4) = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
-      }
-      if (fast & FAST_NORM_SUM) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) part = fadd(part, fmul(v[k][i], v[k][i]));
-      } else {
-        *reinterpret_cast<float4*>(sq + e0) =
-            make_float4(fmul(v[k][0], v[k][0]), fmul(v[k][1], v[k][1]), fmul(v[k][2], v[k][2]), fmul(v[k][3], v[k][3]));
-        *reinterpret_cast<float4*>(sq + e0 + 4) =
-            make_float4(fmul(v[k][4], v[k][4]), fmul(v[k][5], v[k][5]), fmul(v[k][6], v[k][6]), fmul(v[k][7], v[k][7]));
-      }
+      for (int i = 0; i < 8; i++) part = fadd(part, fmul(v[i], v[i]));
+    } else {
+      *reinterpret_cast<float4*>(sq + e0) = make_float4(fmul(v[0], v[0]), fmul(v[1], v[1]), fmul(v[2], v[2]), fmul(v[3], v[3]));
+      *reinterpret_cast<float4*>(sq + e0 + 4) = make_float4(fmul(v[4], v[4]), fmul(v[5], v[5]), fmul(v[6], v[6]), fmul(v[7], v[7]));
     }
   }
   sp.mark(16);
@@ -514,24 +508,15 @@ __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag
     g.sync();
     ss = red_sum(M.red, nw);
   } else {
-    g.sync();
-    ss = group_seq_sum_call(sq, n, M.ss, g.tid, g.nthreads, g.bar_id, sp.prof);
+    ss = group_seq_sum_call(sq, n, M.ss, g.tid, g.nthreads, g.bar_id, sp.prof);  // opens with a barrier
     sp.last = clock64();
   }
   sp.mark(17);
-  const float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
-#pragma unroll
-  for (int k = 0; k < 2; k++) {
-    const int b = warp + k * nw;
-    if (b < nblk) {
-      const float4 w0 = nwt[k][0], w1 = nwt[k][1];
-      float y[8];
-      y[0] = fmul(fmul(v[k][0], r), w0.x); y[1] = fmul(fmul(v[k][1], r), w0.y);
-      y[2] = fmul(fmul(v[k][2], r), w0.z); y[3] = fmul(fmul(v[k][3], r), w0.w);
-      y[4] = fmul(fmul(v[k][4], r), w1.x); y[5] = fmul(fmul(v[k][5], r), w1.y);
-      y[6] = fmul(fmul(v[k][6], r), w1.z); y[7] = fmul(fmul(v[k][7], r), w1.w);
-      warp_quantize_q8k_vals(y, M.sx + b * XK_STRIDE, 1);
-    }
+  if (mine) {
+    const float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
+    quantize_block_call(fmul(fmul(v[0], r), w0.x), fmul(fmul(v[1], r), w0.y), fmul(fmul(v[2], r), w0.z), fmul(fmul(v[3], r), w0.w),
+                        fmul(fmul(v[4], r), w1.x), fmul(fmul(v[5], r), w1.y), fmul(fmul(v[6], r), w1.z), fmul(fmul(v[7], r), w1.w),
+                        M.sx + warp * XK_STRIDE);
   }
   g.sync();
   sp.mark(19);
@@ -548,7 +533,7 @@ __device__ __noinline__ void phase_quant(const LLWord* src, uint32_t tag, int n,
     float v[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) v[i] = ll_settle(p + i, wd[i], tag, M.abort, M.err);
-    warp_quantize_q8k_vals(v, M.sx + b * XK_STRIDE, 1);
+    quantize_block_call(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], M.sx + b * XK_STRIDE);
   }
   g.sync();
 }
@@ -570,9 +555,9 @@ __device__ __forceinline__ void stage_kv_rows(float* buf, int stride, const floa
 
 // Sum of p[0..n) (shared memory, written by any thread of the group) returned to every
 // thread: in the reference's sequential order, or as a tree when `tree` is set. Longer
-// sequential sums go through the segment algorithm of groupsum.cuh; up to SEQ_CHAIN_MAX
+// sequential sums go through the chunked algorithm of groupsum.cuh; up to SEQ_CHAIN_MAX
 // terms one thread's plain add chain (4 cycles per term) is quicker than its set-up.
-constexpr int SEQ_CHAIN_MAX = 1536;
+constexpr int SEQ_CHAIN_MAX = 256;
 __device__ __noinline__ float cta_sum(const float* p, int n, bool tree, const MegaSmem& M, const CtaGroup& g) {
   if (!tree && n > SEQ_CHAIN_MAX) return group_seq_sum_call(p, n, M.ss, g.tid, g.nthreads, g.bar_id, nullptr);
   g.sync();
@@ -600,23 +585,45 @@ __device__ __noinline__ float cta_sum(const float* p, int n, bool tree, const Me
   return M.red[40];
 }
 
-// q.k over one head (ops.rs:160-166): products first (independent), then the adds in
-// element order; with `split`, four interleaved partial chains joined as (a0+a1)+(a2+a3).
-// `kchunk(j)` returns float4 chunk j of the cached row.
-template <class KChunk>
-__device__ __forceinline__ float qk_dot(const float4* qt, KChunk kchunk, int hd4, bool split) {
-  if (split) {
-    float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int i0 = 0; i0 < hd4; i0 += 4) {
+// Softmax over sc[0..n) in place (ops.rs:98-112): `lmax` is this thread's maximum of the
+// scores it wrote. Ends with the scaled values written; callers put a barrier before
+// other threads read them.
+__device__ __noinline__ void softmax_rows(float* sc, int n, float lmax, int fast, const MegaSmem& M, const CtaGroup& g) {
+  const int tid = g.tid, T = g.nthreads;
 #pragma unroll
-      for (int u = 0; u < 4; u++) {
-        const float4 kk = kchunk(i0 + u), qq = qt[i0 + u];
-        a[u] = fadd(a[u], fadd(fadd(fmul(qq.x, kk.x), fmul(qq.y, kk.y)), fadd(fmul(qq.z, kk.z), fmul(qq.w, kk.w))));
-      }
-    }
-    return fadd(fadd(a[0], a[1]), fadd(a[2], a[3]));
+  for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
+  if ((tid & 31) == 0) M.red[tid >> 5] = lmax;
+  g.sync();
+  float mx = M.red[0];
+  for (int w = 1; w < (T >> 5); w++) mx = fmaxf(mx, M.red[w]);
+  for (int t = tid; t < n; t += T) sc[t] = expf_exact(fsub(sc[t], mx));
+  const float sum = cta_sum(sc, n, (fast & FAST_SOFTMAX_SUM) != 0, M, g);  // opens with a barrier
+  const float inv = fdiv(1.0f, sum);
+  g.sync();
+  for (int t = tid; t < n; t += T) sc[t] = fmul(sc[t], inv);
+}
+
+// o + sum over t < cn of a[t] * v[t * stride], positions in order (ops.rs:208-214).
+__device__ __forceinline__ float value_mix(float o, const float* a, const float* v, int stride, int cn) {
+  int t = 0;
+#pragma unroll 1
+  for (; t + 8 <= cn; t += 8) {
+    float pr[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) pr[u] = fmul(a[t + u], v[(t + u) * stride]);
+#pragma unroll
+    for (int u = 0; u < 8; u++) o = fadd(o, pr[u]);
   }
+  for (; t < cn; t++) o = fadd(o, fmul(a[t], v[t * stride]));
+  return o;
+}
+
+// q.k over one head (ops.rs:160-166): products first (independent), then the adds in
+// element order. `kchunk(j)` returns float4 chunk j of the cached row.
+template <class KChunk>
+__device__ __forceinline__ float qk_dot(const float4* qt, KChunk kchunk, int hd4) {
   float s = 0.0f;
+#pragma unroll 1
   for (int i0 = 0; i0 < hd4; i0 += 4) {
     float pr[16];
 #pragma unroll
@@ -638,7 +645,7 @@ __device__ __forceinline__ float qk_dot(const float4* qt, KChunk kchunk, int hd4
 // being decoded): K rows first, then V rows, hd floats each; the 16-byte chunks of K row t
 // are stored at chunk index j ^ (t & 7) so that threads reading different rows hit
 // different banks. Returns false, and stages nothing, when the rows do not fit.
-__device__ __forceinline__ bool attn_stage_early(const StepParams& P, int li, int h, int pos, float* stg, const CtaGroup& g) {
+__device__ __noinline__ bool attn_stage_early(const StepParams& P, int li, int h, int pos, float* stg, int tid, int nthreads) {
   const int hd = P.head_dim, n = pos + 1;
   if ((size_t)2 * n * hd > (size_t)P.stage_floats) return false;
   const int kvd = P.n_kv_head * hd, kvh = h / (P.n_head / P.n_kv_head), hd4 = hd >> 2;
@@ -647,7 +654,8 @@ __device__ __forceinline__ bool attn_stage_early(const StepParams& P, int li, in
   const float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd + kvh * hd;
   float* kbuf = stg;
   float* vbuf = stg + (size_t)n * hd;
-  for (int j = g.tid; j < pos * hd4; j += g.nthreads) {
+#pragma unroll 1
+  for (int j = tid; j < pos * hd4; j += nthreads) {
     const int t = j / hd4, i4 = j - t * hd4;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(kbuf + t * hd + 4 * (i4 ^ (t & mask)))),
                  "l"(kc + (size_t)t * kvd + 4 * i4)
@@ -659,22 +667,82 @@ __device__ __forceinline__ bool attn_stage_early(const StepParams& P, int li, in
   return true;
 }
 
+// Scores and value mix of head h when the cached rows pass through two chunk buffers
+// (contexts whose rows do not fit the staging area): cached K rows are staged in chunks,
+// double buffered, rows padded by one float4 to spread the banks; then the softmax; then
+// the V rows the same way. q, k, v of the token being decoded are in sq, sk, sv.
+__device__ __noinline__ void attention_chunked(const StepParams& P, int li, int h, int pos, uint32_t tag_out, const MegaSmem& M,
+                                               int tid, int T) {
+  const CtaGroup g{tid, T, 1};
+  const int hd = P.head_dim, kvd = P.n_kv_head * hd, kvh = h / (P.n_head / P.n_kv_head), n = pos + 1, hd4 = hd >> 2;
+  float* sq = M.scr;
+  float* sk = sq + hd;
+  float* sv = sk + hd;
+  float* sc = sv + 2 * hd;
+  float* vbuf = M.scr + P.small_floats;
+  const float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd;
+  const float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd;
+  const float scale = 1.0f / sqrtf((float)hd);
+  const float4* qt = reinterpret_cast<const float4*>(sq);
+  const int kstride = hd + 4, chunk = P.v_chunk, buf_floats = chunk * kstride;
+  float lmax = -INFINITY;
+  stage_kv_rows(vbuf, kstride, kc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sk, tid, T);
+#pragma unroll 1
+  for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
+    const int cn = min(chunk, n - c0);
+    float* cur_buf = vbuf + (ci & 1) * buf_floats;
+    if (c0 + chunk < n) {
+      stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, kstride, kc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sk, tid, T);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    g.sync();
+    for (int t = tid; t < cn; t += T) {
+      const float4* kt = reinterpret_cast<const float4*>(cur_buf + t * kstride);
+      float s = qk_dot(qt, [&](int j) { return kt[j]; }, hd4);
+      s = fmul(s, scale);
+      sc[c0 + t] = s;
+      lmax = fmaxf(lmax, s);
+    }
+    g.sync();  // this buffer is refilled two chunks later
+  }
+  // the first chunk of V rows loads while the softmax runs
+  stage_kv_rows(vbuf, hd, vc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sv, tid, T);
+  softmax_rows(sc, n, lmax, P.fast, M, g);
+  float o = 0.0f;
+#pragma unroll 1
+  for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
+    const int cn = min(chunk, n - c0);
+    const float* cur_buf = vbuf + (ci & 1) * buf_floats;
+    if (c0 + chunk < n) {
+      stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, hd, vc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sv, tid, T);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    g.sync();
+    if (tid < hd) o = value_mix(o, sc + c0, cur_buf + tid, hd, cn);
+    g.sync();
+  }
+  if (tid < hd) ll_store(P.attl + h * hd + tid, o, tag_out);
+}
+
 // Per-head q/k norm, RoPE, KV store and attention for head `h` (ops.rs:74-87, 40-70,
 // 152-157, 185-218), by the consumer warps of one CTA. `staged`: attn_stage_early has put
 // the cached rows of this head into the staging area.
 __device__ __noinline__ void phase_attention(const StepParams& P, int li, int h, int pos, uint32_t tag_in, uint32_t tag_out, bool staged,
-                                const MegaSmem& M, const CtaGroup& g, SubProf pf = SubProf{nullptr, 0}) {
-  pf.last = clock64();
+                                             const MegaSmem& M, int tid, int T, unsigned long long* prof) {
+  const CtaGroup g{tid, T, 1};
+  SubProf pf{prof, clock64()};
   const int hd = P.head_dim, kvd = P.n_kv_head * hd, gqa = P.n_head / P.n_kv_head, kvh = h / gqa;
-  const int n = pos + 1, tid = g.tid, T = g.nthreads;
+  const int n = pos + 1;
   float* sq = M.scr;            // hd
   float* sk = sq + hd;          // hd
   float* sv = sk + hd;          // hd
   float* sp = sv + hd;          // hd (squares)
   float* sc = sp + hd;          // n_ctx scores
   float* stg = M.scr + P.small_floats;  // staging area, 16-byte aligned
-  const float* const q_norm_w = P.layers[li].q_norm;
-  const float* const k_norm_w = P.layers[li].k_norm;
   float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd;
   float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd;
   // RoPE factors of this thread's pair, requested before the wait below
@@ -694,11 +762,12 @@ __device__ __noinline__ void phase_attention(const StepParams& P, int li, int h,
   }
   g.sync();
   if (P.qk_norm) {
+#pragma unroll 1
     for (int which = 0; which < 2; which++) {
       float* v = which ? sk : sq;
-      const float* nw = which ? k_norm_w : q_norm_w;
+      const float* nw = which ? P.layers[li].k_norm : P.layers[li].q_norm;
       for (int i = tid; i < hd; i += T) sp[i] = fmul(v[i], v[i]);
-      const float ss = (P.fast & FAST_NORM_SUM) ? cta_sum(sp, hd, true, M, g) : group_seq_sum_call(sp, hd, M.ss, g.tid, g.nthreads, g.bar_id, nullptr);
+      const float ss = cta_sum(sp, hd, (P.fast & FAST_NORM_SUM) != 0, M, g);
       const float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)hd), P.eps)));
       g.sync();
       for (int i = tid; i < hd; i += T) v[i] = fmul(fmul(v[i], r), nw[i]);
@@ -721,136 +790,38 @@ __device__ __noinline__ void phase_attention(const StepParams& P, int li, int h,
     }
   }
   pf.mark(20);
+  if (!staged) {
+    attention_chunked(P, li, h, pos, tag_out, M, tid, T);
+    pf.mark(24);
+    return;
+  }
+  // the row of the token being decoded joins the staged rows
+  const int hd4 = hd >> 2, mask = (hd & 31) == 0 ? 7 : 0;
+  float* kbuf = stg;
+  float* vbuf = stg + (size_t)n * hd;
+  for (int i4 = tid; i4 < 2 * hd4; i4 += T) {
+    if (i4 < hd4) reinterpret_cast<float4*>(kbuf + pos * hd)[i4 ^ (pos & mask)] = reinterpret_cast<const float4*>(sk)[i4];
+    else reinterpret_cast<float4*>(vbuf + pos * hd)[i4 - hd4] = reinterpret_cast<const float4*>(sv)[i4 - hd4];
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  g.sync();
   const float scale = 1.0f / sqrtf((float)hd);
-  const int hd4 = hd >> 2;
-  const bool qk_split = (P.fast & FAST_QK_DOT) != 0;
-  float lmax = -INFINITY;
   const float4* qt = reinterpret_cast<const float4*>(sq);
-  float* vbuf;  // generic path: two chunk buffers; staged path: all rows
-  if (staged) {
-    // the row of the token being decoded joins the staged rows
-    const int mask = (hd & 31) == 0 ? 7 : 0;
-    float* kbuf = stg;
-    vbuf = stg + (size_t)n * hd;
-    for (int i4 = tid; i4 < 2 * hd4; i4 += T) {
-      if (i4 < hd4) reinterpret_cast<float4*>(kbuf + pos * hd)[i4 ^ (pos & mask)] = reinterpret_cast<const float4*>(sk)[i4];
-      else reinterpret_cast<float4*>(vbuf + pos * hd)[i4 - hd4] = reinterpret_cast<const float4*>(sv)[i4 - hd4];
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    g.sync();
-    for (int t = tid; t < n; t += T) {
-      const float4* kt = reinterpret_cast<const float4*>(kbuf + t * hd);
-      const int sw = t & mask;
-      float s = qk_dot(qt, [&](int j) { return kt[j ^ sw]; }, hd4, qk_split);
-      s = fmul(s, scale);
-      sc[t] = s;
-      lmax = fmaxf(lmax, s);
-    }
-  } else {
-    // cached K rows are staged through shared memory in chunks, double buffered; rows are
-    // padded by one float4 to spread the banks
-    vbuf = stg;
-    const int kstride = hd + 4, chunk = P.v_chunk;
-    const int buf_floats = chunk * kstride;
-    stage_kv_rows(vbuf, kstride, kc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sk, tid, T);
-    for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
-      const int cn = min(chunk, n - c0);
-      float* cur_buf = vbuf + (ci & 1) * buf_floats;
-      if (c0 + chunk < n) {
-        stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, kstride, kc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sk,
-                      tid, T);
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-      } else {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-      }
-      g.sync();
-      for (int t = tid; t < cn; t += T) {
-        const float4* kt = reinterpret_cast<const float4*>(cur_buf + t * kstride);
-        float s = qk_dot(qt, [&](int j) { return kt[j]; }, hd4, qk_split);
-        s = fmul(s, scale);
-        sc[c0 + t] = s;
-        lmax = fmaxf(lmax, s);
-      }
-      g.sync();  // this buffer is refilled two chunks later
-    }
-    // the first chunk of V rows loads while the softmax runs
-    stage_kv_rows(vbuf, hd, vc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sv, tid, T);
+  float lmax = -INFINITY;
+  for (int t = tid; t < n; t += T) {
+    const float4* kt = reinterpret_cast<const float4*>(kbuf + t * hd);
+    const int sw = t & mask;
+    float s = qk_dot(qt, [&](int j) { return kt[j ^ sw]; }, hd4);
+    s = fmul(s, scale);
+    sc[t] = s;
+    lmax = fmaxf(lmax, s);
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
-  if ((tid & 31) == 0) M.red[tid >> 5] = lmax;
-  g.sync();
   pf.mark(21);
-  float mx = M.red[0];
-  for (int w = 1; w < (T >> 5); w++) mx = fmaxf(mx, M.red[w]);
-  for (int t = tid; t < n; t += T) sc[t] = expf_exact_call(fsub(sc[t], mx));
-  pf.mark(22);
-  const float sum = cta_sum(sc, n, (P.fast & FAST_SOFTMAX_SUM) != 0, M, g);  // opens with a barrier
+  softmax_rows(sc, n, lmax, P.fast, M, g);
   pf.mark(23);
-  const float inv = fdiv(1.0f, sum);
   g.sync();
-  for (int t = tid; t < n; t += T) sc[t] = fmul(sc[t], inv);
   // value mix, positions in order (ops.rs:208-214)
-  if (staged) {
-    g.sync();
-    if (P.fast & FAST_VALUE_MIX) {
-      // positions split over up to four thread groups, partial sums joined in group order
-      int G = T / hd;
-      G = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
-      const int grp = tid / hd, d = tid - grp * hd, per = (n + G - 1) / G;
-      if (grp < G) {
-        float o = 0.0f;
-        const int t1 = min(n, (grp + 1) * per);
-        for (int t = grp * per; t < t1; t++) o = fadd(o, fmul(sc[t], vbuf[t * hd + d]));
-        sq[grp * hd + d] = o;  // q, k, v and the squares are no longer needed: 4 x hd floats
-      }
-      g.sync();
-      if (tid < hd) {
-        float o = sq[tid];
-        for (int k = 1; k < G; k++) o = fadd(o, sq[k * hd + tid]);
-        ll_store(P.attl + h * hd + tid, o, tag_out);
-      }
-    } else if (tid < hd) {
-      float o = 0.0f;
-      int t = 0;
-      for (; t + 8 <= n; t += 8) {
-        float pr[8];
-#pragma unroll
-        for (int u = 0; u < 8; u++) pr[u] = fmul(sc[t + u], vbuf[(t + u) * hd + tid]);
-#pragma unroll
-        for (int u = 0; u < 8; u++) o = fadd(o, pr[u]);
-      }
-      for (; t < n; t++) o = fadd(o, fmul(sc[t], vbuf[t * hd + tid]));
-      ll_store(P.attl + h * hd + tid, o, tag_out);
-    }
-  } else {
-    const int chunk = P.v_chunk, buf_floats = chunk * (hd + 4);
-    float o = 0.0f;
-    for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
-      const int cn = min(chunk, n - c0);
-      const float* cur_buf = vbuf + (ci & 1) * buf_floats;
-      if (c0 + chunk < n) {
-        stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, hd, vc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, n - c0 - chunk), pos, sv, tid, T);
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-      } else {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-      }
-      g.sync();
-      if (tid < hd) {
-        int t = 0;
-        for (; t + 8 <= cn; t += 8) {
-          float pr[8];
-#pragma unroll
-          for (int u = 0; u < 8; u++) pr[u] = fmul(sc[c0 + t + u], cur_buf[(t + u) * hd + tid]);
-#pragma unroll
-          for (int u = 0; u < 8; u++) o = fadd(o, pr[u]);
-        }
-        for (; t < cn; t++) o = fadd(o, fmul(sc[c0 + t], cur_buf[t * hd + tid]));
-      }
-      g.sync();
-    }
-    if (tid < hd) ll_store(P.attl + h * hd + tid, o, tag_out);
-  }
+  if (tid < hd) ll_store(P.attl + h * hd + tid, value_mix(0.0f, sc, vbuf + tid, hd, n), tag_out);
   pf.mark(24);
 }
 
@@ -904,17 +875,18 @@ __device__ void phase_argmax(const StepParams& P, const MegaSmem& M, const CtaGr
 constexpr int MEGA_THREADS = MEGA_THREADS_N;
 constexpr int MEGA_CONSUMER_WARPS = MEGA_THREADS / 32 - 1;
 constexpr int MEGA_BAR_BYTES = 128;     // up to 8 stages x (full, empty)
-constexpr int MEGA_SEQSUM_BYTES = 2064;  // sizeof(SeqSumScratch) rounded up to 16
-static_assert(sizeof(SeqSumScratch) <= MEGA_SEQSUM_BYTES, "SeqSumScratch layout");
 // Bytes of shared memory besides the ring stages, the activation images and the scratch.
-constexpr int MEGA_TERMS_BYTES = MEGA_CONSUMER_WARPS * WARP_TERMS_FLOATS * 4;  // block-term strips of the consumer warps
-constexpr int MEGA_TAIL_BYTES = MEGA_BAR_BYTES + MEGA_SEQSUM_BYTES + 64 * 4 + 16 + MEGA_TERMS_BYTES;
+// Block-term strips of the consumer warps. Between products the same bytes hold the
+// records of the exact sequential sums (norm and softmax phases never overlap a product).
+constexpr int MEGA_TERMS_BYTES = MEGA_CONSUMER_WARPS * WARP_TERMS_FLOATS * 4;
+static_assert(sizeof(SeqSumScratch) <= MEGA_TERMS_BYTES, "SeqSumScratch must fit the term strips");
+constexpr int MEGA_TAIL_BYTES = MEGA_BAR_BYTES + 64 * 4 + 16 + MEGA_TERMS_BYTES;
 
 // TP: this GPU holds one shard of a row-sharded model and exchanges partial rows with its peers.
 template <bool TP>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const StepParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  // [stages][sx images][scratch][barriers 128 B][SeqSumScratch][red 64 floats][abort][term strips][table]
+  // [stages][sx images][scratch][barriers 128 B][red 64 floats][abort][term strips | SeqSumScratch][table]
   const int nb_max = (max(max(P.dim, P.hidden), P.n_head * P.head_dim)) / 256;
   uint8_t* stages = smem;
   uint8_t* sx = stages + (size_t)P.n_stages * P.stage_bytes;
@@ -923,13 +895,12 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   cur += P.scratch_bytes;                          // a multiple of 128
   uint64_t* bars = reinterpret_cast<uint64_t*>(cur);
   cur += MEGA_BAR_BYTES;
-  SeqSumScratch* ssc = reinterpret_cast<SeqSumScratch*>(cur);
-  cur += MEGA_SEQSUM_BYTES;
   float* red = reinterpret_cast<float*>(cur);
   cur += 64 * sizeof(float);
   volatile int* abort = reinterpret_cast<volatile int*>(cur);
   cur += 16;
   float* const wterms_all = reinterpret_cast<float*>(cur);
+  SeqSumScratch* ssc = reinterpret_cast<SeqSumScratch*>(cur);
   cur += MEGA_TERMS_BYTES;
   // The step's tensor table (one StepLayer per layer + the output head), copied from
   // global memory once so that no phase waits on a descriptor load.
@@ -1037,7 +1008,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
       // decoded: request them into shared memory now, two phases ahead of their use. When
       // they do not fit, at least ask for them into L2 (the weight stream evicts the cache
       // between tokens).
-      staged = attn_stage_early(P, li, blockIdx.x, pos, scr + P.small_floats, g);
+      staged = attn_stage_early(P, li, blockIdx.x, pos, scr + P.small_floats, g.tid, g.nthreads);
       for (int h = blockIdx.x + (staged ? gridDim.x : 0); h < P.n_head; h += gridDim.x) {
         const int kvd = P.n_kv_head * P.head_dim, kvh = h / (P.n_head / P.n_kv_head);
         const int lines = (P.head_dim * 4 + 127) / 128;  // 128-byte lines per cached row of one head
@@ -1086,7 +1057,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     if (ph == 0) {
       // attention, one head per CTA
       for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
-        phase_attention(P, li, h, pos, tl + 1u, tl + 2u, staged && h == (int)blockIdx.x, M, g, SubProf{prof_on ? P.prof : nullptr, 0});
+        phase_attention(P, li, h, pos, tl + 1u, tl + 2u, staged && h == (int)blockIdx.x, M, g.tid, g.nthreads, prof_on ? P.prof : nullptr);
         g.sync();
       }
       MEGA_PROF(4);

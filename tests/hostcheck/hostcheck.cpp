@@ -167,94 +167,55 @@ float hc_seqsum(const float* p, size_t n, int T, int head, int* rounds) {
 }
 
 
-// The speculative segmented evaluation used on the device: 32-term segments, the
-// starting binade of each segment predicted from an inexact prefix sum, one exact
-// composite per segment, then a serial walk that applies a composite when the
-// prediction holds and the result stays inside the binade, and otherwise adds the
-// segment's terms one by one. *fallbacks receives the number of serial segments.
-float hc_seqsum_seg(const float* p, size_t n, int* fallbacks) {
-  const size_t S = (n + 31) / 32;
-  std::vector<float> est(S + 1, 0.0f);
-  for (size_t g = 0; g < S; g++) {
-    float t = 0.0f;  // any estimate works; use a pairwise-looking sum
-    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) t += p[i];
-    est[g + 1] = est[g] + t;
-  }
-  std::vector<SumFn> comp(S);
-  std::vector<int> epred(S);
-  for (size_t g = 0; g < S; g++) {
-    int e, m;
-    uint32_t b = f2u(est[g]);
-    if ((b >> 23) == 255) b = 0x7f000000u;
-    sum_decompose(b, e, m);
-    epred[g] = e;
-    SumFn f = sumfn_identity();
-    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) f = sumfn_compose(f, sumfn_elem(f2u(p[i]), e));
-    comp[g] = f;
-  }
-  float s = 0.0f;
-  int nf = 0;
-  for (size_t g = 0; g < S; g++) {
-    uint32_t sb = f2u(s);
-    int e, m;
-    sum_decompose(sb, e, m);
-    if ((sb >> 23) != 255 && e == epred[g]) {
-      int m2 = sumfn_apply(comp[g], m);
-      if (m2 < SUMFN_LIMIT) {
-        s = u2f(sum_pack(e, m2));
-        continue;
+// Mirror of the device routine (groupsum.cuh): chunks of SEQ_E terms, 32 chunks per
+// group, exponents predicted from an inexact prefix sum (`skew` perturbs it, to provoke
+// wrong predictions), composites of runs of fast chunks, then the walk shared with the
+// device (seqsum_walk). *slow_chunks receives the number of chunks marked slow.
+float hc_seqsum_runs(const float* p, size_t n, float skew, int* slow_chunks) {
+  static SeqSumScratch sc;
+  float total = 0.0f;
+  int n_slow = 0;
+  for (size_t base = 0; base < n; base += (size_t)SEQ_CHUNKS * SEQ_E) {
+    const int len = (int)std::min(n - base, (size_t)SEQ_CHUNKS * SEQ_E), nch = (len + SEQ_E - 1) / SEQ_E;
+    float before = total * skew;
+    for (int c0 = 0; c0 < nch; c0 += 32) {
+      uint32_t slow_mask = 0, start_mask = 0;
+      int eb_prev = 0;
+      bool slow_prev = false;
+      SumFn run = sumfn_identity();
+      for (int lane = 0; lane < 32; lane++) {
+        const int c = c0 + lane, i0 = c * SEQ_E;
+        float v[SEQ_E], t = 0.0f;
+        int cnt = 0;
+        for (int j = 0; j < SEQ_E; j++) {
+          v[j] = i0 + j < len ? p[base + i0 + j] : 0.0f;
+          cnt += i0 + j < len ? 1 : 0;
+          t += v[j];
+        }
+        const int eb = seq_exp_field(before), ea = seq_exp_field(before + t);
+        const bool slow = cnt > 0 && (ea != eb || eb >= 255);
+        const bool starts = lane == 0 || slow_prev || eb != eb_prev;
+        if (slow) slow_mask |= 1u << lane;
+        if (starts) start_mask |= 1u << lane;
+        n_slow += slow ? 1 : 0;
+        if (c < SEQ_CHUNKS) {
+          if (starts) run = sumfn_identity();
+          if (!slow) run = sumfn_compose(run, seq_chunk_fn(v, SEQ_E, eb));
+          sc.a0[c] = slow ? 0 : run.a0;
+          sc.a1[c] = slow ? 0 : run.a1;
+          sc.ep[c] = eb;
+        }
+        eb_prev = eb;
+        slow_prev = slow;
+        before = (before + t) * skew;
       }
+      sc.slow[c0 >> 5] = slow_mask;
+      sc.start[c0 >> 5] = start_mask;
     }
-    nf++;
-    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) s = fadd(s, p[i]);
+    total = seqsum_walk(p + base, len, &sc, nch, total);
   }
-  if (fallbacks) *fallbacks = nf;
-  return s;
-}
-
-
-// Mirror of the device routine's final form: per 32-term segment an integer increment
-// C = sum round(p/u) for the predicted binade, flagged "bad" when a term is an exact
-// tie or leaves the binade; the walk adds integer prefix sums over runs of good
-// segments and falls back to term-by-term adds for bad ones.
-float hc_seqsum_int(const float* p, size_t n, int* fallbacks) {
-  const size_t S = (n + 31) / 32;
-  std::vector<float> est(S + 1, 0.0f);
-  for (size_t g = 0; g < S; g++) {
-    float t = 0.0f;
-    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) t += p[i];
-    est[g + 1] = est[g] + t;
-  }
-  std::vector<int> csum(S), epred(S);
-  for (size_t g = 0; g < S; g++) {
-    uint32_t b = f2u(est[g]);
-    if ((b >> 23) >= 255u || (b >> 31)) b = 0;
-    int e, m;
-    sum_decompose(b, e, m);
-    long long C = 0;
-    bool bad = false;
-    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) {
-      SumFn f = sumfn_elem(f2u(p[i]), e);
-      if (f.a0 != f.a1 || f.a0 >= SUMFN_SAT) bad = true;
-      C += f.a0 > (1 << 25) ? (1 << 25) : f.a0;
-    }
-    csum[g] = (int)C;
-    epred[g] = bad ? -1 : e;
-  }
-  int e, m, nf = 0;
-  sum_decompose(0u, e, m);
-  for (size_t g = 0; g < S; g++) {
-    if (epred[g] == e && m + csum[g] < SUMFN_LIMIT) {
-      m += csum[g];
-      continue;
-    }
-    nf++;
-    float s = u2f(sum_pack(e, m));
-    for (size_t i = g * 32; i < n && i < (g + 1) * 32; i++) s = fadd(s, p[i]);
-    sum_decompose(f2u(s), e, m);
-  }
-  if (fallbacks) *fallbacks = nf;
-  return u2f(sum_pack(e, m));
+  if (slow_chunks) *slow_chunks = n_slow;
+  return total;
 }
 
 }  // extern "C"

@@ -146,11 +146,26 @@ def test_parallel_sequential_sum_is_exact(hostcheck):
             x = np.full(n, rest, dtype=np.float32)
             x[0] = first
             cases.append(x)
+    hostcheck.hc_seqsum_runs.restype = C.c_float
+    hostcheck.hc_seqsum_runs.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.POINTER(C.c_int)]
+    for n in (300, 2048, 5000):
+        # sums that sit on a binade boundary for long stretches, and ties at every step
+        cases += [np.full(n, 2.0 ** -3, dtype=np.float32), np.full(n, 1.5, dtype=np.float32),
+                  np.concatenate([[np.float32(2.0 ** 20)], np.full(n - 1, 0.5 * 2.0 ** -3, dtype=np.float32)]).astype(np.float32),
+                  np.concatenate([(rng.standard_normal(n - 3) ** 2), [np.inf, 1.0, 2.0]]).astype(np.float32),
+                  np.concatenate([(rng.standard_normal(n - 3) ** 2), [np.nan, 1.0, 2.0]]).astype(np.float32)]
     for p in cases:
         want = _naive_sum(p)
         for T, head in ((992, 48), (32, 0), (256, 8), (7, 3)):
             got = np.float32(hostcheck.hc_seqsum(p.ctypes.data_as(C.c_void_p), p.size, T, head, None))
             assert got.view(np.uint32) == want.view(np.uint32) or (np.isnan(got) and np.isnan(want)), (p.size, T)
+        # the chunked form the device runs, with honest and with deliberately wrong predictions
+        for skew in (1.0, 1.0 + 2.0 ** -20, 0.75, 1.5, 0.0, 1e30):
+            n_slow = C.c_int(0)
+            got = np.float32(hostcheck.hc_seqsum_runs(p.ctypes.data_as(C.c_void_p), p.size, skew, C.byref(n_slow)))
+            assert got.view(np.uint32) == want.view(np.uint32) or (np.isnan(got) and np.isnan(want)), (p.size, skew)
+            if skew == 1.0 and p.size == 2048 and np.isfinite(p).all() and 1e-3 < float(p.mean()) < 1e3 and p.std() > 0:
+                assert n_slow.value <= 24, n_slow.value  # a handful of binade crossings, not a serial sum
 
 
 def test_bench_kind_table_matches_the_library(pkg):
