@@ -183,8 +183,13 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   op.cols = (int)call.cols;
   op.span_rows = (int)span;
   op.rows_per_cta = (int)((span + c->n_sm - 1) / c->n_sm);
+  {
+    const int grid_ctas = span < (size_t)c->n_sm ? (int)span : c->n_sm;
+    op.cta_base = (int)(span / grid_ctas);
+    op.cta_rem = (int)(span % grid_ctas);
+  }
   const int tr = (int)((STREAM_STAGE_BYTES - 192) / (max_rb * (call.pair ? 2 : 1)));
-  op.tile_rows = tr < 1 ? 1 : tr;
+  op.tile_rows = tr < 1 ? 1 : (tr > TILE_MAX_UNITS ? TILE_MAX_UNITS : tr);
   op.epilogue = call.epilogue;
   op.ll = 0;
   P.x_image = call.x_mode == 1;
@@ -422,7 +427,7 @@ struct aotcu_gpu {
   void* tp_peer_map[8] = {};          // peers' inboxes mapped into this process
   StepLayer* d_step_layers = nullptr;
   unsigned* d_grid_bar = nullptr;     // [0] barrier arrivals of one launch, [1] launch count
-  LLWord* d_ll = nullptr;             // tagged activation vectors of the one-kernel step
+  void* d_ll = nullptr;               // tagged activation vectors of the one-kernel step
   StepParams step_params = {};
   size_t mega_smem = 0;
   cudaGraphExec_t decode_graph[2] = {nullptr, nullptr};  // [want_logits]
@@ -782,9 +787,9 @@ static int mega_setup(aotcu_gpu* g) {
   ok = ok && d.n_layer <= 200 && (size_t)d.dim >= (size_t)c->n_sm && (size_t)d.hidden >= (size_t)c->n_sm;
   if (!ok) return 0;
   size_t nb_max = std::max(std::max((size_t)d.dim, (size_t)d.hidden), qd) / 256;
-  // Block-term strips hold two rows of a gate/up pair, norm rows stay in registers (one
-  // super-block per warp).
-  if (((nb_max | 1) * 2 > (size_t)WARP_TERMS_FLOATS) || (size_t)d.dim > (size_t)256 * MEGA_CONSUMER_WARPS) return 0;
+  // Block-term strips hold two rows of a gate/up pair, norm rows stay in registers (two
+  // super-blocks per warp).
+  if (((nb_max | 1) * 2 > (size_t)WARP_TERMS_FLOATS) || (size_t)d.dim > (size_t)512 * MEGA_CONSUMER_WARPS) return 0;
   // The largest row of any matrix must fit a ring stage twice (a gate/up pair).
   size_t max_rb = 0;
   for (const auto& l : g->layers) {
@@ -846,8 +851,10 @@ static int mega_setup(aotcu_gpu* g) {
     op.cols = cols;
     op.span_rows = pair ? op.seg[0].rows : span;
     op.rows_per_cta = (op.span_rows + c->n_sm - 1) / c->n_sm;
+    op.cta_base = op.span_rows / c->n_sm;
+    op.cta_rem = op.span_rows % c->n_sm;
     int tr = (int)((size_t)(stage_bytes - 192) / (max_rb * (pair ? 2 : 1)));
-    op.tile_rows = tr < 1 ? 1 : tr;
+    op.tile_rows = tr < 1 ? 1 : (tr > TILE_MAX_UNITS ? TILE_MAX_UNITS : tr);
     op.epilogue = epilogue;
     return op;
   };
@@ -856,7 +863,7 @@ static int mega_setup(aotcu_gpu* g) {
   const size_t ll_words = (size_t)d.dim + qd + 2 * kvd + qd + (size_t)d.hidden;
   CU_TRY(cudaMalloc(&g->d_ll, ll_words * sizeof(LLWord)));
   CU_TRY(cudaMemset(g->d_ll, 0, ll_words * sizeof(LLWord)));
-  LLWord* const xl = g->d_ll;
+  LLWord* const xl = reinterpret_cast<LLWord*>(g->d_ll);
   LLWord* const ql = xl + d.dim;
   LLWord* const kl = ql + qd;
   LLWord* const vl = kl + kvd;
@@ -908,11 +915,13 @@ static int mega_setup(aotcu_gpu* g) {
 }
 
 static int enqueue_mega(aotcu_gpu* g, int want_logits, bool with_argmax, unsigned long long* prof = nullptr,
-                        int prof_cta = 0) {
+                        int prof_cta = 0, unsigned long long* timeline = nullptr, int timeline_layer = 0) {
   aotcu_ctx* c = g->c;
   StepParams P = g->step_params;
   P.prof = prof;
   P.prof_cta = prof_cta;
+  P.timeline = timeline;
+  P.timeline_layer = timeline_layer;
   P.want_logits = want_logits;
   P.with_argmax = with_argmax ? 1 : 0;
   CU_TRY(cudaMemsetAsync(g->d_grid_bar, 0, sizeof(unsigned), c->stream));
@@ -1987,6 +1996,29 @@ int aotcu_gpu_profile_step(aotcu_gpu* g, uint32_t token, size_t pos, int cta, ui
 
 
 }  // extern "C"
+
+extern "C" int aotcu_gpu_timeline_step(aotcu_gpu* g, uint32_t token, size_t pos, int layer, uint64_t* out, int* n_cta) {
+  ARG_CHECK(g && out && n_cta, "NULL argument");
+  ARG_CHECK(g->mega_ok, "this model cannot use the one-kernel decode step");
+  ARG_CHECK(token < (uint32_t)g->head.dims.vocab && pos < g->n_ctx, "token or position out of range");
+  ARG_CHECK(layer >= 0 && layer < g->head.dims.n_layer && g->c->n_sm <= 256, "layer out of range");
+  aotcu_ctx* c = g->c;
+  if (int rc = ctx_set_device(c)) return rc;
+  const size_t bytes = (size_t)c->n_sm * 16 * sizeof(unsigned long long);
+  unsigned long long* d = nullptr;
+  CU_TRY(cudaMalloc(&d, bytes));
+  CU_TRY(cudaMemsetAsync(d, 0, bytes, c->stream));
+  int rc = set_step(g, token, pos, 0);
+  if (!rc) rc = enqueue_mega(g, 1, false, nullptr, 0, d, layer);
+  if (!rc) rc = check_device_errors(c);
+  if (!rc) {
+    cudaError_t e = cudaMemcpy(out, d, bytes, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) rc = fail(AOTCU_ERR_CUDA, "timeline copy: %s", cudaGetErrorString(e));
+  }
+  cudaFree(d);
+  *n_cta = c->n_sm;
+  return rc;
+}
 
 // ---- a matrix-vector product for callers that may not allocate ---------------------------
 // The f32 activation vector has to be quantized to Q8_K block images before the product

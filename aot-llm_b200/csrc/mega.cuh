@@ -21,18 +21,35 @@
 
 namespace aot {
 
+// 512 threads (15 consumer warps and the producer warp) leave 128 registers per thread:
+// measured faster than 640 or 768 threads, whose register budgets spill in the row products.
+#ifndef MEGA_THREADS_N
+#define MEGA_THREADS_N 512
+#endif
+// The gate and up rows of a pair go through the arithmetic side by side when the register
+// budget allows it (128 registers per thread up to 512 threads, 80 at 768).
+#ifndef MEGA_PAIR_INTERLEAVE
+#define MEGA_PAIR_INTERLEAVE (MEGA_THREADS_N <= 512)
+#endif
+
 // ---- tagged activation words ---------------------------------------------------------------
 // Activation vectors that cross CTAs inside the step travel as 64-bit words {f32 value,
 // 32-bit tag}. A writer stores value and tag with one 8-byte store; a reader polls the word
 // until it carries the tag of the phase it expects. Data and "ready" arrive together, so
-// no fence, counter or grid-wide barrier sits between a matrix product and its consumers.
+// no fence, counter or grid-wide barrier sits between a matrix product and its consumers:
+// one trip through L2 instead of the three of a fence + flag + data scheme (measured:
+// about 7 K cycles per hand-over with per-CTA flags, most of it the two fences).
+// A reader asks for all of its words at once and asks again, for all of them, until every
+// tag matches; examining them one after the other would cost one L2 round trip per word
+// that was still missing at the first look.
 // Tags are unique per (launch, phase): (launch count << 10) | phase id, phase id >= 1;
 // a zeroed buffer therefore never matches.
+//
+// Every wait is bounded: `abort` points at two shared words of the CTA, [0] = a wait of this
+// CTA has given up, [1] = polls (about a microsecond each) before a wait gives up. The host
+// raises the limit when several GPUs step together: a rank whose host thread is late must
+// not make its peers give up.
 typedef unsigned long long LLWord;
-// Every wait below is bounded: `abort` points at two shared words of the CTA, [0] = a wait
-// of this CTA has given up, [1] = polls (about a microsecond each) before a wait gives up.
-// The host raises the limit when several GPUs step together: a rank whose host thread is
-// late must not make its peers give up.
 
 __device__ __forceinline__ void ll_store(LLWord* p, float v, uint32_t tag) {
   const LLWord w = ((LLWord)tag << 32) | (LLWord)__float_as_uint(v);
@@ -49,32 +66,51 @@ __device__ __forceinline__ void ll_load2(const LLWord* p, LLWord& a, LLWord& b) 
 // Value of a word whose tag may be ignored (this CTA wrote it in an earlier phase).
 __device__ __forceinline__ float ll_value(const LLWord* p) { return __uint_as_float((uint32_t)ll_load(p)); }
 
-// Spin (bounded) until the word carries `tag`. On expiry the CTA's abort flag and the
-// device error word are set; every later wait then returns at once, so the kernel drains.
-__device__ __noinline__ LLWord ll_spin(const LLWord* p, uint32_t tag, volatile int* abort, int* err) {
-  LLWord w = 0;
-  uint32_t it = 0;
-  const uint32_t limit = (uint32_t)abort[1];
-  for (; it < limit; ++it) {
-    w = ll_load(p);
-    if ((uint32_t)(w >> 32) == tag) break;
-    if ((it & 31u) == 31u && *abort) break;
-  }
-  if ((uint32_t)(w >> 32) != tag && !*abort) {
+// A wait gave up: the CTA's abort flag and the device error word are set; every later wait
+// then returns at once, so the kernel drains.
+__device__ __noinline__ void ll_give_up(volatile int* abort, int* err) {
+  if (!*abort) {
     *abort = 1;
     if (err) atomicOr(err, DEVERR_GRID_TIMEOUT);
   }
-  return w;
 }
-__device__ __forceinline__ float ll_settle(const LLWord* p, LLWord w, uint32_t tag, volatile int* abort, int* err) {
-  if ((uint32_t)(w >> 32) != tag) w = ll_spin(p, tag, abort, err);
+// One word.
+__device__ __forceinline__ float ll_wait(const LLWord* p, uint32_t tag, volatile int* abort, int* err) {
+  LLWord w = ll_load(p);
+  if ((uint32_t)(w >> 32) != tag) {
+    const uint32_t limit = (uint32_t)abort[1];
+    for (uint32_t it = 0;; ++it) {
+      w = ll_load(p);
+      if ((uint32_t)(w >> 32) == tag) break;
+      if (it >= limit || *abort) {
+        ll_give_up(abort, err);
+        break;
+      }
+    }
+  }
   return __uint_as_float((uint32_t)w);
 }
-__device__ __forceinline__ float ll_wait(const LLWord* p, uint32_t tag, volatile int* abort, int* err) {
-  return ll_settle(p, ll_load(p), tag, abort, err);
+// Eight consecutive words (64-byte aligned), requested together in every round.
+__device__ __forceinline__ void ll_wait8(const LLWord* p, uint32_t tag, float (&v)[8], volatile int* abort, int* err) {
+  LLWord w[8];
+  const uint32_t limit = (uint32_t)abort[1];
+  for (uint32_t it = 0;; ++it) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) ll_load2(p + 2 * i, w[2 * i], w[2 * i + 1]);
+    bool all = true;
+#pragma unroll
+    for (int i = 0; i < 8; i++) all = all && (uint32_t)(w[i] >> 32) == tag;
+    if (all) break;
+    if (it >= limit || *abort) {
+      ll_give_up(abort, err);
+      break;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) v[i] = __uint_as_float((uint32_t)w[i]);
 }
 
-// Rows [c0, c1) of a row space of `span` rows that belong to this CTA: an even split with
+// Rows [c0, c1) of a vector of `span` rows that belong to this CTA: an even split with
 // the remainder spread over the first CTAs, so every CTA owns a row when span >= gridDim.x.
 __device__ __forceinline__ void cta_rows(int span, int& c0, int& c1) {
   const int base = span / (int)gridDim.x, rem = span - base * (int)gridDim.x, b = (int)blockIdx.x;
@@ -121,8 +157,7 @@ __device__ __forceinline__ float ll_wait_sys(const LLWord* p, uint32_t tag, vola
 __device__ __noinline__ float silu_mul_call(float g, float u) { return fmul(fdiv(g, fadd(1.0f, expf_exact(-g))), u); }
 __device__ __noinline__ float group_seq_sum_call(const float* p, int n, SeqSumScratch* sc, int tid, int nthreads, int bar_id,
                                                  unsigned long long* prof) {
-  SubProf sp{prof, clock64()};
-  return group_seq_sum(p, n, sc, CtaGroup{tid, nthreads, bar_id}, prof ? &sp : nullptr);
+  return group_seq_sum(p, n, sc, CtaGroup{tid, nthreads, bar_id}, prof);
 }
 __device__ __noinline__ float dequant_elem_call(int kind, const uint8_t* row, size_t e) { return dequant_elem(kind, row, e); }
 
@@ -135,6 +170,7 @@ struct MegaOp {
   uint32_t row_bytes[3];
   int nseg, pair, cols, span_rows, rows_per_cta, tile_rows, epilogue;
   int ll;  // outputs are tagged words (seg[].out points at LLWord), not plain floats
+  int cta_base, cta_rem;  // span_rows / grid and span_rows % grid: CTA b owns cta_base (+1 when b < cta_rem) rows
 };
 
 struct StepLayer {
@@ -178,13 +214,38 @@ struct StepParams {
   int table_bytes;     // bytes of the StepLayer table staged in shared memory (n_layer + 1 entries)
   unsigned long long* prof;  // optional: cycles per phase, accumulated by one CTA
   int prof_cta;
+  unsigned long long* timeline;  // optional: [grid][16] global-timer stamps at the phase boundaries of one layer
+  int timeline_layer;
 };
 
 // ---- shared-memory ring --------------------------------------------------------------------
+// What a ring stage holds, written by the producer warp before it arms the stage and read
+// by the consumers after the stage's barrier completes: up to three parts (segments of a
+// concatenated row space, or the gate and up rows of a pair), each a run of whole rows, and
+// one record per unit (a row, or a gate/up row pair) with everything a consumer warp needs:
+// the producer's 32 lanes do the index arithmetic off the consumers' path.
+struct TileUnit {
+  uint32_t row[2];  // shared address of the unit's row(s), weight kind in bits 24..31
+  float* out;       // where the row's result goes (first matrix of a pair)
+};
+constexpr int TILE_MAX_UNITS = 32;
+struct TileDesc {
+  uint32_t base[3];  // shared address of the part's first row
+  int row0[3];       // index of that row inside its segment
+  int rows[3];
+  int seg[3];
+  int u0, n_units;   // CTA-relative index of the tile's first unit, and the number of units
+  int pad[2];
+  uint8_t first[32];  // per consumer warp: its first unit in this tile (then every n_warps-th)
+  TileUnit unit[TILE_MAX_UNITS];
+};
+static_assert(sizeof(TileDesc) == 608, "TileDesc layout");
+
 struct Ring {
   uint8_t* stages;
   uint64_t* full;
   uint64_t* empty;
+  TileDesc* desc;
   int n_stages, stage_bytes;
   volatile int* abort;  // set when any bounded wait of this CTA expired
   int* err;
@@ -216,59 +277,86 @@ __device__ __forceinline__ bool ring_wait(const Ring& R, uint64_t* bar, uint32_t
   return false;
 }
 
-// Byte ranges of the tile covering rows [t0, t1) of the op's row space.
-__device__ __noinline__ int op_tile_parts(const MegaOp& op, int t0, int t1, TilePart parts[3]) {
-  if (op.pair || op.nseg == 1) {
-    const int np = op.pair ? 2 : 1;
-    uint32_t soff = 0;
-#pragma unroll
-    for (int s = 0; s < 2; s++) {
-      if (s < np) {
-        TilePart& tp = parts[s];
-        tp.seg = s;
-        tp.row0 = t0;
-        tp.rows = t1 - t0;
-        tp.src = op.seg[s].w + (size_t)t0 * op.row_bytes[s];
-        tp.len = (uint32_t)(t1 - t0) * op.row_bytes[s];
-        tp.soff = soff;
-        soff += bulk_superset_bytes(tp.src, tp.len) + 16;
-      }
-    }
-    return np;
-  }
-  int n = 0, base = 0;
-  uint32_t soff = 0;
-  for (int s = 0; s < op.nseg; s++) {
-    const int a = max(t0, base), b = min(t1, base + op.seg[s].rows);
-    if (a < b) {
-      TilePart& tp = parts[n++];
-      tp.seg = s;
-      tp.row0 = a - base;
-      tp.rows = b - a;
-      tp.src = op.seg[s].w + (size_t)(a - base) * op.row_bytes[s];
-      tp.len = (uint32_t)(b - a) * op.row_bytes[s];
-      tp.soff = soff;
-      soff += bulk_superset_bytes(tp.src, tp.len) + 16;
-    }
-    base += op.seg[s].rows;
-  }
-  return n;
+// Rows [c0, c1) of the op's row space that belong to this CTA.
+__device__ __forceinline__ void op_cta_rows(const MegaOp& op, int& c0, int& c1) {
+  const int b = (int)blockIdx.x;
+  c0 = b * op.cta_base + min(b, op.cta_rem);
+  c1 = c0 + op.cta_base + (b < op.cta_rem ? 1 : 0);
 }
 
-// Producer side (one thread): request every tile of this CTA's share of `op`.
-__device__ __noinline__ void produce_op(const MegaOp& op, const Ring& R, RingPos& pp) {
+// Producer side (the whole producer warp): request every tile of this CTA's share of `op`
+// and describe it for the consumers. Lane 0 waits for the stage and issues the copies, part
+// by part; every lane then writes one unit record; the stage's single arrival, which
+// carries the byte count of all copies, comes last (a barrier's pending byte count may run
+// negative in between).
+__device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, RingPos& pp, int n_consumers) {
+  const int lane = threadIdx.x & 31;
   int c0, c1;
-  cta_rows(op.span_rows, c0, c1);
-  for (int t0 = c0; t0 < c1; t0 += op.tile_rows) {
-    if (!ring_wait(R, &R.empty[pp.st], pp.parity ^ 1u)) return;
-    TilePart parts[3];
-    const int t1 = min(t0 + op.tile_rows, c1);
-    const int np = op_tile_parts(op, t0, t1, parts);
-    uint32_t total = 0;
-    for (int i = 0; i < np; i++) total += bulk_superset_bytes(parts[i].src, parts[i].len);
-    mbar_expect_tx(&R.full[pp.st], total);
-    for (int i = 0; i < np; i++)
-      bulk_g2s_superset(R.stages + (size_t)pp.st * R.stage_bytes + parts[i].soff, parts[i].src, parts[i].len, &R.full[pp.st]);
+  op_cta_rows(op, c0, c1);
+  const int nseg = op.nseg, pair = op.pair, tile_rows = op.tile_rows;
+#pragma unroll 1
+  for (int t0 = c0; t0 < c1; t0 += tile_rows) {
+    int ok = 1;
+    if (lane == 0) ok = ring_wait(R, &R.empty[pp.st], pp.parity ^ 1u) ? 1 : 0;
+    if (!__shfl_sync(0xffffffffu, ok, 0)) return;
+    const int t1 = min(t0 + tile_rows, c1);
+    TileDesc& D = R.desc[pp.st];
+    uint8_t* const stage = R.stages + (size_t)pp.st * R.stage_bytes;
+    // parts: the two matrices of a pair share the row range; concatenated segments split it
+    // (every lane computes them; lane 0 issues the copies)
+    uint32_t total = 0, off = 0;
+    int np = 0, base = 0;
+    // this lane's unit: rows [t0 + lane] of the row space
+    const int my = t0 + lane;
+    uint32_t my_row[2] = {0u, 0u};
+    float* my_out = nullptr;
+#pragma unroll 1
+    for (int sgi = 0; sgi < nseg; sgi++) {
+      const int rows = op.seg[sgi].rows;
+      const int a = pair ? t0 : max(t0, base) - base, b = pair ? t1 : min(t1, base + rows) - base;
+      if (a < b) {
+        const uint32_t rb = op.row_bytes[sgi];
+        const uint8_t* src = op.seg[sgi].w + (size_t)a * rb;
+        const uint32_t len = (uint32_t)(b - a) * rb, sup = bulk_superset_bytes(src, len);
+        const uint32_t pbase = smem_addr(stage + off) + ((uint32_t)(uintptr_t)src & 15u);
+        if (lane == 0) {
+          D.base[np] = pbase;
+          D.row0[np] = a;
+          D.rows[np] = b - a;
+          D.seg[np] = sgi;
+          bulk_g2s_superset(stage + off, src, len, &R.full[pp.st]);
+        }
+        // does this lane's unit lie in the part?
+        const int lr = pair ? lane : my - base - a;
+        if (lr >= 0 && lr < b - a && my < t1) {
+          my_row[pair ? sgi : 0] = (pbase + (uint32_t)lr * rb) | ((uint32_t)op.seg[sgi].kind << 24);
+          if (!pair || sgi == 0)
+            my_out = op.ll ? reinterpret_cast<float*>(reinterpret_cast<LLWord*>(op.seg[sgi].out) + a + lr) : op.seg[sgi].out + a + lr;
+        }
+        off += sup + 16;
+        total += sup;
+        np++;
+      }
+      base += rows;
+    }
+    if (lane == 0) {
+      for (int i = np; i < 3; i++) D.rows[i] = 0;
+      D.u0 = t0 - c0;
+      D.n_units = t1 - t0;
+    }
+    if (my < t1) {
+      TileUnit U;
+      U.row[0] = my_row[0];
+      U.row[1] = my_row[1];
+      U.out = my_out;
+      D.unit[lane] = U;
+    }
+    if (lane < n_consumers) {
+      const int f = (lane - (t0 - c0) % n_consumers + n_consumers) % n_consumers;
+      D.first[lane] = (uint8_t)(f < t1 - t0 ? f : 255);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_expect_tx(&R.full[pp.st], total);
     pp.advance(R.n_stages);
   }
 }
@@ -276,16 +364,18 @@ __device__ __noinline__ void produce_op(const MegaOp& op, const Ring& R, RingPos
 // Consumer side (every consumer warp). The rows (gate/up row pairs in pair mode) of this
 // CTA's share are dealt to the warps round robin, continuing across tiles, and a warp takes
 // a whole row: four lanes per super-block with the activation slices in registers
-// (rowdot.cuh). Block terms are parked in the warp's strip `wterms`; when the strip is
-// full or the product ends, lane i adds the terms of parked row i in block order and runs
-// the epilogue (residual add, SiLU gate, exchange with the other ranks). `sx` holds the
-// Q8_K images of the activation vector; `op` lives in shared memory.
+// (rowdot.cuh); the gate and up rows of a pair go through the arithmetic side by side.
+// Block terms are parked in the warp's strip `wterms`; when the strip is full or the
+// product ends, lane i adds the terms of parked row i in block order and runs the epilogue
+// (residual add, SiLU gate, exchange with the other ranks). `sx` holds the Q8_K images of
+// the activation vector; `op` lives in shared memory.
 constexpr int WARP_TERMS_FLOATS = 128;  // strip per consumer warp
 
+// Lane i finishes parked unit i: `my_out` is the address of its output word, `my_old` the
+// residual value asked for when the unit was parked (ACCUM into tagged words only).
 template <bool TP>
-__device__ __noinline__ void warp_flush(const MegaOp& op, const float* wterms, int pend, int u0, int n_warps, int c0, int nb,
-                                           int tstride, uint32_t tag, const TpExchange* tpx, int which, float old_pref,
-                                           bool have_pref) {
+__device__ __forceinline__ void warp_flush(const MegaOp& op, const float* wterms, int pend, int nb, int tstride, uint32_t tag,
+                                           const TpExchange* tpx, int which, float* my_out, float my_old) {
   __syncwarp();
   const int lane = threadIdx.x & 31;
   if (op.pair) {
@@ -295,33 +385,27 @@ __device__ __noinline__ void warp_flush(const MegaOp& op, const float* wterms, i
     if (i < pend) v = terms_seq_sum(wterms + (2 * i + mt) * tstride, nb);
     const float up = __shfl_down_sync(0xffffffffu, v, 16);
     if (lane < pend) {
-      const int r = c0 + u0 + lane * n_warps;
       const float hv = op.epilogue == EPI_SILU_MUL ? silu_mul_call(v, up) : v;
       if (op.ll) {
-        ll_store(reinterpret_cast<LLWord*>(op.seg[0].out) + r, hv, tag);
+        ll_store(reinterpret_cast<LLWord*>(my_out), hv, tag);
       } else {
-        op.seg[0].out[r] = hv;
-        op.seg[1].out[r] = up;
+        *my_out = hv;
+        op.seg[1].out[my_out - op.seg[0].out] = up;
       }
     }
   } else if (lane < pend) {
     const float v = terms_seq_sum(wterms + lane * tstride, nb);
-    int sg = 0, oi = c0 + u0 + lane * n_warps;
-    while (sg < op.nseg - 1 && oi >= op.seg[sg].rows) {
-      oi -= op.seg[sg].rows;
-      sg++;
-    }
     if (TP && op.ll && tpx && op.epilogue == EPI_ACCUM) {
       // a partial row of a sharded product: hand it to every rank (this one included)
       for (int dst = 0; dst < tpx->world; dst++)
-        ll_store_sys(tpx->inbox[dst] + ((size_t)which * tpx->world + tpx->rank) * tpx->dim + oi, v, tag);
+        ll_store_sys(tpx->inbox[dst] + ((size_t)which * tpx->world + tpx->rank) * tpx->dim +
+                         (reinterpret_cast<LLWord*>(my_out) - reinterpret_cast<LLWord*>(op.seg[0].out)),
+                     v, tag);
     } else if (op.ll) {
       // a residual row is only ever written by its owner, so its old value needs no tag check
-      LLWord* o = reinterpret_cast<LLWord*>(op.seg[sg].out) + oi;
-      ll_store(o, op.epilogue == EPI_ACCUM ? fadd(have_pref ? old_pref : ll_value(o), v) : v, tag);
+      ll_store(reinterpret_cast<LLWord*>(my_out), op.epilogue == EPI_ACCUM ? fadd(my_old, v) : v, tag);
     } else {
-      float* o = op.seg[sg].out + oi;
-      *o = op.epilogue == EPI_ACCUM ? fadd(__ldcg(o), v) : v;
+      *my_out = op.epilogue == EPI_ACCUM ? fadd(__ldcg(my_out), v) : v;
     }
   }
   __syncwarp();
@@ -329,65 +413,76 @@ __device__ __noinline__ void warp_flush(const MegaOp& op, const float* wterms, i
 
 template <bool TP = false>
 __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, float* wterms, int warp,
-                                           int n_warps, uint32_t tag, const TpExchange* tpx = nullptr, int which = 0) {
-  const int tile_rows = op.tile_rows, pair = op.pair, nb = op.cols >> 8;
+                                           int n_warps, uint32_t tag, const TpExchange* tpx = nullptr, int which = 0,
+                                           SubProf sp = SubProf{nullptr, 0}) {
+  sp.last = clock64();
+  const int tile_rows = op.tile_rows, pair = op.pair, nb = op.cols >> 8, ll = op.ll;
   int c0, c1;
-  cta_rows(op.span_rows, c0, c1);
+  op_cta_rows(op, c0, c1);
   const int lane = threadIdx.x & 31;
   const int mats = pair ? 2 : 1;
   const int tstride = nb | 1;  // odd, so the lane-parallel reads of the flush spread over the banks
   int cap = WARP_TERMS_FLOATS / (tstride * mats);
   cap = cap > (pair ? 16 : 32) ? (pair ? 16 : 32) : cap;
   const uint32_t sxa = smem_addr(sx);
+  const bool accum_ll = !pair && ll && op.epilogue == EPI_ACCUM && !(TP && tpx);
   YCache yc;
   yc.lay = YL_NONE;
   yc.g0 = -1;
-  // Old residual values of the first batch of rows, asked for before the first tile arrives.
-  float old_pref = 0.0f;
-  const bool pref = !pair && op.ll && op.epilogue == EPI_ACCUM && !(TP && tpx) && op.nseg == 1;
-  if (pref) {
-    const int r = c0 + warp + lane * n_warps;
-    if (lane < cap && r < c1) old_pref = ll_value(reinterpret_cast<const LLWord*>(op.seg[0].out) + r);
-  }
-  int pend = 0, pend_u0 = 0, batch = 0;
-  for (int t0 = c0; t0 < c1; t0 += tile_rows) {
-    if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
-    const int t1 = min(t0 + tile_rows, c1);
-    const uint32_t stage = smem_addr(R.stages + (size_t)cp.st * R.stage_bytes);
-    const int lo = t0 - c0, hi = t1 - c0;  // this tile's units, CTA-relative
-    int u = lo + (warp - lo % n_warps + n_warps) % n_warps;
-    if (u < hi) {
-      TilePart parts[3];
-      const int np = op_tile_parts(op, t0, t1, parts);
-      for (; u < hi; u += n_warps) {
-        if (pend == 0) pend_u0 = u;
-        const int lr0 = u - lo;  // row inside the tile
-        float* tdst = wterms + pend * mats * tstride;
-        int pi = 0, lr = lr0;
-        if (!pair) {
-          while (pi < np - 1 && lr >= parts[pi].rows) {
-            lr -= parts[pi].rows;
-            pi++;
-          }
-        }
+  int pend = 0;
+  float* my_out = nullptr;
+  float my_old = 0.0f;
+  const int n_tiles = (c1 - c0 + tile_rows - 1) / tile_rows;
 #pragma unroll 1
-        for (int mt = 0; mt < mats; mt++) {
-          const TilePart& tp = parts[pair ? mt : pi];
-          const uint32_t row = stage + tp.soff + ((uint32_t)(uintptr_t)tp.src & 15u) + (uint32_t)lr * op.row_bytes[tp.seg];
-          warp_row_terms(op.seg[tp.seg].kind, row, sxa, nb, yc, tdst + mt * tstride);
+  for (int tile = 0; tile < n_tiles; tile++) {
+    sp.mark(18);
+    if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
+    sp.mark(25);
+    const TileDesc& D = R.desc[cp.st];
+    const int n_units = D.n_units;
+#pragma unroll 1
+    for (int i = D.first[warp]; i < n_units; i += n_warps) {
+      const TileUnit U = D.unit[i];
+      if (lane == pend) {
+        // this lane will finish the unit: note where its result goes
+        my_out = U.out;
+        if (accum_ll) my_old = ll_value(reinterpret_cast<const LLWord*>(my_out));
+      }
+      float* const tdst = wterms + pend * mats * tstride;
+      const int kind = (int)(U.row[0] >> 24);
+      sp.mark(18);
+      if (pair) {
+#if MEGA_PAIR_INTERLEAVE
+        const uint32_t rows2[2] = {U.row[0] & 0xFFFFFFu, U.row[1] & 0xFFFFFFu};
+        float* const t2[2] = {tdst, tdst + tstride};
+        warp_rows_terms<2>(kind, rows2, sxa, nb, yc, t2);
+#else
+#pragma unroll 1
+        for (int mt = 0; mt < 2; mt++) {
+          const uint32_t rows1[1] = {U.row[mt] & 0xFFFFFFu};
+          float* const t1[1] = {tdst + mt * tstride};
+          warp_rows_terms<1>(kind, rows1, sxa, nb, yc, t1);
         }
-        if (++pend == cap) {
-          warp_flush<TP>(op, wterms, pend, pend_u0, n_warps, c0, nb, tstride, tag, tpx, which, old_pref, pref && batch == 0);
-          pend = 0;
-          batch++;
-        }
+#endif
+      } else {
+        const uint32_t rows1[1] = {U.row[0] & 0xFFFFFFu};
+        float* const t1[1] = {tdst};
+        warp_rows_terms<1>(kind, rows1, sxa, nb, yc, t1);
+      }
+      sp.mark(27);
+      if (++pend == cap) {
+        warp_flush<TP>(op, wterms, pend, nb, tstride, tag, tpx, which, my_out, my_old);
+        pend = 0;
+        sp.mark(30);
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&R.empty[cp.st]);
     cp.advance(R.n_stages);
   }
-  if (pend) warp_flush<TP>(op, wterms, pend, pend_u0, n_warps, c0, nb, tstride, tag, tpx, which, old_pref, pref && batch == 0);
+  sp.mark(18);
+  if (pend) warp_flush<TP>(op, wterms, pend, nb, tstride, tag, tpx, which, my_out, my_old);
+  sp.mark(30);
 }
 
 // ---- grid-wide barrier for the consumer warps ---------------------------------------------
@@ -446,9 +541,9 @@ __device__ __forceinline__ float red_sum(const float* red, int nw) {
 }
 
 // quant.rs:248-283 for the 256 values a warp holds (lane l: elements 8l..8l+7), written as
-// a block image. Out of line: the step uses it from three places.
-__device__ __noinline__ void quantize_block_call(float v0, float v1, float v2, float v3, float v4, float v5, float v6, float v7,
-                                                 uint8_t* dst) {
+// a block image.
+__device__ __forceinline__ void quantize_block_call(float v0, float v1, float v2, float v3, float v4, float v5, float v6, float v7,
+                                                    uint8_t* dst) {
   const float v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
   warp_quantize_q8k_vals(v, dst, 1);
 }
@@ -457,46 +552,51 @@ __device__ __noinline__ void quantize_block_call(float v0, float v1, float v2, f
 // `src` holds tagged words other CTAs publish under `tag`; for the embedding the row is
 // already in scr[0..n). `mirror`, when given, receives a plain copy of the row. The warp
 // that owns a super-block keeps its 256 values in registers from the load to the quantized
-// image (n <= 256 * warps).
+// image (at most two super-blocks per warp: n <= 512 * warps).
 __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag, bool src_in_scr, float* mirror, const float* w,
                                                  int n, float eps, int fast, const MegaSmem& M, const CtaGroup& g,
-                                                 SubProf sp = SubProf{nullptr, 0}) {
+                                                 SubProf sp = SubProf{nullptr, 0}, unsigned long long* walker_prof = nullptr) {
   sp.last = clock64();
   float* row = M.scr;
   float* sq = M.scr + n;
   const int warp = g.tid >> 5, nw = g.nthreads >> 5, lane = g.tid & 31, nblk = n >> 8;
-  const bool mine = warp < nblk;
-  const int e0 = warp * 256 + 8 * lane;
-  float v[8];
+  float v[2][8];
+  float4 w0[2], w1[2];
   float part = 0.0f;
-  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
-  if (mine) {
-    // the norm weights are requested before the wait on the row
-    w0 = __ldg(reinterpret_cast<const float4*>(w + e0));
-    w1 = __ldg(reinterpret_cast<const float4*>(w + e0) + 1);
-    if (src_in_scr) {
-      const float4 a0 = *reinterpret_cast<const float4*>(row + e0), a1 = *reinterpret_cast<const float4*>(row + e0 + 4);
-      v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w;
-      v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
-    } else {
-      // all eight words are requested before the first one is examined
-      const LLWord* p = src + e0;
-      LLWord wd[8];
 #pragma unroll
-      for (int i = 0; i < 4; i++) ll_load2(p + 2 * i, wd[2 * i], wd[2 * i + 1]);
-#pragma unroll
-      for (int i = 0; i < 8; i++) v[i] = ll_settle(p + i, wd[i], tag, M.abort, M.err);
+  for (int k = 0; k < 2; k++) {
+    const int b = warp + k * nw;
+    if (b < nblk) {
+      // the norm weights are requested before the wait on the row
+      w0[k] = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane));
+      w1[k] = __ldg(reinterpret_cast<const float4*>(w + b * 256 + 8 * lane) + 1);
     }
-    if (mirror) {
-      *reinterpret_cast<float4*>(mirror + e0) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(mirror + e0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
-    }
-    if (fast & FAST_NORM_SUM) {
+  }
 #pragma unroll
-      for (int i = 0; i < 8; i++) part = fadd(part, fmul(v[i], v[i]));
-    } else {
-      *reinterpret_cast<float4*>(sq + e0) = make_float4(fmul(v[0], v[0]), fmul(v[1], v[1]), fmul(v[2], v[2]), fmul(v[3], v[3]));
-      *reinterpret_cast<float4*>(sq + e0 + 4) = make_float4(fmul(v[4], v[4]), fmul(v[5], v[5]), fmul(v[6], v[6]), fmul(v[7], v[7]));
+  for (int k = 0; k < 2; k++) {
+    const int b = warp + k * nw;
+    if (b < nblk) {
+      const int e0 = b * 256 + 8 * lane;
+      if (src_in_scr) {
+        const float4 a0 = *reinterpret_cast<const float4*>(row + e0), a1 = *reinterpret_cast<const float4*>(row + e0 + 4);
+        v[k][0] = a0.x; v[k][1] = a0.y; v[k][2] = a0.z; v[k][3] = a0.w;
+        v[k][4] = a1.x; v[k][5] = a1.y; v[k][6] = a1.z; v[k][7] = a1.w;
+      } else {
+        ll_wait8(src + e0, tag, v[k], M.abort, M.err);
+      }
+      if (mirror) {
+        *reinterpret_cast<float4*>(mirror + e0) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+        *reinterpret_cast<float4*>(mirror + e0 + 4) = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
+      }
+      if (fast & FAST_NORM_SUM) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) part = fadd(part, fmul(v[k][i], v[k][i]));
+      } else {
+        *reinterpret_cast<float4*>(sq + e0) =
+            make_float4(fmul(v[k][0], v[k][0]), fmul(v[k][1], v[k][1]), fmul(v[k][2], v[k][2]), fmul(v[k][3], v[k][3]));
+        *reinterpret_cast<float4*>(sq + e0 + 4) =
+            make_float4(fmul(v[k][4], v[k][4]), fmul(v[k][5], v[k][5]), fmul(v[k][6], v[k][6]), fmul(v[k][7], v[k][7]));
+      }
     }
   }
   sp.mark(16);
@@ -508,31 +608,29 @@ __device__ __forceinline__ void phase_norm_quant(const LLWord* src, uint32_t tag
     g.sync();
     ss = red_sum(M.red, nw);
   } else {
-    ss = group_seq_sum_call(sq, n, M.ss, g.tid, g.nthreads, g.bar_id, sp.prof);  // opens with a barrier
+    ss = group_seq_sum_call(sq, n, M.ss, g.tid, g.nthreads, g.bar_id, walker_prof ? walker_prof : sp.prof);  // opens with a barrier
     sp.last = clock64();
   }
   sp.mark(17);
-  if (mine) {
-    const float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
-    quantize_block_call(fmul(fmul(v[0], r), w0.x), fmul(fmul(v[1], r), w0.y), fmul(fmul(v[2], r), w0.z), fmul(fmul(v[3], r), w0.w),
-                        fmul(fmul(v[4], r), w1.x), fmul(fmul(v[5], r), w1.y), fmul(fmul(v[6], r), w1.z), fmul(fmul(v[7], r), w1.w),
-                        M.sx + warp * XK_STRIDE);
+  const float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)n), eps)));
+#pragma unroll
+  for (int k = 0; k < 2; k++) {
+    const int b = warp + k * nw;
+    if (b < nblk)
+      quantize_block_call(fmul(fmul(v[k][0], r), w0[k].x), fmul(fmul(v[k][1], r), w0[k].y), fmul(fmul(v[k][2], r), w0[k].z),
+                          fmul(fmul(v[k][3], r), w0[k].w), fmul(fmul(v[k][4], r), w1[k].x), fmul(fmul(v[k][5], r), w1[k].y),
+                          fmul(fmul(v[k][6], r), w1[k].z), fmul(fmul(v[k][7], r), w1[k].w), M.sx + b * XK_STRIDE);
   }
   g.sync();
   sp.mark(19);
 }
 
 // A vector other CTAs publish under `tag` -> Q8_K images.
-__device__ __noinline__ void phase_quant(const LLWord* src, uint32_t tag, int n, const MegaSmem& M, const CtaGroup& g) {
+__device__ __forceinline__ void phase_quant(const LLWord* src, uint32_t tag, int n, const MegaSmem& M, const CtaGroup& g) {
   const int warp = g.tid >> 5, nw = g.nthreads >> 5, lane = g.tid & 31;
   for (int b = warp; b < n / 256; b += nw) {
-    const LLWord* p = src + b * 256 + 8 * lane;
-    LLWord wd[8];
-#pragma unroll
-    for (int i = 0; i < 4; i++) ll_load2(p + 2 * i, wd[2 * i], wd[2 * i + 1]);
     float v[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = ll_settle(p + i, wd[i], tag, M.abort, M.err);
+    ll_wait8(src + b * 256 + 8 * lane, tag, v, M.abort, M.err);
     quantize_block_call(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], M.sx + b * XK_STRIDE);
   }
   g.sync();
@@ -558,7 +656,7 @@ __device__ __forceinline__ void stage_kv_rows(float* buf, int stride, const floa
 // sequential sums go through the chunked algorithm of groupsum.cuh; up to SEQ_CHAIN_MAX
 // terms one thread's plain add chain (4 cycles per term) is quicker than its set-up.
 constexpr int SEQ_CHAIN_MAX = 256;
-__device__ __noinline__ float cta_sum(const float* p, int n, bool tree, const MegaSmem& M, const CtaGroup& g) {
+__device__ __forceinline__ float cta_sum(const float* p, int n, bool tree, const MegaSmem& M, const CtaGroup& g) {
   if (!tree && n > SEQ_CHAIN_MAX) return group_seq_sum_call(p, n, M.ss, g.tid, g.nthreads, g.bar_id, nullptr);
   g.sync();
   if (tree) {
@@ -588,7 +686,7 @@ __device__ __noinline__ float cta_sum(const float* p, int n, bool tree, const Me
 // Softmax over sc[0..n) in place (ops.rs:98-112): `lmax` is this thread's maximum of the
 // scores it wrote. Ends with the scaled values written; callers put a barrier before
 // other threads read them.
-__device__ __noinline__ void softmax_rows(float* sc, int n, float lmax, int fast, const MegaSmem& M, const CtaGroup& g) {
+__device__ __forceinline__ void softmax_rows(float* sc, int n, float lmax, int fast, const MegaSmem& M, const CtaGroup& g) {
   const int tid = g.tid, T = g.nthreads;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
@@ -645,7 +743,7 @@ __device__ __forceinline__ float qk_dot(const float4* qt, KChunk kchunk, int hd4
 // being decoded): K rows first, then V rows, hd floats each; the 16-byte chunks of K row t
 // are stored at chunk index j ^ (t & 7) so that threads reading different rows hit
 // different banks. Returns false, and stages nothing, when the rows do not fit.
-__device__ __noinline__ bool attn_stage_early(const StepParams& P, int li, int h, int pos, float* stg, int tid, int nthreads) {
+__device__ __forceinline__ bool attn_stage_early(const StepParams& P, int li, int h, int pos, float* stg, int tid, int nthreads) {
   const int hd = P.head_dim, n = pos + 1;
   if ((size_t)2 * n * hd > (size_t)P.stage_floats) return false;
   const int kvd = P.n_kv_head * hd, kvh = h / (P.n_head / P.n_kv_head), hd4 = hd >> 2;
@@ -671,7 +769,7 @@ __device__ __noinline__ bool attn_stage_early(const StepParams& P, int li, int h
 // (contexts whose rows do not fit the staging area): cached K rows are staged in chunks,
 // double buffered, rows padded by one float4 to spread the banks; then the softmax; then
 // the V rows the same way. q, k, v of the token being decoded are in sq, sk, sv.
-__device__ __noinline__ void attention_chunked(const StepParams& P, int li, int h, int pos, uint32_t tag_out, const MegaSmem& M,
+__device__ __forceinline__ void attention_chunked(const StepParams& P, int li, int h, int pos, uint32_t tag_out, const MegaSmem& M,
                                                int tid, int T) {
   const CtaGroup g{tid, T, 1};
   const int hd = P.head_dim, kvd = P.n_kv_head * hd, kvh = h / (P.n_head / P.n_kv_head), n = pos + 1, hd4 = hd >> 2;
@@ -731,7 +829,7 @@ __device__ __noinline__ void attention_chunked(const StepParams& P, int li, int 
 // Per-head q/k norm, RoPE, KV store and attention for head `h` (ops.rs:74-87, 40-70,
 // 152-157, 185-218), by the consumer warps of one CTA. `staged`: attn_stage_early has put
 // the cached rows of this head into the staging area.
-__device__ __noinline__ void phase_attention(const StepParams& P, int li, int h, int pos, uint32_t tag_in, uint32_t tag_out, bool staged,
+__device__ __forceinline__ void phase_attention(const StepParams& P, int li, int h, int pos, uint32_t tag_in, uint32_t tag_out, bool staged,
                                              const MegaSmem& M, int tid, int T, unsigned long long* prof) {
   const CtaGroup g{tid, T, 1};
   SubProf pf{prof, clock64()};
@@ -869,12 +967,10 @@ __device__ void phase_argmax(const StepParams& P, const MegaSmem& M, const CtaGr
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
-#ifndef MEGA_THREADS_N
-#define MEGA_THREADS_N 768
-#endif
+
 constexpr int MEGA_THREADS = MEGA_THREADS_N;
 constexpr int MEGA_CONSUMER_WARPS = MEGA_THREADS / 32 - 1;
-constexpr int MEGA_BAR_BYTES = 128;     // up to 8 stages x (full, empty)
+constexpr int MEGA_BAR_BYTES = 128 + 8 * 608;  // up to 8 stages x (full, empty), then their tile descriptors
 // Bytes of shared memory besides the ring stages, the activation images and the scratch.
 // Block-term strips of the consumer warps. Between products the same bytes hold the
 // records of the exact sequential sums (norm and softmax phases never overlap a product).
@@ -915,6 +1011,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   R.stages = stages;
   R.full = bars;
   R.empty = bars + P.n_stages;
+  R.desc = reinterpret_cast<TileDesc*>(bars + 16);
   R.n_stages = P.n_stages;
   R.stage_bytes = P.stage_bytes;
   R.abort = abort;
@@ -942,16 +1039,14 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   }
 
   if (warp == MEGA_CONSUMER_WARPS) {
-    // ---- producer warp: one thread walks every matrix product of the step ----
-    if ((threadIdx.x & 31) == 0) {
-      RingPos pp{0, 0u};
-      for (int li = 0; li < P.n_layer && !*abort; li++) {
-        const StepLayer& L = table[li];
+    // ---- producer warp: walks every matrix product of the step ----
+    RingPos pp{0, 0u};
+    for (int li = 0; li < P.n_layer && !*abort; li++) {
+      const StepLayer& L = table[li];
 #pragma unroll 1
-        for (int ph = 0; ph < 4; ph++) produce_op((&L.qkv)[ph], R, pp);  // qkv, wo, gu, down are consecutive members
-      }
-      if (P.want_logits && !*abort) produce_op(table[P.n_layer].qkv, R, pp);
+      for (int ph = 0; ph < 4; ph++) produce_op((&L.qkv)[ph], R, pp, MEGA_CONSUMER_WARPS);  // qkv, wo, gu, down are consecutive members
     }
+    if (P.want_logits && !*abort) produce_op(table[P.n_layer].qkv, R, pp, MEGA_CONSUMER_WARPS);
     return;
   }
 
@@ -967,8 +1062,14 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   const uint32_t tag_base = *P.epoch << 10;
   const bool prof_on = P.prof && (int)blockIdx.x == P.prof_cta && g.tid == 0;
   long long prof_last = clock64();
+  int prof_li = -1;  // layer the phase marks belong to
 #define MEGA_PROF(slot)                                 \
   do {                                                  \
+    if (P.timeline && g.tid == 0 && prof_li == P.timeline_layer) {      \
+      unsigned long long t_;                            \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+      P.timeline[blockIdx.x * 16 + (slot)] = t_;        \
+    }                                                   \
     if (prof_on) {                                      \
       long long now_ = clock64();                       \
       atomicAdd(&P.prof[slot], (unsigned long long)(now_ - prof_last)); \
@@ -999,6 +1100,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   for (int st = 0; st < n_stage; st++) {
     const int li = st >> 2, ph = st & 3;
     const bool head = li == P.n_layer;
+    prof_li = li;
     const StepLayer& L = table[li];
     const MegaOp& op = (&L.qkv)[ph];  // qkv, wo, gu, down are consecutive members
     const int slot = ph == 0 ? 1 : 3 * ph + 3;
@@ -1026,7 +1128,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
       const float* w = head ? P.output_norm : (ph == 0 ? L.attn_norm : L.ffn_norm);
       const uint32_t tin = ph == 0 ? tl : tl + 3u;  // residual after the previous layer's down / this layer's wo
       phase_norm_quant(P.xl, tin, st == 0, head && blockIdx.x == 0 ? P.x : nullptr, w, P.dim, P.eps, P.fast, M, g,
-                       SubProf{prof_on && ph == 0 && !head ? P.prof : nullptr, 0});
+                       SubProf{prof_on && ph == 0 && !head ? P.prof : nullptr, 0},
+                       P.prof && (int)blockIdx.x == P.prof_cta && ph == 0 && !head && g.tid == (MEGA_CONSUMER_WARPS - 1) * 32 ? P.prof : nullptr);
     } else {
       // attention output -> wo, activated hidden -> down; both join the residual stream
       if (ph == 1) phase_quant(P.attl, tl + 2u, qd, M, g);
@@ -1036,7 +1139,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     // q/k/v: tl+1, wo: tl+3, gate/up: tl+4, down: tl+5 (the head writes plain floats)
     const uint32_t tag_out = tl + (ph == 0 ? 1u : (uint32_t)ph + 2u);
     const bool exchange = TP && (ph & 1) && !head;
-    consume_op<TP>(op, R, cp, sx, wterms, warp, MEGA_CONSUMER_WARPS, tag_out, exchange ? &P.tp : nullptr, ph >> 1);
+    consume_op<TP>(op, R, cp, sx, wterms, warp, MEGA_CONSUMER_WARPS, tag_out, exchange ? &P.tp : nullptr, ph >> 1,
+                   SubProf{nullptr, 0});
     if (head) break;
     // The next phase rewrites the activation images and the scratch rows; warps that are
     // done must also not start polling while others still compute.
@@ -1118,59 +1222,56 @@ __device__ __forceinline__ void consume_op_q80(const MegaOp& op, const Ring& R, 
                                                int n_warps, int m) {
   const int tile_rows = op.tile_rows, pair = op.pair, epilogue = op.epilogue, nb = op.cols >> 5;
   int c0, c1;
-  cta_rows(op.span_rows, c0, c1);
+  op_cta_rows(op, c0, c1);
   const int lane = threadIdx.x & 31, k = lane & 7, gi = lane >> 3;
   const uint32_t sxa = smem_addr(sx);
   int rot = 0;
-  for (int t0 = c0; t0 < c1; t0 += tile_rows) {
+  const int n_tiles = (c1 - c0 + tile_rows - 1) / tile_rows;
+  for (int tile = 0; tile < n_tiles; tile++) {
     if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
-    const int t1 = min(t0 + tile_rows, c1);
-    const uint32_t stage = smem_addr(R.stages + (size_t)cp.st * R.stage_bytes);
-    const int R_rows = t1 - t0;
+    const TileDesc& D = R.desc[cp.st];
+    const int R_rows = D.n_units;
     const int n_pass = (R_rows + 3) / 4;  // four rows per warp pass
     int ps = warp - rot;
     if (ps < 0) ps += n_warps;
-    if (ps < n_pass) {
-      TilePart parts[3];
-      const int np = op_tile_parts(op, t0, t1, parts);
-      for (; ps < n_pass; ps += n_warps) {
-        const int u = ps * 4 + gi;
-        float v[2] = {0.0f, 0.0f};
-        int pi = 0, lr = u;
-        if (!pair && u < R_rows) {
-          while (pi < np - 1 && lr >= parts[pi].rows) {
-            lr -= parts[pi].rows;
-            pi++;
-          }
+    for (; ps < n_pass; ps += n_warps) {
+      const int u = ps * 4 + gi;
+      float v[2] = {0.0f, 0.0f};
+      int pi = 0, lr = u;
+      if (!pair && u < R_rows) {
+        while (pi < 2 && lr >= D.rows[pi]) {
+          lr -= D.rows[pi];
+          pi++;
         }
-        const int n_mat = pair ? 2 : 1;
-        for (int tok = 0; tok < m; tok++) {
-          const uint32_t sxt = sxa + (uint32_t)tok * (uint32_t)nb * X0_STRIDE;
-          for (int mt = 0; mt < n_mat; mt++) {
-            const TilePart& tp = parts[pair ? mt : pi];
-            const int kind = op.seg[tp.seg].kind;
-            const uint32_t row = stage + tp.soff + ((uint32_t)(uintptr_t)tp.src & 15u) + (uint32_t)(pair ? u : lr) * op.row_bytes[tp.seg];
-            float a = 0.0f;
-            if (u < R_rows) {
-              if (kind == Q4_0) a = row_chain_q80<Q4_0>(row, sxt, nb, k);
-              else if (kind == Q5_0) a = row_chain_q80<Q5_0>(row, sxt, nb, k);
-              else a = row_chain_q80<Q8_0>(row, sxt, nb, k);
-            }
-            // ((a0+a4)+(a2+a6)) + ((a1+a5)+(a3+a7)) over the row's eight lanes
-            a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 4));
-            a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 2));
-            a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 1));
-            v[mt] = a;
+      }
+      const int n_mat = pair ? 2 : 1;
+      for (int tok = 0; tok < m; tok++) {
+        const uint32_t sxt = sxa + (uint32_t)tok * (uint32_t)nb * X0_STRIDE;
+        for (int mt = 0; mt < n_mat; mt++) {
+          const int part = pair ? mt : pi, sg = D.seg[part];
+          const int kind = op.seg[sg].kind;
+          const uint32_t row = D.base[part] + (uint32_t)(pair ? u : lr) * op.row_bytes[sg];
+          float a = 0.0f;
+          if (u < R_rows) {
+            if (kind == Q4_0) a = row_chain_q80<Q4_0>(row, sxt, nb, k);
+            else if (kind == Q5_0) a = row_chain_q80<Q5_0>(row, sxt, nb, k);
+            else a = row_chain_q80<Q8_0>(row, sxt, nb, k);
           }
-          if (u < R_rows && k == 0) {
-            if (pair) {
-              const size_t r = (size_t)tok * op.seg[0].rows + t0 + u;
-              op.seg[0].out[r] = epilogue == EPI_SILU_MUL ? silu_mul_exact(v[0], v[1]) : v[0];
-              op.seg[1].out[r] = v[1];
-            } else {
-              float* o = op.seg[parts[pi].seg].out + (size_t)tok * op.seg[parts[pi].seg].rows + parts[pi].row0 + lr;
-              *o = epilogue == EPI_ACCUM ? fadd(__ldcg(o), v[0]) : v[0];
-            }
+          // ((a0+a4)+(a2+a6)) + ((a1+a5)+(a3+a7)) over the row's eight lanes
+          a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 4));
+          a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 2));
+          a = fadd(a, __shfl_xor_sync(0xffffffffu, a, 1));
+          v[mt] = a;
+        }
+        if (u < R_rows && k == 0) {
+          if (pair) {
+            const size_t r = (size_t)tok * op.seg[0].rows + D.row0[0] + u;
+            op.seg[0].out[r] = epilogue == EPI_SILU_MUL ? silu_mul_exact(v[0], v[1]) : v[0];
+            op.seg[1].out[r] = v[1];
+          } else {
+            const int sg = D.seg[pi];
+            float* o = op.seg[sg].out + (size_t)tok * op.seg[sg].rows + D.row0[pi] + lr;
+            *o = epilogue == EPI_ACCUM ? fadd(__ldcg(o), v[0]) : v[0];
           }
         }
       }
@@ -1211,6 +1312,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   R.stages = stages;
   R.full = bars;
   R.empty = bars + P.n_stages;
+  R.desc = reinterpret_cast<TileDesc*>(bars + 16);
   R.n_stages = P.n_stages;
   R.stage_bytes = P.stage_bytes;
   R.abort = abort;
@@ -1228,10 +1330,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   pdl_launch_dependents();
   if (warp == MEGA_CONSUMER_WARPS) {
     // weights do not depend on the previous kernel: stream them right away
-    if ((threadIdx.x & 31) == 0) {
-      RingPos pp{0, 0u};
-      produce_op(P.op, R, pp);
-    }
+    RingPos pp{0, 0u};
+    produce_op(P.op, R, pp, MEGA_CONSUMER_WARPS);
     return;
   }
   pdl_wait();

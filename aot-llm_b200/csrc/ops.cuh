@@ -50,29 +50,26 @@ __device__ __forceinline__ float block_seq_sum(const float* p, int n, float* slo
 // Core: lane holds elements 8*lane .. 8*lane+7 of the block in v[].
 __device__ __forceinline__ void warp_quantize_q8k_vals(const float (&v)[8], uint8_t* dst, int image) {
   const int lane = threadIdx.x & 31;
-  // signed extreme: first element with strictly larger |v|
-  float amax = 0.0f, mx = 0.0f;
-  int idx = 0;
+  // signed extreme: the first element with strictly larger |v|. |v| orders like its bit
+  // pattern; a NaN never compares larger in the reference and counts as zero here. Two
+  // warp-wide integer reductions find the largest pattern and the first index holding it.
+  uint32_t best = 0;
+  float mx = 0.0f;
+  int idx = 8 * lane;
 #pragma unroll
   for (int i = 0; i < 8; i++) {
-    float a = fabsf(v[i]);
-    if (a > amax) {
-      amax = a;
+    uint32_t a = __float_as_uint(v[i]) & 0x7FFFFFFFu;
+    a = a > 0x7F800000u ? 0u : a;
+    if (a > best) {
+      best = a;
       mx = v[i];
       idx = 8 * lane + i;
     }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    float a2 = __shfl_xor_sync(0xffffffffu, amax, o);
-    float m2 = __shfl_xor_sync(0xffffffffu, mx, o);
-    int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (a2 > amax || (a2 == amax && i2 < idx)) {
-      amax = a2;
-      mx = m2;
-      idx = i2;
-    }
-  }
+  const uint32_t wmax = __reduce_max_sync(0xffffffffu, best);
+  const uint32_t widx = __reduce_min_sync(0xffffffffu, best == wmax ? (uint32_t)idx : 256u);
+  mx = __shfl_sync(0xffffffffu, mx, (int)(widx >> 3));
+  const float amax = __uint_as_float(wmax);
   int8_t* qs = reinterpret_cast<int8_t*>(dst + (image ? 0 : 4));
   int16_t* bs = reinterpret_cast<int16_t*>(dst + (image ? 256 : 260));
   float* dptr = reinterpret_cast<float*>(dst + (image ? 288 : 0));

@@ -86,11 +86,11 @@ __device__ __forceinline__ void yq_load_q6(YQuarter& Y, uint32_t xb, int c) {
   Y.d = __uint_as_float(rd_lds32(xb + XK_D));
 }
 
-// Quarter c of a Q4_K / Q5_K block at shared address wb (16-byte aligned). Returns the two
-// integers of the whole block (matvec.rs:89-103), summed over its four lanes, to all four
-// lanes, and the block's d|dmin word.
+// Quarter c of a Q4_K / Q5_K block at shared address wb (16-byte aligned): this lane's
+// share of the two integers of matvec.rs:89-103 (the four lanes of a block add theirs up
+// with two shuffles), and the block's d|dmin word.
 template <bool Q5>
-__device__ __forceinline__ void quarter_k4_y(uint32_t wb, int c, const YQuarter& Y, int& sumi, int& summ, uint32_t& dd) {
+__device__ __forceinline__ void k4_partial(uint32_t wb, int c, const YQuarter& Y, int& sumi, int& summ, uint32_t& dd) {
   const U4 hdr = rd_lds128(wb);
   dd = hdr.x;
   const uint32_t qs = wb + (Q5 ? 48 : 16) + 32 * c;
@@ -101,42 +101,41 @@ __device__ __forceinline__ void quarter_k4_y(uint32_t wb, int c, const YQuarter&
     h1 = rd_lds128(wb + 32);
   }
   const K4Scales s = k4_unpack(hdr.y, hdr.z, hdr.w);
-  int s_lo = 0, s_hi = 0;
+  // two accumulators per sub-block halve the length of the dp4a chains
+  int lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     const uint32_t w = i < 4 ? u4_get(wa, i) : u4_get(wc, i - 4);
+    int& alo = (i & 1) ? lo1 : lo0;
+    int& ahi = (i & 1) ? hi1 : hi0;
     if (Q5) {
       const uint32_t h = i < 4 ? u4_get(h0, i) : u4_get(h1, i - 4);
       const uint32_t lo = (w & 0x0F0F0F0Fu) | (((h >> (2 * c)) & 0x01010101u) << 4);
       const uint32_t hi = ((w >> 4) & 0x0F0F0F0Fu) | (((h >> (2 * c + 1)) & 0x01010101u) << 4);
-      s_lo = __dp4a((int)lo, (int)Y.y[i], s_lo);
-      s_hi = __dp4a((int)hi, (int)Y.y[8 + i], s_hi);
+      alo = __dp4a((int)lo, (int)Y.y[i], alo);
+      ahi = __dp4a((int)hi, (int)Y.y[8 + i], ahi);
     } else {
       // the high nibbles stay in place (16 x their value, as unsigned bytes); the sum is
       // an exact multiple of 16 and is shifted back below
-      s_lo = __dp4a((int)(w & 0x0F0F0F0Fu), (int)Y.y[i], s_lo);
-      s_hi = dp4a_us(w & 0xF0F0F0F0u, Y.y[8 + i], s_hi);
+      alo = __dp4a((int)(w & 0x0F0F0F0Fu), (int)Y.y[i], alo);
+      ahi = dp4a_us(w & 0xF0F0F0F0u, Y.y[8 + i], ahi);
     }
   }
+  const int s_lo = lo0 + lo1;
+  int s_hi = hi0 + hi1;
   if (!Q5) s_hi >>= 4;
   const uint32_t scw = c < 2 ? s.sc_lo : s.sc_hi, mw = c < 2 ? s.m_lo : s.m_hi;
   const int sh = (c & 1) * 16;
   const int sc0 = (scw >> sh) & 0xFF, sc1 = (scw >> (sh + 8)) & 0xFF;
   const int m0 = (mw >> sh) & 0xFF, m1 = (mw >> (sh + 8)) & 0xFF;
-  int si = sc0 * s_lo + sc1 * s_hi;
-  int sm = m0 * Y.b[0] + m1 * Y.b[1];
-  si += __shfl_xor_sync(0xffffffffu, si, 1);
-  sm += __shfl_xor_sync(0xffffffffu, sm, 1);
-  si += __shfl_xor_sync(0xffffffffu, si, 2);
-  sm += __shfl_xor_sync(0xffffffffu, sm, 2);
-  sumi = si;
-  summ = sm;
+  sumi = sc0 * s_lo + sc1 * s_hi;
+  summ = m0 * Y.b[0] + m1 * Y.b[1];
 }
 
 // Lane c's share of a Q6_K block at shared address wb (2-byte aligned): words come from the
 // 4-byte aligned stream through a funnel shift, four consecutive words from five loads.
-// Returns the block's integer sum (matvec.rs:146-163) to its four lanes and the d half.
-__device__ __forceinline__ int quarter_q6k_y(uint32_t wb, int c, const YQuarter& Y, uint32_t& dbits) {
+// Returns the lane's share of the block's integer sum (matvec.rs:146-163) and the d half.
+__device__ __forceinline__ int q6k_partial(uint32_t wb, int c, const YQuarter& Y, uint32_t& dbits) {
   const uint32_t sh = (wb & 2u) * 8u, p = wb & ~3u;
   auto load4 = [&](int k, uint32_t w[4]) {
     const uint32_t a0 = rd_lds32(p + 4 * k), a1 = rd_lds32(p + 4 * k + 4), a2 = rd_lds32(p + 4 * k + 8),
@@ -173,8 +172,6 @@ __device__ __forceinline__ int quarter_q6k_y(uint32_t wb, int c, const YQuarter&
   const int c3 = (int)(int8_t)((s23 >> (8 * half)) & 0xFF), c4 = (int)(int8_t)((s23 >> (8 * half + 16)) & 0xFF);
   int tot = c1 * a1 + c2 * a2 + c3 * a3 + c4 * a4;
   tot -= 32 * (c1 * Y.b[0] + c2 * Y.b[1] + c3 * Y.b[2] + c4 * Y.b[3]);
-  tot += __shfl_xor_sync(0xffffffffu, tot, 1);
-  tot += __shfl_xor_sync(0xffffffffu, tot, 2);
   return tot;
 }
 
@@ -185,13 +182,17 @@ struct YCache {
   int lay, g0;
 };
 
-// Block terms of one K-quant row: `row` = shared address of the row's first block, `sxa` =
-// shared address of the activation images, nb blocks. terms[b] receives the f32 term of
+// Block terms of NR K-quant rows of the same kind (NR = 2: a gate row and its up row, whose
+// dependent chains interleave): row[r] = shared address of the row's first block, `sxa` =
+// shared address of the activation images, nb blocks. terms[r][b] receives the f32 term of
 // block b. Every lane of the warp calls it; control flow is warp-uniform.
-__device__ __forceinline__ void warp_row_terms(int kind, uint32_t row, uint32_t sxa, int nb, YCache& yc, float* terms) {
+template <int NR>
+__device__ __forceinline__ void warp_rows_terms(int kind, const uint32_t (&row)[NR], uint32_t sxa, int nb, YCache& yc,
+                                                float* const (&terms)[NR]) {
   const int lane = threadIdx.x & 31, bl = lane >> 2, c = lane & 3;
   const int bs = kind_size(kind);
   const int lay = kind == Q6_K ? YL_Q6 : YL_K4;
+#pragma unroll 1
   for (int g0 = 0; g0 < nb; g0 += 8) {
     const int b = g0 + bl;
     // idle lanes recompute the last block so that every lane reaches the shuffles
@@ -202,19 +203,35 @@ __device__ __forceinline__ void warp_row_terms(int kind, uint32_t row, uint32_t 
       yc.lay = lay;
       yc.g0 = g0;
     }
-    const uint32_t wb = row + (uint32_t)bb * bs;
-    float term;
+    int si[NR], sm[NR];
+    uint32_t dd[NR];
     if (kind == Q6_K) {
-      uint32_t dbits;
-      const int si = quarter_q6k_y(wb, c, yc.Y, dbits);
-      term = q6k_term(half_bits_hw(dbits), yc.Y.d, si);
+#pragma unroll
+      for (int r = 0; r < NR; r++) {
+        si[r] = q6k_partial(row[r] + (uint32_t)bb * bs, c, yc.Y, dd[r]);
+        sm[r] = 0;
+      }
+    } else if (kind == Q5_K) {
+#pragma unroll
+      for (int r = 0; r < NR; r++) k4_partial<true>(row[r] + (uint32_t)bb * bs, c, yc.Y, si[r], sm[r], dd[r]);
     } else {
-      int si, sm;
-      uint32_t dd;
-      if (kind == Q5_K) quarter_k4_y<true>(wb, c, yc.Y, si, sm, dd); else quarter_k4_y<false>(wb, c, yc.Y, si, sm, dd);
-      term = k4_term(half_bits_hw(dd & 0xFFFFu), half_bits_hw(dd >> 16), yc.Y.d, si, sm);
+#pragma unroll
+      for (int r = 0; r < NR; r++) k4_partial<false>(row[r] + (uint32_t)bb * bs, c, yc.Y, si[r], sm[r], dd[r]);
     }
-    if (c == 0 && b < nb) terms[b] = term;
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+#pragma unroll
+      for (int r = 0; r < NR; r++) {
+        si[r] += __shfl_xor_sync(0xffffffffu, si[r], o);
+        if (kind != Q6_K) sm[r] += __shfl_xor_sync(0xffffffffu, sm[r], o);
+      }
+    }
+    if (c == 0 && b < nb) {
+#pragma unroll
+      for (int r = 0; r < NR; r++)
+        terms[r][b] = kind == Q6_K ? q6k_term(half_bits_hw(dd[r]), yc.Y.d, si[r])
+                                   : k4_term(half_bits_hw(dd[r] & 0xFFFFu), half_bits_hw(dd[r] >> 16), yc.Y.d, si[r], sm[r]);
+    }
   }
 }
 

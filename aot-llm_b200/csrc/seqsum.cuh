@@ -16,6 +16,7 @@
 // grid), and the scan restarts from there. Ties, subnormals, zeros and overflow
 // to infinity follow the same rules as the scalar loop.
 #pragma once
+#include <stdint.h>
 #include "blockmath.cuh"
 
 namespace aot {
@@ -78,66 +79,88 @@ AOT_HD SumFn sumfn_elem(uint32_t p_bits, int e) {
 // The device routine (groupsum.cuh) cuts the terms into chunks of SEQ_E consecutive terms,
 // one chunk per lane, 32 chunks per group. From an inexact prefix sum it predicts the
 // exponent field with which the running sum enters each chunk. A chunk whose predicted
-// sum changes binade inside it is "slow": its terms will be added one by one with real
-// f32 adds. Every other chunk gets the composite function of its terms for its predicted
-// exponent, and consecutive fast chunks with the same predicted exponent form a run
-// whose composite is built by a segmented scan. One thread then walks the records below:
-// a run is applied in one step when the running sum really has the predicted exponent
-// and stays inside the binade, and is otherwise added term by term. Predictions decide
-// only which path is taken, never the result.
+// sum changes binade inside it, or that holds an exact tie or a term as large as the
+// binade, is "slow": its terms will be added one by one with real f32 adds. Every other
+// chunk gets the integer by which its terms advance the mantissa for its predicted
+// exponent, and consecutive fast chunks with the same predicted exponent form a run whose
+// increment is built by a segmented scan. The result is a short list of items per group,
+// in term order; one thread walks it: an item is applied in one step when the running sum
+// really has the predicted exponent and stays inside the binade, and is otherwise added
+// term by term. Predictions decide only which path is taken, never the result. The first
+// SEQ_HEAD terms, where the sum changes binade every few terms, are one plain add chain.
 constexpr int SEQ_E = 8;         // terms per chunk
 constexpr int SEQ_CHUNKS = 256;  // chunks per pass (2048 terms)
+constexpr int SEQ_HEAD = 64;     // terms of the opening add chain (a multiple of SEQ_E)
 
-struct SeqSumScratch {
-  int a0[SEQ_CHUNKS];               // composite of the run of fast chunks that ends at this chunk, even start ...
-  int a1[SEQ_CHUNKS];               // ... odd start
-  int ep[SEQ_CHUNKS];               // predicted exponent field at the chunk's start
-  uint32_t slow[SEQ_CHUNKS / 32];   // per group: chunks handled term by term
-  uint32_t start[SEQ_CHUNKS / 32];  // per group: chunks at which a run starts
-  float gtot[SEQ_CHUNKS / 32];      // inexact sum of each group
-  float s;                          // running and final sum
+struct SeqItem {
+  int csum;   // mantissa increment of the whole item for exponent field ep
+  int ep;     // predicted exponent field at the item's start; -1: add term by term
+  int first;  // index of the item's first term inside the pass
+  int count;  // terms
 };
 
-AOT_HD int seq_ffs(uint32_t v) {  // index of the lowest set bit, v != 0
-#if AOT_DEVICE_CODE
-  return __ffs((int)v) - 1;
-#else
-  return __builtin_ctz(v);
-#endif
+struct SeqSumScratch {
+  SeqItem item[SEQ_CHUNKS];        // group g's items start at item[32 g]
+  int n_items[SEQ_CHUNKS / 32];
+  float gtot[SEQ_CHUNKS / 32];     // inexact sum of each group
+  float excl[SEQ_CHUNKS];          // inexact sum of the group's chunks before this one
+  float s;                         // running and final sum
+  float head;                      // sum of the opening chain
+};
+
+// Mantissa increment of adding p (bit pattern, non-negative) while the sum has exponent
+// field e, without branches. `bad` is set when the add cannot be an integer step: p is as
+// large as the binade, or the dropped bits are an exact tie.
+AOT_HD int seq_increment(uint32_t bits, int e, bool& bad) {
+  int pe = (int)(bits >> 23);
+  const uint32_t pm = (bits & 0x7FFFFFu) | (pe ? 0x800000u : 0u);
+  pe = pe ? pe : 1;
+  const int sh = e - pe;
+  const int shc = sh < 1 ? 1 : (sh > 25 ? 25 : sh);
+  const uint32_t y = pm >> shc, r = pm & ((1u << shc) - 1u), half = 1u << (shc - 1);
+  bad = bad || (sh < 1 && bits != 0u) || (r == half && pm != 0u);
+  return (int)(y + (r > half ? 1u : 0u));
 }
 
-// Terms p[0..len) of one pass, `nch` chunks, records in `sc`; returns start + the terms,
-// rounded as the scalar loop rounds.
-AOT_HD float seqsum_walk(const float* p, int len, const SeqSumScratch* sc, int nch, float start) {
-  int e, m;
-  sum_decompose(f2u(start) & 0x7FFFFFFFu, e, m);
-  for (int c0 = 0; c0 < nch; c0 += 32) {
-    const int gr = c0 >> 5, lanes = nch - c0 < 32 ? nch - c0 : 32;
-    const uint32_t slow = sc->slow[gr], bounds = slow | sc->start[gr];
-    int lane = 0;
-    while (lane < lanes) {
-      int end;  // one past the last chunk of this step
-      bool by_terms = (slow >> lane) & 1u;
-      if (by_terms) {
-        end = lane + 1;
+// Items of one pass in order -> start + the terms p[0..), rounded as the scalar loop rounds.
+// The running sum is kept as its bit pattern: for a normal float, adding an integer to the
+// pattern adds it to the mantissa, and the sum has left the binade exactly when the
+// exponent field changes. The next item is fetched while the current one is applied.
+AOT_HD float seqsum_walk(const float* p, const SeqSumScratch* sc, int n_groups, float start) {
+  uint32_t bits = f2u(start) & 0x7FFFFFFFu;
+  for (int g = 0; g < n_groups; g++) {
+    const int cnt = sc->n_items[g];
+    const SeqItem* items = sc->item + 32 * g;
+    SeqItem nxt = items[0];
+    for (int k = 0; k < cnt; k++) {
+      const SeqItem it = nxt;
+      if (k + 1 < cnt) nxt = items[k + 1];
+      // ep >= 2: the pattern arithmetic needs a normal sum (the lowest binade, which
+      // includes the subnormals, goes term by term)
+      const uint32_t nb = bits + (uint32_t)it.csum;
+      if (it.ep >= 2 && (int)(bits >> 23) == it.ep && (int)(nb >> 23) == it.ep) {
+        bits = nb;
+        continue;
+      }
+      float s = u2f(bits);
+      const float* q = p + it.first;
+      if (it.count == SEQ_E) {
+        const float a0 = q[0], a1 = q[1], a2 = q[2], a3 = q[3], a4 = q[4], a5 = q[5], a6 = q[6], a7 = q[7];
+        s = fadd(s, a0);
+        s = fadd(s, a1);
+        s = fadd(s, a2);
+        s = fadd(s, a3);
+        s = fadd(s, a4);
+        s = fadd(s, a5);
+        s = fadd(s, a6);
+        s = fadd(s, a7);
       } else {
-        const uint32_t above = lane >= 31 ? 0u : (bounds >> (lane + 1)) << (lane + 1);
-        end = above ? seq_ffs(above) : 32;
-        if (end > lanes) end = lanes;
-        const int last = c0 + end - 1;
-        const int m2 = m + ((m & 1) ? sc->a1[last] : sc->a0[last]);
-        if (e < 255 && sc->ep[c0 + lane] == e && m2 < SUMFN_LIMIT) m = m2; else by_terms = true;
+        for (int i = 0; i < it.count; i++) s = fadd(s, q[i]);
       }
-      if (by_terms) {
-        float s = u2f(sum_pack(e, m));
-        const int i1 = (c0 + end) * SEQ_E < len ? (c0 + end) * SEQ_E : len;
-        for (int i = (c0 + lane) * SEQ_E; i < i1; i++) s = fadd(s, p[i]);
-        sum_decompose(f2u(s) & 0x7FFFFFFFu, e, m);
-      }
-      lane = end;
+      bits = f2u(s) & 0x7FFFFFFFu;
     }
   }
-  return u2f(sum_pack(e, m));
+  return u2f(bits);
 }
 
 // Exponent field used for predictions: that of sum_decompose, 255 for anything not finite.
@@ -145,13 +168,6 @@ AOT_HD int seq_exp_field(float v) {
   const uint32_t b = f2u(v) & 0x7FFFFFFFu;
   const int e = (int)(b >> 23);
   return e == 0 ? 1 : e;
-}
-
-// Composite of the (up to SEQ_E) terms of one chunk for exponent field e.
-AOT_HD SumFn seq_chunk_fn(const float* v, int cnt, int e) {
-  SumFn f = sumfn_identity();
-  for (int j = 0; j < cnt; j++) f = sumfn_compose(f, sumfn_elem(f2u(v[j]) & 0x7FFFFFFFu, e));
-  return f;
 }
 
 }  // namespace aot

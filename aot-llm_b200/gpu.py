@@ -331,6 +331,13 @@ class Gpu:
         check(L.load().aotcu_gpu_profile_step(self.h, token, pos, cta, ptr(out)))
         return out
 
+    def timeline_step(self, token: int, pos: int, layer: int) -> np.ndarray:
+        """[n_cta, 16] device-timer nanoseconds at which each CTA left each phase of `layer`."""
+        out = np.zeros(16 * 256, dtype=np.uint64)
+        n = C.c_int(0)
+        check(L.load().aotcu_gpu_timeline_step(self.h, token, pos, layer, ptr(out), C.byref(n)))
+        return out.reshape(256, 16)[: n.value]
+
     def dispatches(self) -> int:
         return L.load().aotcu_gpu_dispatches(self.h)
 

@@ -142,6 +142,7 @@ SYMBOLS = {
     "aotcu_tp_attach": (_i, [_vp, C.c_char_p, _i, _i, _vp, _vp]),
     "aotcu_bench_matmul": (_i, [_vp, _i, _vp, _vp, _sz, _sz, _vp, _sz, _sz, _sz, _i, C.POINTER(_f)]),
     "aotcu_gpu_profile_step": (_i, [_vp, _u32, _sz, _i, _vp]),
+    "aotcu_gpu_timeline_step": (_i, [_vp, _u32, _sz, _i, _vp, _vp]),
     "aotcu_synth_quantize_row": (_i, [_i, _vp, _sz, _vp]),
     "aotcu_synth_tensor": (_i, [_i, _sz, _sz, _f, _f, C.c_uint64, _vp]),
     "aotcu_synth_blocks": (_i, [_i, _sz, C.c_uint64, _vp]),

@@ -314,6 +314,12 @@ int aotcu_bench_matmul(aotcu_ctx* ctx, int kind, float* out, const uint8_t* w, s
  * one step and returns the SM cycles CTA `cta` spent in each of its 16 phases
  * (slots 16..31: sub-phases of the first norm and of attention). */
 int aotcu_gpu_profile_step(aotcu_gpu* g, uint32_t token, size_t pos, int cta, uint64_t out[32]);
+/* The same step with a global timestamp per CTA at each phase boundary of one layer:
+   out[cta * 16 + k] = nanoseconds (device global timer) at which CTA `cta` left phase k
+   of layer `layer` (k as in aotcu_gpu_profile_step; unused slots stay 0). `n_cta`
+   receives the grid size; out must hold 16 * 256 values. Shows which CTAs the others
+   wait for. */
+int aotcu_gpu_timeline_step(aotcu_gpu* g, uint32_t token, size_t pos, int layer, uint64_t* out, int* n_cta);
 
 /* ---- synthetic test data (the encoders of crates/aot-kernels/src/quantize.rs) */
 /* quantize_row (quantize.rs:16-294): encodes n floats as one row of `kind` into

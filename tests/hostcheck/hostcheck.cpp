@@ -167,52 +167,76 @@ float hc_seqsum(const float* p, size_t n, int T, int head, int* rounds) {
 }
 
 
-// Mirror of the device routine (groupsum.cuh): chunks of SEQ_E terms, 32 chunks per
-// group, exponents predicted from an inexact prefix sum (`skew` perturbs it, to provoke
-// wrong predictions), composites of runs of fast chunks, then the walk shared with the
-// device (seqsum_walk). *slow_chunks receives the number of chunks marked slow.
+// Mirror of the device routine (groupsum.cuh): the opening add chain, chunks of SEQ_E
+// terms, 32 chunks per group, exponents predicted from an inexact prefix sum (`skew`
+// perturbs it, to provoke wrong predictions), integer increments of runs of fast chunks,
+// item lists, then the walk shared with the device (seqsum_walk). *slow_chunks receives
+// the number of chunks marked slow.
 float hc_seqsum_runs(const float* p, size_t n, float skew, int* slow_chunks) {
   static SeqSumScratch sc;
-  float total = 0.0f;
   int n_slow = 0;
+  if (n <= (size_t)SEQ_HEAD) {
+    float s = 0.0f;
+    for (size_t i = 0; i < n; i++) s = fadd(s, p[i]);
+    if (slow_chunks) *slow_chunks = 0;
+    return s;
+  }
+  float total = 0.0f;
+  for (int i = 0; i < SEQ_HEAD; i++) total = fadd(total, p[i]);
+  float approx = 0.0f;
   for (size_t base = 0; base < n; base += (size_t)SEQ_CHUNKS * SEQ_E) {
-    const int len = (int)std::min(n - base, (size_t)SEQ_CHUNKS * SEQ_E), nch = (len + SEQ_E - 1) / SEQ_E;
-    float before = total * skew;
-    for (int c0 = 0; c0 < nch; c0 += 32) {
-      uint32_t slow_mask = 0, start_mask = 0;
-      int eb_prev = 0;
-      bool slow_prev = false;
-      SumFn run = sumfn_identity();
+    const int len = (int)std::min(n - base, (size_t)SEQ_CHUNKS * SEQ_E), nch = (len + SEQ_E - 1) / SEQ_E, ngr = (nch + 31) / 32;
+    float before = approx * skew;
+    for (int gr = 0; gr < ngr; gr++) {
+      const int head_lanes = base == 0 && gr == 0 ? SEQ_HEAD / SEQ_E : 0;
+      int n_items = 0, eb_prev = 0, run_inc = 0, run_ep = 0, run_first = 0;
+      bool slow_prev = false, in_run = false;
+      auto close_run = [&](int end_elem) {
+        if (!in_run) return;
+        sc.item[32 * gr + n_items++] = SeqItem{run_inc, run_ep, run_first, std::max(0, std::min(len, end_elem) - run_first)};
+        in_run = false;
+      };
       for (int lane = 0; lane < 32; lane++) {
-        const int c = c0 + lane, i0 = c * SEQ_E;
-        float v[SEQ_E], t = 0.0f;
+        const int c = gr * 32 + lane, i0 = c * SEQ_E;
+        float t = 0.0f;
+        uint32_t vb[SEQ_E];
         int cnt = 0;
         for (int j = 0; j < SEQ_E; j++) {
-          v[j] = i0 + j < len ? p[base + i0 + j] : 0.0f;
+          const float v = i0 + j < len ? p[base + i0 + j] : 0.0f;
+          vb[j] = f2u(v) & 0x7FFFFFFFu;
           cnt += i0 + j < len ? 1 : 0;
-          t += v[j];
+          t += v;
         }
         const int eb = seq_exp_field(before), ea = seq_exp_field(before + t);
-        const bool slow = cnt > 0 && (ea != eb || eb >= 255);
-        const bool starts = lane == 0 || slow_prev || eb != eb_prev;
-        if (slow) slow_mask |= 1u << lane;
-        if (starts) start_mask |= 1u << lane;
-        n_slow += slow ? 1 : 0;
-        if (c < SEQ_CHUNKS) {
-          if (starts) run = sumfn_identity();
-          if (!slow) run = sumfn_compose(run, seq_chunk_fn(v, SEQ_E, eb));
-          sc.a0[c] = slow ? 0 : run.a0;
-          sc.a1[c] = slow ? 0 : run.a1;
-          sc.ep[c] = eb;
+        const bool live = lane >= head_lanes;
+        bool bad = ea != eb || eb >= 255;
+        int inc = 0;
+        for (int j = 0; j < SEQ_E; j++) inc += seq_increment(vb[j], eb, bad);
+        const bool slow = live && cnt > 0 && bad;
+        inc = slow || !live ? 0 : std::min(inc, SUMFN_SAT);
+        const bool starts = live && (lane == head_lanes || slow_prev || eb != eb_prev);
+        if (slow || starts) close_run(i0);
+        if (slow) {
+          n_slow++;
+          sc.item[32 * gr + n_items++] = SeqItem{0, -1, i0, std::max(0, std::min(len, i0 + SEQ_E) - i0)};
+        } else if (live) {
+          if (!in_run) {
+            in_run = true;
+            run_inc = 0;
+            run_ep = eb;
+            run_first = i0;
+          }
+          run_inc = std::min(run_inc + inc, SUMFN_SAT);
         }
         eb_prev = eb;
         slow_prev = slow;
         before = (before + t) * skew;
       }
-      sc.slow[c0 >> 5] = slow_mask;
-      sc.start[c0 >> 5] = start_mask;
+      close_run((gr + 1) * 32 * SEQ_E);
+      sc.n_items[gr] = n_items;
     }
-    total = seqsum_walk(p + base, len, &sc, nch, total);
+    total = seqsum_walk(p + base, &sc, ngr, total);
+    approx = before;
   }
   if (slow_chunks) *slow_chunks = n_slow;
   return total;

@@ -164,8 +164,21 @@ def test_parallel_sequential_sum_is_exact(hostcheck):
             n_slow = C.c_int(0)
             got = np.float32(hostcheck.hc_seqsum_runs(p.ctypes.data_as(C.c_void_p), p.size, skew, C.byref(n_slow)))
             assert got.view(np.uint32) == want.view(np.uint32) or (np.isnan(got) and np.isnan(want)), (p.size, skew)
-            if skew == 1.0 and p.size == 2048 and np.isfinite(p).all() and 1e-3 < float(p.mean()) < 1e3 and p.std() > 0:
-                assert n_slow.value <= 24, n_slow.value  # a handful of binade crossings, not a serial sum
+
+
+def test_sequential_sum_of_squares_takes_the_fast_path(hostcheck):
+    """For the sums the decode step evaluates (squares of a normalised row) only a handful of
+    chunks fall back to term-by-term adds: the binade crossings and the odd exact tie."""
+    hostcheck.hc_seqsum_runs.restype = C.c_float
+    hostcheck.hc_seqsum_runs.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.POINTER(C.c_int)]
+    rng = np.random.default_rng(5)
+    for n in (2048, 4096):
+        for _ in range(20):
+            p = (rng.standard_normal(n) ** 2).astype(np.float32)
+            n_slow = C.c_int(0)
+            got = np.float32(hostcheck.hc_seqsum_runs(p.ctypes.data_as(C.c_void_p), p.size, 1.0, C.byref(n_slow)))
+            assert got.view(np.uint32) == _naive_sum(p).view(np.uint32)
+            assert n_slow.value <= 16, n_slow.value
 
 
 def test_bench_kind_table_matches_the_library(pkg):
