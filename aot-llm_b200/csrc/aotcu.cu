@@ -165,6 +165,18 @@ static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
   return call.pair ? launch_gemm_t<true>(c, P, grid, smem) : launch_gemm_t<false>(c, P, grid, smem);
 }
 
+// Fields of a MegaOp the kernels would otherwise derive with integer divisions.
+static void megaop_derive(MegaOp& op) {
+  const int mats = op.pair ? 2 : 1;
+  op.nb = op.cols >> 8;
+  op.tstride = op.nb | 1;
+  int cap = WARP_TERMS_FLOATS / (op.tstride * mats);
+  const int cap_max = op.pair ? 16 : 32;
+  op.cap = cap > cap_max ? cap_max : (cap < 1 ? 1 : cap);
+  op.n_tiles_lo = (op.cta_base + op.tile_rows - 1) / op.tile_rows;
+  op.n_tiles_hi = (op.cta_base + 1 + op.tile_rows - 1) / op.tile_rows;
+}
+
 // One product on the ring producer/consumer kernel: a single activation row for K-quants,
 // one or more rows for the Q8_0 family (as many at a time as their images fit in shared
 // memory; the matrix is streamed once per such group).
@@ -192,6 +204,7 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   op.tile_rows = tr < 1 ? 1 : (tr > TILE_MAX_UNITS ? TILE_MAX_UNITS : tr);
   op.epilogue = call.epilogue;
   op.ll = 0;
+  megaop_derive(op);
   P.x_image = call.x_mode == 1;
   P.q80 = kind_act(call.seg[0].kind) == ACT_Q8_0;
   P.err = c->d_err;
@@ -856,6 +869,7 @@ static int mega_setup(aotcu_gpu* g) {
     int tr = (int)((size_t)(stage_bytes - 192) / (max_rb * (pair ? 2 : 1)));
     op.tile_rows = tr < 1 ? 1 : (tr > TILE_MAX_UNITS ? TILE_MAX_UNITS : tr);
     op.epilogue = epilogue;
+    megaop_derive(op);
     return op;
   };
   // Tagged vectors: residual, q, k, v, attention output, activated hidden. Zeroed once:

@@ -84,11 +84,13 @@ __device__ float group_seq_sum(const float* p, int n, SeqSumScratch* sc, const C
     if (prof && tid == 0) sp.mark(26);
     // 2. predicted exponents, increments, runs, items
     float total = approx;
-    for (int k = 0; k < ngr; k++) total += sc->gtot[k];
+#pragma unroll
+    for (int k = 0; k < SEQ_CHUNKS / 32; k++) total += k < ngr ? sc->gtot[k] : 0.0f;
     for (int gr = warp; gr < ngr; gr += nwarps) {
       const int c = gr * 32 + lane, i0 = c * SEQ_E;
       float before = approx;
-      for (int k = 0; k < gr; k++) before += sc->gtot[k];
+#pragma unroll
+      for (int k = 0; k < SEQ_CHUNKS / 32; k++) before += k < gr ? sc->gtot[k] : 0.0f;  // all loads issue together
       before += sc->excl[c];
       float t = 0.0f;
       uint32_t vb[SEQ_E];

@@ -171,6 +171,9 @@ struct MegaOp {
   int nseg, pair, cols, span_rows, rows_per_cta, tile_rows, epilogue;
   int ll;  // outputs are tagged words (seg[].out points at LLWord), not plain floats
   int cta_base, cta_rem;  // span_rows / grid and span_rows % grid: CTA b owns cta_base (+1 when b < cta_rem) rows
+  // derived by the host so that no consumer warp divides: blocks per row, stride of a row's
+  // terms in the warp's strip, units a strip holds, tiles of a CTA with cta_base / cta_base + 1 rows
+  int nb, tstride, cap, n_tiles_lo, n_tiles_hi;
 };
 
 struct StepLayer {
@@ -416,14 +419,11 @@ __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, Ring
                                            int n_warps, uint32_t tag, const TpExchange* tpx = nullptr, int which = 0,
                                            SubProf sp = SubProf{nullptr, 0}) {
   sp.last = clock64();
-  const int tile_rows = op.tile_rows, pair = op.pair, nb = op.cols >> 8, ll = op.ll;
-  int c0, c1;
-  op_cta_rows(op, c0, c1);
+  const int pair = op.pair, nb = op.nb, ll = op.ll;
   const int lane = threadIdx.x & 31;
   const int mats = pair ? 2 : 1;
-  const int tstride = nb | 1;  // odd, so the lane-parallel reads of the flush spread over the banks
-  int cap = WARP_TERMS_FLOATS / (tstride * mats);
-  cap = cap > (pair ? 16 : 32) ? (pair ? 16 : 32) : cap;
+  const int tstride = op.tstride;  // odd, so the lane-parallel reads of the flush spread over the banks
+  const int cap = op.cap;
   const uint32_t sxa = smem_addr(sx);
   const bool accum_ll = !pair && ll && op.epilogue == EPI_ACCUM && !(TP && tpx);
   YCache yc;
@@ -432,7 +432,7 @@ __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, Ring
   int pend = 0;
   float* my_out = nullptr;
   float my_old = 0.0f;
-  const int n_tiles = (c1 - c0 + tile_rows - 1) / tile_rows;
+  const int n_tiles = (int)blockIdx.x < op.cta_rem ? op.n_tiles_hi : op.n_tiles_lo;
 #pragma unroll 1
   for (int tile = 0; tile < n_tiles; tile++) {
     sp.mark(18);

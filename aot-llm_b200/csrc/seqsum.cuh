@@ -138,7 +138,8 @@ AOT_HD float seqsum_walk(const float* p, const SeqSumScratch* sc, int n_groups, 
       // ep >= 2: the pattern arithmetic needs a normal sum (the lowest binade, which
       // includes the subnormals, goes term by term)
       const uint32_t nb = bits + (uint32_t)it.csum;
-      if (it.ep >= 2 && (int)(bits >> 23) == it.ep && (int)(nb >> 23) == it.ep) {
+      const bool fits = (it.ep >= 2) & ((int)(bits >> 23) == it.ep) & ((int)(nb >> 23) == it.ep);
+      if (fits) {
         bits = nb;
         continue;
       }
