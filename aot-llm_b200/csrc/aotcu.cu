@@ -18,6 +18,7 @@
 #include "../../include/aot_cuda.h"
 #include "gemv.cuh"
 #include "gemm.cuh"
+#include "gemm_tc.cuh"
 #include "mega.cuh"
 #include "ops.cuh"
 
@@ -126,7 +127,56 @@ static int launch_gemm_t(aotcu_ctx* c, const GemmParams& P, int grid, size_t sme
   return launch(c, gemm_q8k_mma_kernel<PAIR>, dim3(grid), dim3(GEMM_WARPS * 32), smem, P);
 }
 
+// Q4_K / Q5_K matrices: the tcgen05 kernel (gemm_tc.cuh). A gate/up pair runs as two
+// matrices of one launch, the SiLU gate as a separate element-wise pass (the same two
+// operations in the same order as the fused epilogue).
+static bool g_use_tc = []() {
+  const char* e = getenv("AOTCU_TC_GEMM");  // "0": keep prompt chunks on the mma.sync tiles
+  return !(e && e[0] == '0');
+}();
+static int launch_gemm_tc(aotcu_ctx* c, const GemvCall& call) {
+  GemmTcParams P = {};
+  int tiles = 0;
+  for (int s = 0; s < call.nseg; s++) {
+    P.seg[s] = call.seg[s];
+    P.tiles_before[s] = tiles;
+    tiles += (call.seg[s].rows + TC_ROWS - 1) / TC_ROWS;
+  }
+  for (int s = call.nseg; s < 4; s++) P.tiles_before[s] = tiles;
+  P.nseg = call.nseg;
+  P.cols = (int)call.cols;
+  P.m = (int)call.m;
+  P.epilogue = call.epilogue == EPI_ACCUM ? EPI_ACCUM : EPI_STORE;
+  P.x = reinterpret_cast<const uint8_t*>(call.x);
+  P.x_image = call.x_mode == 1;
+  P.n_tiles = tiles;
+  P.err = c->d_err;
+  static bool attr_set[64] = {};
+  if (c->device >= 0 && c->device < 64 && !attr_set[c->device]) {
+    CU_TRY(cudaFuncSetAttribute(gemm_k4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
+    attr_set[c->device] = true;
+  }
+  const int grid = tiles < c->n_sm ? tiles : c->n_sm;
+  if (int rc = launch(c, gemm_k4_tc_kernel, dim3(grid), dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, P)) return rc;
+  if (call.pair && call.epilogue == EPI_SILU_MUL) {
+    const size_t n = call.m * (size_t)call.seg[0].rows;
+    return launch(c, silu_mul_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, call.seg[0].out, (const float*)call.seg[1].out, n);
+  }
+  return 0;
+}
+
+// 0: choose by size (the tcgen05 kernel works on tiles of 128 rows, one CTA each: it wins
+// once a launch has enough tiles to occupy the GPU, measured 32 us against 45 us for the
+// gate/up pair of the TinyLlama shape, and loses on 16..20 tiles); 1: always; -1: never.
+static int g_tc_force = 0;
 static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
+  bool k4 = g_use_tc && g_tc_force >= 0;
+  int tc_tiles = 0;
+  for (int s = 0; s < call.nseg; s++) {
+    k4 = k4 && (call.seg[s].kind == Q4_K || call.seg[s].kind == Q5_K);
+    tc_tiles += (call.seg[s].rows + TC_ROWS - 1) / TC_ROWS;
+  }
+  if (k4 && (g_tc_force > 0 || tc_tiles >= c->n_sm / 2)) return launch_gemm_tc(c, call);
   GemmParams P = {};
   int tiles = 0;
   for (int s = 0; s < call.nseg; s++) {
@@ -1815,6 +1865,13 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
     return 0;
   }
   if (!strcmp(name, "mega_available")) return g->mega_ok ? 1 : 0;
+  if (!strcmp(name, "tc_gemm")) {
+    // process-wide: prompt chunks of Q4_K / Q5_K matrices on tcgen05 (2: always, 1: when the
+    // launch has enough 128-row tiles to occupy the GPU) or on mma.sync tiles (0)
+    g_use_tc = value != 0;
+    g_tc_force = value >= 2 ? 1 : 0;
+    return 0;
+  }
   if (!strcmp(name, "fast") || !strcmp(name, "exact") || !strcmp(name, "spin_limit")) {
     // Parameters of the one-kernel step are baked into the captured graphs: drop them.
     CU_TRY(cudaStreamSynchronize(g->c->stream));
