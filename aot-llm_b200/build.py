@@ -16,7 +16,9 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libaot_cuda.so"
-SOURCES = [CSRC / "aotcu.cu", CSRC / "synth.cpp"]
+SOURCES = [CSRC / "aotcu.cu"]
+SYNTH_SRC = HERE / "synth" / "synth.cpp"
+SYNTH_LIB = HERE / "libaot_synth.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -42,7 +44,7 @@ STAMP = HERE / "libaot_cuda.so.srchash"
 def source_hash() -> str:
     """Hash of everything the library is built from (contents, not timestamps: a copied
     tree does not keep modification times in a useful order)."""
-    deps = sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.cpp"))) + \
+    deps = sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh"))) + \
         [HERE.parent / "include" / "aot_cuda.h"]
     h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
     for d in deps:
@@ -81,6 +83,25 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+def build_synth(force: bool = False) -> Path:
+    """libaot_synth.so: the host-only generator of synthetic weights (tests, benchmarks).
+    Plain g++, no CUDA: a process that only needs test data never maps the CUDA library."""
+    deps = [SYNTH_SRC, HERE / "synth" / "aot_synth.h", CSRC / "blockmath.cuh"]
+    if not force and SYNTH_LIB.exists() and all(SYNTH_LIB.stat().st_mtime >= d.stat().st_mtime for d in deps):
+        return SYNTH_LIB
+    with open(HERE / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        tmp = HERE / f".libaot_synth.{os.getpid()}.so"
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-pthread", "-o", str(tmp), str(SYNTH_SRC)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            tmp.unlink(missing_ok=True)
+            raise RuntimeError("g++ failed:\n" + r.stdout + r.stderr)
+        os.replace(tmp, SYNTH_LIB)
+    return SYNTH_LIB
+
+
 if __name__ == "__main__":
+    build_synth(force="--force" in sys.argv)
     build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(LIB)

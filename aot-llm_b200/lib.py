@@ -143,13 +143,31 @@ SYMBOLS = {
     "aotcu_bench_matmul": (_i, [_vp, _i, _vp, _vp, _sz, _sz, _vp, _sz, _sz, _sz, _i, C.POINTER(_f)]),
     "aotcu_gpu_profile_step": (_i, [_vp, _u32, _sz, _i, _vp]),
     "aotcu_gpu_timeline_step": (_i, [_vp, _u32, _sz, _i, _vp, _vp]),
-    "aotcu_synth_quantize_row": (_i, [_i, _vp, _sz, _vp]),
-    "aotcu_synth_tensor": (_i, [_i, _sz, _sz, _f, _f, C.c_uint64, _vp]),
-    "aotcu_synth_blocks": (_i, [_i, _sz, C.c_uint64, _vp]),
     "aotcu_row_bytes": (_sz, [_i, _sz]),
 }
 
+# Host-only generator of synthetic weights (libaot_synth.so), separate from the CUDA library.
+SYNTH_SYMBOLS = {
+    "aotcu_synth_quantize_row": (_i, [_i, _vp, _sz, _vp]),
+    "aotcu_synth_tensor": (_i, [_i, _sz, _sz, _f, _f, C.c_uint64, _vp]),
+    "aotcu_synth_blocks": (_i, [_i, _sz, C.c_uint64, _vp]),
+}
+
 _lib = None
+_synth = None
+
+
+def synth() -> C.CDLL:
+    """Load (building first if needed) libaot_synth.so."""
+    global _synth
+    if _synth is None:
+        L = C.CDLL(str(_build.build_synth()))
+        for name, (res, args) in SYNTH_SYMBOLS.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _synth = L
+    return _synth
 
 
 def load() -> C.CDLL:

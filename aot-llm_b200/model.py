@@ -67,7 +67,7 @@ class _Builder:
         nbytes = rows * row_bytes(kind, cols)
         buf = np.empty(nbytes, dtype=np.uint8)
         self.n += 1
-        check(L.load().aotcu_synth_tensor(kind, rows, cols, amp, offset, self.seed * 1000003 + self.n, ptr(buf)))
+        check(L.synth().aotcu_synth_tensor(kind, rows, cols, amp, offset, self.seed * 1000003 + self.n, ptr(buf)))
         t = Tensor(kind=kind, present=1, off=self.off, len=nbytes, rows=rows, cols=cols)
         self.chunks.append(buf)
         self.off += nbytes

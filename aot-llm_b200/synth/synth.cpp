@@ -11,7 +11,8 @@
 #include <vector>
 
 #include "../../include/aot_cuda.h"
-#include "blockmath.cuh"
+#include "../csrc/blockmath.cuh"
+#include "aot_synth.h"
 
 using namespace aot;
 

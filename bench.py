@@ -108,7 +108,7 @@ def _synth_matrix(pkg, kind: int, rows: int, cols: int, seed: int) -> np.ndarray
     """Seeded random blocks of one quant type, every field of the layout filled uniformly (benchmark configuration 0)."""
     rb = pkg.lib.row_bytes(kind, cols)
     w = np.zeros(rows * rb, dtype=np.uint8)
-    pkg.lib.check(pkg.lib.load().aotcu_synth_tensor(kind, rows, cols, 1e-3, 1e-2, seed, w.ctypes.data))
+    pkg.lib.check(pkg.lib.synth().aotcu_synth_tensor(kind, rows, cols, 1e-3, 1e-2, seed, w.ctypes.data))
     return w
 
 
@@ -225,7 +225,7 @@ def run_reference(args, rank: int, world: int):
     spec = pkg.model.tinyllama()
     cores = os.cpu_count() or 1
     steps = max(1, min(args.steps, 64))
-    warmup = max(1, min(args.warmup, 4))
+    warmup = max(1, min(args.warmup, 16))
     # The reference defaults to min(cores, 8) threads (crates/aot-kernels/src/app.rs:214-216)
     # and takes --threads; both settings are timed and the faster one is the line's value.
     tried = {}
@@ -481,6 +481,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference" and not (args.sweep or args.tp):
+        graft.build_host_only()  # the CPU arm maps no product library
+        run_reference(args, rank, world)
+        return
     graft.build()
     if args.sweep:
         if rank == 0:

@@ -321,18 +321,6 @@ int aotcu_gpu_profile_step(aotcu_gpu* g, uint32_t token, size_t pos, int cta, ui
    wait for. */
 int aotcu_gpu_timeline_step(aotcu_gpu* g, uint32_t token, size_t pos, int layer, uint64_t* out, int* n_cta);
 
-/* ---- synthetic test data (the encoders of crates/aot-kernels/src/quantize.rs) */
-/* quantize_row (quantize.rs:16-294): encodes n floats as one row of `kind` into
- * out (row_bytes(kind, n) bytes). Host memory, CPU code: this is data
- * generation for tests and benchmarks, not part of the forward pass. */
-int aotcu_synth_quantize_row(int kind, const float* x, size_t n, uint8_t* out);
-/* Fills `rows` x `cols` weights drawn uniform in (-amp, amp) from a counter-based
- * generator keyed by `seed`, encoded as `kind`, multi-threaded. */
-int aotcu_synth_tensor(int kind, size_t rows, size_t cols, float amp, float offset, uint64_t seed, uint8_t* out);
-/* Fills `n_blocks` blocks of `kind` with field-uniform random content (f16
- * scales uniform in [1e-3, 1e-2], quant bytes uniform), as the single-kernel
- * benchmark configurations specify. */
-int aotcu_synth_blocks(int kind, size_t n_blocks, uint64_t seed, uint8_t* out);
 size_t aotcu_row_bytes(int kind, size_t cols);
 
 #ifdef __cplusplus

@@ -106,7 +106,7 @@ def make_weights(pkg, kind: int, rows: int, cols: int, seed: int, mode: str = "e
     L = pkg.lib
     w = np.empty(rows * L.row_bytes(kind, cols), dtype=np.uint8)
     if mode == "enc" or kind < 3:
-        L.check(L.load().aotcu_synth_tensor(kind, rows, cols, 1.0, 0.0, seed, L.ptr(w)))
+        L.check(L.synth().aotcu_synth_tensor(kind, rows, cols, 1.0, 0.0, seed, L.ptr(w)))
     else:
-        L.check(L.load().aotcu_synth_blocks(kind, rows * cols // L.BLOCK[kind], seed, L.ptr(w)))
+        L.check(L.synth().aotcu_synth_blocks(kind, rows * cols // L.BLOCK[kind], seed, L.ptr(w)))
     return w

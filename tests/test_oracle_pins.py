@@ -151,7 +151,7 @@ def test_dot_tables_agree(pkg, ob, kind, cols, seed):
     w = rng.floats(cols)
     x = rng.floats(cols, 3.0)
     wq = np.empty(pkg.lib.row_bytes(kind, cols), dtype=np.uint8)
-    pkg.lib.check(pkg.lib.load().aotcu_synth_quantize_row(kind, pkg.lib.ptr(w), cols, pkg.lib.ptr(wq)))
+    pkg.lib.check(pkg.lib.synth().aotcu_synth_quantize_row(kind, pkg.lib.ptr(w), cols, pkg.lib.ptr(wq)))
     fref = float(np.dot(ob.dequant_row(kind, wq, cols).astype(np.float32), x))
     tol = float(np.abs(x).sum()) * 0.02 + 1e-3
     xq = ob.quantize_act(kind, x)
@@ -217,7 +217,7 @@ def test_matvec2_matvec3_match_matvec(pkg, ob):
 def test_encoder_roundtrip_error(pkg, ob, kind, tol):
     x = (np.random.default_rng(kind + 1).random(512, dtype=np.float32) * 2 - 1).astype(np.float32)
     enc = np.empty(pkg.lib.row_bytes(kind, 512), dtype=np.uint8)
-    pkg.lib.check(pkg.lib.load().aotcu_synth_quantize_row(kind, pkg.lib.ptr(x), 512, pkg.lib.ptr(enc)))
+    pkg.lib.check(pkg.lib.synth().aotcu_synth_quantize_row(kind, pkg.lib.ptr(x), 512, pkg.lib.ptr(enc)))
     dec = ob.dequant_row(kind, enc, 512)
     assert float(np.abs(x - dec).mean()) < tol
 
