@@ -130,6 +130,11 @@ static int launch_gemm_t(aotcu_ctx* c, const GemmParams& P, int grid, size_t sme
 // Q4_K / Q5_K matrices: the tcgen05 kernel (gemm_tc.cuh). A gate/up pair runs as two
 // matrices of one launch, the SiLU gate as a separate element-wise pass (the same two
 // operations in the same order as the fused epilogue).
+// Set only by aotcu_block_sums_of around its one launch: where the product kernels leave
+// their integer block sums.
+static int32_t* g_dbg_sumi = nullptr;
+static int32_t* g_dbg_summ = nullptr;
+
 static bool g_use_tc = []() {
   const char* e = getenv("AOTCU_TC_GEMM");  // "0": keep prompt chunks on the mma.sync tiles
   return !(e && e[0] == '0');
@@ -151,6 +156,8 @@ static int launch_gemm_tc(aotcu_ctx* c, const GemvCall& call) {
   P.x_image = call.x_mode == 1;
   P.n_tiles = tiles;
   P.err = c->d_err;
+  P.dbg_sumi = g_dbg_sumi;
+  P.dbg_summ = g_dbg_summ;
   static bool attr_set[64] = {};
   if (c->device >= 0 && c->device < 64 && !attr_set[c->device]) {
     CU_TRY(cudaFuncSetAttribute(gemm_k4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
@@ -254,6 +261,8 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   op.tile_rows = tr < 1 ? 1 : (tr > TILE_MAX_UNITS ? TILE_MAX_UNITS : tr);
   op.epilogue = call.epilogue;
   op.ll = 0;
+  op.dbg_sumi = g_dbg_sumi;
+  op.dbg_summ = g_dbg_summ;
   megaop_derive(op);
   P.x_image = call.x_mode == 1;
   P.q80 = kind_act(call.seg[0].kind) == ACT_Q8_0;
@@ -1285,6 +1294,48 @@ int aotcu_block_sums(aotcu_ctx* c, int kind, const uint8_t* w, const void* x, si
   if (rows == 0 || nb == 0) return 0;
   return launch(c, block_sums_kernel, dim3(grid_for(c, rows * nb, 128)), dim3(128), 0, kind, w, (const uint8_t*)x,
                 (int)rows, nb, sumi, summ);
+}
+
+int aotcu_block_sums_of(aotcu_ctx* c, int kernel, int kind, const uint8_t* w, const void* x, size_t m, size_t rows, size_t cols,
+                        int32_t* sumi, int32_t* summ) {
+  ARG_CHECK(c && w && x && sumi && summ, "NULL argument");
+  ARG_CHECK(kind == AOTCU_Q4_K || kind == AOTCU_Q5_K || kind == AOTCU_Q6_K, "kind %d is not a K-quant", kind);
+  ARG_CHECK(cols > 0 && cols % 256 == 0 && rows > 0, "bad shape");
+  ARG_CHECK(kernel == 0 || kernel == 1, "kernel: 0 = streaming single-row product, 1 = tcgen05 prompt product");
+  if (int rc = ctx_set_device(c)) return rc;
+  float* out = nullptr;
+  CU_TRY(cudaMalloc(&out, m * rows * sizeof(float)));
+  int rc = 0;
+  if (kernel == 0) {
+    if (m != 1) rc = fail(AOTCU_ERR_BAD_ARG, "the streaming product takes one activation row");
+    GemvCall call;
+    call.seg[0] = GemvSeg{w, out, (int)rows, kind};
+    call.nseg = 1;
+    call.cols = cols;
+    call.x = x;
+    call.x_mode = 0;
+    call.m = 1;
+    g_dbg_sumi = sumi;
+    g_dbg_summ = summ;
+    if (!rc) rc = launch_gemv_stream(c, call, rows);
+    g_dbg_sumi = g_dbg_summ = nullptr;
+  } else {
+    if (kind == AOTCU_Q6_K || m < 1 || m > (size_t)TC_TOK) rc = fail(AOTCU_ERR_BAD_ARG, "the tcgen05 product takes Q4_K / Q5_K and 1..64 rows");
+    GemvCall call;
+    call.seg[0] = GemvSeg{w, out, (int)rows, kind};
+    call.nseg = 1;
+    call.cols = cols;
+    call.x = x;
+    call.x_mode = 0;
+    call.m = m;
+    g_dbg_sumi = sumi;
+    g_dbg_summ = summ;
+    if (!rc) rc = launch_gemm_tc(c, call);
+    g_dbg_sumi = g_dbg_summ = nullptr;
+  }
+  if (!rc) rc = check_device_errors(c);
+  cudaFree(out);
+  return rc;
 }
 
 int aotcu_rmsnorm(aotcu_ctx* c, float* out, const float* x, const float* w, size_t n, size_t m, float eps) {

@@ -55,6 +55,9 @@ struct GemmTcParams {
   int tiles_before[4];  // first tile of each matrix in the concatenated tile space
   int n_tiles;
   int* err;
+  // parity export (one matrix): integers per (token, row, block) before any float arithmetic, or null
+  int* dbg_sumi;
+  int* dbg_summ;
 };
 
 // ---- tcgen05 wrappers ----------------------------------------------------------------------
@@ -141,7 +144,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_k4_tc_kernel(const GemmTcP
   uint64_t* const acc_full = bars + 2 * TC_STAGES;       // [2] MMA -> epilogue
   uint64_t* const acc_empty = bars + 2 * TC_STAGES + 2;  // [2] epilogue -> MMA and fill
   uint64_t* const side_full = bars + 2 * TC_STAGES + 4;  // [2] fill -> epilogue: side data of the super-block written
-  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 6);
+  uint64_t* const drain = bars + 2 * TC_STAGES + 6;      // all MMAs of the CTA have completed
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 7);
   volatile int* const abort = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -156,6 +160,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_k4_tc_kernel(const GemmTcP
       mbar_init(&acc_empty[b], TC_EPI_WARPS);
       mbar_init(&side_full[b], TC_FILL_WARPS);
     }
+    mbar_init(drain, 1);
     *abort = 0;
     mbar_fence_init();
   }
@@ -341,6 +346,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_k4_tc_kernel(const GemmTcP
           summ = __dp2a_lo((int)sp.z, (int)ri.w, summ);
           summ = __dp2a_hi((int)sp.w, (int)ri.w, summ);
           const int sumi = hi[t] * 8 + lo[t];
+          if (P.dbg_sumi && row < S.rows && col0 + t < m) {
+            const size_t di = ((size_t)(col0 + t) * S.rows + row) * nb + b;
+            P.dbg_sumi[di] = sumi;
+            P.dbg_summ[di] = summ;
+          }
           acc[t] = fadd(acc[t], k4_term(d_w, dmin_w, d_x, sumi, summ));
         }
         tc_fence_before();
@@ -384,7 +394,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_k4_tc_kernel(const GemmTcP
         tc_commit(&acc_full[buf]);
       }
     }
-  mma_done:;
+  mma_done:
+    // Tensor memory is freed after the CTA-wide barrier below: every MMA issued above has to
+    // be complete by then, also when a wait gave up half way through a super-block.
+    tc_commit(drain);
+    for (uint32_t k = 0; k < (1u << 20); ++k)
+      if (mbar_try_wait(drain, 0)) break;
   }
   tc_fence_before();
   __syncthreads();

@@ -174,6 +174,9 @@ struct MegaOp {
   // derived by the host so that no consumer warp divides: blocks per row, stride of a row's
   // terms in the warp's strip, units a strip holds, tiles of a CTA with cta_base / cta_base + 1 rows
   int nb, tstride, cap, n_tiles_lo, n_tiles_hi;
+  // parity export (single plain matrix only): integer block sums per (row, block), or null
+  int* dbg_sumi;
+  int* dbg_summ;
 };
 
 struct StepLayer {
@@ -287,12 +290,25 @@ __device__ __forceinline__ void op_cta_rows(const MegaOp& op, int& c0, int& c1) 
   c1 = c0 + op.cta_base + (b < op.cta_rem ? 1 : 0);
 }
 
+// Before a CTA returns, every bulk copy it requested into its shared memory must have
+// landed: the producer (lane 0) waits, with a limit, for the last arrival it armed on each
+// stage. After a normal run they have all completed long ago; this matters when a wait
+// gave up and the consumers left tiles unread.
+__device__ __forceinline__ void produce_drain(const Ring& R, const RingPos& pp, uint32_t tiles_issued) {
+  for (int st = 0; st < R.n_stages; st++) {
+    if ((uint32_t)st >= tiles_issued) break;  // never armed
+    const uint32_t parity = st < pp.st ? pp.parity : pp.parity ^ 1u;  // parity of the stage's last use
+    for (uint32_t it = 0; it < (1u << 20); ++it)
+      if (mbar_try_wait(&R.full[st], parity)) break;
+  }
+}
+
 // Producer side (the whole producer warp): request every tile of this CTA's share of `op`
 // and describe it for the consumers. Lane 0 waits for the stage and issues the copies, part
 // by part; every lane then writes one unit record; the stage's single arrival, which
 // carries the byte count of all copies, comes last (a barrier's pending byte count may run
 // negative in between).
-__device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, RingPos& pp, int n_consumers) {
+__device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, RingPos& pp, int n_consumers, uint32_t& tiles_issued) {
   const int lane = threadIdx.x & 31;
   int c0, c1;
   op_cta_rows(op, c0, c1);
@@ -360,6 +376,7 @@ __device__ __forceinline__ void produce_op(const MegaOp& op, const Ring& R, Ring
     }
     __syncwarp();
     if (lane == 0) mbar_expect_tx(&R.full[pp.st], total);
+    tiles_issued++;
     pp.advance(R.n_stages);
   }
 }
@@ -467,7 +484,8 @@ __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, Ring
       } else {
         const uint32_t rows1[1] = {U.row[0] & 0xFFFFFFu};
         float* const t1[1] = {tdst};
-        warp_rows_terms<1>(kind, rows1, sxa, nb, yc, t1);
+        const int drow[1] = {op.dbg_sumi ? (int)(U.out - op.seg[0].out) : 0};
+        warp_rows_terms<1>(kind, rows1, sxa, nb, yc, t1, op.dbg_sumi, op.dbg_summ, drow);
       }
       sp.mark(27);
       if (++pend == cap) {
@@ -1041,12 +1059,14 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   if (warp == MEGA_CONSUMER_WARPS) {
     // ---- producer warp: walks every matrix product of the step ----
     RingPos pp{0, 0u};
+    uint32_t tiles_issued = 0;
     for (int li = 0; li < P.n_layer && !*abort; li++) {
       const StepLayer& L = table[li];
 #pragma unroll 1
-      for (int ph = 0; ph < 4; ph++) produce_op((&L.qkv)[ph], R, pp, MEGA_CONSUMER_WARPS);  // qkv, wo, gu, down are consecutive members
+      for (int ph = 0; ph < 4; ph++) produce_op((&L.qkv)[ph], R, pp, MEGA_CONSUMER_WARPS, tiles_issued);  // qkv, wo, gu, down are consecutive members
     }
-    if (P.want_logits && !*abort) produce_op(table[P.n_layer].qkv, R, pp, MEGA_CONSUMER_WARPS);
+    if (P.want_logits && !*abort) produce_op(table[P.n_layer].qkv, R, pp, MEGA_CONSUMER_WARPS, tiles_issued);
+    if ((threadIdx.x & 31) == 0) produce_drain(R, pp, tiles_issued);
     return;
   }
 
@@ -1331,7 +1351,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   if (warp == MEGA_CONSUMER_WARPS) {
     // weights do not depend on the previous kernel: stream them right away
     RingPos pp{0, 0u};
-    produce_op(P.op, R, pp, MEGA_CONSUMER_WARPS);
+    uint32_t tiles_issued = 0;
+    produce_op(P.op, R, pp, MEGA_CONSUMER_WARPS, tiles_issued);
+    if ((threadIdx.x & 31) == 0) produce_drain(R, pp, tiles_issued);
     return;
   }
   pdl_wait();

@@ -186,9 +186,12 @@ struct YCache {
 // dependent chains interleave): row[r] = shared address of the row's first block, `sxa` =
 // shared address of the activation images, nb blocks. terms[r][b] receives the f32 term of
 // block b. Every lane of the warp calls it; control flow is warp-uniform.
+// `dbg_i` / `dbg_m`, when given, receive the integers of every (row, block) before any
+// float arithmetic (parity export): dbg_i[dbg_row[r] * nb + b].
 template <int NR>
 __device__ __forceinline__ void warp_rows_terms(int kind, const uint32_t (&row)[NR], uint32_t sxa, int nb, YCache& yc,
-                                                float* const (&terms)[NR]) {
+                                                float* const (&terms)[NR], int* dbg_i = nullptr, int* dbg_m = nullptr,
+                                                const int* dbg_row = nullptr) {
   const int lane = threadIdx.x & 31, bl = lane >> 2, c = lane & 3;
   const int bs = kind_size(kind);
   const int lay = kind == Q6_K ? YL_Q6 : YL_K4;
@@ -224,6 +227,13 @@ __device__ __forceinline__ void warp_rows_terms(int kind, const uint32_t (&row)[
       for (int r = 0; r < NR; r++) {
         si[r] += __shfl_xor_sync(0xffffffffu, si[r], o);
         if (kind != Q6_K) sm[r] += __shfl_xor_sync(0xffffffffu, sm[r], o);
+      }
+    }
+    if (dbg_i && c == 0 && b < nb) {
+#pragma unroll
+      for (int r = 0; r < NR; r++) {
+        dbg_i[(size_t)dbg_row[r] * nb + b] = si[r];
+        if (dbg_m && kind != Q6_K) dbg_m[(size_t)dbg_row[r] * nb + b] = sm[r];
       }
     }
     if (c == 0 && b < nb) {

@@ -141,6 +141,10 @@ class Context:
         area: no device allocation anywhere on this call path (see include/aot_cuda.h)."""
         check(L.load().aotcu_matvec_k_static(self.h, kind, _dp(out), _dp(w), _dp(x_f32), rows, cols))
 
+    def block_sums_of(self, kernel: int, kind: int, w, x, m: int, rows: int, cols: int, sumi, summ):
+        """Integer block sums as production kernel `kernel` forms them (0 streaming row product, 1 tcgen05)."""
+        check(L.load().aotcu_block_sums_of(self.h, kernel, kind, _dp(w), _dp(x), m, rows, cols, _dp(sumi), _dp(summ)))
+
     def block_sums(self, kind: int, w, x, rows: int, cols: int, sumi, summ=None):
         check(L.load().aotcu_block_sums(self.h, kind, _dp(w), _dp(x), rows, cols, _dp(sumi),
                                         _dp(summ) if summ is not None else None))

@@ -108,6 +108,7 @@ SYMBOLS = {
     "aotcu_matmul2": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "aotcu_matvec_k_static": (_i, [_vp, _i, _vp, _vp, _vp, _sz, _sz]),
     "aotcu_block_sums": (_i, [_vp, _i, _vp, _vp, _sz, _sz, _vp, _vp]),
+    "aotcu_block_sums_of": (_i, [_vp, _i, _i, _vp, _vp, _sz, _sz, _sz, _vp, _vp]),
     "aotcu_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _f]),
     "aotcu_rmsnorm_heads": (_i, [_vp, _vp, _vp, _sz, _sz, _f]),
     "aotcu_rope": (_i, [_vp, _vp, _sz, _sz, _sz, _sz, _vp, _i]),

@@ -143,7 +143,10 @@ int aotcu_matmul2(aotcu_ctx* ctx, int kind, float* out_a, float* out_b, const ui
  *   - All calls on a device share the one array: two calls whose kernels can overlap
  *     on the GPU (different contexts or streams) race on it. Calls through one context
  *     are ordered by its stream and are safe. Nothing in the array needs clearing
- *     between calls: each call rewrites every block it reads. */
+ *     between calls: each call rewrites every block it reads.
+ *     The first call on a device looks up the array's address and caches it without a
+ *     lock: make that first call from one host thread (two threads racing there would
+ *     store the same value, but nothing promises that to stay harmless). */
 int aotcu_matvec_k_static(aotcu_ctx* ctx, int kind, float* out, const uint8_t* w, const float* x, size_t rows,
                           size_t cols);
 /* Parity export: the integers of one matvec before any float arithmetic.
@@ -151,6 +154,13 @@ int aotcu_matvec_k_static(aotcu_ctx* ctx, int kind, float* out, const uint8_t* w
  * matvec.rs:89-103 / 146-163 / 38-43 form them. Device pointers. */
 int aotcu_block_sums(aotcu_ctx* ctx, int kind, const uint8_t* w, const void* x, size_t rows, size_t cols,
                      int32_t* sumi, int32_t* summ);
+/* The same integers as the production kernels form them, written by the kernels themselves
+ * while they compute the product: kernel 0 = the streaming single-row product
+ * (aotcu_matvec_* of a K-quant; m = 1; sumi[r*nb + b]), kernel 1 = the tcgen05 prompt product
+ * (Q4_K / Q5_K, m <= 64; sumi[(t*rows + r)*nb + b]). x: reference-layout BlockQ8_K rows.
+ * For Q6_K summ is left untouched. Device pointers. */
+int aotcu_block_sums_of(aotcu_ctx* ctx, int kernel, int kind, const uint8_t* w, const void* x, size_t m, size_t rows,
+                        size_t cols, int32_t* sumi, int32_t* summ);
 
 /* ---- kernel level: ops.rs / sampler.rs ---------------------------------- */
 /* rmsnorm_rows (ops.rs:7-18, 358-363): m rows of n. out may alias x. */

@@ -316,3 +316,107 @@ def test_bad_arguments_are_reported_not_fatal(pkg, ctx):
     with pytest.raises(pkg.AotCudaError):
         ctx.quantize_q8_k(d, 100, d)
     ctx.device_status()  # the context is still usable
+
+
+# north_star: "integer per-block dot products are bit-exact" -- checked on the integers the
+# production kernels themselves form (the streaming single-row product and the tcgen05 prompt
+# product write them out while they compute), not on a separate checker kernel.
+@pytest.mark.parametrize("kind", [Q4_K, Q5_K, Q6_K])
+def test_streaming_product_exports_exact_block_sums(pkg, ob, ctx, kind):
+    rows, cols = 300, 2048
+    nb = cols // 256
+    w = make_weights(pkg, kind, rows, cols, 900 + kind, "uniform")
+    xq = ob.quantize_q8_k(_x(cols, 5 + kind))
+    dsi, dsm = ctx.alloc(rows * nb * 4), ctx.alloc(rows * nb * 4)
+    ctx.block_sums_of(0, kind, ctx.to_device(w), ctx.to_device(xq.view(np.uint8)), 1, rows, cols, dsi, dsm)
+    si = dsi.download(np.int32, rows * nb).reshape(rows, nb)
+    sm = dsm.download(np.int32, rows * nb).reshape(rows, nb)
+    rb = pkg.lib.row_bytes(kind, cols)
+    for r in range(rows):
+        osi, osm = ob.block_sums(kind, w[r * rb:(r + 1) * rb].copy(), xq, cols)
+        assert np.array_equal(si[r], osi), (kind, r)
+        if kind != Q6_K:
+            assert np.array_equal(sm[r], osm), (kind, r)
+    ctx.device_status()
+
+
+@pytest.mark.parametrize("kind", [Q4_K, Q5_K])
+def test_tcgen05_product_exports_exact_block_sums(pkg, ob, ctx, kind):
+    rows, cols, m = 150, 1024, 21   # a full and a partial 128-row tile, a partial token tile
+    nb = cols // 256
+    w = make_weights(pkg, kind, rows, cols, 950 + kind, "uniform")
+    xs = _x(m * cols, 31 + kind)
+    xq = ob.quantize_q8_k(xs)
+    dsi, dsm = ctx.alloc(m * rows * nb * 4), ctx.alloc(m * rows * nb * 4)
+    ctx.block_sums_of(1, kind, ctx.to_device(w), ctx.to_device(xq.view(np.uint8)), m, rows, cols, dsi, dsm)
+    si = dsi.download(np.int32, m * rows * nb).reshape(m, rows, nb)
+    sm = dsm.download(np.int32, m * rows * nb).reshape(m, rows, nb)
+    rb = pkg.lib.row_bytes(kind, cols)
+    for t in (0, 7, m - 1):
+        xt = xq[t * nb:(t + 1) * nb]
+        for r in (0, 1, 63, 127, 128, rows - 1):
+            osi, osm = ob.block_sums(kind, w[r * rb:(r + 1) * rb].copy(), xt, cols)
+            assert np.array_equal(si[t, r], osi) and np.array_equal(sm[t, r], osm), (kind, t, r)
+    ctx.device_status()
+
+
+# Prompt chunks through the tcgen05 kernel whatever the launch size (the library picks it by
+# itself only when a launch fills the GPU): batched == per-token, bit for bit.
+@pytest.mark.parametrize("kind", [Q4_K, Q5_K])
+def test_tcgen05_product_bit_exact_when_forced(pkg, ob, ctx, kind):
+    spec = pkg.model.tiny("llama", n_layer=1)
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 16, 4)   # any Gpu: the switch is process-wide
+    g.set_option("tc_gemm", 2)
+    try:
+        pool, tab = ob.Pool(4), ob.detect_table()
+        for rows, cols in ((37, 512), (300, 2048), (130, 5632)):
+            w = make_weights(pkg, kind, rows, cols, 70 + kind + rows)
+            for m in (8, 33, 64):
+                xs = _x(m * cols, 60 + m, 1.0)
+                q = ob.quantize_act(kind, xs)
+                dout = ctx.alloc(m * rows * 4)
+                ctx.matmul(kind, dout, ctx.to_device(w), ctx.to_device(q.view(np.uint8)), m, rows, cols)
+                assert_bits_equal(dout.download(np.float32, m * rows).reshape(m, rows), ob.matmul(pool, tab, kind, w, q, m, rows, cols),
+                                  f"tcgen05 matmul kind {kind} {rows}x{cols} m {m}")
+    finally:
+        g.set_option("tc_gemm", 1)
+        g.close()
+    ctx.device_status()
+
+
+def test_scale_inplace(pkg, ctx):
+    # ops.rs:138-142: x[i] *= s
+    x = _x(5000, 77)
+    d = ctx.to_device(x)
+    ctx.scale_inplace(d, 0.37, 5000)
+    assert_bits_equal(d.download(np.float32, 5000), x * np.float32(0.37), "scale_inplace")
+
+
+# The shapes of the kernel sweep (4096 x 14336 for every kind at M = 1 and M = 64, and the
+# 128256 x 4096 output-head shape for three kinds at M = 1), field-uniform blocks.
+@pytest.mark.parametrize("kind", list(range(9)))
+def test_sweep_shape_4096x14336_bit_exact(pkg, ob, ctx, kind):
+    rows, cols = 4096, 14336
+    pool, tab = ob.Pool(8), ob.detect_table()
+    w = make_weights(pkg, kind, rows, cols, 500 + kind, "uniform")
+    dw = ctx.to_device(w)
+    for m in (1, 64):
+        xs = _x(m * cols, 90 + m, 1.0)
+        q = ob.quantize_act(kind, xs)
+        want = ob.matmul(pool, tab, kind, w, q, m, rows, cols)
+        dout = ctx.alloc(m * rows * 4)
+        ctx.matmul(kind, dout, dw, ctx.to_device(q.view(np.uint8)), m, rows, cols)
+        assert_bits_equal(dout.download(np.float32, m * rows).reshape(m, rows), want, f"kind {kind} 4096x14336 m {m}")
+    ctx.device_status()
+
+
+@pytest.mark.parametrize("kind", [Q4_K, Q6_K, Q8_0])
+def test_sweep_shape_128256x4096_matvec_bit_exact(pkg, ob, ctx, kind):
+    rows, cols = 128256, 4096
+    w = make_weights(pkg, kind, rows, cols, 600 + kind, "uniform")
+    xq = ob.quantize_act(kind, _x(cols, 3))
+    want = ob.matvec(ob.Pool(8), ob.detect_table(), kind, w, xq, rows, cols)
+    dout = ctx.alloc(rows * 4)
+    ctx.matvec(kind, dout, ctx.to_device(w), ctx.to_device(xq.view(np.uint8)), rows, cols)
+    assert_bits_equal(dout.download(np.float32, rows), want, f"kind {kind} 128256x4096")
+    ctx.device_status()

@@ -250,3 +250,65 @@ def test_dependent_launch_switch_keeps_results(pkg, ob, ctx, arch):
             tok, pos = ob.argmax(om.logits()), pos + 1
     g.set_option("pdl", 0)
     ctx.device_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.timeout(900)
+def test_qwen3_8b_shape_prompt_and_decode_bit_exact(pkg, ob, ctx):
+    """Benchmark configuration 3's shape (dim 4096, hidden 12288, 32 query / 8 KV heads of 128,
+    per-head q/k RMSNorm, NEOX RoPE, vocabulary 151936, Q4_K_M mix) with three layers: a
+    64-token prompt chunk, then greedy tokens through the one-kernel step, bit-equal to the
+    oracle at every step."""
+    spec = pkg.model.qwen3_8b(n_layer=3)
+    n_ctx, n_prompt, n_gen = 128, 64, 12
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 64)
+    assert g.set_option("mega_available", 0) == 1, "the one-kernel step must accept the 8B shape"
+    om = ob.model_from_spec(spec, n_ctx, 64, n_threads=min(16, os.cpu_count() or 1))
+    toks = np.random.default_rng(9).integers(0, 151936, n_prompt).tolist()
+    g.forward_batch(toks, 0, True)
+    om.forward_batch(toks, 0, True)
+    assert_bits_equal(g.logits(), om.logits(), "logits after the prompt chunk")
+    tok = ob.argmax(om.logits())
+    for i in range(3):   # step by step, comparing the residual stream as well
+        g.forward(tok, n_prompt + i, True)
+        om.forward(tok, n_prompt + i, True)
+        assert_bits_equal(g.read("X"), om.buf("x"), f"x at {n_prompt + i}")
+        assert_bits_equal(g.logits(), om.logits(), f"logits at {n_prompt + i}")
+        tok = ob.argmax(om.logits())
+    ids, _ = g.generate(tok, n_prompt + 3, n_gen)
+    want = []
+    for i in range(n_gen):
+        om.forward(tok, n_prompt + 3 + i, True)
+        tok = ob.argmax(om.logits())
+        want.append(tok)
+    assert ids.tolist() == want
+    assert_bits_equal(g.logits(), om.logits(), "final logits")
+    ctx.device_status()
+
+
+@pytest.mark.gpu
+def test_bounded_wait_expires_and_the_context_stays_usable(pkg, ob, ctx):
+    """Every wait inside the one-kernel step is bounded. With the limit lowered to a single
+    poll the step cannot finish: it must return (nothing hangs), report a timeout, and leave
+    the context usable: with the limit restored the same position decodes bit-equal to the
+    oracle, and steps queued behind a failed one drain without working."""
+    spec = pkg.model.tiny("llama", n_layer=3, kinds=_kquant_kinds, dim=512, hidden=768, vocab=600)
+    n_ctx = 64
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 8)
+    om = ob.model_from_spec(spec, n_ctx, 8, n_threads=4)
+    prompt = [5, 17, 300, 42]
+    g.forward_batch(prompt, 0, True)
+    om.forward_batch(prompt, 0, True)
+    tok = ob.argmax(om.logits())
+    g.set_option("spin_limit", 1)
+    with pytest.raises(pkg.AotCudaError) as e:
+        g.generate(tok, len(prompt), 5)      # five queued steps: the first gives up, the rest drain
+    assert e.value.status == pkg.lib.ERR_TIMEOUT, e.value
+    g.set_option("spin_limit", 1 << 21)
+    ctx.device_status()                       # the error word was consumed with the failed call
+    for i in range(3):
+        g.forward(tok, len(prompt) + i, True)
+        om.forward(tok, len(prompt) + i, True)
+        assert_bits_equal(g.logits(), om.logits(), f"logits at {len(prompt) + i} after the expired wait")
+        tok = ob.argmax(om.logits())
+    ctx.device_status()

@@ -20,11 +20,13 @@ Q4_K, Q5_K, Q6_K = 6, 7, 8
 
 
 @pytest.mark.parametrize("kind", [Q4_K, Q5_K, Q6_K])
-def test_static_area_product_matches_two_call_route(pkg, ctx, kind):
+def test_static_area_product_matches_two_call_route(pkg, ob, ctx, kind):
     rng = np.random.default_rng(100 + kind)
-    # Two calls in a row with different widths: the second reads fewer blocks than the
-    # first wrote, so stale images sit behind it in the shared array.
-    for rows, cols in ((300, 5632), (257, 2048)):
+    pool, tab = ob.Pool(4), ob.detect_table()
+    # Calls in a row with different widths: the widest vector the built-in area takes
+    # (16384 columns, where a Q6_K row is 13,440 bytes), then narrower ones that read fewer
+    # blocks than the call before wrote, so stale images sit behind them in the shared array.
+    for rows, cols in ((33, 16384), (300, 5632), (257, 2048)):
         w = make_weights(pkg, kind, rows, cols, 40 + kind + cols)
         x = (rng.standard_normal(cols) * 2).astype(np.float32)
         dw, dx = ctx.to_device(w), ctx.to_device(x)
@@ -34,6 +36,8 @@ def test_static_area_product_matches_two_call_route(pkg, ctx, kind):
         ctx.quantize_q8_k(dx, cols, xq)
         ctx.matvec(kind, want_buf, dw, xq, rows, cols)
         want = want_buf.download(np.float32, rows)
+        # ... and both must be the CPU oracle's bits, not merely each other's
+        assert_bits_equal(want, ob.matvec(pool, tab, kind, w, ob.quantize_q8_k(x), rows, cols), f"two-call route vs oracle, kind {kind}")
         # allocation-free route, twice: same input, same answer, both times
         out = ctx.alloc(rows * 4)
         for _ in range(2):
