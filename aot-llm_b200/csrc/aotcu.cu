@@ -443,6 +443,7 @@ struct TpState {
   int (*get_unique_id)(void*) = nullptr;
   int (*comm_init_rank)(void**, int, /* ncclUniqueId by value: 128 bytes */ struct NcclId, int) = nullptr;
   int (*all_reduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*all_gather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
   int (*comm_destroy)(void*) = nullptr;
   const char* (*get_error_string)(int) = nullptr;
 };
@@ -457,9 +458,10 @@ static int tp_load(TpState* t, const char* path) {
   t->get_unique_id = reinterpret_cast<decltype(t->get_unique_id)>(dlsym(t->lib, "ncclGetUniqueId"));
   t->comm_init_rank = reinterpret_cast<decltype(t->comm_init_rank)>(dlsym(t->lib, "ncclCommInitRank"));
   t->all_reduce = reinterpret_cast<decltype(t->all_reduce)>(dlsym(t->lib, "ncclAllReduce"));
+  t->all_gather = reinterpret_cast<decltype(t->all_gather)>(dlsym(t->lib, "ncclAllGather"));
   t->comm_destroy = reinterpret_cast<decltype(t->comm_destroy)>(dlsym(t->lib, "ncclCommDestroy"));
   t->get_error_string = reinterpret_cast<decltype(t->get_error_string)>(dlsym(t->lib, "ncclGetErrorString"));
-  if (!t->get_unique_id || !t->comm_init_rank || !t->all_reduce || !t->comm_destroy || !t->get_error_string)
+  if (!t->get_unique_id || !t->comm_init_rank || !t->all_reduce || !t->all_gather || !t->comm_destroy || !t->get_error_string)
     return fail(AOTCU_ERR_UNSUPPORTED, "the NCCL library lacks a required entry point");
   return 0;
 }
@@ -497,15 +499,23 @@ struct aotcu_gpu {
   TpState* tp = nullptr;              // set by aotcu_tp_attach: this Gpu holds one shard of the model
   LLWord* tp_inbox = nullptr;         // partial rows from every rank (aotcu_tp_inbox_handle)
   void* tp_peer_map[8] = {};          // peers' inboxes mapped into this process
+  // Vocabulary-sharded output head: this rank's `output` holds rows [head_row0, head_row0 +
+  // rows) of the vocabulary; its logits sit at the front of the logits buffer and the whole
+  // vector is gathered (NCCL) only when the host asks for it.
+  bool head_sharded = false;
+  size_t head_row0 = 0;
+  float* tp_logits_full = nullptr;
   StepLayer* d_step_layers = nullptr;
   unsigned* d_grid_bar = nullptr;     // [0] barrier arrivals of one launch, [1] launch count
   void* d_ll = nullptr;               // tagged activation vectors of the one-kernel step
   StepParams step_params = {};
   size_t mega_smem = 0;
-  cudaGraphExec_t decode_graph[2] = {nullptr, nullptr};  // [want_logits]
-  cudaGraphExec_t gen_graph = nullptr;
-  uint64_t decode_graph_kernels[2] = {0, 0};  // kernel nodes per replay
-  uint64_t gen_graph_kernels = 0;
+  // Captured decode steps: [want_logits + 2 * long-context variant of the one-kernel step]
+  cudaGraphExec_t decode_graph[4] = {};
+  cudaGraphExec_t gen_graph[2] = {};            // [long-context variant]
+  uint64_t decode_graph_kernels[4] = {};        // kernel nodes per replay
+  uint64_t gen_graph_kernels[2] = {};
+  int split_now = 0;                            // the step being enqueued shares heads between CTAs (mega_split)
   int smem_scores = 0;
 };
 
@@ -754,6 +764,15 @@ static int tp_all_reduce(aotcu_gpu* g, float* buf, size_t n) {
   return 0;
 }
 
+// Every rank's slice of the logits, in rank order, into tp_logits_full (collective).
+static int tp_gather_logits(aotcu_gpu* g) {
+  TpState* t = g->tp;
+  const aotcu_tensor& out_t = g->head.output.present ? g->head.output : g->head.token_embd;
+  const int r = t->all_gather(g->bufs[AOTCU_BUF_LOGITS], g->tp_logits_full, (size_t)out_t.rows, NCCL_FLOAT32, t->comm, g->c->stream);
+  if (r != 0) return fail(AOTCU_ERR_CUDA, "ncclAllGather: %s", t->get_error_string(r));
+  return 0;
+}
+
 static int gpu_add(aotcu_gpu* g, float* x, const float* y, size_t n) {
   note_write(g, x);
   return launch(g->c, add_inplace_kernel, dim3(grid_for(g->c, n, 256)), dim3(256), 0, x, y, n);
@@ -898,11 +917,13 @@ static int mega_setup(aotcu_gpu* g) {
   const int v_chunk = (int)(stage_floats / 2 / (d.head_dim + 4));  // positions per chunk buffer
   if (v_chunk < 8) return 0;
   // One CTA per SM must be resident for the grid barriers.
-  CU_TRY(cudaFuncSetAttribute(decode_step_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
-  CU_TRY(cudaFuncSetAttribute(decode_step_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  CU_TRY(cudaFuncSetAttribute(decode_step_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  CU_TRY(cudaFuncSetAttribute(decode_step_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  CU_TRY(cudaFuncSetAttribute(decode_step_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+  CU_TRY(cudaFuncSetAttribute(decode_step_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
   g->mega_smem = (size_t)n_stages * stage_bytes + fixed;
   int per_sm = 0;
-  CU_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel<true>, MEGA_THREADS, g->mega_smem));
+  CU_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel<true, true>, MEGA_THREADS, g->mega_smem));
   if (per_sm < 1) return 0;
 
   auto seg = [&](const aotcu_tensor& t, float* out) { return GemvSeg{wptr(g, t), out, (int)t.rows, t.kind}; };
@@ -933,7 +954,7 @@ static int mega_setup(aotcu_gpu* g) {
   };
   // Tagged vectors: residual, q, k, v, attention output, activated hidden. Zeroed once:
   // tag 0 is never waited for.
-  const size_t ll_words = (size_t)d.dim + qd + 2 * kvd + qd + (size_t)d.hidden;
+  const size_t ll_words = (size_t)d.dim + qd + 2 * kvd + qd + (size_t)d.hidden + (size_t)d.n_head * g->n_ctx;
   CU_TRY(cudaMalloc(&g->d_ll, ll_words * sizeof(LLWord)));
   CU_TRY(cudaMemset(g->d_ll, 0, ll_words * sizeof(LLWord)));
   LLWord* const xl = reinterpret_cast<LLWord*>(g->d_ll);
@@ -942,6 +963,7 @@ static int mega_setup(aotcu_gpu* g) {
   LLWord* const vl = kl + kvd;
   LLWord* const attl = vl + kvd;
   LLWord* const hbl = attl + qd;
+  LLWord* const scl = hbl + d.hidden;
   auto as_out = [](LLWord* p) { return reinterpret_cast<float*>(p); };
   std::vector<StepLayer> hl(d.n_layer + 1);
   for (int i = 0; i < d.n_layer; i++) {
@@ -964,7 +986,7 @@ static int mega_setup(aotcu_gpu* g) {
   CU_TRY(cudaMemset(g->d_grid_bar, 0, 2 * sizeof(unsigned)));
   StepParams& P = g->step_params;
   P.dim = d.dim; P.hidden = d.hidden; P.n_layer = d.n_layer; P.n_head = d.n_head; P.n_kv_head = d.n_kv_head;
-  P.head_dim = d.head_dim; P.rot_dim = d.rot_dim; P.vocab = d.vocab; P.n_ctx = (int)g->n_ctx;
+  P.head_dim = d.head_dim; P.rot_dim = d.rot_dim; P.vocab = (int)out_t.rows; P.n_ctx = (int)g->n_ctx;
   P.eps = d.eps; P.qk_norm = d.qk_norm; P.neox = d.rope_neox;
   P.layers = g->d_step_layers;
   P.output_norm = wf32(g, g->head.output_norm);
@@ -972,7 +994,7 @@ static int mega_setup(aotcu_gpu* g) {
   P.token_embd = wptr(g, g->head.token_embd);
   P.embd_kind = g->head.token_embd.kind;
   P.embd_row_bytes = kind_row_bytes(g->head.token_embd.kind, g->head.token_embd.cols);
-  P.xl = xl; P.ql = ql; P.kl = kl; P.vl = vl; P.attl = attl; P.hbl = hbl;
+  P.xl = xl; P.ql = ql; P.kl = kl; P.vl = vl; P.attl = attl; P.hbl = hbl; P.scl = scl;
   P.x = g->bufs[AOTCU_BUF_X];
   P.logits = g->bufs[AOTCU_BUF_LOGITS]; P.k_cache = g->bufs[AOTCU_BUF_KCACHE]; P.v_cache = g->bufs[AOTCU_BUF_VCACHE];
   P.epoch = g->d_grid_bar + 1;
@@ -985,6 +1007,28 @@ static int mega_setup(aotcu_gpu* g) {
   P.spin_limit = 1 << 21;  // about two seconds of polling
   g->mega_ok = true;
   return 0;
+}
+
+static void drop_graphs(aotcu_gpu* g) {
+  for (auto& e : g->decode_graph)
+    if (e) {
+      cudaGraphExecDestroy(e);
+      e = nullptr;
+    }
+  for (auto& e : g->gen_graph)
+    if (e) {
+      cudaGraphExecDestroy(e);
+      e = nullptr;
+    }
+}
+
+// Whether the one-kernel step at position `pos` shares each head between several CTAs: the
+// head's cached K and V rows no longer fit one CTA's staging area, and there are at least
+// two CTAs per head. The choice is the host's (it selects the kernel variant), so that the
+// short-context variant carries none of the long-context code.
+static int mega_split(const aotcu_gpu* g, size_t pos) {
+  const StepParams& P = g->step_params;
+  return g->mega_ok && g->use_mega && g->c->n_sm >= 2 * P.n_head && 2 * (pos + 1) * (size_t)P.head_dim > (size_t)P.stage_floats;
 }
 
 static int enqueue_mega(aotcu_gpu* g, int want_logits, bool with_argmax, unsigned long long* prof = nullptr,
@@ -1008,8 +1052,11 @@ static int enqueue_mega(aotcu_gpu* g, int want_logits, bool with_argmax, unsigne
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = P.tp.world > 1 ? cudaLaunchKernelEx(&cfg, decode_step_kernel<true>, P)
-                                 : cudaLaunchKernelEx(&cfg, decode_step_kernel<false>, P);
+  cudaError_t e;
+  if (g->split_now)
+    e = P.tp.world > 1 ? cudaLaunchKernelEx(&cfg, decode_step_kernel<true, true>, P) : cudaLaunchKernelEx(&cfg, decode_step_kernel<false, true>, P);
+  else
+    e = P.tp.world > 1 ? cudaLaunchKernelEx(&cfg, decode_step_kernel<true, false>, P) : cudaLaunchKernelEx(&cfg, decode_step_kernel<false, false>, P);
   if (e != cudaSuccess) return fail(AOTCU_ERR_CUDA, "decode_step_kernel launch: %s", cudaGetErrorString(e));
   c->launches++;
   g->qsrc = aotcu_gpu::QSrc();
@@ -1027,7 +1074,10 @@ static int enqueue_decode(aotcu_gpu* g, int want_logits, bool with_argmax) {
   if (want_logits) {
     if (int rc = logits_from(g, g->bufs[AOTCU_BUF_X])) return rc;
     if (with_argmax) {
-      if (int rc = launch(g->c, argmax_kernel, dim3(1), dim3(1024), 0, (const float*)g->bufs[AOTCU_BUF_LOGITS], (int)d.vocab,
+      if (g->head_sharded)
+        if (int rc = tp_gather_logits(g)) return rc;
+      if (int rc = launch(g->c, argmax_kernel, dim3(1), dim3(1024), 0,
+                          (const float*)(g->head_sharded ? g->tp_logits_full : g->bufs[AOTCU_BUF_LOGITS]), (int)d.vocab,
                           g->d_out_token, g->d_step, g->d_history, (int)g->history_cap))
         return rc;
     }
@@ -1564,9 +1614,7 @@ void aotcu_gpu_free(aotcu_gpu* g) {
   if (!g) return;
   cudaSetDevice(g->c->device);
   cudaStreamSynchronize(g->c->stream);
-  for (int i = 0; i < 2; i++)
-    if (g->decode_graph[i]) cudaGraphExecDestroy(g->decode_graph[i]);
-  if (g->gen_graph) cudaGraphExecDestroy(g->gen_graph);
+  drop_graphs(g);
   for (int i = 0; i < AOTCU_N_BUFS; i++) cudaFree(g->bufs[i]);
   cudaFree(g->d_weights);
   cudaFree(g->rope_table);
@@ -1588,6 +1636,7 @@ void aotcu_gpu_free(aotcu_gpu* g) {
   for (void* p : g->tp_peer_map)
     if (p) cudaIpcCloseMemHandle(p);
   cudaFree(g->tp_inbox);
+  cudaFree(g->tp_logits_full);
   if (g->h_pinned) cudaFreeHost(g->h_pinned);
   delete g;
 }
@@ -1723,11 +1772,13 @@ int aotcu_forward(aotcu_gpu* g, uint32_t token, size_t pos, int want_logits) {
   if (int rc = ctx_set_device(g->c)) return rc;
   if (int rc = set_step(g, token, pos, 0)) return rc;
   want_logits = want_logits ? 1 : 0;
+  g->split_now = mega_split(g, pos);
   if (g->use_graph) {
-    if (!g->decode_graph[want_logits])
-      if (int rc = capture_graph(g, &g->decode_graph[want_logits], &g->decode_graph_kernels[want_logits], want_logits, false)) return rc;
-    CU_TRY(cudaGraphLaunch(g->decode_graph[want_logits], g->c->stream));
-    g->c->launches += g->decode_graph_kernels[want_logits];
+    const int gi = want_logits + 2 * g->split_now;
+    if (!g->decode_graph[gi])
+      if (int rc = capture_graph(g, &g->decode_graph[gi], &g->decode_graph_kernels[gi], want_logits, false)) return rc;
+    CU_TRY(cudaGraphLaunch(g->decode_graph[gi], g->c->stream));
+    g->c->launches += g->decode_graph_kernels[gi];
   } else {
     if (int rc = enqueue_decode(g, want_logits, false)) return rc;
   }
@@ -1758,6 +1809,12 @@ int aotcu_forward_batch(aotcu_gpu* g, const uint32_t* tokens, size_t n, size_t p
 
 int aotcu_logits(aotcu_gpu* g, float* host_dst) {
   ARG_CHECK(g && host_dst, "NULL argument");
+  if (g->head_sharded) {
+    // collective: every rank of the group calls this after the same forward call
+    if (int rc = ctx_set_device(g->c)) return rc;
+    if (int rc = tp_gather_logits(g)) return rc;
+    return aotcu_d2h(g->c, host_dst, g->tp_logits_full, (size_t)g->head.dims.vocab * sizeof(float));
+  }
   return aotcu_d2h(g->c, host_dst, g->bufs[AOTCU_BUF_LOGITS], (size_t)g->head.dims.vocab * sizeof(float));
 }
 
@@ -1771,16 +1828,21 @@ int aotcu_generate(aotcu_gpu* g, uint32_t token, size_t pos, size_t n_steps, uin
   aotcu_ctx* c = g->c;
   if (int rc = ctx_set_device(c)) return rc;
   if (int rc = set_step(g, token, pos, 0)) return rc;
-  if (g->use_graph && !g->gen_graph)
-    if (int rc = capture_graph(g, &g->gen_graph, &g->gen_graph_kernels, 1, true)) return rc;
+  if (g->use_graph)
+    for (int v = mega_split(g, pos); v <= mega_split(g, pos + n_steps - 1); v++) {
+      g->split_now = v;
+      if (!g->gen_graph[v])
+        if (int rc = capture_graph(g, &g->gen_graph[v], &g->gen_graph_kernels[v], 1, true)) return rc;
+    }
   cudaEvent_t e0, e1;
   CU_TRY(cudaEventCreate(&e0));
   CU_TRY(cudaEventCreate(&e1));
   CU_TRY(cudaEventRecord(e0, c->stream));
   for (size_t s = 0; s < n_steps; s++) {
+    g->split_now = mega_split(g, pos + s);  // the device advances the position by one per step
     if (g->use_graph) {
-      CU_TRY(cudaGraphLaunch(g->gen_graph, c->stream));
-      c->launches += g->gen_graph_kernels;
+      CU_TRY(cudaGraphLaunch(g->gen_graph[g->split_now], c->stream));
+      c->launches += g->gen_graph_kernels[g->split_now];
     } else {
       if (int rc = enqueue_decode(g, 1, true)) return rc;
     }
@@ -1812,7 +1874,7 @@ int aotcu_tp_inbox_handle(aotcu_gpu* g, uint8_t out_handle[64]) {
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
   if (int rc = ctx_set_device(g->c)) return rc;
   if (!g->tp_inbox) {
-    const size_t words = (size_t)2 * TP_MAX_WORLD * g->head.dims.dim;
+    const size_t words = (size_t)2 * TP_MAX_WORLD * g->head.dims.dim + 2 * TP_MAX_WORLD;  // partial rows, argmax slots
     CU_TRY(cudaMalloc(&g->tp_inbox, words * sizeof(LLWord)));
     CU_TRY(cudaMemset(g->tp_inbox, 0, words * sizeof(LLWord)));
   }
@@ -1830,6 +1892,15 @@ int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world,
   ARG_CHECK(!g->tp, "this Gpu already belongs to a tensor-parallel group");
   if (int rc = ctx_set_device(g->c)) return rc;
   CU_TRY(cudaStreamSynchronize(g->c->stream));
+  const aotcu_tensor& out_t = g->head.output.present ? g->head.output : g->head.token_embd;
+  const size_t vocab = (size_t)g->head.dims.vocab;
+  ARG_CHECK((size_t)out_t.rows == vocab || (size_t)out_t.rows * world == vocab,
+            "the output head has %zu rows: neither the vocabulary (%zu) nor one of %d equal slices", (size_t)out_t.rows, vocab, world);
+  if ((size_t)out_t.rows != vocab) {
+    g->head_sharded = true;
+    g->head_row0 = (size_t)rank * out_t.rows;
+    CU_TRY(cudaMalloc(&g->tp_logits_full, vocab * sizeof(float)));
+  }
   // Peers' inboxes first, the (blocking, collective) communicator second: once any rank is
   // back from this call, every rank has mapped every inbox.
   const bool fused = world > 1 && peer_handles && g->tp_inbox && g->mega_ok;
@@ -1838,6 +1909,9 @@ int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world,
     x.world = world;
     x.rank = rank;
     x.dim = g->head.dims.dim;
+    x.head_sharded = g->head_sharded ? 1 : 0;
+    x.head_row0 = (int)g->head_row0;
+    x.arg_off = 2 * TP_MAX_WORLD * x.dim;
     for (int r = 0; r < world; r++) {
       if (r == rank) {
         x.inbox[r] = g->tp_inbox;
@@ -1874,15 +1948,7 @@ int aotcu_tp_attach(aotcu_gpu* g, const char* nccl_library, int rank, int world,
       return rc;
     }
   }
-  for (int i = 0; i < 2; i++)
-    if (g->decode_graph[i]) {
-      cudaGraphExecDestroy(g->decode_graph[i]);
-      g->decode_graph[i] = nullptr;
-    }
-  if (g->gen_graph) {
-    cudaGraphExecDestroy(g->gen_graph);
-    g->gen_graph = nullptr;
-  }
+  drop_graphs(g);
   g->tp = t;
   // Without mapped inboxes the one-kernel step has no exchange between ranks: the sharded
   // model then takes the per-operator path with NCCL all-reduces.
@@ -1902,15 +1968,7 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
     if (value && !g->mega_ok) return fail(AOTCU_ERR_UNSUPPORTED, "this model cannot use the one-kernel decode step");
     if (g->use_mega != (value != 0)) {
       CU_TRY(cudaStreamSynchronize(g->c->stream));
-      for (int i = 0; i < 2; i++)
-        if (g->decode_graph[i]) {
-          cudaGraphExecDestroy(g->decode_graph[i]);
-          g->decode_graph[i] = nullptr;
-        }
-      if (g->gen_graph) {
-        cudaGraphExecDestroy(g->gen_graph);
-        g->gen_graph = nullptr;
-      }
+      drop_graphs(g);
     }
     g->use_mega = value != 0;
     return 0;
@@ -1926,15 +1984,7 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
   if (!strcmp(name, "fast") || !strcmp(name, "exact") || !strcmp(name, "spin_limit")) {
     // Parameters of the one-kernel step are baked into the captured graphs: drop them.
     CU_TRY(cudaStreamSynchronize(g->c->stream));
-    for (int i = 0; i < 2; i++)
-      if (g->decode_graph[i]) {
-        cudaGraphExecDestroy(g->decode_graph[i]);
-        g->decode_graph[i] = nullptr;
-      }
-    if (g->gen_graph) {
-      cudaGraphExecDestroy(g->gen_graph);
-      g->gen_graph = nullptr;
-    }
+    drop_graphs(g);
     if (!strcmp(name, "spin_limit")) {
       ARG_CHECK(value >= 1, "spin_limit must be at least 1");
       g->step_params.spin_limit = value;
@@ -1950,15 +2000,7 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
     if (g->c->pdl != (value != 0)) {
       // Captured graphs bake the launch attributes in; drop them.
       CU_TRY(cudaStreamSynchronize(g->c->stream));
-      for (int i = 0; i < 2; i++)
-        if (g->decode_graph[i]) {
-          cudaGraphExecDestroy(g->decode_graph[i]);
-          g->decode_graph[i] = nullptr;
-        }
-      if (g->gen_graph) {
-        cudaGraphExecDestroy(g->gen_graph);
-        g->gen_graph = nullptr;
-      }
+      drop_graphs(g);
     }
     g->c->pdl = value != 0;
     return 0;
@@ -2106,6 +2148,7 @@ int aotcu_gpu_profile_step(aotcu_gpu* g, uint32_t token, size_t pos, int cta, ui
   CU_TRY(cudaMalloc(&d, 32 * sizeof(unsigned long long)));
   CU_TRY(cudaMemsetAsync(d, 0, 32 * sizeof(unsigned long long), c->stream));
   int rc = set_step(g, token, pos, 0);
+  g->split_now = mega_split(g, pos);
   if (!rc) rc = enqueue_mega(g, 1, false, d, cta);
   if (!rc) rc = check_device_errors(c);
   if (!rc) {
@@ -2131,6 +2174,7 @@ extern "C" int aotcu_gpu_timeline_step(aotcu_gpu* g, uint32_t token, size_t pos,
   CU_TRY(cudaMalloc(&d, bytes));
   CU_TRY(cudaMemsetAsync(d, 0, bytes, c->stream));
   int rc = set_step(g, token, pos, 0);
+  g->split_now = mega_split(g, pos);
   if (!rc) rc = enqueue_mega(g, 1, false, nullptr, 0, d, layer);
   if (!rc) rc = check_device_errors(c);
   if (!rc) {

@@ -42,7 +42,7 @@ namespace aot {
 // A reader asks for all of its words at once and asks again, for all of them, until every
 // tag matches; examining them one after the other would cost one L2 round trip per word
 // that was still missing at the first look.
-// Tags are unique per (launch, phase): (launch count << 10) | phase id, phase id >= 1;
+// Tags are unique per (launch, phase): (launch count << 11) | phase id, phase id >= 1;
 // a zeroed buffer therefore never matches.
 //
 // Every wait is bounded: `abort` points at two shared words of the CTA, [0] = a wait of this
@@ -126,7 +126,11 @@ __device__ __forceinline__ void cta_rows(int span, int& c0, int& c1) {
 // rank order (so every rank gets the same bits) and publishes the new residual row locally.
 struct TpExchange {
   int world, rank, dim;
-  LLWord* inbox[8];  // inbox of rank d (peer mapping), layout [2 products][world][dim]
+  int head_sharded;  // the output head is split by vocabulary rows: ranks exchange their best (logit, id)
+  int head_row0;     // first vocabulary row of this rank's slice
+  int arg_off;       // word offset of the [world][2] argmax slots behind the partial rows
+  int pad_[2];       // keeps the members behind this struct on their former 16-byte phase
+  LLWord* inbox[8];  // inbox of rank d (peer mapping), layout [2 products][world][dim], then [world][2]
 };
 
 __device__ __forceinline__ void ll_store_sys(LLWord* p, float v, uint32_t tag) {
@@ -222,6 +226,7 @@ struct StepParams {
   int prof_cta;
   unsigned long long* timeline;  // optional: [grid][16] global-timer stamps at the phase boundaries of one layer
   int timeline_layer;
+  LLWord* scl;  // [n_head][n_ctx] attention scores, when several CTAs share a head
 };
 
 // ---- shared-memory ring --------------------------------------------------------------------
@@ -844,11 +849,135 @@ __device__ __forceinline__ void attention_chunked(const StepParams& P, int li, i
   if (tid < hd) ll_store(P.attl + h * hd + tid, o, tag_out);
 }
 
+// How `S` CTAs share one head when its cached rows do not fit one CTA's staging area.
+// Scores: positions are cut into S contiguous ranges, one per CTA; every score is published
+// as a tagged word. Value mix: the head's dimensions are cut into slices of `dw` (a multiple
+// of 16, so staged slices stay 16-byte aligned and at least half a cache line); the first
+// `n2` CTAs wait for all of the head's scores, run the softmax (each the same arithmetic on
+// the same values, so the same bits) and mix their slice, positions in order.
+struct AttnSplit {
+  int S, dw, n2;
+};
+__device__ __forceinline__ AttnSplit attn_split_plan(int grid, int n_head, int hd) {
+  AttnSplit a;
+  a.S = n_head > 0 ? grid / n_head : 0;
+  const int h16 = hd >> 4;
+  a.dw = a.S > 0 ? 16 * ((h16 + a.S - 1) / a.S) : hd;
+  a.n2 = (hd + a.dw - 1) / a.dw;
+  return a;
+}
+
+// Requests the cached rows split-CTA `s` of head `h` will read into L2, long before use.
+__device__ __noinline__ void attn_split_prefetch(const float* k_cache, const float* v_cache, int n_ctx, int hd, int n_head, int n_kv_head,
+                                                 int li, int pos, int tid, int T) {
+  const AttnSplit a = attn_split_plan(gridDim.x, n_head, hd);
+  if ((int)blockIdx.x >= a.S * n_head) return;
+  const int h = blockIdx.x % n_head, s = blockIdx.x / n_head;
+  const int kvd = n_kv_head * hd, kvh = h / (n_head / n_kv_head), n = pos + 1;
+  const int per = (n + a.S - 1) / a.S, t0 = min(pos, s * per), t1 = min(pos, t0 + per);
+  const float* kc = k_cache + (size_t)li * n_ctx * kvd + kvh * hd;
+  const float* vc = v_cache + (size_t)li * n_ctx * kvd + kvh * hd + s * a.dw;
+  const int lines = (hd * 4 + 127) / 128;
+  for (int j = tid; j < (t1 - t0) * lines; j += T) {
+    const int t = t0 + j / lines, ln = j % lines;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(kc + (size_t)t * kvd + 32 * ln));
+  }
+  if (s < a.n2) {
+    const int vlines = (a.dw * 4 + 127) / 128;
+    for (int j = tid; j < pos * vlines; j += T) {
+      const int t = j / vlines, ln = j % vlines;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(vc + (size_t)t * kvd + 32 * ln));
+    }
+  }
+}
+
+// Scores and value mix of split-CTA `s` of head h. q, k, v of the token being decoded are in
+// sq, sk, sv (every CTA of the head prepared the same values). Only the long-context
+// variant of the kernel contains this code; its inputs are gathered by value.
+struct AttnSplitArgs {
+  int li, h, s, pos, tid, T;
+  int head_dim, n_head, n_kv_head, n_ctx, small_floats, v_chunk, fast;
+  uint32_t tag_out;
+  float *k_cache, *v_cache;
+  LLWord *scl, *attl;
+  float *scr, *red;
+  SeqSumScratch* ss;
+  volatile int* abort;
+  int* err;
+};
+__device__ __forceinline__ void attention_split(const AttnSplitArgs A) {
+  const int tid = A.tid, T = A.T, pos = A.pos, s = A.s;
+  const CtaGroup g{tid, T, 1};
+  const MegaSmem M{nullptr, A.scr, A.ss, A.red, A.abort, A.err};
+  const AttnSplit a = attn_split_plan(gridDim.x, A.n_head, A.head_dim);
+  const uint32_t tag_sc = A.tag_out | 1024u;
+  const int hd = A.head_dim, kvd = A.n_kv_head * hd, kvh = A.h / (A.n_head / A.n_kv_head), n = pos + 1, hd4 = hd >> 2;
+  float* sq = A.scr;
+  float* sk = sq + hd;
+  float* sv = sk + hd;
+  float* sc = sv + 2 * hd;
+  float* vbuf = A.scr + A.small_floats;
+  const float* kc = A.k_cache + (size_t)A.li * A.n_ctx * kvd;
+  const float* vc = A.v_cache + (size_t)A.li * A.n_ctx * kvd;
+  const float scale = 1.0f / sqrtf((float)hd);
+  const float4* qt = reinterpret_cast<const float4*>(sq);
+  const int kstride = hd + 4, chunk = A.v_chunk, buf_floats = chunk * kstride;
+  LLWord* scl = A.scl + (size_t)A.h * A.n_ctx;
+  const int per = (n + a.S - 1) / a.S, t0 = min(n, s * per), t1 = min(n, t0 + per);
+  if (t0 < t1) stage_kv_rows(vbuf, kstride, kc, kvd, kvh * hd, hd4, t0, min(chunk, t1 - t0), pos, sk, tid, T);
+#pragma unroll 1
+  for (int c0 = t0, ci = 0; c0 < t1; c0 += chunk, ci++) {
+    const int cn = min(chunk, t1 - c0);
+    float* cur_buf = vbuf + (ci & 1) * buf_floats;
+    if (c0 + chunk < t1) {
+      stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, kstride, kc, kvd, kvh * hd, hd4, c0 + chunk, min(chunk, t1 - c0 - chunk), pos, sk, tid, T);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    g.sync();
+    for (int t = tid; t < cn; t += T) {
+      const float4* kt = reinterpret_cast<const float4*>(cur_buf + t * kstride);
+      const float dot = qk_dot(qt, [&](int j) { return kt[j]; }, hd4);
+      ll_store(scl + c0 + t, fmul(dot, scale), tag_sc);
+    }
+    g.sync();  // this buffer is refilled two chunks later
+  }
+  if (s >= a.n2) return;
+  const int d0 = s * a.dw, dn = min(a.dw, hd - d0), dn4 = dn >> 2;
+  const int vchunk = buf_floats / dn;  // positions per buffer when rows are dn floats
+  stage_kv_rows(vbuf, dn, vc, kvd, kvh * hd + d0, dn4, 0, min(vchunk, n), pos, sv + d0, tid, T);
+  float lmax = -INFINITY;
+  for (int t = tid; t < n; t += T) {
+    const float v = ll_wait(scl + t, tag_sc, A.abort, A.err);
+    sc[t] = v;
+    lmax = fmaxf(lmax, v);
+  }
+  softmax_rows(sc, n, lmax, A.fast, M, g);
+  float o = 0.0f;
+#pragma unroll 1
+  for (int c0 = 0, ci = 0; c0 < n; c0 += vchunk, ci++) {
+    const int cn = min(vchunk, n - c0);
+    const float* cur_buf = vbuf + (ci & 1) * buf_floats;
+    if (c0 + vchunk < n) {
+      stage_kv_rows(vbuf + ((ci + 1) & 1) * buf_floats, dn, vc, kvd, kvh * hd + d0, dn4, c0 + vchunk, min(vchunk, n - c0 - vchunk), pos, sv + d0, tid, T);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    g.sync();
+    if (tid < dn) o = value_mix(o, sc + c0, cur_buf + tid, dn, cn);
+    g.sync();
+  }
+  if (tid < dn) ll_store(A.attl + A.h * hd + d0 + tid, o, A.tag_out);
+}
+
 // Per-head q/k norm, RoPE, KV store and attention for head `h` (ops.rs:74-87, 40-70,
 // 152-157, 185-218), by the consumer warps of one CTA. `staged`: attn_stage_early has put
 // the cached rows of this head into the staging area.
+template <bool SPLIT>
 __device__ __forceinline__ void phase_attention(const StepParams& P, int li, int h, int pos, uint32_t tag_in, uint32_t tag_out, bool staged,
-                                             const MegaSmem& M, int tid, int T, unsigned long long* prof) {
+                                             const MegaSmem& M, int tid, int T, unsigned long long* prof, int split_s) {
   const CtaGroup g{tid, T, 1};
   SubProf pf{prof, clock64()};
   const int hd = P.head_dim, kvd = P.n_kv_head * hd, gqa = P.n_head / P.n_kv_head, kvh = h / gqa;
@@ -899,13 +1028,19 @@ __device__ __forceinline__ void phase_attention(const StepParams& P, int li, int
     v[i1] = fadd(fmul(x0, rope_s), fmul(x1, rope_c));
   }
   g.sync();
-  if (h % gqa == 0) {
+  if (h % gqa == 0 && split_s == 0) {
     for (int i = tid; i < hd; i += T) {
       kc[(size_t)pos * kvd + kvh * hd + i] = sk[i];
       vc[(size_t)pos * kvd + kvh * hd + i] = sv[i];
     }
   }
   pf.mark(20);
+  if (SPLIT) {
+    attention_split(AttnSplitArgs{li, h, split_s, pos, tid, T, P.head_dim, P.n_head, P.n_kv_head, P.n_ctx, P.small_floats, P.v_chunk,
+                                  P.fast, tag_out, P.k_cache, P.v_cache, P.scl, P.attl, M.scr, M.red, M.ss, M.abort, M.err});
+    pf.mark(24);
+    return;
+  }
   if (!staged) {
     attention_chunked(P, li, h, pos, tag_out, M, tid, T);
     pf.mark(24);
@@ -941,7 +1076,11 @@ __device__ __forceinline__ void phase_attention(const StepParams& P, int li, int
   pf.mark(24);
 }
 
-// Greedy argmax of the logits (sampler.rs:99-109) and the cursor update, CTA 0 only.
+// Greedy argmax of the logits (sampler.rs:99-109) and the cursor update, CTA 0 only. With a
+// vocabulary-sharded head (TP) every rank finds the best of its slice, stores {logit, id}
+// into every rank's inbox and picks the best of the world: highest logit, lowest id on ties,
+// which is the first maximum of the whole vector.
+template <bool TP>
 __device__ void phase_argmax(const StepParams& P, const MegaSmem& M, const CtaGroup& g) {
   float best = -INFINITY;
   int idx = 0x7fffffff;
@@ -975,6 +1114,27 @@ __device__ void phase_argmax(const StepParams& P, const MegaSmem& M, const CtaGr
       }
     }
     if (idx == 0x7fffffff) idx = 0;
+    if (TP && P.tp.head_sharded) {
+      const uint32_t tag = (*P.epoch << 11) + 5u * (uint32_t)P.n_layer + 8u;
+      idx += P.tp.head_row0;
+      for (int r = 0; r < P.tp.world; r++) {
+        LLWord* slot = P.tp.inbox[r] + P.tp.arg_off + 2 * P.tp.rank;
+        ll_store_sys(slot, best, tag);
+        ll_store_sys(slot + 1, __int_as_float(idx), tag);
+      }
+      best = -INFINITY;
+      idx = 0x7fffffff;
+      for (int r = 0; r < P.tp.world; r++) {
+        const LLWord* slot = P.tp.inbox[P.tp.rank] + P.tp.arg_off + 2 * r;
+        const float v = ll_wait_sys(slot, tag, M.abort, M.err);
+        const int i = __float_as_int(ll_wait_sys(slot + 1, tag, M.abort, M.err));
+        if (v > best || (v == best && i < idx)) {
+          best = v;
+          idx = i;
+        }
+      }
+      if (idx == 0x7fffffff) idx = 0;
+    }
     if (P.out_token) *P.out_token = idx;
     int gcount = P.step[2];
     if (P.history && gcount < P.history_cap) P.history[gcount] = idx;
@@ -997,7 +1157,9 @@ static_assert(sizeof(SeqSumScratch) <= MEGA_TERMS_BYTES, "SeqSumScratch must fit
 constexpr int MEGA_TAIL_BYTES = MEGA_BAR_BYTES + 64 * 4 + 16 + MEGA_TERMS_BYTES;
 
 // TP: this GPU holds one shard of a row-sharded model and exchanges partial rows with its peers.
-template <bool TP>
+// SPLIT: the long-context variant, in which several CTAs share each head's attention (the
+// host picks the variant from the position; see attention_split).
+template <bool TP, bool SPLIT>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const StepParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   // [stages][sx images][scratch][barriers 128 B][red 64 floats][abort][term strips | SeqSumScratch][table]
@@ -1078,8 +1240,12 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   unsigned bar_target = 0;
   bool staged = false;
   const int token = P.step[0], pos = P.step[1];
+  // Long contexts: the cached rows of a head no longer fit one CTA's staging area, and the
+  // CTAs beyond the head count would idle through the attention phase; share each head.
+  // (The plan is a few integer operations: it is recomputed where it is used rather than
+  // kept in registers across the whole step.)
   // Tags of this launch: phase k (1..5) of layer li is tag_base + 5 * li + k.
-  const uint32_t tag_base = *P.epoch << 10;
+  const uint32_t tag_base = *P.epoch << 11;
   const bool prof_on = P.prof && (int)blockIdx.x == P.prof_cta && g.tid == 0;
   long long prof_last = clock64();
   int prof_li = -1;  // layer the phase marks belong to
@@ -1125,7 +1291,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     const MegaOp& op = (&L.qkv)[ph];  // qkv, wo, gu, down are consecutive members
     const int slot = ph == 0 ? 1 : 3 * ph + 3;
     const uint32_t tl = tag_base + 5u * (uint32_t)li;  // + k: phase k of this layer
-    if (ph == 0 && !head && (int)blockIdx.x < P.n_head) {
+    if (SPLIT) {
+      if (ph == 0 && !head) attn_split_prefetch(P.k_cache, P.v_cache, P.n_ctx, P.head_dim, P.n_head, P.n_kv_head, li, pos, g.tid, g.nthreads);
+    } else if (ph == 0 && !head && (int)blockIdx.x < P.n_head) {
       // The cached K and V rows this CTA's head will read do not depend on the token being
       // decoded: request them into shared memory now, two phases ahead of their use. When
       // they do not fit, at least ask for them into L2 (the weight stream evicts the cache
@@ -1179,10 +1347,19 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     }
     MEGA_PROF(slot + 1);
     if (ph == 0) {
-      // attention, one head per CTA
-      for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
-        phase_attention(P, li, h, pos, tl + 1u, tl + 2u, staged && h == (int)blockIdx.x, M, g.tid, g.nthreads, prof_on ? P.prof : nullptr);
-        g.sync();
+      // attention: one head per CTA, or several CTAs per head once the context is long
+      if (SPLIT) {
+        if ((int)blockIdx.x < ((int)gridDim.x / P.n_head) * P.n_head) {
+          phase_attention<true>(P, li, blockIdx.x % P.n_head, pos, tl + 1u, tl + 2u, false, M, g.tid, g.nthreads, prof_on ? P.prof : nullptr,
+                                blockIdx.x / P.n_head);
+          g.sync();
+        }
+      } else {
+        for (int h = blockIdx.x; h < P.n_head; h += gridDim.x) {
+          phase_attention<false>(P, li, h, pos, tl + 1u, tl + 2u, staged && h == (int)blockIdx.x, M, g.tid, g.nthreads,
+                                 prof_on ? P.prof : nullptr, 0);
+          g.sync();
+        }
       }
       MEGA_PROF(4);
     }
@@ -1194,7 +1371,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
   }
   if (P.want_logits && P.with_argmax) {
     const bool ok = grid_sync(P, g, bar_target, abort);  // uniform across the CTA
-    if (blockIdx.x == 0 && ok) phase_argmax(P, M, g);
+    if (blockIdx.x == 0 && ok) phase_argmax<TP>(P, M, g);
   }
   // Next launch, next tags. Every CTA read the count before it published anything, and
   // CTA 0 gets here only after consuming words from every CTA.

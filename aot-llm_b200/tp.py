@@ -7,7 +7,12 @@ The split (one rank per GPU):
   columns of this rank's heads (row-parallel) and yields a partial sum;
 * FFN: `ffn_gate` / `ffn_up` lose rows, `ffn_down` keeps the matching columns and yields a
   partial sum;
-* norms, the token embedding and the output head are replicated.
+* the output head loses rows: rank r keeps vocabulary rows [r * vocab / world, (r + 1) * vocab /
+  world). Each rank finds the best logit of its slice and the ranks exchange {logit, id}
+  (the greedy choice is the first maximum of the whole vector, as on one device); the whole
+  logits vector is gathered only when the host asks for it. A tied head (the token embedding
+  doubles as the output matrix) or a vocabulary that does not divide stays replicated;
+* norms and the token embedding are replicated.
 
 Column slices are cut on 256-weight super-block boundaries (32-weight blocks for the Q8_0
 family, single weights for float kinds), so every block of a shard is byte-identical to
@@ -87,8 +92,9 @@ def slice_cols(spec: ModelSpec, t: Tensor, c0: int, c1: int):
     return np.ascontiguousarray(data).reshape(-1), t.rows, c1 - c0
 
 
-def shard_spec(spec: ModelSpec, rank: int, world: int) -> ModelSpec:
-    """The model one rank of `world` holds. world == 1 returns the spec unchanged."""
+def shard_spec(spec: ModelSpec, rank: int, world: int, shard_head: bool = True) -> ModelSpec:
+    """The model one rank of `world` holds. world == 1 returns the spec unchanged.
+    `shard_head=False` keeps the whole output head on every rank."""
     if world == 1:
         return spec
     if not 0 <= rank < world:
@@ -136,7 +142,12 @@ def shard_spec(spec: ModelSpec, rank: int, world: int) -> ModelSpec:
         n.local_attn = l.local_attn
         layers.append(n)
     output_norm = whole("output_norm.weight", spec.head.output_norm)
-    output = whole("output.weight", spec.head.output)
+    out_t = spec.head.output
+    if out_t.present and shard_head and d.vocab % world == 0:
+        per = d.vocab // world
+        output = put("output.weight", slice_rows(spec, out_t, rank * per, (rank + 1) * per)[0], out_t.kind, per, out_t.cols)
+    else:
+        output = whole("output.weight", out_t)
     nd = Dims()
     C.memmove(C.byref(nd), C.byref(d), C.sizeof(Dims))
     nd.n_head, nd.n_kv_head, nd.hidden = nh, nkv, hid

@@ -158,6 +158,18 @@ def cpu_matvec_gbs(pkg, kind: int, rows: int, cols: int, threads: int, seconds: 
     return w.nbytes * n / dt / 1e9, n
 
 
+def profiled_traffic(name: str):
+    """DRAM bytes (read + write) of one launch from the committed ncu summary `profiles/<name>`:
+    the line `dram_bytes_per_launch = N`. None when the summary or the line is missing."""
+    import re
+    try:
+        text = open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles", name)).read()
+    except OSError:
+        return None
+    m = re.search(r"^dram_bytes_per_launch\s*=\s*(\d+)", text, re.M)
+    return int(m.group(1)) if m else None
+
+
 def prompt_tokens_n(vocab: int, n: int):
     return np.random.default_rng(PROMPT_SEED + 1).integers(0, vocab, n).tolist()
 
@@ -328,6 +340,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     barrier()
     gp.close()
 
+    # ---- configs[3]: the 8B-shaped model, sharded over the ranks (one token stream) -----------
+    tp = None
+    if not args.no_tp:
+        g.close()
+        tp = measure_tp(args, pkg, ranks, ctx, local_rank, min(steps, 64), min(warmup, 4))
+
     if rank != 0:
         ranks.close()
         return
@@ -373,10 +391,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": "decode_step_kernel" if one_kernel else "per-operator kernels (whole step)",
                      "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
-                     "peak_source": peak_src, "traffic": 639746560 if one_kernel else None,
+                     "peak_source": peak_src, "traffic": profiled_traffic("decode_step_kernel_tinyllama_decode.md") if one_kernel else None,
                      "algorithmic_bytes_per_launch": int(step_bytes), "avg_launch_us": ms * 1e3 / steps,
                      "roofline_tok_s": peak * 1e9 / step_bytes,
-                     "how": "weights + KV bytes of one token / (device time of the timed loop / steps), CUDA events on the launching stream; traffic = dram read+write of one launch from ncu (profiles/)"},
+                     "how": "weights + KV bytes of one token / (device time of the timed loop / steps), CUDA events on the launching stream; traffic = dram read+write of one launch from the ncu capture summarised in profiles/decode_step_kernel_tinyllama_decode.md (position 9; it grows by 90 KB of KV rows per position)"},
         "gemv_kernel_sweep": {"kernel": "gemv_stream_kernel", "achieved": gemv_gbs, "unit": "GB/s", "frac": gemv_gbs / peak,
                               "launches": int(sweep_launches), "algorithmic_bytes": int(sweep_bytes),
                               "avg_launch_us": sweep_ms * 1e3 / sweep_launches},
@@ -390,16 +408,67 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     }
     if cpu:
         out["cpu_baseline"] = cpu
+    if tp:
+        for k in ("metric", "unit", "higher_is_better", "vs_baseline", "dtype", "data"):
+            tp.pop(k, None)
+        tp["tok_s"], tp["ms_per_token"] = tp.pop("value"), tp.pop("ms_per_step")
+        out["tp"] = tp
     print(json.dumps(out))
     ranks.close()
 
 
-def run_tp(args, rank: int, world: int, local_rank: int):
+def tp_parity(pkg, ranks, ctx, n_layer: int = 2, n_steps: int = 8):
+    """The sharded path against the whole model on rank 0's GPU: a short 8B-shaped model, one
+    prompt chunk and a few decode steps; every rank's gathered logits must agree with the
+    single-device ones to f32 rounding (only the order of the additions over blocks differs)."""
+    info = ranks.info
+    full = pkg.model.qwen3_8b(n_layer=n_layer, seed=0x7A11)
+    sh = pkg.tp.shard_spec(full, info.rank, info.world)
+    g = pkg.Gpu(ctx, sh.head, sh.layers, sh.weights, 128, 64)
+    pkg.tp.join(g, ranks, fused=True)
+    one = pkg.Gpu(ctx, full.head, full.layers, full.weights, 128, 64) if ranks.is_root and info.world > 1 else None
+    toks = prompt_tokens_n(full.head.dims.vocab, 48)
+    worst, agree, total = 0.0, 0, 0
+
+    def compare(lg):
+        nonlocal worst, agree, total
+        if one is None:
+            return
+        lf = one.logits()
+        worst = max(worst, float(np.max(np.abs(lg - lf)) / np.max(np.abs(lf))))
+        agree += int(np.argmax(lg) == np.argmax(lf))
+        total += 1
+
+    g.forward_batch(toks, 0, True)
+    if one:
+        one.forward_batch(toks, 0, True)
+    lg = g.logits()
+    compare(lg)
+    tok, pos = int(np.argmax(lg)), len(toks)
+    for _ in range(n_steps):
+        g.forward(tok, pos, True)
+        if one:
+            one.forward(tok, pos, True)
+        lg = g.logits()
+        compare(lg)
+        tok, pos = int(np.argmax(lg)), pos + 1
+    ids, _ = g.generate(tok, pos, 8)         # in-kernel argmax exchange
+    same = None
+    if one:
+        ids1, _ = one.generate(tok, pos, 8)
+        same = [int(i) for i in ids] == [int(i) for i in ids1]
+        one.close()
+    ranks.barrier()
+    g.close()
+    return {"layers": n_layer, "worst_rel_logit_diff": worst, "same_greedy_choice": f"{agree}/{total}",
+            "same_generated_ids": same, "tolerance": 1e-3}
+
+
+def measure_tp(args, pkg, ranks, ctx, local_rank: int, steps: int, warmup: int):
     """Benchmark configuration 3: Qwen3-8B-shaped decode, row-sharded over the ranks, one token
     stream (strong scaling). Every rank builds the synthetic model from the same seed and
-    keeps its shard."""
-    pkg = graft.import_package()
-    ranks = pkg.ranks.Ranks(pkg.ranks.RankInfo(rank, world, local_rank), backend="nccl")
+    keeps its shard. Returns the result on rank 0, None elsewhere."""
+    rank, world = ranks.info.rank, ranks.info.world
     t_build = time.perf_counter()
     full = pkg.model.qwen3_8b(n_layer=args.tp_layers)
     full_bytes = full.weight_bytes_per_token()
@@ -407,8 +476,7 @@ def run_tp(args, rank: int, world: int, local_rank: int):
     del full
     t_build = time.perf_counter() - t_build
     d = spec.head.dims
-    ctx = pkg.Context(local_rank)
-    n_prompt, steps, warmup = 512, args.steps, max(args.warmup, 3)
+    n_prompt = 512
     g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_prompt + warmup + steps + 8, 64)
     pkg.tp.join(g, ranks, fused=not args.tp_nccl)
     one_kernel = bool(g.set_option("mega_available", 0))
@@ -435,32 +503,51 @@ def run_tp(args, rank: int, world: int, local_rank: int):
     ranks.barrier()
     launches = g.dispatches() - launches0
     ms = ranks.max_over_ranks(ms)
+    g.close()
     tps = steps / (ms * 1e-3)
     peak, peak_src = measured_peak_gbs()
     mid_pos = n_prompt + warmup + steps // 2
     step_bytes = spec.weight_bytes_per_token() + spec.kv_bytes_per_position() * (mid_pos + 1)
     gbs = step_bytes / (ms * 1e-3 / steps) / 1e9
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
-            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "int8 block dot products with f32 accumulation (Q8 activations x Q4_K/Q6_K weights)", "data": "synthetic",
-            "config": {"workload": "configs[3]: Qwen3-8B-shaped decode, Q4_K_M mix, random-init weights, 512-token prompt then greedy decode; "
-                                   "query/KV heads and FFN rows sharded over the ranks, all-reduce after attn_output and ffn_down",
-                       "dim": d.dim, "hidden_per_rank": d.hidden, "n_layer": d.n_layer, "n_head_per_rank": d.n_head,
-                       "n_kv_head_per_rank": d.n_kv_head, "head_dim": d.head_dim, "vocab": d.vocab, "parallelism": f"tp{world}",
-                       "exchange": ("tagged words over peer memory inside the one-kernel step" if one_kernel and world > 1 else
-                                    "none" if world == 1 else "NCCL all-reduce between per-operator kernels"),
-                       "weight_bytes_per_token_whole_model": int(full_bytes),
-                       "weight_bytes_per_token_per_rank": int(spec.weight_bytes_per_token()),
-                       "l2_policy": "inputs_larger_than_l2"},
-            "clocks": clk.summary(), "gpu_launches": int(launches),
-            "prompt": {"value": n_prompt / (prompt_ms * 1e-3), "unit": "tok/s", "ms": prompt_ms},
-            "roofline": {"bound": "hbm", "kernel": "whole decode step of one rank", "achieved": gbs, "peak": peak, "unit": "GB/s",
-                         "frac": gbs / peak, "peak_source": peak_src, "traffic": None,
-                         "algorithmic_bytes_per_launch": int(step_bytes), "roofline_tok_s": peak * 1e9 / step_bytes},
-            "host_build_s": t_build, "generated_head": [int(x) for x in ids[:8]],
-        }))
+    sharded_head = spec.head.output.rows != d.vocab
+    rank_bytes = spec.weight_bytes_per_token()
+    del spec
+    parity = tp_parity(pkg, ranks, ctx) if world > 1 and not args.tp_nccl else None
+    if rank != 0:
+        return None
+    return {
+        "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 block dot products with f32 accumulation (Q8 activations x Q4_K/Q6_K weights)", "data": "synthetic",
+        "config": {"workload": "configs[3]: Qwen3-8B-shaped decode, Q4_K_M mix, random-init weights, 512-token prompt then greedy decode; "
+                               "query/KV heads, FFN rows and the output head's vocabulary rows sharded over the ranks; partial rows of "
+                               "attn_output and ffn_down summed across ranks, best {logit, id} exchanged for the greedy choice",
+                   "dim": d.dim, "hidden_per_rank": d.hidden, "n_layer": d.n_layer, "n_head_per_rank": d.n_head,
+                   "n_kv_head_per_rank": d.n_kv_head, "head_dim": d.head_dim, "vocab": d.vocab, "parallelism": f"tp{world}",
+                   "output_head": "vocabulary rows sharded" if sharded_head else "whole on every rank",
+                   "exchange": ("tagged words over peer memory inside the one-kernel step" if one_kernel and world > 1 else
+                                "none" if world == 1 else "NCCL all-reduce between per-operator kernels"),
+                   "weight_bytes_per_token_whole_model": int(full_bytes),
+                   "weight_bytes_per_token_per_rank": int(rank_bytes),
+                   "l2_policy": "inputs_larger_than_l2"},
+        "clocks": clk.summary(), "gpu_launches": int(launches),
+        "prompt": {"value": n_prompt / (prompt_ms * 1e-3), "unit": "tok/s", "ms": prompt_ms},
+        "roofline": {"bound": "hbm", "kernel": "decode_step_kernel of one rank" if one_kernel else "whole decode step of one rank",
+                     "achieved": gbs, "peak": peak, "unit": "GB/s",
+                     "frac": gbs / peak, "peak_source": peak_src, "traffic": None,
+                     "algorithmic_bytes_per_launch": int(step_bytes), "roofline_tok_s": peak * 1e9 / step_bytes},
+        "parity": parity,
+        "host_build_s": t_build, "generated_head": [int(x) for x in ids[:8]],
+    }
+
+
+def run_tp(args, rank: int, world: int, local_rank: int):
+    pkg = graft.import_package()
+    ranks = pkg.ranks.Ranks(pkg.ranks.RankInfo(rank, world, local_rank), backend="nccl")
+    ctx = pkg.Context(local_rank)
+    out = measure_tp(args, pkg, ranks, ctx, local_rank, args.steps, max(args.warmup, 3))
+    if out is not None:
+        print(json.dumps(out))
     ranks.close()
 
 
@@ -474,6 +561,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp", action="store_true", help="configs[3]: Qwen3-8B-shaped decode sharded over the ranks")
     ap.add_argument("--tp-layers", type=int, default=36)
+    ap.add_argument("--no-tp", action="store_true", help="skip the sharded 8B-shaped model (the line's \"tp\" key)")
     ap.add_argument("--tp-nccl", action="store_true", help="with --tp: exchange through NCCL all-reduces (per-operator path)")
     ap.add_argument("--sweep", action="store_true", help="quant-type kernel sweep (configs[4]) instead of the decode benchmark")
     ap.add_argument("--sweep-small", action="store_true", help="with --sweep: only the two smaller shapes")

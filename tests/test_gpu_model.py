@@ -195,6 +195,41 @@ def test_prompt_chunks_on_tensor_core_tiles_bit_exact(pkg, ob, ctx, arch):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("n_head,n_kv,hd", [(4, 1, 128), (16, 4, 80), (40, 8, 64)])
+def test_heads_shared_by_several_ctas_bit_exact(pkg, ob, ctx, n_head, n_kv, hd):
+    """Once a head's cached rows outgrow one CTA's staging area, the one-kernel step deals
+    each head's positions (scores) and dimensions (value mix) out to several CTAs. Few heads
+    of 128 (the per-rank shape of a sharded 8B model: 37 CTAs per head, 16-wide slices), a
+    head width that is not a power of two (five slices of 16), and a head count that leaves
+    three CTAs per head of which two mix values."""
+    spec = pkg.model.build("split", dim=512, hidden=768, n_layer=2, n_head=n_head, n_kv_head=n_kv, head_dim=hd, vocab=600,
+                           seed=31, kinds=_kquant_kinds, n_ctx_train=512, qk_norm=(hd == 128), rope_neox=(hd == 128))
+    n_ctx, n_prompt, n_gen = 384, 320, 5
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 64)
+    assert g.set_option("mega_available", 0)
+    om = ob.model_from_spec(spec, n_ctx, 64, n_threads=min(8, os.cpu_count() or 1))
+    toks = np.random.default_rng(hd).integers(0, 600, n_prompt).tolist()
+    for c0 in range(0, n_prompt, 64):
+        g.forward_batch(toks[c0:c0 + 64], c0, c0 + 64 == n_prompt)
+        om.forward_batch(toks[c0:c0 + 64], c0, c0 + 64 == n_prompt)
+    tok = ob.argmax(om.logits())
+    for i in range(n_gen):
+        g.forward(tok, n_prompt + i, True)
+        om.forward(tok, n_prompt + i, True)
+        assert_bits_equal(g.read("X"), om.buf("x"), f"x at position {n_prompt + i}")
+        assert_bits_equal(g.logits(), om.logits(), f"logits at position {n_prompt + i}")
+        tok = ob.argmax(om.logits())
+    ids, _ = g.generate(tok, n_prompt + n_gen, 4)
+    want = []
+    for i in range(4):
+        om.forward(tok, n_prompt + n_gen + i, True)
+        tok = ob.argmax(om.logits())
+        want.append(tok)
+    assert ids.tolist() == want
+    ctx.device_status()
+
+
+@pytest.mark.gpu
 @pytest.mark.timeout(600)
 def test_long_context_decode_bit_exact(pkg, ob, ctx):
     """Near the end of a 2048-position context: prompt chunks of 64 fill the cache, then the

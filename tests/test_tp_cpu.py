@@ -50,6 +50,19 @@ def test_shards_are_exact_slices(pkg):
         parts = [sh.weights[sh.layers[i].down.off:sh.layers[i].down.off + sh.layers[i].down.len].reshape(l.down.rows, rbf // world)
                  for sh in shards]
         assert np.array_equal(np.concatenate(parts, axis=1), rows_full)
+    # the output head: vocabulary rows dealt out in rank order; the greedy choice over the
+    # shards' best (logit, id) pairs, lowest id on ties, is the first maximum of the whole
+    out = spec.head.output
+    got = np.concatenate([sh.weights[sh.head.output.off:sh.head.output.off + sh.head.output.len] for sh in shards])
+    assert np.array_equal(got, spec.weights[out.off:out.off + out.len])
+    assert all(sh.head.output.rows * world == d.vocab for sh in shards)
+    logits = np.random.default_rng(1).integers(-3, 4, d.vocab).astype(np.float32)   # many ties
+    per = d.vocab // world
+    best = [(float(logits[r * per:(r + 1) * per].max()), r * per + int(np.argmax(logits[r * per:(r + 1) * per]))) for r in range(world)]
+    pick = min(best, key=lambda b: (-b[0], b[1]))[1]
+    assert pick == int(np.argmax(logits))
+    whole = pkg.tp.shard_spec(spec, 1, world, shard_head=False)
+    assert whole.head.output.rows == d.vocab
     with pytest.raises(ValueError):
         pkg.tp.shard_spec(spec, 0, 3)                      # heads do not split three ways
     assert pkg.tp.shard_spec(spec, 0, 1) is spec
