@@ -60,6 +60,7 @@ struct aotcu_ctx {
   bool pdl = true;  // programmatic dependent launch between the kernels of a stream
   uint64_t launches = 0;
   cudaEvent_t t0 = nullptr, t1 = nullptr;
+  std::vector<struct aotcu_gpu*> gpus;  // live Gpus of this context (freed with it)
 };
 
 constexpr size_t WEIGHT_PAD = 256;
@@ -891,7 +892,7 @@ static int mega_setup(aotcu_gpu* g) {
   // Scratch: a head of norm rows (2 x dim) or attention vectors (q, k, v, squares, scores),
   // then the area that stages cached K and V rows. 72 KB of staging hold every cached row of
   // one head up to 140 positions at head_dim 64; longer contexts go through two chunk buffers.
-  const size_t small_floats = (std::max((size_t)2 * d.dim, (size_t)4 * d.head_dim + ((g->n_ctx + 3) & ~(size_t)3)) + 31) & ~(size_t)31;
+  const size_t small_floats = (std::max((size_t)2 * d.dim, (size_t)5 * d.head_dim + ((g->n_ctx + 3) & ~(size_t)3)) + 31) & ~(size_t)31;
   size_t stage_floats = 18432;
   const size_t table_bytes = (((size_t)d.n_layer + 1) * sizeof(StepLayer) + 15) & ~(size_t)15;
   size_t scratch = 0, fixed = 0;
@@ -914,7 +915,7 @@ static int mega_setup(aotcu_gpu* g) {
     stage_floats -= 2048;  // a small ring starves the products: give staging space back
   }
   if (n_stages < 2) return 0;
-  const int v_chunk = (int)(stage_floats / 2 / (d.head_dim + 4));  // positions per chunk buffer
+  const int v_chunk = (int)(stage_floats / 2 / (d.head_dim + 4)) & ~7;  // positions per chunk buffer (a multiple of 8)
   if (v_chunk < 8) return 0;
   // One CTA per SM must be resident for the grid barriers.
   CU_TRY(cudaFuncSetAttribute(decode_step_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
@@ -1160,6 +1161,8 @@ int aotcu_init(int device, aotcu_ctx** out) {
 void aotcu_free(aotcu_ctx* c) {
   if (!c) return;
   cudaSetDevice(c->device);
+  // A Gpu must not outlive its context: whatever the caller left alive goes first.
+  while (!c->gpus.empty()) aotcu_gpu_free(c->gpus.back());
   if (c->stream) {
     cudaStreamSynchronize(c->stream);
     cudaStreamDestroy(c->stream);
@@ -1479,6 +1482,7 @@ int aotcu_gpu_new(aotcu_ctx* c, const aotcu_model_head* head, const aotcu_layer*
   if (int rc = ctx_set_device(c)) return rc;
   aotcu_gpu* g = new aotcu_gpu();
   g->c = c;
+  c->gpus.push_back(g);
   g->head = *head;
   g->layers.assign(layers, layers + d.n_layer);
   g->n_ctx = n_ctx;
@@ -1612,6 +1616,10 @@ int aotcu_gpu_new(aotcu_ctx* c, const aotcu_model_head* head, const aotcu_layer*
 
 void aotcu_gpu_free(aotcu_gpu* g) {
   if (!g) return;
+  {
+    auto& v = g->c->gpus;
+    v.erase(std::remove(v.begin(), v.end(), g), v.end());
+  }
   cudaSetDevice(g->c->device);
   cudaStreamSynchronize(g->c->stream);
   drop_graphs(g);

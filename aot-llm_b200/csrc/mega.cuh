@@ -724,39 +724,49 @@ __device__ __forceinline__ void softmax_rows(float* sc, int n, float lmax, int f
   for (int t = tid; t < n; t += T) sc[t] = fmul(sc[t], inv);
 }
 
-// o + sum over t < cn of a[t] * v[t * stride], positions in order (ops.rs:208-214).
+// o + sum over t < cn of a[t] * v[t * stride], positions in order (ops.rs:208-214): eight
+// products, then their adds; the add chain is the only dependent work and the compiler's
+// own unrolling of this plain loop overlaps the loads of later rounds with it (measured:
+// 8 cycles per term against 12 to 14 for hand-pipelined or non-unrolled forms). `a` is
+// 16-byte aligned.
 __device__ __forceinline__ float value_mix(float o, const float* a, const float* v, int stride, int cn) {
   int t = 0;
-#pragma unroll 1
   for (; t + 8 <= cn; t += 8) {
-    float pr[8];
-#pragma unroll
-    for (int u = 0; u < 8; u++) pr[u] = fmul(a[t + u], v[(t + u) * stride]);
-#pragma unroll
-    for (int u = 0; u < 8; u++) o = fadd(o, pr[u]);
+    const float4 x = *reinterpret_cast<const float4*>(a + t), y = *reinterpret_cast<const float4*>(a + t + 4);
+    const float p0 = fmul(x.x, v[(t + 0) * stride]), p1 = fmul(x.y, v[(t + 1) * stride]);
+    const float p2 = fmul(x.z, v[(t + 2) * stride]), p3 = fmul(x.w, v[(t + 3) * stride]);
+    const float p4 = fmul(y.x, v[(t + 4) * stride]), p5 = fmul(y.y, v[(t + 5) * stride]);
+    const float p6 = fmul(y.z, v[(t + 6) * stride]), p7 = fmul(y.w, v[(t + 7) * stride]);
+    o = fadd(o, p0); o = fadd(o, p1); o = fadd(o, p2); o = fadd(o, p3);
+    o = fadd(o, p4); o = fadd(o, p5); o = fadd(o, p6); o = fadd(o, p7);
   }
   for (; t < cn; t++) o = fadd(o, fmul(a[t], v[t * stride]));
   return o;
 }
 
+// Which of `nd` head dimensions this thread mixes, or -1: the dimensions are spread over
+// the group's warps, 8 (or 16, or 32) lanes of each, so that the per-warp instruction
+// streams run on all four schedulers instead of one or two.
+__device__ __forceinline__ int mix_dim(int tid, int T, int nd) {
+  const int nwarps = T >> 5;
+  const int per = 8 * nwarps >= nd ? 8 : (16 * nwarps >= nd ? 16 : 32);
+  const int lane = tid & 31, d = (tid >> 5) * per + lane;
+  return lane < per && d < nd ? d : -1;
+}
+
 // q.k over one head (ops.rs:160-166): products first (independent), then the adds in
-// element order. `kchunk(j)` returns float4 chunk j of the cached row.
+// element order. `kchunk(j)` returns float4 chunk j of the cached row; hd4 is even. A plain
+// loop: the compiler's unrolling overlaps later loads with the add chain.
 template <class KChunk>
 __device__ __forceinline__ float qk_dot(const float4* qt, KChunk kchunk, int hd4) {
   float s = 0.0f;
-#pragma unroll 1
-  for (int i0 = 0; i0 < hd4; i0 += 4) {
-    float pr[16];
-#pragma unroll
-    for (int u = 0; u < 4; u++) {
-      const float4 kk = kchunk(i0 + u), qq = qt[i0 + u];
-      pr[4 * u] = fmul(qq.x, kk.x);
-      pr[4 * u + 1] = fmul(qq.y, kk.y);
-      pr[4 * u + 2] = fmul(qq.z, kk.z);
-      pr[4 * u + 3] = fmul(qq.w, kk.w);
-    }
-#pragma unroll
-    for (int u = 0; u < 16; u++) s = fadd(s, pr[u]);
+#pragma unroll 2
+  for (int i0 = 0; i0 < hd4; i0 += 2) {
+    const float4 k0 = kchunk(i0), q0 = qt[i0], k1 = kchunk(i0 + 1), q1 = qt[i0 + 1];
+    const float p0 = fmul(q0.x, k0.x), p1 = fmul(q0.y, k0.y), p2 = fmul(q0.z, k0.z), p3 = fmul(q0.w, k0.w);
+    const float p4 = fmul(q1.x, k1.x), p5 = fmul(q1.y, k1.y), p6 = fmul(q1.z, k1.z), p7 = fmul(q1.w, k1.w);
+    s = fadd(s, p0); s = fadd(s, p1); s = fadd(s, p2); s = fadd(s, p3);
+    s = fadd(s, p4); s = fadd(s, p5); s = fadd(s, p6); s = fadd(s, p7);
   }
   return s;
 }
@@ -799,7 +809,7 @@ __device__ __forceinline__ void attention_chunked(const StepParams& P, int li, i
   float* sq = M.scr;
   float* sk = sq + hd;
   float* sv = sk + hd;
-  float* sc = sv + 2 * hd;
+  float* sc = sv + 3 * hd;
   float* vbuf = M.scr + P.small_floats;
   const float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd;
   const float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd;
@@ -832,6 +842,7 @@ __device__ __forceinline__ void attention_chunked(const StepParams& P, int li, i
   stage_kv_rows(vbuf, hd, vc, kvd, kvh * hd, hd4, 0, min(chunk, n), pos, sv, tid, T);
   softmax_rows(sc, n, lmax, P.fast, M, g);
   float o = 0.0f;
+  const int md = mix_dim(tid, T, hd);
 #pragma unroll 1
   for (int c0 = 0, ci = 0; c0 < n; c0 += chunk, ci++) {
     const int cn = min(chunk, n - c0);
@@ -843,10 +854,10 @@ __device__ __forceinline__ void attention_chunked(const StepParams& P, int li, i
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     g.sync();
-    if (tid < hd) o = value_mix(o, sc + c0, cur_buf + tid, hd, cn);
+    if (md >= 0) o = value_mix(o, sc + c0, cur_buf + md, hd, cn);
     g.sync();
   }
-  if (tid < hd) ll_store(P.attl + h * hd + tid, o, tag_out);
+  if (md >= 0) ll_store(P.attl + h * hd + md, o, tag_out);
 }
 
 // How `S` CTAs share one head when its cached rows do not fit one CTA's staging area.
@@ -904,6 +915,7 @@ struct AttnSplitArgs {
   SeqSumScratch* ss;
   volatile int* abort;
   int* err;
+  unsigned long long* prof;
 };
 __device__ __forceinline__ void attention_split(const AttnSplitArgs A) {
   const int tid = A.tid, T = A.T, pos = A.pos, s = A.s;
@@ -911,11 +923,12 @@ __device__ __forceinline__ void attention_split(const AttnSplitArgs A) {
   const MegaSmem M{nullptr, A.scr, A.ss, A.red, A.abort, A.err};
   const AttnSplit a = attn_split_plan(gridDim.x, A.n_head, A.head_dim);
   const uint32_t tag_sc = A.tag_out | 1024u;
+  SubProf pf{A.prof, clock64()};
   const int hd = A.head_dim, kvd = A.n_kv_head * hd, kvh = A.h / (A.n_head / A.n_kv_head), n = pos + 1, hd4 = hd >> 2;
   float* sq = A.scr;
   float* sk = sq + hd;
   float* sv = sk + hd;
-  float* sc = sv + 2 * hd;
+  float* sc = sv + 3 * hd;
   float* vbuf = A.scr + A.small_floats;
   const float* kc = A.k_cache + (size_t)A.li * A.n_ctx * kvd;
   const float* vc = A.v_cache + (size_t)A.li * A.n_ctx * kvd;
@@ -943,9 +956,10 @@ __device__ __forceinline__ void attention_split(const AttnSplitArgs A) {
     }
     g.sync();  // this buffer is refilled two chunks later
   }
+  pf.mark(21);
   if (s >= a.n2) return;
   const int d0 = s * a.dw, dn = min(a.dw, hd - d0), dn4 = dn >> 2;
-  const int vchunk = buf_floats / dn;  // positions per buffer when rows are dn floats
+  const int vchunk = (buf_floats / dn) & ~7;  // positions per buffer when rows are dn floats (a multiple of 8: aligned reads)
   stage_kv_rows(vbuf, dn, vc, kvd, kvh * hd + d0, dn4, 0, min(vchunk, n), pos, sv + d0, tid, T);
   float lmax = -INFINITY;
   for (int t = tid; t < n; t += T) {
@@ -953,8 +967,11 @@ __device__ __forceinline__ void attention_split(const AttnSplitArgs A) {
     sc[t] = v;
     lmax = fmaxf(lmax, v);
   }
+  pf.mark(22);
   softmax_rows(sc, n, lmax, A.fast, M, g);
+  pf.mark(23);
   float o = 0.0f;
+  const int md = mix_dim(tid, T, dn);
 #pragma unroll 1
   for (int c0 = 0, ci = 0; c0 < n; c0 += vchunk, ci++) {
     const int cn = min(vchunk, n - c0);
@@ -966,10 +983,13 @@ __device__ __forceinline__ void attention_split(const AttnSplitArgs A) {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     g.sync();
-    if (tid < dn) o = value_mix(o, sc + c0, cur_buf + tid, dn, cn);
+    pf.mark(25);
+    if (md >= 0) o = value_mix(o, sc + c0, cur_buf + md, dn, cn);
+    pf.mark(27);
     g.sync();
   }
-  if (tid < dn) ll_store(A.attl + A.h * hd + d0 + tid, o, A.tag_out);
+  if (md >= 0) ll_store(A.attl + A.h * hd + d0 + md, o, A.tag_out);
+  pf.mark(24);
 }
 
 // Per-head q/k norm, RoPE, KV store and attention for head `h` (ops.rs:74-87, 40-70,
@@ -985,8 +1005,8 @@ __device__ __forceinline__ void phase_attention(const StepParams& P, int li, int
   float* sq = M.scr;            // hd
   float* sk = sq + hd;          // hd
   float* sv = sk + hd;          // hd
-  float* sp = sv + hd;          // hd (squares)
-  float* sc = sp + hd;          // n_ctx scores
+  float* sp = sv + hd;          // 2 x hd (squares of q and of k)
+  float* sc = sp + 2 * hd;      // n_ctx scores
   float* stg = M.scr + P.small_floats;  // staging area, 16-byte aligned
   float* kc = P.k_cache + (size_t)li * P.n_ctx * kvd;
   float* vc = P.v_cache + (size_t)li * P.n_ctx * kvd;
@@ -1007,17 +1027,38 @@ __device__ __forceinline__ void phase_attention(const StepParams& P, int li, int
   }
   g.sync();
   if (P.qk_norm) {
-#pragma unroll 1
-    for (int which = 0; which < 2; which++) {
-      float* v = which ? sk : sq;
-      const float* nw = which ? P.layers[li].k_norm : P.layers[li].q_norm;
-      for (int i = tid; i < hd; i += T) sp[i] = fmul(v[i], v[i]);
-      const float ss = cta_sum(sp, hd, (P.fast & FAST_NORM_SUM) != 0, M, g);
-      const float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)hd), P.eps)));
+    // per-head RMS norm of q and of k (ops.rs:74-87): the two sums of squares are
+    // sequential add chains; one thread each, side by side
+    for (int i = tid; i < 2 * hd; i += T) sp[i] = fmul(sq[i], sq[i]);  // sq, sk consecutive; sp holds 2 x hd
+    float ss[2];
+    if (!(P.fast & FAST_NORM_SUM) && hd <= SEQ_CHAIN_MAX) {
       g.sync();
-      for (int i = tid; i < hd; i += T) v[i] = fmul(fmul(v[i], r), nw[i]);
+      if ((tid & 31) == 0 && tid < 64) {
+        const float* p = sp + (tid >> 5) * hd;
+        float a = 0.0f;
+        for (int i = 0; i < hd; i += 8) {
+          const float4 u = *reinterpret_cast<const float4*>(p + i), w = *reinterpret_cast<const float4*>(p + i + 4);
+          a = fadd(a, u.x); a = fadd(a, u.y); a = fadd(a, u.z); a = fadd(a, u.w);
+          a = fadd(a, w.x); a = fadd(a, w.y); a = fadd(a, w.z); a = fadd(a, w.w);
+        }
+        M.red[40 + (tid >> 5)] = a;
+      }
       g.sync();
+      ss[0] = M.red[40];
+      ss[1] = M.red[41];
+    } else {
+      ss[0] = cta_sum(sp, hd, (P.fast & FAST_NORM_SUM) != 0, M, g);
+      g.sync();
+      ss[1] = cta_sum(sp + hd, hd, (P.fast & FAST_NORM_SUM) != 0, M, g);
     }
+    g.sync();
+    for (int i = tid; i < 2 * hd; i += T) {
+      const int which = i >= hd;
+      const float r = fdiv(1.0f, fsqrt(fadd(fdiv(ss[which], (float)hd), P.eps)));
+      const float* nw = which ? P.layers[li].k_norm : P.layers[li].q_norm;
+      sq[i] = fmul(fmul(sq[i], r), nw[i - which * hd]);
+    }
+    g.sync();
   }
   if (tid < 2 * rope_half) {  // rot_dim <= head_dim <= the group's thread count
     float* v = tid < rope_half ? sq : sk;
@@ -1037,8 +1078,7 @@ __device__ __forceinline__ void phase_attention(const StepParams& P, int li, int
   pf.mark(20);
   if (SPLIT) {
     attention_split(AttnSplitArgs{li, h, split_s, pos, tid, T, P.head_dim, P.n_head, P.n_kv_head, P.n_ctx, P.small_floats, P.v_chunk,
-                                  P.fast, tag_out, P.k_cache, P.v_cache, P.scl, P.attl, M.scr, M.red, M.ss, M.abort, M.err});
-    pf.mark(24);
+                                  P.fast, tag_out, P.k_cache, P.v_cache, P.scl, P.attl, M.scr, M.red, M.ss, M.abort, M.err, prof});
     return;
   }
   if (!staged) {
@@ -1072,7 +1112,10 @@ __device__ __forceinline__ void phase_attention(const StepParams& P, int li, int
   pf.mark(23);
   g.sync();
   // value mix, positions in order (ops.rs:208-214)
-  if (tid < hd) ll_store(P.attl + h * hd + tid, value_mix(0.0f, sc, vbuf + tid, hd, n), tag_out);
+  {
+    const int md = mix_dim(tid, T, hd);
+    if (md >= 0) ll_store(P.attl + h * hd + md, value_mix(0.0f, sc, vbuf + md, hd, n), tag_out);
+  }
   pf.mark(24);
 }
 

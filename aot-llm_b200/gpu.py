@@ -8,6 +8,7 @@ here is a thin call into the C-ABI library; there is no computation in Python.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 
 import numpy as np
 
@@ -65,6 +66,9 @@ class Context:
 
     def close(self):
         if self.h:
+            # the library frees the context's Gpus with it; drop their handles first
+            for g in list(getattr(self, "_gpus", ())):
+                g.close()
             L.load().aotcu_free(self.h)
             self.h = None
 
@@ -238,10 +242,14 @@ class Gpu:
         check(L.load().aotcu_gpu_new(ctx.h, C.byref(head), self.layers, ptr(weights), weights.size, n_ctx, max_batch,
                                      C.byref(h)))
         self.h = h
+        if not hasattr(ctx, "_gpus"):
+            ctx._gpus = weakref.WeakSet()
+        ctx._gpus.add(self)
 
     def close(self):
         if self.h:
-            L.load().aotcu_gpu_free(self.h)
+            if self.ctx.h:
+                L.load().aotcu_gpu_free(self.h)
             self.h = None
 
     def __del__(self):

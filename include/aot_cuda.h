@@ -67,6 +67,8 @@ const char* aotcu_version(void);
 /* Opens CUDA device `device` (replaces Pool::new + Gpu::new's device setup,
  * crates/aot-kernels/src/metal.rs:366). */
 int aotcu_init(int device, aotcu_ctx** out);
+/* Also frees every aotcu_gpu created on the context that is still alive (their handles
+ * become invalid): a Gpu does not outlive its context. */
 void aotcu_free(aotcu_ctx* ctx);
 int aotcu_sync(aotcu_ctx* ctx);
 /* Device memory helpers so a foreign-language host needs no CUDA binding. */

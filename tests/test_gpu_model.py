@@ -347,3 +347,24 @@ def test_bounded_wait_expires_and_the_context_stays_usable(pkg, ob, ctx):
         assert_bits_equal(g.logits(), om.logits(), f"logits at {len(prompt) + i} after the expired wait")
         tok = ob.argmax(om.logits())
     ctx.device_status()
+
+
+@pytest.mark.gpu
+def test_context_closed_before_its_gpu(pkg):
+    """Closing a context releases the Gpus still alive on it; closing (or collecting) such a
+    Gpu afterwards is a no-op instead of a use after free."""
+    spec = pkg.model.tiny("llama", n_layer=1)
+    ctx2 = pkg.Context(0)
+    g = pkg.Gpu(ctx2, spec.head, spec.layers, spec.weights, 32, 4)
+    g.forward(1, 0, True)
+    first = g.logits().copy()
+    ctx2.close()
+    assert g.h is None
+    g.close()
+    del g
+    ctx3 = pkg.Context(0)
+    g3 = pkg.Gpu(ctx3, spec.head, spec.layers, spec.weights, 32, 4)
+    g3.forward(1, 0, True)
+    assert_bits_equal(g3.logits(), first, "same model on a fresh context")
+    g3.close()
+    ctx3.close()
