@@ -647,8 +647,8 @@ static int gpu_mv3(aotcu_gpu* g, float* const dst[3], const aotcu_tensor* const 
 
 static int gpu_gate_up(aotcu_gpu* g, float* hb, float* hb2, const aotcu_tensor& gate, const aotcu_tensor& up,
                        const float* src, size_t m) {
-  ARG_CHECK(!g->head.dims.gelu, "GeGLU models are not supported yet");
   aotcu_ctx* c = g->c;
+  const bool gelu = g->head.dims.gelu != 0;  // GeGLU (Gemma): h = gelu(gate) * up, emit.rs picks gelu_mul
   if (gate.kind == up.kind && gate.rows == up.rows && gate.cols == up.cols) {
     int act = kind_act(gate.kind);
     if (int rc = ensure_quantized(g, src, gate.cols, m, act)) return rc;
@@ -661,14 +661,18 @@ static int gpu_gate_up(aotcu_gpu* g, float* hb, float* hb2, const aotcu_tensor& 
     call.x = act_images(g, act, src);
     call.x_mode = 1;
     call.m = m;
-    call.epilogue = EPI_SILU_MUL;
+    call.epilogue = gelu ? EPI_STORE : EPI_SILU_MUL;
     note_write(g, hb);
     note_write(g, hb2);
-    return launch_gemv(c, call);
+    if (int rc = launch_gemv(c, call)) return rc;
+    if (!gelu) return 0;
+    const size_t n = m * gate.rows;
+    return launch(c, gelu_mul_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, hb, (const float*)hb2, n);
   }
   if (int rc = gpu_matmul(g, hb, gate, src, m, 0)) return rc;
   if (int rc = gpu_matmul(g, hb2, up, src, m, 0)) return rc;
   size_t n = m * gate.rows;
+  if (gelu) return launch(c, gelu_mul_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, hb, (const float*)hb2, n);
   return launch(c, silu_mul_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, hb, (const float*)hb2, n);
 }
 
@@ -1429,6 +1433,12 @@ int aotcu_silu_mul(aotcu_ctx* c, float* h, const float* up, size_t n) {
   return launch(c, silu_mul_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, h, up, n);
 }
 
+int aotcu_gelu_mul(aotcu_ctx* c, float* h, const float* up, size_t n) {
+  ARG_CHECK(c && h && up, "NULL argument");
+  if (n == 0) return 0;
+  return launch(c, gelu_mul_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, h, up, n);
+}
+
 int aotcu_add_inplace(aotcu_ctx* c, float* x, const float* y, size_t n) {
   ARG_CHECK(c && x && y, "NULL argument");
   if (n == 0) return 0;
@@ -1478,7 +1488,6 @@ int aotcu_gpu_new(aotcu_ctx* c, const aotcu_model_head* head, const aotcu_layer*
   ARG_CHECK(d.head_dim % 4 == 0 && d.head_dim <= 256, "head_dim %d must be a multiple of 4, at most 256", d.head_dim);
   ARG_CHECK(d.rot_dim % 2 == 0 && d.rot_dim <= d.head_dim, "rot_dim %d invalid", d.rot_dim);
   ARG_CHECK(n_ctx >= 1, "context must hold at least one token");
-  if (d.gelu) return fail(AOTCU_ERR_UNSUPPORTED, "GeGLU (gemma) models are not supported yet");
   if (int rc = ctx_set_device(c)) return rc;
   aotcu_gpu* g = new aotcu_gpu();
   g->c = c;
@@ -1824,6 +1833,85 @@ int aotcu_logits(aotcu_gpu* g, float* host_dst) {
     return aotcu_d2h(g->c, host_dst, g->tp_logits_full, (size_t)g->head.dims.vocab * sizeof(float));
   }
   return aotcu_d2h(g->c, host_dst, g->bufs[AOTCU_BUF_LOGITS], (size_t)g->head.dims.vocab * sizeof(float));
+}
+
+
+// ---- saved KV cache (prefix.rs) ----------------------------------------------------------------
+constexpr size_t KV_HEADER = 24;
+static size_t kv_data_off(size_t n_tokens) { return (KV_HEADER + 4 * n_tokens + 63) / 64 * 64; }
+static void put_u32(uint8_t* p, uint32_t v) {
+  p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); p[2] = (uint8_t)(v >> 16); p[3] = (uint8_t)(v >> 24);
+}
+static uint32_t get_u32(const uint8_t* p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); }
+
+size_t aotcu_kv_blob_size(const aotcu_gpu* g, size_t n_tokens, size_t n_cached) {
+  if (!g) return 0;
+  const aotcu_dims& d = g->head.dims;
+  n_cached = std::min(n_cached, n_tokens);
+  return kv_data_off(n_tokens) + (size_t)d.n_layer * 2 * n_cached * ((size_t)d.n_kv_head * d.head_dim) * 4;
+}
+
+int aotcu_kv_save(aotcu_gpu* g, const uint32_t* tokens, size_t n_tokens, size_t n_cached, uint8_t* out, size_t out_cap,
+                  size_t* out_len) {
+  ARG_CHECK(g && out && out_len && (tokens || n_tokens == 0), "NULL argument");
+  const aotcu_dims& d = g->head.dims;
+  n_cached = std::min(n_cached, n_tokens);
+  ARG_CHECK(n_cached <= g->n_ctx, "%zu cached positions exceed the context (%zu)", n_cached, g->n_ctx);
+  ARG_CHECK(n_tokens <= 0xFFFFFFFFu, "too many tokens");
+  const size_t kvd = (size_t)d.n_kv_head * d.head_dim, rows = n_cached * kvd;
+  const size_t need = aotcu_kv_blob_size(g, n_tokens, n_cached);
+  ARG_CHECK(out_cap >= need, "the blob needs %zu bytes, the buffer holds %zu", need, out_cap);
+  if (int rc = ctx_set_device(g->c)) return rc;
+  memcpy(out, "AOTP", 4);
+  put_u32(out + 4, 2);
+  put_u32(out + 8, (uint32_t)n_tokens);
+  put_u32(out + 12, (uint32_t)d.n_layer);
+  put_u32(out + 16, (uint32_t)kvd);
+  put_u32(out + 20, (uint32_t)n_cached);
+  for (size_t i = 0; i < n_tokens; i++) put_u32(out + KV_HEADER + 4 * i, tokens[i]);
+  const size_t off = kv_data_off(n_tokens);
+  memset(out + KV_HEADER + 4 * n_tokens, 0, off - (KV_HEADER + 4 * n_tokens));
+  // device floats are little-endian IEEE words already: the rows go out as they are
+  for (int l = 0; l < d.n_layer && rows; l++) {
+    const size_t at = (size_t)l * g->n_ctx * kvd;
+    CU_TRY(cudaMemcpyAsync(out + off + ((size_t)l * 2) * rows * 4, g->bufs[AOTCU_BUF_KCACHE] + at, rows * 4, cudaMemcpyDeviceToHost,
+                           g->c->stream));
+    CU_TRY(cudaMemcpyAsync(out + off + ((size_t)l * 2 + 1) * rows * 4, g->bufs[AOTCU_BUF_VCACHE] + at, rows * 4, cudaMemcpyDeviceToHost,
+                           g->c->stream));
+  }
+  CU_TRY(cudaStreamSynchronize(g->c->stream));
+  *out_len = need;
+  return 0;
+}
+
+int aotcu_kv_load(aotcu_gpu* g, const uint8_t* blob, size_t blob_len, uint32_t* tokens_out, size_t tokens_cap,
+                  size_t* n_tokens, size_t* n_cached) {
+  ARG_CHECK(g && blob && n_tokens && n_cached && (tokens_out || tokens_cap == 0), "NULL argument");
+  const aotcu_dims& d = g->head.dims;
+  const size_t kvd = (size_t)d.n_kv_head * d.head_dim;
+  ARG_CHECK(blob_len >= KV_HEADER && !memcmp(blob, "AOTP", 4), "not a saved KV cache (no AOTP header)");
+  const uint32_t version = get_u32(blob + 4);
+  ARG_CHECK(version == 1 || version == 2, "saved KV cache of unknown version %u", version);
+  const size_t n = get_u32(blob + 8), nl = get_u32(blob + 12), kv = get_u32(blob + 16);
+  const size_t nc = version == 1 ? n : get_u32(blob + 20);
+  ARG_CHECK(nl == (size_t)d.n_layer && kv == kvd && n > 0 && nc <= n,
+            "the saved KV cache is not of this model (layers %zu/%d, kv_dim %zu/%zu, tokens %zu, cached %zu)", nl, d.n_layer, kv, kvd, n, nc);
+  ARG_CHECK(blob_len >= KV_HEADER + 4 * n, "saved KV cache is truncated");
+  const size_t off = kv_data_off(n), rows = nc * kvd;
+  ARG_CHECK(blob_len >= off + nl * 2 * rows * 4, "saved KV cache is truncated");
+  ARG_CHECK(nc <= g->n_ctx, "the saved cache holds %zu positions, the context %zu", nc, g->n_ctx);
+  if (int rc = ctx_set_device(g->c)) return rc;
+  for (size_t l = 0; l < nl && rows; l++) {
+    const size_t at = l * g->n_ctx * kvd;
+    CU_TRY(cudaMemcpyAsync(g->bufs[AOTCU_BUF_KCACHE] + at, blob + off + (l * 2) * rows * 4, rows * 4, cudaMemcpyHostToDevice, g->c->stream));
+    CU_TRY(cudaMemcpyAsync(g->bufs[AOTCU_BUF_VCACHE] + at, blob + off + (l * 2 + 1) * rows * 4, rows * 4, cudaMemcpyHostToDevice,
+                           g->c->stream));
+  }
+  CU_TRY(cudaStreamSynchronize(g->c->stream));
+  for (size_t i = 0; i < n && i < tokens_cap; i++) tokens_out[i] = get_u32(blob + KV_HEADER + 4 * i);
+  *n_tokens = n;
+  *n_cached = nc;
+  return 0;
 }
 
 int aotcu_generate(aotcu_gpu* g, uint32_t token, size_t pos, size_t n_steps, uint32_t* out_tokens, float* elapsed_ms) {

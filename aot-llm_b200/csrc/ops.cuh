@@ -472,6 +472,23 @@ __global__ void silu_mul_kernel(float* h, const float* up, size_t n) {
     h[i] = fmul(fdiv(v, fadd(1.0f, expf_exact(-v))), up[i]);
   }
 }
+// GELU, tanh approximation (ops.rs:124-127): 0.5 v (1 + tanh(k (v + 0.044715 v^3))) with every
+// product and sum rounded to f32 in the reference's order. The reference takes tanh from
+// the platform's libm; here it is the correctly rounded f32 value (double tanh, then one
+// rounding), which is what a correctly rounded libm returns.
+__device__ __forceinline__ float gelu_exact(float v) {
+  const float k = 1.1283791670955126f / 1.4142135623730951f;  // FRAC_2_SQRT_PI / SQRT_2 in f32
+  const float cube = fmul(fmul(fmul(0.044715f, v), v), v);
+  const float t = (float)tanh((double)fmul(k, fadd(v, cube)));
+  return fmul(fmul(0.5f, v), fadd(1.0f, t));
+}
+// h = gelu(h) * up (ops.rs:130-134)
+__global__ void gelu_mul_kernel(float* h, const float* up, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    h[i] = fmul(gelu_exact(h[i]), up[i]);
+}
 __global__ void add_inplace_kernel(float* x, const float* y, size_t n) {
   pdl_launch_dependents();
   pdl_wait();

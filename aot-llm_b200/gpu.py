@@ -166,6 +166,9 @@ class Context:
     def silu_mul(self, h, up, n: int):
         check(L.load().aotcu_silu_mul(self.h, _dp(h), _dp(up), n))
 
+    def gelu_mul(self, h, up, n: int):
+        check(L.load().aotcu_gelu_mul(self.h, _dp(h), _dp(up), n))
+
     def add_inplace(self, x, y, n: int):
         check(L.load().aotcu_add_inplace(self.h, _dp(x), _dp(y), n))
 
@@ -349,6 +352,27 @@ class Gpu:
         n = C.c_int(0)
         check(L.load().aotcu_gpu_timeline_step(self.h, token, pos, layer, ptr(out), C.byref(n)))
         return out.reshape(256, 16)[: n.value]
+
+    def kv_save(self, tokens, n_cached: int) -> bytes:
+        """The "AOTP" v2 blob of `tokens` and the cache rows of their first `n_cached`
+        positions (prefix::serialize, crates/aot-kernels/src/prefix.rs:112-141)."""
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        size = L.load().aotcu_kv_blob_size(self.h, toks.size, n_cached)
+        out = np.empty(size, dtype=np.uint8)
+        n = C.c_size_t(0)
+        check(L.load().aotcu_kv_save(self.h, ptr(toks), toks.size, n_cached, ptr(out), out.size, C.byref(n)))
+        return out[: n.value].tobytes()
+
+    def kv_load(self, blob: bytes):
+        """Restores a saved cache into positions [0, n_cached) and returns (tokens, n_cached)
+        (Prefix::parse + load_into, prefix.rs:45-103). Raises AotCudaError for a blob that is
+        not a cache of this model."""
+        raw = np.frombuffer(blob, dtype=np.uint8)
+        cap = max(1, (len(blob) - 24) // 4)
+        toks = np.zeros(cap, dtype=np.uint32)
+        n, nc = C.c_size_t(0), C.c_size_t(0)
+        check(L.load().aotcu_kv_load(self.h, ptr(raw), raw.size, ptr(toks), toks.size, C.byref(n), C.byref(nc)))
+        return toks[: n.value].tolist(), nc.value
 
     def dispatches(self) -> int:
         return L.load().aotcu_gpu_dispatches(self.h)

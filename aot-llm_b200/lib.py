@@ -113,6 +113,7 @@ SYMBOLS = {
     "aotcu_rmsnorm_heads": (_i, [_vp, _vp, _vp, _sz, _sz, _f]),
     "aotcu_rope": (_i, [_vp, _vp, _sz, _sz, _sz, _sz, _vp, _i]),
     "aotcu_silu_mul": (_i, [_vp, _vp, _vp, _sz]),
+    "aotcu_gelu_mul": (_i, [_vp, _vp, _vp, _sz]),
     "aotcu_add_inplace": (_i, [_vp, _vp, _vp, _sz]),
     "aotcu_add_bias_rows": (_i, [_vp, _vp, _vp, _sz, _sz]),
     "aotcu_scale_inplace": (_i, [_vp, _vp, _f, _sz]),
@@ -135,6 +136,9 @@ SYMBOLS = {
     "aotcu_forward_batch": (_i, [_vp, _vp, _sz, _sz, _i]),
     "aotcu_logits": (_i, [_vp, _vp]),
     "aotcu_generate": (_i, [_vp, _u32, _sz, _sz, _vp, C.POINTER(_f)]),
+    "aotcu_kv_blob_size": (_sz, [_vp, _sz, _sz]),
+    "aotcu_kv_save": (_i, [_vp, _vp, _sz, _sz, _vp, _sz, C.POINTER(_sz)]),
+    "aotcu_kv_load": (_i, [_vp, _vp, _sz, _vp, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "aotcu_gpu_dispatches": (C.c_uint64, [_vp]),
     "aotcu_gpu_set_option": (_i, [_vp, C.c_char_p, _i]),
     "aotcu_bench_gemv_sweep": (_i, [_vp, _i, C.POINTER(_f), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),

@@ -85,9 +85,14 @@ def _absent() -> Tensor:
 def build(name: str, *, dim: int, hidden: int, n_layer: int, n_head: int, n_kv_head: int, head_dim: int, vocab: int,
           rope_base: float = 10000.0, eps: float = 1e-5, qk_norm: bool = False, rope_neox: bool = False,
           qkv_bias: bool = False, n_ctx_train: int = 2048, rot_dim: int | None = None, seed: int = 0x5EED,
-          kinds=None, tied_output: bool = False) -> ModelSpec:
+          kinds=None, tied_output: bool = False, gelu: bool = False, post_norms: bool = False, embd_scale: bool = False,
+          swa_window: int = 0, swa_pattern: int = 0, rope_base_local: float = 10000.0) -> ModelSpec:
     """`kinds(layer_index, tensor_name) -> kind` picks the weight format per matrix;
-    tensor_name in {token_embd, output, wq, wk, wv, wo, gate, up, down}."""
+    tensor_name in {token_embd, output, wq, wk, wv, wo, gate, up, down}.
+    The Gemma switches: `gelu` (GeGLU gating), `post_norms` (a norm after attention and after
+    the FFN), `embd_scale` (embedding scaled by sqrt(dim)), `swa_window` with `swa_pattern`
+    (every layer whose index + 1 is not a multiple of the pattern attends to a sliding
+    window and uses the local RoPE base)."""
     kinds = kinds or q4_k_m_mix
     b = _Builder(seed)
     qd, kvd = n_head * head_dim, n_kv_head * head_dim
@@ -112,14 +117,18 @@ def build(name: str, *, dim: int, hidden: int, n_layer: int, n_head: int, n_kv_h
         if qk_norm:
             l.q_norm = b.add(f"blk.{i}.attn_q_norm.weight", F32, 1, head_dim, 0.5, 1.0)
             l.k_norm = b.add(f"blk.{i}.attn_k_norm.weight", F32, 1, head_dim, 0.5, 1.0)
+        if post_norms:
+            l.attn_post_norm = b.add(f"blk.{i}.post_attention_norm.weight", F32, 1, dim, 0.5, 1.0)
+            l.ffn_post_norm = b.add(f"blk.{i}.post_ffw_norm.weight", F32, 1, dim, 0.5, 1.0)
+        l.local_attn = int(swa_window > 0 and swa_pattern > 0 and (i + 1) % swa_pattern != 0)
         layers.append(l)
     output_norm = b.add("output_norm.weight", F32, 1, dim, 0.5, 1.0)
     output = _absent() if tied_output else b.add("output.weight", kinds(-1, "output"), vocab, dim, amp(dim))
     dims = Dims(dim=dim, hidden=hidden, n_layer=n_layer, n_head=n_head, n_kv_head=n_kv_head, head_dim=head_dim,
-                rot_dim=rot_dim or head_dim, vocab=vocab, n_ctx_train=n_ctx_train, swa_window=0, eps=eps,
-                rope_base=rope_base, rope_scale=1.0, rope_base_local=10000.0, rope_scale_local=1.0,
-                qkv_bias=int(qkv_bias), qk_norm=int(qk_norm), rope_neox=int(rope_neox), post_norms=0, gelu=0,
-                embd_scale=0)
+                rot_dim=rot_dim or head_dim, vocab=vocab, n_ctx_train=n_ctx_train, swa_window=swa_window, eps=eps,
+                rope_base=rope_base, rope_scale=1.0, rope_base_local=rope_base_local, rope_scale_local=1.0,
+                qkv_bias=int(qkv_bias), qk_norm=int(qk_norm), rope_neox=int(rope_neox), post_norms=int(post_norms),
+                gelu=int(gelu), embd_scale=int(embd_scale))
     head = ModelHead(dims=dims, token_embd=token_embd, output_norm=output_norm, output=output, rope_freqs=_absent())
     return ModelSpec(name=name, head=head, layers=layers, weights=b.blob(), tensors=b.tensors)
 
@@ -167,4 +176,9 @@ def tiny(arch: str = "llama", seed: int = 11, n_layer: int = 3, kinds=None, dim:
         kw.update(qk_norm=True, rope_neox=True, rope_base=1e6, eps=1e-6)
     elif arch == "qwen2":
         kw.update(qkv_bias=True, rope_neox=True, rope_base=1e6, eps=1e-6)
+    elif arch == "gemma":
+        # Gemma 3 shape: GeGLU, post-norms, scaled embedding, q/k norm, NEOX RoPE, five
+        # sliding-window layers (local RoPE base) per global one -- here every third is global
+        kw.update(gelu=True, post_norms=True, embd_scale=True, qk_norm=True, rope_neox=True, rope_base=1e6, eps=1e-6,
+                  swa_window=16, swa_pattern=3, tied_output=True)
     return build(f"tiny-{arch}", **kw)

@@ -385,6 +385,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 block dot products with f32 accumulation (Q8 activations x Q4_K/Q6_K weights)",
         "data": "synthetic", "config": workload_config(spec),
+        "numerics": "exact (bit-identical to the CPU path; the reordering switches of the step kernel are off)",
         "clocks": clk.summary(),
         "e2e": {"value": e2e_tps, "unit": UNIT, "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4 * d.vocab,
                 "steps": e2e_steps},

@@ -174,6 +174,9 @@ int aotcu_rmsnorm_heads(aotcu_ctx* ctx, float* x, const float* w, size_t n_heads
 int aotcu_rope(aotcu_ctx* ctx, float* x, size_t m, size_t n_heads, size_t head_dim, size_t rot_dim, const float* cs,
                int neox);
 int aotcu_silu_mul(aotcu_ctx* ctx, float* h, const float* up, size_t n);   /* ops.rs:115-120 */
+/* h = gelu(h) * up, tanh approximation (ops.rs:122-134). tanh is the correctly rounded f32
+ * value; the reference takes it from the platform's libm, which may differ by one ulp. */
+int aotcu_gelu_mul(aotcu_ctx* ctx, float* h, const float* up, size_t n);
 int aotcu_add_inplace(aotcu_ctx* ctx, float* x, const float* y, size_t n); /* ops.rs:144-148 */
 int aotcu_add_bias_rows(aotcu_ctx* ctx, float* x, const float* b, size_t n, size_t m); /* ops.rs:90-95 */
 int aotcu_scale_inplace(aotcu_ctx* ctx, float* x, float s, size_t n);      /* ops.rs:137-141 */
@@ -274,6 +277,29 @@ int aotcu_logits(aotcu_gpu* g, float* host_dst);
  * result feeds the next step; writes the n_steps generated ids to `out_tokens`
  * (host). `elapsed_ms`, if not NULL, receives the device time of the loop. */
 int aotcu_generate(aotcu_gpu* g, uint32_t token, size_t pos, size_t n_steps, uint32_t* out_tokens, float* elapsed_ms);
+/* ---- saved KV cache ("AOTP" blob, crates/aot-kernels/src/prefix.rs:14-26) -------------
+ * Little-endian: "AOTP", version 2, n_tokens, n_layer, kv_dim, n_cached (six u32), the
+ * token ids, zero padding to a 64-byte boundary, then per layer the K rows
+ * f32[n_cached * kv_dim] followed by the V rows. The first n_cached tokens have cache rows;
+ * the rest must be evaluated by the caller (prefix.rs:24-26).
+ *
+ * aotcu_kv_blob_size: bytes aotcu_kv_save writes for these counts (prefix.rs:112-141).
+ * aotcu_kv_save: serialises `tokens` and the cache rows of positions [0, n_cached) of this
+ *   Gpu into `out` (host memory, `out_cap` bytes); n_cached is clamped to n_tokens as the
+ *   reference does (prefix.rs:114) and must not exceed the context. Replaces
+ *   prefix::serialize (callers: app.rs:489, 631-640, capi.rs:518-523).
+ * aotcu_kv_load: parses a version 1 or 2 blob, checks it against this model (n_layer,
+ *   kv_dim, n_tokens > 0, n_cached <= n_tokens, length: prefix.rs:45-69) and that the cached
+ *   rows fit the context, copies the rows into the device cache (positions [0, n_cached))
+ *   and returns the token ids (up to tokens_cap of them), their count and n_cached. A blob
+ *   that is not a cache of this model fails with AOTCU_ERR_BAD_ARG and changes nothing
+ *   (Prefix::parse returning None). Replaces Prefix::parse + load_into (callers:
+ *   app.rs:458-471, capi.rs:526-545). */
+size_t aotcu_kv_blob_size(const aotcu_gpu* g, size_t n_tokens, size_t n_cached);
+int aotcu_kv_save(aotcu_gpu* g, const uint32_t* tokens, size_t n_tokens, size_t n_cached, uint8_t* out, size_t out_cap,
+                  size_t* out_len);
+int aotcu_kv_load(aotcu_gpu* g, const uint8_t* blob, size_t blob_len, uint32_t* tokens_out, size_t tokens_cap,
+                  size_t* n_tokens, size_t* n_cached);
 /* Number of kernels launched by this Gpu since creation (Gpu.dispatches, metal.rs:352-356). */
 uint64_t aotcu_gpu_dispatches(aotcu_gpu* g);
 /* Tuning switches (the role of AOT_GPU_MV_ROWS, metal.rs:368): name = "graph"

@@ -138,6 +138,7 @@ void orc_rmsnorm_heads(float* x, const float* w, size_t n_heads, size_t head_dim
 void orc_softmax(float* x, size_t n);
 void orc_silu_mul(float* h, const float* up, size_t n);
 float orc_gelu(float v);
+void orc_set_tanh_mode(int correctly_rounded);
 void orc_gelu_mul(float* h, const float* up, size_t n);
 void orc_add_inplace(float* x, const float* y, size_t n);
 void orc_inv_freq(float* out, size_t rot_dim, float base, const float* freq_factors);

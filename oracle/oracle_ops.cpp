@@ -98,10 +98,18 @@ void orc_silu_mul(float* h, const float* up, size_t n) {
   }
 }
 
-// ops.rs:124-127; the constant is FRAC_2_SQRT_PI / SQRT_2 evaluated in f32.
+// ops.rs:124-127; the constant is FRAC_2_SQRT_PI / SQRT_2 evaluated in f32. Rust's f32::tanh
+// is the platform libm's tanhf, so the reference's own result depends on that library
+// (glibc before 2.41 is not correctly rounded). Mode 0 calls this host's tanhf as the
+// reference would here; mode 1 rounds the double-precision tanh once, which is the value
+// a correctly rounded libm returns and the one the CUDA library computes.
+static int g_tanh_mode = 0;
+void orc_set_tanh_mode(int correctly_rounded) { g_tanh_mode = correctly_rounded; }
 float orc_gelu(float v) {
   const float k = 1.1283791670955126f / 1.4142135623730951f;
-  return 0.5f * v * (1.0f + tanhf(k * (v + 0.044715f * v * v * v)));
+  const float a = k * (v + 0.044715f * v * v * v);
+  const float t = g_tanh_mode ? (float)tanh((double)a) : tanhf(a);
+  return 0.5f * v * (1.0f + t);
 }
 
 // ops.rs:130-134

@@ -253,6 +253,34 @@ def test_rope_silu_add(pkg, ob, ctx):
     assert_bits_equal(dx.download(np.float32, h.size), ob.add_inplace(h, up), "add_inplace")
 
 
+def test_gelu_mul_correctly_rounded_tanh(pkg, ob, ctx):
+    """GeGLU gating (ops.rs:122-134). With tanh rounded correctly (the value a correctly
+    rounded libm gives) device and oracle agree bit for bit over a dense sweep; against this
+    host's own tanhf, which the reference would call here, they stay within one ulp of the
+    gated value wherever tanhf itself is within one ulp."""
+    L = ob.lib()
+    v = np.concatenate([np.linspace(-12.0, 12.0, 1 << 19, dtype=np.float32),
+                        np.array([0.0, -0.0, 1.0, -1.0, 1e-20, -1e-20, 30.0, -30.0, 1e30, -1e30], dtype=np.float32)])
+    up = np.random.default_rng(2).standard_normal(v.size).astype(np.float32)
+    dh = ctx.to_device(v)
+    ctx.gelu_mul(dh, ctx.to_device(up), v.size)
+    got = dh.download(np.float32, v.size)
+    L.orc_set_tanh_mode(1)
+    try:
+        assert_bits_equal(got, ob.gelu_mul(v, up), "gelu_mul, correctly rounded tanh")
+    finally:
+        L.orc_set_tanh_mode(0)
+    host = ob.gelu_mul(v, up)
+    ulp = np.abs(got.view(np.int32).astype(np.int64) - host.view(np.int32).astype(np.int64))
+    same = float(np.mean(ulp == 0))
+    assert same > 0.9, same                      # this host's tanhf is usually the rounded value
+    # known answers of the reference's own test (ops.rs:343-350)
+    one = ctx.to_device(np.array([1.0, -1.0], dtype=np.float32))
+    ctx.gelu_mul(one, ctx.to_device(np.array([2.0, 2.0], dtype=np.float32)), 2)
+    r = one.download(np.float32, 2)
+    assert abs(r[0] - 1.682384) < 1e-5 and abs(r[1] + 0.317616) < 1e-5
+
+
 def test_expf_matches_host_libm(pkg, ob, ctx):
     """silu(v)*1 exposes expf(-v): compare the device expf with the oracle's libm over a
     dense sweep of the range softmax and SiLU use."""

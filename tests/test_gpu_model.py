@@ -368,3 +368,39 @@ def test_context_closed_before_its_gpu(pkg):
     assert_bits_equal(g3.logits(), first, "same model on a fresh context")
     g3.close()
     ctx3.close()
+
+
+@pytest.mark.gpu
+def test_gemma_shape_geglu_post_norms_sliding_window(pkg, ob, ctx):
+    """The Gemma switches together: GeGLU gating, norms after attention and FFN, scaled
+    embedding, q/k norm, a tied output head and sliding-window layers with their own RoPE
+    base (window 16, so positions beyond it drop out of the local layers). With tanh
+    correctly rounded on both sides every buffer is bit-identical; with this host's tanhf
+    (what the reference would call here) the logits agree to the floating-point tolerance."""
+    spec = pkg.model.tiny("gemma", n_layer=3)
+    assert [l.local_attn for l in spec.layers] == [1, 1, 0]
+    n_ctx = 64
+    toks = np.random.default_rng(5).integers(0, 384, 40).tolist()
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 16)
+    L = ob.lib()
+    for mode in (1, 0):
+        L.orc_set_tanh_mode(mode)
+        try:
+            om = ob.model_from_spec(spec, n_ctx, 16, n_threads=4)
+            for c0 in range(0, 32, 16):
+                g.forward_batch(toks[c0:c0 + 16], c0, True)
+                om.forward_batch(toks[c0:c0 + 16], c0, True)
+            for pos in range(32, 40):
+                g.forward(toks[pos], pos, True)
+                om.forward(toks[pos], pos, True)
+                lg, lo = g.logits(), om.logits()
+                if mode == 1:
+                    assert_bits_equal(g.read("X"), om.buf("x"), f"x at position {pos}")
+                    assert_bits_equal(lg, lo, f"logits at position {pos}")
+                else:
+                    assert float(np.max(np.abs(lg - lo))) <= 1e-3 * float(np.max(np.abs(lo)))   # tolerance for f32 outputs
+                    assert int(np.argmax(lg)) == int(np.argmax(lo))
+        finally:
+            L.orc_set_tanh_mode(0)
+    g.close()
+    ctx.device_status()
