@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include <dlfcn.h>
@@ -106,6 +107,7 @@ struct GemvCall {
   int x_mode = 0;  // 0 reference-layout blocks (or f32 for float kinds), 1 block images
   size_t m = 1;
   int epilogue = EPI_STORE;
+  const uint8_t* prep[3] = {nullptr, nullptr, nullptr};  // prepared tensor-core operands of each matrix, if any
 };
 
 static int check_weight_alignment(int kind, const void* w) {
@@ -159,13 +161,23 @@ static int launch_gemm_tc(aotcu_ctx* c, const GemvCall& call) {
   P.err = c->d_err;
   P.dbg_sumi = g_dbg_sumi;
   P.dbg_summ = g_dbg_summ;
+  bool prep = true;
+  for (int s = 0; s < call.nseg; s++) {
+    P.prep[s] = call.prep[s];
+    prep = prep && call.prep[s] != nullptr;
+  }
   static bool attr_set[64] = {};
   if (c->device >= 0 && c->device < 64 && !attr_set[c->device]) {
     CU_TRY(cudaFuncSetAttribute(gemm_k4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
+    CU_TRY(cudaFuncSetAttribute(gemm_k4_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM_BYTES));
     attr_set[c->device] = true;
   }
   const int grid = tiles < c->n_sm ? tiles : c->n_sm;
-  if (int rc = launch(c, gemm_k4_tc_kernel, dim3(grid), dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, P)) return rc;
+  if (prep) {
+    if (int rc = launch(c, gemm_k4_prep_kernel, dim3(grid), dim3(TP_THREADS), (size_t)TP_SMEM_BYTES, P)) return rc;
+  } else {
+    if (int rc = launch(c, gemm_k4_tc_kernel, dim3(grid), dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, P)) return rc;
+  }
   if (call.pair && call.epilogue == EPI_SILU_MUL) {
     const size_t n = call.m * (size_t)call.seg[0].rows;
     return launch(c, silu_mul_kernel, dim3(grid_for(c, n, 256)), dim3(256), 0, call.seg[0].out, (const float*)call.seg[1].out, n);
@@ -178,12 +190,14 @@ static int launch_gemm_tc(aotcu_ctx* c, const GemvCall& call) {
 // gate/up pair of the TinyLlama shape, and loses on 16..20 tiles); 1: always; -1: never.
 static int g_tc_force = 0;
 static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
-  bool k4 = g_use_tc && g_tc_force >= 0;
+  bool k4 = g_use_tc && g_tc_force >= 0, prep = true;
   int tc_tiles = 0;
   for (int s = 0; s < call.nseg; s++) {
     k4 = k4 && (call.seg[s].kind == Q4_K || call.seg[s].kind == Q5_K);
+    prep = prep && call.prep[s] != nullptr;
     tc_tiles += (call.seg[s].rows + TC_ROWS - 1) / TC_ROWS;
   }
+  // 128-row tiles, one CTA each: either tensor-core kernel needs enough tiles to occupy the GPU
   if (k4 && (g_tc_force > 0 || tc_tiles >= c->n_sm / 2)) return launch_gemm_tc(c, call);
   GemmParams P = {};
   int tiles = 0;
@@ -517,6 +531,10 @@ struct aotcu_gpu {
   uint64_t decode_graph_kernels[4] = {};        // kernel nodes per replay
   uint64_t gen_graph_kernels[2] = {};
   int split_now = 0;                            // the step being enqueued shares heads between CTAs (mega_split)
+  // Prepared tensor-core operands of the Q4_K / Q5_K layer matrices (gemm_tc.cuh), keyed by
+  // the tensor's offset; built before the first prompt chunk of 8 tokens or more.
+  std::unordered_map<uint64_t, uint8_t*> prep;
+  int prep_state = 0;                           // 0 not built yet, 1 built, -1 off (option, memory, or nothing to prepare)
   int smem_scores = 0;
 };
 
@@ -604,6 +622,63 @@ static int gpu_rmsnorm(aotcu_gpu* g, float* dst, size_t dst_stride, const float*
 }
 
 // dst (+)= W . src for m rows (Gpu::mv / Gpu::matmul).
+// Prepared operands of tensor t for a batch of m rows, or null.
+static const uint8_t* prep_of(const aotcu_gpu* g, const aotcu_tensor& t, size_t m) {
+  if (g->prep_state != 1 || m < 8 || m > (size_t)TC_TOK) return nullptr;
+  auto it = g->prep.find(t.off);
+  return it == g->prep.end() ? nullptr : it->second;
+}
+
+// Builds the prepared operands of every Q4_K / Q5_K layer matrix once (3.7 x their bytes):
+// only when they take at most half of the memory that is free, so that a model sized for
+// the device keeps fitting; otherwise prompt chunks keep unpacking weights per launch.
+static int ensure_prepared(aotcu_gpu* g) {
+  if (g->prep_state != 0) return 0;
+  g->prep_state = -1;
+  if (!g_use_tc || g_tc_force < 0) return 0;
+  std::vector<const aotcu_tensor*> ts;
+  size_t total = 0;
+  // only matrices whose launches reach the tensor-core kernel (launch_gemm: at least n_sm / 2
+  // tiles of 128 rows per launch): q/k/v go out as one launch, gate/up as one, wo and down alone
+  auto k4 = [](const aotcu_tensor* t) { return (t->kind == Q4_K || t->kind == Q5_K) && t->cols % 256 == 0; };
+  auto tiles = [](const aotcu_tensor* t) { return (int)((t->rows + TC_ROWS - 1) / TC_ROWS); };
+  const int need = g_tc_force > 0 ? 1 : g->c->n_sm / 2;
+  auto want = [&](std::initializer_list<const aotcu_tensor*> group) {
+    int n = 0;
+    for (auto t : group) {
+      if (!k4(t) || t->cols != (*group.begin())->cols) return;
+      n += tiles(t);
+    }
+    if (n < need) return;
+    for (auto t : group)
+      if (!g->prep.count(t->off) && std::find(ts.begin(), ts.end(), t) == ts.end()) {
+        ts.push_back(t);
+        total += tc_prep_bytes(t->rows, t->cols);
+      }
+  };
+  for (const auto& l : g->layers) {
+    want({&l.wq, &l.wk, &l.wv});
+    want({&l.gate, &l.up});
+    want({&l.wo});
+    want({&l.down});
+  }
+  if (ts.empty()) return 0;
+  size_t free_b = 0, total_b = 0;
+  CU_TRY(cudaMemGetInfo(&free_b, &total_b));
+  if (total > free_b / 2) return 0;
+  for (auto t : ts) {
+    if (g->prep.count(t->off)) continue;  // a tensor shared by two layers
+    uint8_t* p = nullptr;
+    CU_TRY(cudaMalloc(&p, tc_prep_bytes(t->rows, t->cols)));
+    g->prep[t->off] = p;
+    const unsigned blocks = (unsigned)(((t->rows + TC_ROWS - 1) / TC_ROWS) * (t->cols / 256));
+    if (int rc = launch(g->c, k4_prepare_kernel, dim3(blocks), dim3(256), 0, wptr(g, *t), (int)t->kind, (int)t->rows, (int)t->cols, p))
+      return rc;
+  }
+  g->prep_state = 1;
+  return 0;
+}
+
 static int gpu_matmul(aotcu_gpu* g, float* dst, const aotcu_tensor& t, const float* src, size_t m, int accumulate) {
   int act = kind_act(t.kind);
   if (int rc = ensure_quantized(g, src, t.cols, m, act)) return rc;
@@ -615,6 +690,7 @@ static int gpu_matmul(aotcu_gpu* g, float* dst, const aotcu_tensor& t, const flo
   call.x_mode = 1;
   call.m = m;
   call.epilogue = accumulate ? EPI_ACCUM : EPI_STORE;
+  call.prep[0] = prep_of(g, t, m);
   note_write(g, dst);
   return launch_gemv(g->c, call);
 }
@@ -628,8 +704,11 @@ static int gpu_mv3(aotcu_gpu* g, float* const dst[3], const aotcu_tensor* const 
     int act = kind_act(t[a]->kind);
     GemvCall call;
     call.nseg = 0;
+    const bool prepared = prep_of(g, *t[a], m) != nullptr;
     for (int b = a; b < 3; b++) {
-      if (!done[b] && kind_act(t[b]->kind) == act && t[b]->cols == t[a]->cols) {
+      // matrices with prepared tensor-core operands go together, the others together
+      if (!done[b] && kind_act(t[b]->kind) == act && t[b]->cols == t[a]->cols && (prep_of(g, *t[b], m) != nullptr) == prepared) {
+        call.prep[call.nseg] = prep_of(g, *t[b], m);
         call.seg[call.nseg++] = GemvSeg{wptr(g, *t[b]), dst[b], (int)t[b]->rows, t[b]->kind};
         done[b] = true;
         note_write(g, dst[b]);
@@ -662,6 +741,8 @@ static int gpu_gate_up(aotcu_gpu* g, float* hb, float* hb2, const aotcu_tensor& 
     call.x_mode = 1;
     call.m = m;
     call.epilogue = gelu ? EPI_STORE : EPI_SILU_MUL;
+    call.prep[0] = prep_of(g, gate, m);
+    call.prep[1] = prep_of(g, up, m);
     note_write(g, hb);
     note_write(g, hb2);
     if (int rc = launch_gemv(c, call)) return rc;
@@ -1654,6 +1735,7 @@ void aotcu_gpu_free(aotcu_gpu* g) {
     if (p) cudaIpcCloseMemHandle(p);
   cudaFree(g->tp_inbox);
   cudaFree(g->tp_logits_full);
+  for (auto& kv : g->prep) cudaFree(kv.second);
   if (g->h_pinned) cudaFreeHost(g->h_pinned);
   delete g;
 }
@@ -1815,6 +1897,8 @@ int aotcu_forward_batch(aotcu_gpu* g, const uint32_t* tokens, size_t n, size_t p
   for (size_t i = 0; i < n; i++) g->h_pinned[8 + i] = (int)tokens[i];
   CU_TRY(cudaMemcpyAsync(g->d_tokens, g->h_pinned + 8, n * sizeof(int), cudaMemcpyHostToDevice, c->stream));
   g->qsrc = aotcu_gpu::QSrc();
+  if (n >= 8)
+    if (int rc = ensure_prepared(g)) return rc;
   if (int rc = embed(g, g->bufs[AOTCU_BUF_BX], g->d_tokens, n)) return rc;
   for (int i = 0; i < d.n_layer; i++)
     if (int rc = layer_forward(g, (size_t)i, nullptr, pos0, n, true)) return rc;
@@ -2059,6 +2143,28 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
   if (!strcmp(name, "graph")) {
     g->use_graph = value != 0;
     return 0;
+  }
+  if (!strcmp(name, "prepared_operands")) {
+    // 0: prompt chunks unpack the weights in every launch; 1 (default): Q4_K / Q5_K layer
+    // matrices are expanded once into tensor-core operand tiles when memory allows
+    CU_TRY(cudaStreamSynchronize(g->c->stream));
+    if (!value) {
+      for (auto& kv : g->prep) cudaFree(kv.second);
+      g->prep.clear();
+      g->prep_state = -1;
+    } else if (g->prep_state == -1) {
+      g->prep_state = 0;
+    }
+    return 0;
+  }
+  if (!strcmp(name, "prepared_bytes")) {  // query: bytes held by the prepared operands
+    size_t total = 0;
+    for (const auto& l : g->layers) {
+      const aotcu_tensor* c7[7] = {&l.wq, &l.wk, &l.wv, &l.wo, &l.gate, &l.up, &l.down};
+      for (auto t : c7)
+        if (g->prep.count(t->off)) total += tc_prep_bytes(t->rows, t->cols);
+    }
+    return (int)std::min<size_t>(total >> 20, 0x7fffffff);  // MiB
   }
   if (!strcmp(name, "mega")) {
     if (value && !g->mega_ok) return fail(AOTCU_ERR_UNSUPPORTED, "this model cannot use the one-kernel decode step");

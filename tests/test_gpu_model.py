@@ -195,6 +195,47 @@ def test_prompt_chunks_on_tensor_core_tiles_bit_exact(pkg, ob, ctx, arch):
 
 
 @pytest.mark.gpu
+def test_prepared_tensor_core_operands_bit_exact(pkg, ob, ctx):
+    """Q4_K / Q5_K layer matrices expanded once into tensor-core operand tiles (the default
+    when memory allows) against the per-launch unpacking and against the oracle: ragged
+    row counts (rows that do not fill a 128-row tile), Q5_K high bits, chunks of 8..64
+    tokens, accumulate and gate/up epilogues."""
+    Q4_K, Q5_K, Q6_K = pkg.lib.Q4_K, pkg.lib.Q5_K, pkg.lib.Q6_K
+    kinds = lambda l, t: {"wv": Q6_K, "wo": Q5_K, "down": Q5_K if l % 2 else Q4_K, "output": Q6_K}.get(t, Q4_K)
+    spec = pkg.model.build("prep", dim=512, hidden=1280, n_layer=2, n_head=8, n_kv_head=1, head_dim=64, vocab=600, seed=9,
+                           kinds=kinds, n_ctx_train=256)
+    n_ctx = 160
+    om = ob.model_from_spec(spec, n_ctx, 64, n_threads=4)
+    g1 = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 64)
+    g0 = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, n_ctx, 64)
+    g1.set_option("tc_gemm", 2)      # the model is small: send every Q4_K / Q5_K launch to the tensor-core kernels
+    g0.set_option("prepared_operands", 0)
+    rng = np.random.default_rng(12)
+    pos = 0
+    for n in (64, 9, 33, 8):
+        toks = rng.integers(0, 600, n).tolist()
+        for g in (g1, g0):
+            g.forward_batch(toks, pos, True)
+        om.forward_batch(toks, pos, True)
+        assert_bits_equal(g1.logits(), om.logits(), f"prepared operands: logits after a chunk of {n} at {pos}")
+        assert_bits_equal(g0.logits(), om.logits(), f"per-launch unpacking: logits after a chunk of {n} at {pos}")
+        assert_bits_equal(g1.read("KCache"), g0.read("KCache"), "K cache")
+        pos += n
+    assert g1.set_option("prepared_bytes", 0) > 0 and g0.set_option("prepared_bytes", 0) == 0
+    # switching the operands off frees them and keeps the results
+    g1.set_option("prepared_operands", 0)
+    assert g1.set_option("prepared_bytes", 0) == 0
+    toks = rng.integers(0, 600, 16).tolist()
+    g1.forward_batch(toks, pos, True)
+    om.forward_batch(toks, pos, True)
+    assert_bits_equal(g1.logits(), om.logits(), "after switching prepared operands off")
+    g1.set_option("tc_gemm", 1)      # back to the default: by size
+    g1.close()
+    g0.close()
+    ctx.device_status()
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("n_head,n_kv,hd", [(4, 1, 128), (16, 4, 80), (40, 8, 64)])
 def test_heads_shared_by_several_ctas_bit_exact(pkg, ob, ctx, n_head, n_kv, hd):
     """Once a head's cached rows outgrow one CTA's staging area, the one-kernel step deals
