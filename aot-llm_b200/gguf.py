@@ -401,6 +401,8 @@ def spec_to_gguf(spec: ModelSpec, arch: str) -> bytes:
           (f"{arch}.context_length", d.n_ctx_train), (f"{arch}.vocab_size", d.vocab)]
     if d.swa_window:
         md.append((f"{arch}.attention.sliding_window", d.swa_window))
+    if d.rope_scale != 1.0:
+        md += [(f"{arch}.rope.scaling.type", "linear"), (f"{arch}.rope.scaling.factor", float(d.rope_scale))]
     ts = []
     for name, t in spec.tensors.items():
         data = spec.weights[t.off:t.off + t.len]

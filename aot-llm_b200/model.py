@@ -86,13 +86,15 @@ def build(name: str, *, dim: int, hidden: int, n_layer: int, n_head: int, n_kv_h
           rope_base: float = 10000.0, eps: float = 1e-5, qk_norm: bool = False, rope_neox: bool = False,
           qkv_bias: bool = False, n_ctx_train: int = 2048, rot_dim: int | None = None, seed: int = 0x5EED,
           kinds=None, tied_output: bool = False, gelu: bool = False, post_norms: bool = False, embd_scale: bool = False,
-          swa_window: int = 0, swa_pattern: int = 0, rope_base_local: float = 10000.0) -> ModelSpec:
+          swa_window: int = 0, swa_pattern: int = 0, rope_base_local: float = 10000.0, rope_scale: float = 1.0,
+          rope_freqs: bool = False) -> ModelSpec:
     """`kinds(layer_index, tensor_name) -> kind` picks the weight format per matrix;
     tensor_name in {token_embd, output, wq, wk, wv, wo, gate, up, down}.
     The Gemma switches: `gelu` (GeGLU gating), `post_norms` (a norm after attention and after
     the FFN), `embd_scale` (embedding scaled by sqrt(dim)), `swa_window` with `swa_pattern`
     (every layer whose index + 1 is not a multiple of the pattern attends to a sliding
-    window and uses the local RoPE base)."""
+    window and uses the local RoPE base). `rope_scale` is the linear position divisor,
+    `rope_freqs` adds the per-frequency divisors tensor of Llama 3 files (rope_freqs.weight)."""
     kinds = kinds or q4_k_m_mix
     b = _Builder(seed)
     qd, kvd = n_head * head_dim, n_kv_head * head_dim
@@ -126,10 +128,11 @@ def build(name: str, *, dim: int, hidden: int, n_layer: int, n_head: int, n_kv_h
     output = _absent() if tied_output else b.add("output.weight", kinds(-1, "output"), vocab, dim, amp(dim))
     dims = Dims(dim=dim, hidden=hidden, n_layer=n_layer, n_head=n_head, n_kv_head=n_kv_head, head_dim=head_dim,
                 rot_dim=rot_dim or head_dim, vocab=vocab, n_ctx_train=n_ctx_train, swa_window=swa_window, eps=eps,
-                rope_base=rope_base, rope_scale=1.0, rope_base_local=rope_base_local, rope_scale_local=1.0,
+                rope_base=rope_base, rope_scale=rope_scale, rope_base_local=rope_base_local, rope_scale_local=1.0,
                 qkv_bias=int(qkv_bias), qk_norm=int(qk_norm), rope_neox=int(rope_neox), post_norms=int(post_norms),
                 gelu=int(gelu), embd_scale=int(embd_scale))
-    head = ModelHead(dims=dims, token_embd=token_embd, output_norm=output_norm, output=output, rope_freqs=_absent())
+    ff = b.add("rope_freqs.weight", F32, 1, (rot_dim or head_dim) // 2, 3.5, 4.5) if rope_freqs else _absent()
+    head = ModelHead(dims=dims, token_embd=token_embd, output_norm=output_norm, output=output, rope_freqs=ff)
     return ModelSpec(name=name, head=head, layers=layers, weights=b.blob(), tensors=b.tensors)
 
 

@@ -70,10 +70,16 @@ def test_parse_rejects_what_the_reference_rejects(gg):
     assert gg.parse(ok[:4] + struct.pack("<I", 2) + ok[8:]).version == 2
 
 
-@pytest.mark.parametrize("arch,gguf_arch", [("llama", "llama"), ("qwen2", "qwen2"), ("qwen3", "qwen3"), ("gemma", "gemma3")])
+@pytest.mark.parametrize("arch,gguf_arch", [("llama", "llama"), ("qwen2", "qwen2"), ("qwen3", "qwen3"), ("gemma", "gemma3"),
+                                            ("llama3", "llama")])
 def test_model_round_trip(pkg, gg, arch, gguf_arch, tmp_path):
     kw = dict(n_layer=6) if arch == "gemma" else dict(n_layer=2)
-    spec = pkg.model.tiny(arch, **kw)
+    if arch == "llama3":
+        # partial rotation, linear position scale and the frequency-factor tensor
+        spec = pkg.model.build("llama3-file", dim=256, hidden=512, n_layer=2, n_head=8, n_kv_head=2, head_dim=32, vocab=384, seed=13,
+                               rot_dim=16, rope_scale=8.0, rope_freqs=True, rope_base=500000.0, n_ctx_train=512)
+    else:
+        spec = pkg.model.tiny(arch, **kw)
     if arch == "gemma":
         # the file format fixes the pattern: every sixth layer is global (model.rs:190)
         spec = pkg.model.build("gemma-file", dim=256, hidden=512, n_layer=6, n_head=8, n_kv_head=2, head_dim=32, vocab=384, seed=11,
@@ -95,7 +101,7 @@ def test_model_round_trip(pkg, gg, arch, gguf_arch, tmp_path):
             assert np.array_equal(spec.weights[ta.off:ta.off + ta.len], got.weights[tb.off:tb.off + tb.len]), what
             assert tb.off % 32 == 0
 
-    for f in ("token_embd", "output_norm", "output"):
+    for f in ("token_embd", "output_norm", "output", "rope_freqs"):
         same(getattr(spec.head, f), getattr(got.head, f), f)
     for i, (la, lb) in enumerate(zip(spec.layers, got.layers)):
         for f in pkg.lib.LAYER_TENSORS:

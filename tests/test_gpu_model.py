@@ -445,3 +445,30 @@ def test_gemma_shape_geglu_post_norms_sliding_window(pkg, ob, ctx):
             L.orc_set_tanh_mode(0)
     g.close()
     ctx.device_status()
+
+
+@pytest.mark.gpu
+def test_rope_variants_partial_rotation_linear_scale_frequency_factors(pkg, ob, ctx):
+    """RoPE as the remaining model files use it: only part of each head rotated
+    (rope.dimension_count < head_dim), positions divided by a linear scale factor, and the
+    per-frequency divisors of Llama 3 files (rope_freqs.weight); both pair layouts. Prompt
+    chunk, per-operator steps and the one-kernel step against the oracle."""
+    for neox in (False, True):
+        spec = pkg.model.build("rope", dim=512, hidden=768, n_layer=2, n_head=8, n_kv_head=2, head_dim=64, vocab=600, seed=21,
+                               kinds=_kquant_kinds, n_ctx_train=256, rot_dim=32, rope_scale=4.0, rope_freqs=True, rope_neox=neox,
+                               rope_base=500000.0)
+        assert spec.head.rope_freqs.present and spec.head.dims.rot_dim == 32
+        g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 64, 16)
+        om = ob.model_from_spec(spec, 64, 16, n_threads=4)
+        toks = np.random.default_rng(3).integers(0, 600, 20).tolist()
+        g.forward_batch(toks[:12], 0, True)
+        om.forward_batch(toks[:12], 0, True)
+        assert_bits_equal(g.logits(), om.logits(), f"prompt chunk, neox={neox}")
+        for mega in (1, 0):
+            g.set_option("mega", mega)
+            for pos in range(12 + 4 * (1 - mega), 16 + 4 * (1 - mega)):
+                g.forward(toks[pos], pos, True)
+                om.forward(toks[pos], pos, True)
+                assert_bits_equal(g.logits(), om.logits(), f"decode at {pos}, neox={neox}, one-kernel step {mega}")
+        g.close()
+    ctx.device_status()
