@@ -144,3 +144,117 @@ def test_gpu_blob_is_the_oracle_blob_and_continues(pkg, ob, ctx):
     assert len(g.kv_save(first, 0)) == op.data_offset(len(first))
     for x in (g, g2, small):
         x.close()
+
+
+class _FakeGpu:
+    """Records the calls a Session makes (no device)."""
+
+    def __init__(self, n_ctx=64, max_batch=8, vocab=16):
+        self.n_ctx, self.max_batch, self.vocab, self.calls, self.loaded = n_ctx, max_batch, vocab, [], None
+
+    def forward(self, tok, pos, want):
+        self.calls.append(("step", [tok], pos, bool(want)))
+
+    def forward_batch(self, toks, pos, want):
+        self.calls.append(("batch", list(toks), pos, bool(want)))
+
+    def logits(self):
+        v = np.zeros(self.vocab, np.float32)
+        v[3] = v[7] = 1.0                      # a tie: the first maximum wins
+        return v
+
+    def generate(self, tok, pos, n):
+        self.calls.append(("generate", [tok], pos, n))
+        return np.arange(n, dtype=np.uint32) + 100, 0.0
+
+    def kv_load(self, blob):
+        toks = list(struct.unpack_from(f"<{struct.unpack_from('<I', blob, 8)[0]}I", blob, 24))
+        self.loaded = blob
+        return toks, struct.unpack_from("<I", blob, 20)[0]
+
+    def kv_save(self, toks, n_cached):
+        return ("saved", list(toks), n_cached)
+
+
+def test_session_follows_the_reference_run_loop(pkg):
+    S = pkg.session.Session
+    # batches of 8, a single trailing token as a plain step, logits only for the last (app.rs:473-486)
+    g = _FakeGpu()
+    s = S(g, batch=8)
+    s.feed(list(range(17)))
+    assert g.calls == [("batch", list(range(8)), 0, False), ("batch", list(range(8, 16)), 8, False), ("step", [16], 16, True)]
+    out = s.generate_greedy(4)
+    assert out == [3, 100, 101, 102] and g.calls[-1] == ("generate", [3], 17, 3)
+    assert s.pos == 20 and len(s.tokens) == 21                      # the last token was never fed back
+    assert s.save() == ("saved", s.tokens, 20)
+    # a saved run: its tokens come first and only the uncached ones are evaluated (app.rs:396-413)
+    blob = b"AOTP" + struct.pack("<5I", 2, 5, 2, 64, 4) + struct.pack("<5I", 9, 8, 7, 6, 5) + b"\0" * 64
+    g = _FakeGpu()
+    s = S(g, batch=8)
+    assert s.load_saved(blob) == 4
+    s.feed([1, 2])
+    assert g.calls == [("batch", [5, 1, 2], 4, True)] and s.tokens == [9, 8, 7, 6, 5, 1, 2]
+    with pytest.raises(ValueError):
+        s.load_saved(blob)                                            # not empty (capi.rs:527-529)
+    # loading alone and asking for logits re-evaluates the last token
+    g = _FakeGpu()
+    s = S(g, batch=8)
+    full = b"AOTP" + struct.pack("<5I", 2, 3, 2, 64, 3) + struct.pack("<3I", 4, 5, 6) + b"\0" * 64
+    s.load_saved(full)
+    s.feed([])
+    assert g.calls == [("step", [6], 2, True)]
+    # the compile-time prefix: only for a longer prompt that starts with it (app.rs:464-470)
+    g = _FakeGpu()
+    s = S(g, batch=8)
+    assert s.try_prefix(full, [4, 5, 6]) == 0 and g.loaded is None    # not longer
+    assert s.try_prefix(full, [4, 5, 7, 8]) == 0 and g.loaded is None  # another start
+    assert s.try_prefix(b"junk", [4, 5, 6, 7]) == 0
+    assert s.try_prefix(full, [4, 5, 6, 7, 8]) == 3 and g.loaded is full
+    s.feed([4, 5, 6, 7, 8])
+    assert g.calls == [("batch", [7, 8], 3, True)]
+    # errors of the run loop
+    with pytest.raises(ValueError):
+        S(_FakeGpu(), 8).feed([])
+    with pytest.raises(ValueError):
+        S(_FakeGpu(n_ctx=4), 8).feed([1, 2, 3, 4, 5])
+    assert pkg.session.blob_tokens(full) == [4, 5, 6] and pkg.session.blob_tokens(b"AOTQ" + full[4:]) is None
+
+
+@pytest.mark.gpu
+def test_session_saved_run_and_prefix_on_the_gpu(pkg, ob, ctx):
+    """Two turns through save / load and a compile-time prefix give the tokens and logits of
+    one uninterrupted run (e2e.rs:797-805 with generation in between)."""
+    spec = _tiny(pkg)
+    S = pkg.session.Session
+    turn1, turn2 = [5, 17, 300, 42, 7], [9, 1, 250]
+    whole = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 64, 8)
+    w = S(whole, batch=8)
+    w.feed(turn1)
+    gen1 = w.generate_greedy(4)
+    lw = w.feed(turn2)
+    a = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 64, 8)
+    sa = S(a, batch=4)
+    sa.feed(turn1)
+    assert sa.generate_greedy(4) == gen1
+    blob = sa.save()
+    b = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 48, 8)
+    sb = S(b, batch=3)
+    assert sb.load_saved(blob) == len(turn1) + 3
+    lb = sb.feed(turn2)
+    assert sb.tokens == w.tokens
+    assert_bits_equal(lb, lw, "logits after the second turn of a saved run")
+    # the compile-time prefix of the first turn
+    pre = a.kv_save(turn1, len(turn1))
+    c = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 64, 8)
+    sc = S(c, batch=8)
+    assert sc.try_prefix(pre, turn1 + [11, 12]) == len(turn1)
+    n0 = c.dispatches()                      # launches are counted per context
+    lc = sc.feed(turn1 + [11, 12])
+    n1 = c.dispatches()
+    d = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 64, 8)
+    ld = S(d, batch=8).feed(turn1 + [11, 12])
+    n2 = d.dispatches()
+    assert_bits_equal(lc, ld, "logits with and without the prefix cache")
+    assert n1 - n0 <= n2 - n1                # two tokens evaluated instead of seven
+    for x in (whole, a, b, c, d):
+        x.close()

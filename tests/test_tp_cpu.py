@@ -122,10 +122,29 @@ WORKER = textwrap.dedent("""
                      ob.quantize_act(ts.kind, x[info.rank * cw:(info.rank + 1) * cw]), ts.rows, ts.cols)
     buf = torch.from_numpy(part.copy())
     dist.all_reduce(buf)                      # what aotcu_tp_attach arranges on the GPU with NCCL
+    # the vocabulary-sharded head: every rank's slice of the logits, gathered in rank order, is
+    # the whole vector bit for bit (rows are independent), and the best {{logit, id}} over the
+    # ranks' slices (highest logit, lowest id on ties) is the first maximum of the whole
+    xh = np.random.default_rng(10).standard_normal(spec.head.dims.dim).astype(np.float32)
+    oh, os_ = spec.head.output, sh.head.output
+    mine = ob.matvec(pool, tab, os_.kind, sh.weights[os_.off:os_.off + os_.len].copy(), ob.quantize_act(os_.kind, xh), os_.rows, os_.cols)
+    mine[::7] = np.float32(3.0)               # ties across the ranks
+    parts = [torch.zeros(os_.rows) for _ in range(info.world)]
+    dist.all_gather(parts, torch.from_numpy(mine.copy()))
+    gathered = torch.cat(parts).numpy()
+    best = torch.tensor([float(mine.max()), float(info.rank * os_.rows + int(np.argmax(mine)))], dtype=torch.float64)
+    bests = [torch.zeros(2, dtype=torch.float64) for _ in range(info.world)]
+    dist.all_gather(bests, best)
+    pick = min(((float(b[0]), int(b[1])) for b in bests), key=lambda b: (-b[0], b[1]))[1]
     if ranks.is_root:
         want = ob.matvec(pool, tab, t.kind, spec.weights[t.off:t.off + t.len].copy(), ob.quantize_act(t.kind, x), t.rows, t.cols)
         err = float(np.max(np.abs(buf.numpy() - want) / (np.abs(want) + 1e-3)))
-        print(json.dumps({{"world": info.world, "max_rel_err": err}}))
+        full = ob.matvec(pool, tab, oh.kind, spec.weights[oh.off:oh.off + oh.len].copy(), ob.quantize_act(oh.kind, xh), oh.rows, oh.cols)
+        for r in range(info.world):
+            full[r * os_.rows:(r + 1) * os_.rows:7] = np.float32(3.0)
+        print(json.dumps({{"world": info.world, "max_rel_err": err, "head_rows": int(os_.rows),
+                          "gathered_equal": bool(np.array_equal(gathered.view(np.uint32), full.view(np.uint32))),
+                          "pick": pick, "argmax": int(np.argmax(full))}}))
     ranks.close()
 """)
 
@@ -144,3 +163,4 @@ def test_two_gloo_ranks_reduce_partial_ffn_down(tmp_path):
     assert len(lines) == 1, r.stdout
     out = json.loads(lines[0])
     assert out["world"] == 2 and out["max_rel_err"] < 1e-4
+    assert out["head_rows"] == 150 and out["gathered_equal"] and out["pick"] == out["argmax"]
