@@ -784,11 +784,23 @@ static int gpu_qk_post(aotcu_gpu* g, size_t li, const int* pos_ptr, size_t pos0,
 
 // Shared memory of the attention kernel with the scores of rows up to `max_len` positions
 // kept on chip, and what a CTA may use.
-static size_t attn_smem_budget(const aotcu_ctx* c) { return c->max_smem - sizeof(SeqSumScratch) * 8 - 1024; }
-static size_t attn_smem_bytes(int n_head, int n_kv_head, int head_dim, size_t max_len) {
-  const int gqa = n_head / n_kv_head, hpc = gqa < 8 ? gqa : 8;
+// Shared memory of the attention kernel with the scores of rows up to `max_len` positions
+// kept on chip, and what a CTA may use. A CTA has heads_per_cta x rows_per_cta warps, each
+// with its exact-sum scratch, its query row and (when they fit) its scores.
+static size_t attn_smem_budget(const aotcu_ctx* c) { return c->max_smem - 1024; }
+static void attn_shape(int n_head, int n_kv_head, size_t m, int* hpc, int* rpc) {
+  const int gqa = n_head / n_kv_head;
+  *hpc = gqa < 8 ? gqa : 8;
+  int r = ATTN_MAX_WARPS / *hpc;
+  if ((size_t)r > m) r = (int)m;
+  *rpc = r < 1 ? 1 : r;
+}
+static size_t attn_smem_bytes(int n_head, int n_kv_head, int head_dim, size_t max_len, size_t m = 1) {
+  int hpc, rpc;
+  attn_shape(n_head, n_kv_head, m, &hpc, &rpc);
+  const size_t warps = (size_t)hpc * rpc;
   max_len = (max_len + 3) & ~(size_t)3;
-  return ((size_t)hpc * head_dim + (size_t)2 * ATTN_CHUNK * (head_dim + 4) + (size_t)hpc * max_len) * sizeof(float);
+  return attn_ssc_bytes(warps) + (warps * head_dim + (size_t)2 * ATTN_CHUNK * (head_dim + 4) + warps * max_len) * sizeof(float);
 }
 
 static int launch_attention(aotcu_ctx* c, float* out, const float* q, const float* kc, const float* vc, float* scratch,
@@ -810,13 +822,15 @@ static int launch_attention(aotcu_ctx* c, float* out, const float* q, const floa
   P.scale = 1.0f / sqrtf((float)head_dim);
   ARG_CHECK(head_dim % 4 == 0 && head_dim <= 256, "head_dim must be a multiple of 4, at most 256");
   const int gqa = n_head / n_kv_head;
-  P.heads_per_cta = gqa < 8 ? gqa : 8;
+  attn_shape(n_head, n_kv_head, m, &P.heads_per_cta, &P.rows_per_cta);
+  P.m = (int)m;
   const int splits = (gqa + P.heads_per_cta - 1) / P.heads_per_cta;
+  const size_t warps = (size_t)P.heads_per_cta * P.rows_per_cta;
   // Scores in shared memory when the longest row of this call fits, else in `scratch`.
   size_t max_len = pos_ptr ? n_ctx : std::min(n_ctx, pos0 + m);
   max_len = (max_len + 3) & ~(size_t)3;
-  const size_t fixed = ((size_t)P.heads_per_cta * head_dim + (size_t)2 * ATTN_CHUNK * (head_dim + 4)) * sizeof(float);
-  const size_t with_scores = fixed + (size_t)P.heads_per_cta * max_len * sizeof(float);
+  const size_t fixed = attn_ssc_bytes(warps) + (warps * head_dim + (size_t)2 * ATTN_CHUNK * (head_dim + 4)) * sizeof(float);
+  const size_t with_scores = fixed + warps * max_len * sizeof(float);
   const size_t budget = attn_smem_budget(c);
   size_t smem = fixed;
   if (smem_scores && with_scores <= budget) {
@@ -826,7 +840,8 @@ static int launch_attention(aotcu_ctx* c, float* out, const float* q, const floa
     ARG_CHECK(scratch, "attention needs a score scratch buffer for this context length");
     P.smem_scores = 0;
   }
-  return launch(c, attention_kernel, dim3((unsigned)(n_kv_head * splits), (unsigned)m), dim3(ATTN_THREADS), smem, P);
+  const unsigned row_groups = (unsigned)((m + P.rows_per_cta - 1) / P.rows_per_cta);
+  return launch(c, attention_kernel, dim3((unsigned)(n_kv_head * splits), row_groups), dim3((unsigned)warps * 32), smem, P);
 }
 
 static int gpu_attention(aotcu_gpu* g, float* out, const float* q, size_t li, const int* pos_ptr, size_t pos0, size_t m,
@@ -1546,7 +1561,7 @@ int aotcu_attention(aotcu_ctx* c, float* out, const float* q, const float* k_cac
   ARG_CHECK(head_dim % 4 == 0 && head_dim <= 256, "head_dim %zu must be a multiple of 4, at most 256", head_dim);
   ARG_CHECK(pos0 + m <= ctx_len, "positions exceed the context");
   if (m == 0) return 0;
-  ARG_CHECK(attn_smem_bytes((int)n_head, (int)n_kv_head, (int)head_dim, pos0 + m) <= attn_smem_budget(c),
+  ARG_CHECK(attn_smem_bytes((int)n_head, (int)n_kv_head, (int)head_dim, pos0 + m, m) <= attn_smem_budget(c),
             "%zu positions are too many for the stand-alone attention entry point (scores are kept in shared memory)", pos0 + m);
   return launch_attention(c, out, q, k_cache, v_cache, nullptr, nullptr, pos0, m, (int)n_head, (int)n_kv_head,
                           (int)head_dim, ctx_len, window, (int)ctx_len);
@@ -1683,7 +1698,7 @@ int aotcu_gpu_new(aotcu_ctx* c, const aotcu_model_head* head, const aotcu_layer*
   }
   // Attention scores: shared memory when the context fits, else a global scratch.
   {
-    if (attn_smem_bytes(d.n_head, d.n_kv_head, d.head_dim, n_ctx) <= attn_smem_budget(c)) {
+    if (attn_smem_bytes(d.n_head, d.n_kv_head, d.head_dim, n_ctx, g->max_batch) <= attn_smem_budget(c)) {
       g->smem_scores = (int)n_ctx;
     } else {
       g->smem_scores = 0;

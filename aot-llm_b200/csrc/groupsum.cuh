@@ -11,6 +11,10 @@ struct CtaGroup {
   int nthreads;  // multiple of 32
   int bar_id;    // hardware barrier id (0 = the whole CTA, like __syncthreads)
   __device__ __forceinline__ void sync() const {
+    if (nthreads == 32) {  // a single warp needs no hardware barrier (there are only 16 of them)
+      __syncwarp();
+      return;
+    }
     asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory");
   }
 };

@@ -337,47 +337,63 @@ struct AttnParams {
   int n_head, n_kv_head, head_dim, ctx, window;
   int smem_scores;    // capacity (floats per head) of the shared score buffer, 0 = use scratch
   int heads_per_cta;  // query heads of one KV head handled by a CTA (<= 8)
+  int rows_per_cta;   // consecutive query rows handled by a CTA (heads_per_cta x rows_per_cta warps, <= 16)
+  int m;              // query rows
   float scale;
 };
 
-constexpr int ATTN_THREADS = 256;
+constexpr int ATTN_MAX_WARPS = 16;
+// Bytes of the warps' exact-sum scratch at the head of the kernel's shared memory, rounded so
+// that what follows stays 16-byte aligned for any warp count.
+__host__ __device__ inline size_t attn_ssc_bytes(size_t warps) { return (warps * sizeof(SeqSumScratch) + 15) & ~(size_t)15; }
 constexpr int ATTN_CHUNK = 64;  // cached positions staged at a time
 
-__global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParams P) {
+// One CTA serves `rows_per_cta` consecutive query rows of one KV head: a warp per (row, query
+// head). The cached rows the CTA stages cover the union of its rows' ranges (rows differ by
+// one position each, and by their window start), so they are fetched once for all of them.
+__global__ void __launch_bounds__(ATTN_MAX_WARPS * 32) attention_kernel(const AttnParams P) {
   extern __shared__ __align__(16) float sm_f[];
-  __shared__ SeqSumScratch ssc[8];
   pdl_launch_dependents();
   pdl_wait();
   const int hd = P.head_dim, hd4 = hd >> 2, kv_dim = P.n_kv_head * hd, q_dim = P.n_head * hd;
-  const int gqa = P.n_head / P.n_kv_head, hpc = P.heads_per_cta;
+  const int gqa = P.n_head / P.n_kv_head, hpc = P.heads_per_cta, rpc = P.rows_per_cta;
+  const int nthreads = blockDim.x, nwarps = nthreads >> 5;
   const int splits = (gqa + hpc - 1) / hpc;
   const int kvh = blockIdx.x / splits, part = blockIdx.x - kvh * splits;
-  const int row = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h_local = part * hpc + warp;                      // head inside the KV group
-  const bool has_head = warp < hpc && h_local < gqa;
-  const int h = kvh * gqa + (has_head ? h_local : 0);
-  const int pos = (P.pos_ptr ? *P.pos_ptr : P.pos0) + row;
+  const int rs = warp / hpc, wh = warp - rs * hpc;            // row slot and head slot of this warp
+  const int row = blockIdx.y * rpc + rs;
+  const int h_local = part * hpc + wh;                        // head inside the KV group
+  const bool has_head = rs < rpc && row < P.m && h_local < gqa;
+  const int h = kvh * gqa + (h_local < gqa ? h_local : 0);
+  const int base_pos = P.pos_ptr ? *P.pos_ptr : P.pos0;
+  const int pos = base_pos + row;
   const int n = pos + 1;
   const int t0 = (P.window > 0 && pos + 1 > P.window) ? pos + 1 - P.window : 0;
   const int len = n - t0;
+  // the CTA's rows: first and last valid one, and the union [T0, N) of their ranges
+  const int row_a = blockIdx.y * rpc, row_b = min(row_a + rpc, P.m) - 1;
+  const int pos_a = base_pos + row_a, pos_b = base_pos + row_b;
+  const int T0 = (P.window > 0 && pos_a + 1 > P.window) ? pos_a + 1 - P.window : 0;
+  const int LEN = pos_b + 1 - T0;
   const int kstride = hd + 4;
-  float* qs = sm_f;                                  // hpc x hd
-  float* kv = qs + hpc * hd;                         // two buffers of ATTN_CHUNK x (hd + 4)
+  SeqSumScratch* ssc = reinterpret_cast<SeqSumScratch*>(sm_f);
+  float* qs = sm_f + attn_ssc_bytes(nwarps) / sizeof(float);  // nwarps x hd, 16-byte aligned
+  float* kv = qs + nwarps * hd;                       // two buffers of ATTN_CHUNK x (hd + 4)
   const int buf_floats = ATTN_CHUNK * kstride;
-  float* sc_all = kv + 2 * buf_floats;               // hpc x smem_scores
-  float* sc = P.smem_scores ? sc_all + warp * P.smem_scores : P.scratch + ((size_t)row * P.n_head + h) * P.ctx;
-  for (int i = threadIdx.x; i < hpc * hd; i += ATTN_THREADS) {
-    const int w = i / hd, hl = part * hpc + w;
-    qs[i] = hl < gqa ? P.q[(size_t)row * q_dim + (kvh * gqa + hl) * hd + (i - w * hd)] : 0.0f;
+  float* sc_all = kv + 2 * buf_floats;                // nwarps x smem_scores
+  float* sc = P.smem_scores ? sc_all + warp * P.smem_scores : P.scratch + ((size_t)(has_head ? row : 0) * P.n_head + h) * P.ctx;
+  for (int i = threadIdx.x; i < nwarps * hd; i += nthreads) {
+    const int w = i / hd, wr = w / hpc, hl = part * hpc + (w - wr * hpc), r = row_a + wr;
+    qs[i] = (wr < rpc && r < P.m && hl < gqa) ? P.q[(size_t)r * q_dim + (kvh * gqa + hl) * hd + (i - w * hd)] : 0.0f;
   }
-  // Cached rows [c0, c0 + cn) of this KV head into a chunk buffer with cp.async: the next
-  // chunk loads while the current one is consumed.
+  // Cached rows [c0, c0 + cn) of the union, of this KV head, into a chunk buffer with cp.async:
+  // the next chunk loads while the current one is consumed.
   auto stage = [&](float* buf, const float* cache, int stride, int c0, int cn) {
-    for (int j = threadIdx.x; j < cn * hd4; j += ATTN_THREADS) {
+    for (int j = threadIdx.x; j < cn * hd4; j += nthreads) {
       const int t = j / hd4, i4 = j - t * hd4;
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(buf + t * stride + 4 * i4)),
-                   "l"(cache + (size_t)(t0 + c0 + t) * kv_dim + kvh * hd + 4 * i4)
+                   "l"(cache + (size_t)(T0 + c0 + t) * kv_dim + kvh * hd + 4 * i4)
                    : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -385,12 +401,13 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParam
   // scores: dot(q, k_t) * scale, each dot a sequential f32 loop (ops.rs:160-166)
   float lmax = -INFINITY;
   const float* qh = qs + warp * hd;
-  stage(kv, P.k_cache, kstride, 0, min(ATTN_CHUNK, len));
-  for (int c0 = 0, ci = 0; c0 < len; c0 += ATTN_CHUNK, ci++) {
-    const int cn = min(ATTN_CHUNK, len - c0);
+  const int off = t0 - T0;                            // this row's first position inside the union
+  stage(kv, P.k_cache, kstride, 0, min(ATTN_CHUNK, LEN));
+  for (int c0 = 0, ci = 0; c0 < LEN; c0 += ATTN_CHUNK, ci++) {
+    const int cn = min(ATTN_CHUNK, LEN - c0);
     const float* cur = kv + (ci & 1) * buf_floats;
-    if (c0 + ATTN_CHUNK < len) {
-      stage(kv + ((ci + 1) & 1) * buf_floats, P.k_cache, kstride, c0 + ATTN_CHUNK, min(ATTN_CHUNK, len - c0 - ATTN_CHUNK));
+    if (c0 + ATTN_CHUNK < LEN) {
+      stage(kv + ((ci + 1) & 1) * buf_floats, P.k_cache, kstride, c0 + ATTN_CHUNK, min(ATTN_CHUNK, LEN - c0 - ATTN_CHUNK));
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -398,6 +415,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParam
     __syncthreads();
     if (has_head) {
       for (int t = lane; t < cn; t += 32) {
+        const int u = c0 + t - off;                   // position index inside this row's range
+        if (u < 0 || u >= len) continue;
         const float4* kt = reinterpret_cast<const float4*>(cur + t * kstride);
         float s = 0.0f;
 #pragma unroll 4
@@ -410,14 +429,14 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParam
           s = fadd(s, fmul(qq.w, kk.w));
         }
         s = fmul(s, P.scale);
-        sc[c0 + t] = s;
+        sc[u] = s;
         lmax = fmaxf(lmax, s);
       }
     }
     __syncthreads();  // this buffer is refilled two chunks later
   }
   // the first chunk of V rows loads while the softmax runs
-  stage(kv, P.v_cache, hd, 0, min(ATTN_CHUNK, len));
+  stage(kv, P.v_cache, hd, 0, min(ATTN_CHUNK, LEN));
   if (has_head) {
     // this head's softmax, by its own warp: max (order-free), exp, the denominator in
     // position order (ops.rs:103-107)
@@ -435,20 +454,22 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_kernel(const AttnParam
   float o[8];
 #pragma unroll
   for (int j = 0; j < 8; j++) o[j] = 0.0f;
-  for (int c0 = 0, ci = 0; c0 < len; c0 += ATTN_CHUNK, ci++) {
-    const int cn = min(ATTN_CHUNK, len - c0);
+  for (int c0 = 0, ci = 0; c0 < LEN; c0 += ATTN_CHUNK, ci++) {
+    const int cn = min(ATTN_CHUNK, LEN - c0);
     const float* cur = kv + (ci & 1) * buf_floats;
-    if (c0 + ATTN_CHUNK < len) {
-      stage(kv + ((ci + 1) & 1) * buf_floats, P.v_cache, hd, c0 + ATTN_CHUNK, min(ATTN_CHUNK, len - c0 - ATTN_CHUNK));
+    if (c0 + ATTN_CHUNK < LEN) {
+      stage(kv + ((ci + 1) & 1) * buf_floats, P.v_cache, hd, c0 + ATTN_CHUNK, min(ATTN_CHUNK, LEN - c0 - ATTN_CHUNK));
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     if (has_head) {
+      // this row's positions inside the chunk
+      const int ta = max(0, off - c0), tb = min(cn, off + len - c0);
 #pragma unroll 4
-      for (int t = 0; t < cn; t++) {
-        const float a = sc[c0 + t];
+      for (int t = ta; t < tb; t++) {
+        const float a = sc[c0 + t - off];
 #pragma unroll
         for (int j = 0; j < 8; j++)
           if (lane + 32 * j < hd) o[j] = fadd(o[j], fmul(a, cur[t * hd + lane + 32 * j]));

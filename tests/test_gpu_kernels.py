@@ -291,7 +291,7 @@ def test_expf_matches_host_libm(pkg, ob, ctx):
 
 
 # crates/aot-kernels/src/ops.rs:602-636 plus GQA shapes of both configured models
-@pytest.mark.parametrize("n_head,n_kv,hd", [(32, 4, 64), (32, 8, 128), (2, 1, 4)])
+@pytest.mark.parametrize("n_head,n_kv,hd", [(32, 4, 64), (32, 8, 128), (2, 1, 4), (40, 8, 64), (6, 2, 32), (3, 3, 16), (24, 2, 32)])
 def test_attention_bit_exact(pkg, ob, ctx, n_head, n_kv, hd):
     ctxlen = 128
     kvd = n_kv * hd
@@ -309,12 +309,15 @@ def test_attention_bit_exact(pkg, ob, ctx, n_head, n_kv, hd):
             ctx.attention(dout, ctx.to_device(q), dk, dv, n_head, n_kv, hd, ctxlen, pos, 1, window)
             assert_bits_equal(dout.download(np.float32, n_head * hd),
                               ob.attention(pool, q, kc, vc, d, ctxlen, 0, pos, window), f"attention pos {pos} w {window}")
-    m, pos0 = 9, 40
-    q = (rng.random(m * n_head * hd, dtype=np.float32) * 8 - 4)
-    dout = ctx.alloc(q.size * 4)
-    ctx.attention(dout, ctx.to_device(q), dk, dv, n_head, n_kv, hd, ctxlen, pos0, m, 0)
-    assert_bits_equal(dout.download(np.float32, q.size), ob.attention_rows(pool, q, kc, vc, d, ctxlen, 0, pos0, m, 0),
-                      "attention_rows")
+    # several rows per call: a CTA serves consecutive rows of one KV head (row counts that do
+    # and do not fill the CTAs, a window that cuts differently into each row, a chunk
+    # boundary inside the rows' ranges)
+    for m, pos0, window in ((9, 40, 0), (1, 3, 0), (16, 0, 0), (7, 60, 5), (13, 57, 64), (64, 64, 0), (5, 123, 100)):
+        q = (rng.random(m * n_head * hd, dtype=np.float32) * 8 - 4)
+        dout = ctx.alloc(q.size * 4)
+        ctx.attention(dout, ctx.to_device(q), dk, dv, n_head, n_kv, hd, ctxlen, pos0, m, window)
+        assert_bits_equal(dout.download(np.float32, q.size), ob.attention_rows(pool, q, kc, vc, d, ctxlen, 0, pos0, m, window),
+                          f"attention_rows m {m} pos0 {pos0} window {window}")
 
 
 def test_argmax_first_maximum(pkg, ob, ctx):
