@@ -788,19 +788,47 @@ static int gpu_qk_post(aotcu_gpu* g, size_t li, const int* pos_ptr, size_t pos0,
 // kept on chip, and what a CTA may use. A CTA has heads_per_cta x rows_per_cta warps, each
 // with its exact-sum scratch, its query row and (when they fit) its scores.
 static size_t attn_smem_budget(const aotcu_ctx* c) { return c->max_smem - 1024; }
-static void attn_shape(int n_head, int n_kv_head, size_t m, int* hpc, int* rpc) {
-  const int gqa = n_head / n_kv_head;
-  *hpc = gqa < 8 ? gqa : 8;
-  int r = ATTN_MAX_WARPS / *hpc;
-  if ((size_t)r > m) r = (int)m;
-  *rpc = r < 1 ? 1 : r;
+struct AttnShape {
+  int hpc, rpc, chunk;
+  bool scores_in_smem;
+  size_t smem;
+};
+static size_t attn_smem_of(int warps, int head_dim, int chunk, size_t score_floats) {
+  return attn_ssc_bytes(warps) + ((size_t)warps * head_dim + (size_t)2 * chunk * (head_dim + 4) + (size_t)warps * score_floats) * sizeof(float);
 }
-static size_t attn_smem_bytes(int n_head, int n_kv_head, int head_dim, size_t max_len, size_t m = 1) {
-  int hpc, rpc;
-  attn_shape(n_head, n_kv_head, m, &hpc, &rpc);
-  const size_t warps = (size_t)hpc * rpc;
+// Warps per CTA and staging chunk for rows of up to `max_len` positions: scores stay in shared
+// memory if any shape allows it (fewer rows per CTA rather than scores in global memory),
+// and the larger chunk is taken when it still fits.
+static AttnShape attn_shape(const aotcu_ctx* c, int n_head, int n_kv_head, int head_dim, size_t m, size_t max_len, bool want_smem_scores) {
+  const int gqa = n_head / n_kv_head;
+  AttnShape a;
+  a.hpc = gqa < 8 ? gqa : 8;
+  int rmax = ATTN_MAX_WARPS / a.hpc;
+  if ((size_t)rmax > m) rmax = (int)m;
+  if (rmax < 1) rmax = 1;
   max_len = (max_len + 3) & ~(size_t)3;
-  return attn_ssc_bytes(warps) + (warps * head_dim + (size_t)2 * ATTN_CHUNK * (head_dim + 4) + warps * max_len) * sizeof(float);
+  const size_t budget = attn_smem_budget(c);
+  if (want_smem_scores)
+    for (int r = rmax; r >= 1; r--)
+      for (int chunk : {ATTN_CHUNK_BIG, ATTN_CHUNK}) {
+        const size_t need = attn_smem_of(a.hpc * r, head_dim, chunk, max_len);
+        if (need <= budget) {
+          a.rpc = r;
+          a.chunk = chunk;
+          a.scores_in_smem = true;
+          a.smem = need;
+          return a;
+        }
+      }
+  a.rpc = rmax;
+  a.chunk = ATTN_CHUNK;
+  a.scores_in_smem = false;
+  a.smem = attn_smem_of(a.hpc * rmax, head_dim, ATTN_CHUNK, 0);
+  return a;
+}
+static size_t attn_smem_bytes(const aotcu_ctx* c, int n_head, int n_kv_head, int head_dim, size_t max_len, size_t m = 1) {
+  const AttnShape a = attn_shape(c, n_head, n_kv_head, head_dim, m, max_len, true);
+  return a.scores_in_smem ? a.smem : (size_t)-1;
 }
 
 static int launch_attention(aotcu_ctx* c, float* out, const float* q, const float* kc, const float* vc, float* scratch,
@@ -822,20 +850,19 @@ static int launch_attention(aotcu_ctx* c, float* out, const float* q, const floa
   P.scale = 1.0f / sqrtf((float)head_dim);
   ARG_CHECK(head_dim % 4 == 0 && head_dim <= 256, "head_dim must be a multiple of 4, at most 256");
   const int gqa = n_head / n_kv_head;
-  attn_shape(n_head, n_kv_head, m, &P.heads_per_cta, &P.rows_per_cta);
-  P.m = (int)m;
-  const int splits = (gqa + P.heads_per_cta - 1) / P.heads_per_cta;
-  const size_t warps = (size_t)P.heads_per_cta * P.rows_per_cta;
   // Scores in shared memory when the longest row of this call fits, else in `scratch`.
   size_t max_len = pos_ptr ? n_ctx : std::min(n_ctx, pos0 + m);
   max_len = (max_len + 3) & ~(size_t)3;
-  const size_t fixed = attn_ssc_bytes(warps) + (warps * head_dim + (size_t)2 * ATTN_CHUNK * (head_dim + 4)) * sizeof(float);
-  const size_t with_scores = fixed + warps * max_len * sizeof(float);
-  const size_t budget = attn_smem_budget(c);
-  size_t smem = fixed;
-  if (smem_scores && with_scores <= budget) {
+  const AttnShape a = attn_shape(c, n_head, n_kv_head, head_dim, m, max_len, smem_scores != 0);
+  P.heads_per_cta = a.hpc;
+  P.rows_per_cta = a.rpc;
+  P.chunk = a.chunk;
+  P.m = (int)m;
+  const int splits = (gqa + P.heads_per_cta - 1) / P.heads_per_cta;
+  const size_t warps = (size_t)P.heads_per_cta * P.rows_per_cta;
+  const size_t smem = a.smem;
+  if (a.scores_in_smem) {
     P.smem_scores = (int)max_len;
-    smem = with_scores;
   } else {
     ARG_CHECK(scratch, "attention needs a score scratch buffer for this context length");
     P.smem_scores = 0;
@@ -1561,7 +1588,7 @@ int aotcu_attention(aotcu_ctx* c, float* out, const float* q, const float* k_cac
   ARG_CHECK(head_dim % 4 == 0 && head_dim <= 256, "head_dim %zu must be a multiple of 4, at most 256", head_dim);
   ARG_CHECK(pos0 + m <= ctx_len, "positions exceed the context");
   if (m == 0) return 0;
-  ARG_CHECK(attn_smem_bytes((int)n_head, (int)n_kv_head, (int)head_dim, pos0 + m, m) <= attn_smem_budget(c),
+  ARG_CHECK(attn_smem_bytes(c, (int)n_head, (int)n_kv_head, (int)head_dim, pos0 + m, m) <= attn_smem_budget(c),
             "%zu positions are too many for the stand-alone attention entry point (scores are kept in shared memory)", pos0 + m);
   return launch_attention(c, out, q, k_cache, v_cache, nullptr, nullptr, pos0, m, (int)n_head, (int)n_kv_head,
                           (int)head_dim, ctx_len, window, (int)ctx_len);
@@ -1698,7 +1725,7 @@ int aotcu_gpu_new(aotcu_ctx* c, const aotcu_model_head* head, const aotcu_layer*
   }
   // Attention scores: shared memory when the context fits, else a global scratch.
   {
-    if (attn_smem_bytes(d.n_head, d.n_kv_head, d.head_dim, n_ctx, g->max_batch) <= attn_smem_budget(c)) {
+    if (attn_smem_bytes(c, d.n_head, d.n_kv_head, d.head_dim, n_ctx, g->max_batch) <= attn_smem_budget(c)) {
       g->smem_scores = (int)n_ctx;
     } else {
       g->smem_scores = 0;

@@ -339,6 +339,7 @@ struct AttnParams {
   int heads_per_cta;  // query heads of one KV head handled by a CTA (<= 8)
   int rows_per_cta;   // consecutive query rows handled by a CTA (heads_per_cta x rows_per_cta warps, <= 16)
   int m;              // query rows
+  int chunk;          // cached positions per staging buffer
   float scale;
 };
 
@@ -346,7 +347,8 @@ constexpr int ATTN_MAX_WARPS = 16;
 // Bytes of the warps' exact-sum scratch at the head of the kernel's shared memory, rounded so
 // that what follows stays 16-byte aligned for any warp count.
 __host__ __device__ inline size_t attn_ssc_bytes(size_t warps) { return (warps * sizeof(SeqSumScratch) + 15) & ~(size_t)15; }
-constexpr int ATTN_CHUNK = 64;  // cached positions staged at a time
+constexpr int ATTN_CHUNK = 64;      // cached positions staged at a time ...
+constexpr int ATTN_CHUNK_BIG = 128;  // ... or this many when shared memory allows: half the staging rounds
 
 // One CTA serves `rows_per_cta` consecutive query rows of one KV head: a warp per (row, query
 // head). The cached rows the CTA stages cover the union of its rows' ranges (rows differ by
@@ -376,11 +378,11 @@ __global__ void __launch_bounds__(ATTN_MAX_WARPS * 32) attention_kernel(const At
   const int pos_a = base_pos + row_a, pos_b = base_pos + row_b;
   const int T0 = (P.window > 0 && pos_a + 1 > P.window) ? pos_a + 1 - P.window : 0;
   const int LEN = pos_b + 1 - T0;
-  const int kstride = hd + 4;
+  const int kstride = hd + 4, CH = P.chunk;
   SeqSumScratch* ssc = reinterpret_cast<SeqSumScratch*>(sm_f);
   float* qs = sm_f + attn_ssc_bytes(nwarps) / sizeof(float);  // nwarps x hd, 16-byte aligned
-  float* kv = qs + nwarps * hd;                       // two buffers of ATTN_CHUNK x (hd + 4)
-  const int buf_floats = ATTN_CHUNK * kstride;
+  float* kv = qs + nwarps * hd;                       // two buffers of CH x (hd + 4)
+  const int buf_floats = CH * kstride;
   float* sc_all = kv + 2 * buf_floats;                // nwarps x smem_scores
   float* sc = P.smem_scores ? sc_all + warp * P.smem_scores : P.scratch + ((size_t)(has_head ? row : 0) * P.n_head + h) * P.ctx;
   for (int i = threadIdx.x; i < nwarps * hd; i += nthreads) {
@@ -402,12 +404,12 @@ __global__ void __launch_bounds__(ATTN_MAX_WARPS * 32) attention_kernel(const At
   float lmax = -INFINITY;
   const float* qh = qs + warp * hd;
   const int off = t0 - T0;                            // this row's first position inside the union
-  stage(kv, P.k_cache, kstride, 0, min(ATTN_CHUNK, LEN));
-  for (int c0 = 0, ci = 0; c0 < LEN; c0 += ATTN_CHUNK, ci++) {
-    const int cn = min(ATTN_CHUNK, LEN - c0);
+  stage(kv, P.k_cache, kstride, 0, min(CH, LEN));
+  for (int c0 = 0, ci = 0; c0 < LEN; c0 += CH, ci++) {
+    const int cn = min(CH, LEN - c0);
     const float* cur = kv + (ci & 1) * buf_floats;
-    if (c0 + ATTN_CHUNK < LEN) {
-      stage(kv + ((ci + 1) & 1) * buf_floats, P.k_cache, kstride, c0 + ATTN_CHUNK, min(ATTN_CHUNK, LEN - c0 - ATTN_CHUNK));
+    if (c0 + CH < LEN) {
+      stage(kv + ((ci + 1) & 1) * buf_floats, P.k_cache, kstride, c0 + CH, min(CH, LEN - c0 - CH));
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -436,7 +438,7 @@ __global__ void __launch_bounds__(ATTN_MAX_WARPS * 32) attention_kernel(const At
     __syncthreads();  // this buffer is refilled two chunks later
   }
   // the first chunk of V rows loads while the softmax runs
-  stage(kv, P.v_cache, hd, 0, min(ATTN_CHUNK, LEN));
+  stage(kv, P.v_cache, hd, 0, min(CH, LEN));
   if (has_head) {
     // this head's softmax, by its own warp: max (order-free), exp, the denominator in
     // position order (ops.rs:103-107)
@@ -454,11 +456,11 @@ __global__ void __launch_bounds__(ATTN_MAX_WARPS * 32) attention_kernel(const At
   float o[8];
 #pragma unroll
   for (int j = 0; j < 8; j++) o[j] = 0.0f;
-  for (int c0 = 0, ci = 0; c0 < LEN; c0 += ATTN_CHUNK, ci++) {
-    const int cn = min(ATTN_CHUNK, LEN - c0);
+  for (int c0 = 0, ci = 0; c0 < LEN; c0 += CH, ci++) {
+    const int cn = min(CH, LEN - c0);
     const float* cur = kv + (ci & 1) * buf_floats;
-    if (c0 + ATTN_CHUNK < LEN) {
-      stage(kv + ((ci + 1) & 1) * buf_floats, P.v_cache, hd, c0 + ATTN_CHUNK, min(ATTN_CHUNK, LEN - c0 - ATTN_CHUNK));
+    if (c0 + CH < LEN) {
+      stage(kv + ((ci + 1) & 1) * buf_floats, P.v_cache, hd, c0 + CH, min(CH, LEN - c0 - CH));
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
