@@ -350,6 +350,21 @@ __host__ __device__ inline size_t attn_ssc_bytes(size_t warps) { return (warps *
 constexpr int ATTN_CHUNK = 64;      // cached positions staged at a time ...
 constexpr int ATTN_CHUNK_BIG = 128;  // ... or this many when shared memory allows: half the staging rounds
 
+// o[j] += a[t] * v[t][lane + 32 j] for t in [ta, tb), positions in order (ops.rs:208-214), for
+// the NJ dims a lane owns; only the last of them can lie beyond the head width.
+template <int NJ>
+__device__ __forceinline__ void attn_value_mix(float (&o)[8], const float* a, const float* cur, int ta, int tb, int hd, int lane) {
+  const bool last = lane + 32 * (NJ - 1) < hd;
+#pragma unroll 4
+  for (int t = ta; t < tb; t++) {
+    const float at = a[t];
+    const float* v = cur + t * hd + lane;
+#pragma unroll
+    for (int j = 0; j < NJ - 1; j++) o[j] = fadd(o[j], fmul(at, v[32 * j]));
+    if (last) o[NJ - 1] = fadd(o[NJ - 1], fmul(at, v[32 * (NJ - 1)]));
+  }
+}
+
 // One CTA serves `rows_per_cta` consecutive query rows of one KV head: a warp per (row, query
 // head). The cached rows the CTA stages cover the union of its rows' ranges (rows differ by
 // one position each, and by their window start), so they are fetched once for all of them.
@@ -467,14 +482,19 @@ __global__ void __launch_bounds__(ATTN_MAX_WARPS * 32) attention_kernel(const At
     }
     __syncthreads();
     if (has_head) {
-      // this row's positions inside the chunk
+      // this row's positions inside the chunk; the loop over a lane's dims is instantiated for
+      // the head width (predicated-off iterations of a fixed eight would still issue)
       const int ta = max(0, off - c0), tb = min(cn, off + len - c0);
-#pragma unroll 4
-      for (int t = ta; t < tb; t++) {
-        const float a = sc[c0 + t - off];
-#pragma unroll
-        for (int j = 0; j < 8; j++)
-          if (lane + 32 * j < hd) o[j] = fadd(o[j], fmul(a, cur[t * hd + lane + 32 * j]));
+      const float* a = sc + (c0 - off);
+      switch ((hd + 31) >> 5) {
+        case 1: attn_value_mix<1>(o, a, cur, ta, tb, hd, lane); break;
+        case 2: attn_value_mix<2>(o, a, cur, ta, tb, hd, lane); break;
+        case 3: attn_value_mix<3>(o, a, cur, ta, tb, hd, lane); break;
+        case 4: attn_value_mix<4>(o, a, cur, ta, tb, hd, lane); break;
+        case 5: attn_value_mix<5>(o, a, cur, ta, tb, hd, lane); break;
+        case 6: attn_value_mix<6>(o, a, cur, ta, tb, hd, lane); break;
+        case 7: attn_value_mix<7>(o, a, cur, ta, tb, hd, lane); break;
+        default: attn_value_mix<8>(o, a, cur, ta, tb, hd, lane); break;  // head_dim <= 256
       }
     }
     __syncthreads();

@@ -291,7 +291,8 @@ def test_expf_matches_host_libm(pkg, ob, ctx):
 
 
 # crates/aot-kernels/src/ops.rs:602-636 plus GQA shapes of both configured models
-@pytest.mark.parametrize("n_head,n_kv,hd", [(32, 4, 64), (32, 8, 128), (2, 1, 4), (40, 8, 64), (6, 2, 32), (3, 3, 16), (24, 2, 32)])
+@pytest.mark.parametrize("n_head,n_kv,hd", [(32, 4, 64), (32, 8, 128), (2, 1, 4), (40, 8, 64), (6, 2, 32), (3, 3, 16), (24, 2, 32), (4, 2, 80),
+                                            (2, 1, 160), (2, 2, 256), (3, 1, 200)])
 def test_attention_bit_exact(pkg, ob, ctx, n_head, n_kv, hd):
     ctxlen = 128
     kvd = n_kv * hd
