@@ -253,6 +253,10 @@ static void megaop_derive(MegaOp& op) {
 // one or more rows for the Q8_0 family (as many at a time as their images fit in shared
 // memory; the matrix is streamed once per such group).
 constexpr size_t STREAM_STAGE_BYTES = 32768;
+#ifndef AOT_WIDE_ROWS
+#define AOT_WIDE_ROWS 1
+#endif
+static int g_wide_rows = AOT_WIDE_ROWS;  // rows per CTA from which the single-row kernel goes one lane per super-block (option "wide_rows")
 static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   StreamGemvParams P = {};
   MegaOp& op = P.op;
@@ -281,6 +285,10 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   megaop_derive(op);
   P.x_image = call.x_mode == 1;
   P.q80 = kind_act(call.seg[0].kind) == ACT_Q8_0;
+  // One lane per super-block for everything but gate/up pairs. (By measurement, back-to-back
+  // launches: 128256 x 4096 Q4_K 54 us against 96 us with four lanes per block, 5632 x 2048
+  // 3.7 against 5.0 us, 2048 x 5632 4.7 against 5.5 us, and no shape where it loses.)
+  P.wide = !P.q80 && !call.pair && call.epilogue != EPI_SILU_MUL && !g_dbg_sumi && op.rows_per_cta >= g_wide_rows ? 1 : 0;
   P.err = c->d_err;
   P.stage_bytes = (int)STREAM_STAGE_BYTES;
   const size_t x_image_bytes = P.q80 ? (call.cols / 32) * X0_STRIDE : (call.cols / 256) * XK_STRIDE;
@@ -2218,6 +2226,11 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
     return 0;
   }
   if (!strcmp(name, "mega_available")) return g->mega_ok ? 1 : 0;
+  if (!strcmp(name, "wide_rows")) {  // process-wide: rows per CTA from which single-row products use one lane per super-block
+    ARG_CHECK(value >= 1, "wide_rows must be at least 1");
+    g_wide_rows = value;
+    return 0;
+  }
   if (!strcmp(name, "tc_gemm")) {
     // process-wide: prompt chunks of Q4_K / Q5_K matrices on tcgen05 (2: always, 1: when the
     // launch has enough 128-row tiles to occupy the GPU) or on mma.sync tiles (0)

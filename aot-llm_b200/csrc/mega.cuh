@@ -17,6 +17,7 @@
 #include "groupsum.cuh"
 #include "ops.cuh"
 #include "rowdot.cuh"
+#include "rowwide.cuh"
 #include "seqsum.cuh"
 
 namespace aot {
@@ -1534,9 +1535,50 @@ struct StreamGemvParams {
   int x_image;
   int q80;        // matrices of the Q8_0 family (Q8_0 activations) instead of K-quants
   int m;          // activation rows (more than one only for the Q8_0 family)
+  int wide;       // many rows per CTA: one lane per super-block (rowwide.cuh) instead of four
   int n_stages, stage_bytes;
   int* err;
 };
+
+// Consumer side for launches with many rows per CTA (rowwide.cuh): passes of 32 / L rows are
+// dealt to the warps round robin across tiles, so that with several tiles in the ring every
+// warp has rows; a warp that has no pass in a tile still takes part in the tile's barriers.
+// Plain stores or residual adds only (no tagged words, no pairs): the single-row entry points.
+__device__ __forceinline__ void consume_op_wide(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp, int n_warps) {
+  const int nb = op.nb, lane = threadIdx.x & 31;
+  int L = 1;
+  while (L < nb && L < 32) L <<= 1;
+  const int rpp = 32 / L, gi = lane / L, bl = lane & (L - 1);
+  const uint32_t sxa = smem_addr(sx);
+  const int n_tiles = (int)blockIdx.x < op.cta_rem ? op.n_tiles_hi : op.n_tiles_lo;
+  int pass_base = 0;  // passes of the tiles before this one
+#pragma unroll 1
+  for (int tile = 0; tile < n_tiles; tile++) {
+    if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
+    const TileDesc& D = R.desc[cp.st];
+    const int n_units = D.n_units, n_pass = (n_units + rpp - 1) / rpp;
+    int p = (warp - pass_base % n_warps + n_warps) % n_warps;  // this warp's first pass inside the tile
+#pragma unroll 1
+    for (; p < n_pass; p += n_warps) {
+      const int i = p * rpp + gi;
+      uint32_t row = 0;
+      int kind = Q4_K;
+      float* out = nullptr;
+      if (i < n_units) {
+        const TileUnit U = D.unit[i];
+        row = U.row[0] & 0xFFFFFFu;
+        kind = (int)(U.row[0] >> 24);
+        out = U.out;
+      }
+      const float sum = wide_row_dot(row, kind, sxa, nb, L);
+      if (row != 0 && bl == 0) *out = op.epilogue == EPI_ACCUM ? fadd(__ldcg(out), sum) : sum;
+    }
+    pass_base += n_pass;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&R.empty[cp.st]);
+    cp.advance(R.n_stages);
+  }
+}
 
 __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const StreamGemvParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -1600,6 +1642,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   g.sync();
   RingPos cp{0, 0u};
   if (P.q80) consume_op_q80(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, P.m);
+  else if (P.wide) consume_op_wide(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
   else consume_op(P.op, R, cp, sx, wterms_all + warp * WARP_TERMS_FLOATS, warp, MEGA_CONSUMER_WARPS, 0u);
 }
 

@@ -452,3 +452,44 @@ def test_sweep_shape_128256x4096_matvec_bit_exact(pkg, ob, ctx, kind):
     ctx.matvec(kind, dout, ctx.to_device(w), ctx.to_device(xq.view(np.uint8)), rows, cols)
     assert_bits_equal(dout.download(np.float32, rows), want, f"kind {kind} 128256x4096")
     ctx.device_status()
+
+
+def test_single_row_products_one_lane_per_block(pkg, ob, ctx):
+    """The streaming kernel's two row arithmetics, one lane per super-block (the default for
+    single matrices and q/k/v launches) and four lanes per super-block (gate/up pairs; here
+    forced for everything by raising the switch point), against the oracle: every K-quant
+    kind, block counts that are and are not powers of two, more blocks than lanes, a mixed
+    q/k/v launch, and the 14336 x 4096 shape."""
+    spec = pkg.model.tiny("llama", n_layer=1)
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 16, 2)   # only to reach the process-wide switch
+    pool, tab = ob.Pool(4), ob.detect_table()
+    try:
+        for switch in (1, 1 << 30):
+            g.set_option("wide_rows", switch)
+            for kind in (Q4_K, Q5_K, Q6_K):
+                for rows, cols in ((1, 256), (37, 512), (700, 2048), (300, 5632), (96, 768), (40, 12288)):
+                    for mode in ("enc", "uniform"):
+                        w = make_weights(pkg, kind, rows, cols, 3 * kind + rows, mode)
+                        xq = ob.quantize_act(kind, _x(cols, rows + cols))
+                        dout = ctx.alloc(rows * 4)
+                        ctx.matvec(kind, dout, ctx.to_device(w), ctx.to_device(xq.view(np.uint8)), rows, cols)
+                        assert_bits_equal(dout.download(np.float32, rows), ob.matvec(pool, tab, kind, w, xq, rows, cols),
+                                          f"switch {switch}: kind {kind} {rows}x{cols} {mode}")
+            cols, rows3, kinds = 2048, (2048, 256, 256), (Q4_K, Q5_K, Q6_K)
+            ws = [make_weights(pkg, k, r, cols, 60 + i) for i, (k, r) in enumerate(zip(kinds, rows3))]
+            xq = ob.quantize_q8_k(_x(cols, 4))
+            douts = [ctx.alloc(r * 4) for r in rows3]
+            ctx.matvec3(kinds, douts, [ctx.to_device(w) for w in ws], ctx.to_device(xq.view(np.uint8)), rows3, cols)
+            for k, w, o, r in zip(kinds, ws, douts, rows3):
+                assert_bits_equal(o.download(np.float32, r), ob.matvec(pool, tab, k, w, xq, r, cols), f"switch {switch}: mixed kinds, kind {k}")
+    finally:
+        g.set_option("wide_rows", 1)
+    rows, cols = 14336, 4096
+    for kind in (Q4_K, Q6_K):
+        w = make_weights(pkg, kind, rows, cols, 11 + kind, "uniform")
+        xq = ob.quantize_act(kind, _x(cols, 5))
+        dout = ctx.alloc(rows * 4)
+        ctx.matvec(kind, dout, ctx.to_device(w), ctx.to_device(xq.view(np.uint8)), rows, cols)
+        assert_bits_equal(dout.download(np.float32, rows), ob.matvec(pool, tab, kind, w, xq, rows, cols), f"14336 x 4096 kind {kind}")
+    g.close()
+    ctx.device_status()
