@@ -21,6 +21,8 @@
 #include "gemm.cuh"
 #include "gemm_tc.cuh"
 #include "mega.cuh"
+#include "q80stream.cuh"
+#include "floatstream.cuh"
 #include "ops.cuh"
 
 using namespace aot;
@@ -320,6 +322,211 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   return 0;
 }
 
+// Q4_0 / Q5_0 / Q8_0 products on the chunk-streaming kernel (q80stream.cuh): matrices of one
+// kind, up to Q80S_MAX_TOK activation rows per launch (fewer when their images leave no room
+// for three ring stages). Returns 1 when the call does not fit this kernel.
+static int g_q80_chunks = 1;         // 0: keep Q8_0-family products on the whole-row kernels (option "q80_chunks")
+static int g_q80_rows_per_lane = 0;  // 0: by shape; 1 / 2: forced (option "q80_rows_per_lane")
+template <int KIND, int NR, int NT>
+static int launch_q80_stream_t(aotcu_ctx* c, const Q80StreamParams& P, int grid, size_t smem) {
+  static bool attr_set[64] = {};
+  if (c->device >= 0 && c->device < 64 && !attr_set[c->device]) {
+    CU_TRY(cudaFuncSetAttribute(q80_stream_kernel<KIND, NR, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+    attr_set[c->device] = true;
+  }
+  return launch(c, q80_stream_kernel<KIND, NR, NT>, dim3(grid), dim3(MEGA_THREADS), smem, P);
+}
+template <int KIND>
+static int launch_q80_stream_k(aotcu_ctx* c, const Q80StreamParams& P, int nr, int nt, int grid, size_t smem) {
+  if (nt == 16) return launch_q80_stream_t<KIND, 2, 16>(c, P, grid, smem);
+  if (nt == 8) return nr == 2 ? launch_q80_stream_t<KIND, 2, 8>(c, P, grid, smem) : launch_q80_stream_t<KIND, 1, 8>(c, P, grid, smem);
+  return nr == 2 ? launch_q80_stream_t<KIND, 2, 1>(c, P, grid, smem) : launch_q80_stream_t<KIND, 1, 1>(c, P, grid, smem);
+}
+// 2-D tensor map over 32-bit elements: [dim1][dim0] with rows `stride_bytes` apart, box
+// [box1][box0]. cuTensorMapEncodeTiled comes from the driver through the runtime (no link
+// against libcuda). Returns false when the driver refuses the map.
+static bool tensor_map_2d(CUtensorMap* out, CUtensorMapDataType dtype, const void* base, size_t dim0, size_t dim1, size_t stride_bytes,
+                          int box0, int box1) {
+  using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult st;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &st) != cudaSuccess || st != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode) return false;
+  const cuuint64_t gdim[2] = {dim0, dim1}, gstride[1] = {stride_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box0, (cuuint32_t)box1}, estride[2] = {1, 1};
+  return encode(out, dtype, 2, const_cast<void*>(base), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// A weight matrix as rows of u32 words, box of four rows by one chunk.
+static bool weight_tensor_map(CUtensorMap* out, const uint8_t* w, size_t rows, size_t row_bytes, int chunk_bytes) {
+  return tensor_map_2d(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, w, row_bytes / 4, rows, row_bytes, chunk_bytes / 4, 4);
+}
+
+// Shape of a stage of the chunk-streaming kernels. One activation row: every consumer warp
+// owns a quad, or two where a CTA has more quads than warps (and for pairs). Several: up to
+// 16 rows per launch, as 16 per lane, or as two token groups of 8 on half of the warps each
+// where a CTA has few quads.
+struct ChunkShape {
+  int nr, nt, qw, ts;
+};
+static ChunkShape chunk_shape(int quads_per_cta, bool pair, size_t m, int force_nr) {
+  ChunkShape s = {1, 1, MEGA_CONSUMER_WARPS, 1};
+  if (m == 1) {
+    s.nr = pair || quads_per_cta > MEGA_CONSUMER_WARPS ? 2 : 1;
+    if (force_nr && !pair) s.nr = force_nr;
+    return s;
+  }
+  const int half = MEGA_CONSUMER_WARPS / 2;
+  s.nr = pair || quads_per_cta > half ? 2 : 1;
+  const int lane_quads = pair ? quads_per_cta : (quads_per_cta + s.nr - 1) / s.nr;  // quads (pair quads) a warp column must cover
+  if (lane_quads <= half) {
+    s.qw = half;
+    s.ts = 2;
+    s.nt = 8;
+  } else {
+    s.nr = 2;
+    s.nt = 16;
+  }
+  return s;
+}
+
+static int launch_q80_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
+  const int kind = call.seg[0].kind;
+  const size_t row_bytes = kind_row_bytes(kind, call.cols);
+  // what the tensor copies need: one kind, rows in fours, 16-byte aligned rows
+  if (row_bytes % 16 || span % 4) return 1;
+  for (int s = 0; s < call.nseg; s++)
+    if (call.seg[s].kind != kind || call.seg[s].rows % 4 || ((uintptr_t)call.seg[s].w & 15)) return 1;
+  Q80StreamParams P = {};
+  for (int s = 0; s < call.nseg; s++) {
+    P.seg[s] = call.seg[s];
+    if (!weight_tensor_map(&P.map[s], call.seg[s].w, (size_t)call.seg[s].rows, row_bytes, q80s_chunk_bytes(kind))) return 1;
+  }
+  P.nseg = call.nseg;
+  P.pair = call.pair;
+  P.cols = (int)call.cols;
+  P.epilogue = call.epilogue;
+  P.x_image = call.x_mode == 1;
+  P.err = c->d_err;
+  const size_t quads = span / 4;
+  const int grid = quads < (size_t)c->n_sm ? (int)quads : c->n_sm;
+  P.quad_base = (int)(quads / grid);
+  P.quad_rem = (int)(quads % grid);
+  const size_t nb = call.cols / 32, x_image_bytes = nb * X0_STRIDE, x_src_bytes = P.x_image ? x_image_bytes : nb * 36;
+  const size_t tail = 128 + 16 + 128;
+  const ChunkShape shape = chunk_shape(P.quad_base + (P.quad_rem ? 1 : 0), call.pair != 0, call.m, g_q80_rows_per_lane);
+  int nr = shape.nr, nt = shape.nt, qw = shape.qw, ts = shape.ts;
+  const size_t quad_bytes = (size_t)4 * q80s_chunk_bytes(kind);
+  size_t stage = (size_t)qw * nr * quad_bytes;
+  if (c->max_smem < tail + 2 * stage + x_image_bytes) return 1;
+  // Activation rows per launch: as many as fit beside two stages. (With several rows the
+  // arithmetic, not the copies, sets the pace: a deeper ring buys less than rows that share
+  // each expanded weight.)
+  size_t group = (c->max_smem - tail - 2 * stage) / x_image_bytes;
+  group = std::min(std::min(group, (size_t)ts * nt), call.m);
+  if (ts == 2 && group <= (size_t)nt) {  // one token group is enough: give its warps the whole CTA
+    ts = 1;
+    qw = MEGA_CONSUMER_WARPS;
+    stage = (size_t)qw * nr * quad_bytes;
+    if (c->max_smem < tail + 2 * stage + group * x_image_bytes) return 1;
+  }
+  if (nt == 16 && group <= 8) nt = 8;
+  P.qw = qw;
+  P.ts = ts;
+  for (size_t t0 = 0; t0 < call.m; t0 += group) {
+    const size_t mg = std::min(group, call.m - t0);
+    P.m = (int)mg;
+    P.x = reinterpret_cast<const uint8_t*>(call.x) + t0 * x_src_bytes;
+    for (int s = 0; s < call.nseg; s++) P.seg[s].out = call.seg[s].out + t0 * (size_t)call.seg[s].rows;
+    const size_t fixed = ((mg * x_image_bytes + 127) & ~(size_t)127) + tail;
+    int n_stages = (int)((c->max_smem - fixed) / stage);
+    n_stages = n_stages > 8 ? 8 : n_stages;
+    P.n_stages = n_stages;
+    const size_t smem = (size_t)n_stages * stage + fixed;
+    int rc;
+    if (kind == Q4_0) rc = launch_q80_stream_k<Q4_0>(c, P, nr, nt, grid, smem);
+    else if (kind == Q5_0) rc = launch_q80_stream_k<Q5_0>(c, P, nr, nt, grid, smem);
+    else rc = launch_q80_stream_k<Q8_0>(c, P, nr, nt, grid, smem);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// F16 / BF16 / F32 products on the chunk-streaming kernel (floatstream.cuh): matrices of one
+// kind, columns in eights, rows in fours, 16-byte aligned rows and activations. Returns 1
+// when the call does not fit.
+template <int KIND, int NR, int NT>
+static int launch_float_stream_t(aotcu_ctx* c, const FloatStreamParams& P, int grid, size_t smem) {
+  static bool attr_set[64] = {};
+  if (c->device >= 0 && c->device < 64 && !attr_set[c->device]) {
+    CU_TRY(cudaFuncSetAttribute(float_stream_kernel<KIND, NR, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+    attr_set[c->device] = true;
+  }
+  return launch(c, float_stream_kernel<KIND, NR, NT>, dim3(grid), dim3(MEGA_THREADS), smem, P);
+}
+template <int KIND>
+static int launch_float_stream_k(aotcu_ctx* c, const FloatStreamParams& P, int nr, int nt, int grid, size_t smem) {
+  if (nt == 16) return launch_float_stream_t<KIND, 2, 16>(c, P, grid, smem);
+  if (nt == 8) return nr == 2 ? launch_float_stream_t<KIND, 2, 8>(c, P, grid, smem) : launch_float_stream_t<KIND, 1, 8>(c, P, grid, smem);
+  return nr == 2 ? launch_float_stream_t<KIND, 2, 1>(c, P, grid, smem) : launch_float_stream_t<KIND, 1, 1>(c, P, grid, smem);
+}
+static int g_float_chunks = 1;  // 0: keep float-kind products on gemv_float_kernel (option "float_chunks")
+static int launch_float_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
+  const int kind = call.seg[0].kind;
+  const size_t row_bytes = kind_row_bytes(kind, call.cols);
+  if (call.cols % 8 || row_bytes % 16 || span % 4 || ((uintptr_t)call.x & 15)) return 1;
+  for (int s = 0; s < call.nseg; s++)
+    if (call.seg[s].kind != kind || call.seg[s].rows % 4 || ((uintptr_t)call.seg[s].w & 15)) return 1;
+  const int cb = fs_chunk_bytes(call.m);
+  FloatStreamParams P = {};
+  for (int s = 0; s < call.nseg; s++) {
+    P.seg[s] = call.seg[s];
+    if (!weight_tensor_map(&P.map[s], call.seg[s].w, (size_t)call.seg[s].rows, row_bytes, cb)) return 1;
+  }
+  P.nseg = call.nseg;
+  P.pair = call.pair;
+  P.cols = (int)call.cols;
+  P.epilogue = call.epilogue;
+  P.err = c->d_err;
+  const size_t quads = span / 4;
+  const int grid = quads < (size_t)c->n_sm ? (int)quads : c->n_sm;
+  P.quad_base = (int)(quads / grid);
+  P.quad_rem = (int)(quads % grid);
+  const ChunkShape shape = chunk_shape(P.quad_base + (P.quad_rem ? 1 : 0), call.pair != 0, call.m, 0);
+  P.qw = shape.qw;
+  P.ts = shape.ts;
+  const int chunk_cols = cb / (kind == F32 ? 4 : 2), xrows = call.m == 1 ? 1 : FS_MAX_TOK;
+  const int x_copies = chunk_cols > 256 ? 2 : 1, xbox = chunk_cols / x_copies;  // a box row holds at most 256 elements
+  const size_t stage = (size_t)shape.qw * shape.nr * 4 * cb + x_copies * (((size_t)xrows * xbox * 4 + 127) & ~(size_t)127);
+  const size_t tail = 128 + 16 + 128;
+  int n_stages = (int)((c->max_smem - tail) / stage);
+  n_stages = n_stages > 8 ? 8 : n_stages;
+  if (n_stages < 2) return 1;
+  P.n_stages = n_stages;
+  const size_t smem = (size_t)n_stages * stage + tail;
+  const size_t group = (size_t)shape.ts * shape.nt;
+  const float* x = reinterpret_cast<const float*>(call.x);
+  for (size_t t0 = 0; t0 < call.m; t0 += group) {
+    const size_t mg = std::min(group, call.m - t0);
+    P.m = (int)mg;
+    if (!tensor_map_2d(&P.xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, x + t0 * call.cols, call.cols, mg, call.cols * 4, xbox, xrows))
+      return t0 == 0 ? 1 : fail(AOTCU_ERR_CUDA, "tensor map of the activation rows refused");
+    for (int s = 0; s < call.nseg; s++) P.seg[s].out = call.seg[s].out + t0 * (size_t)call.seg[s].rows;
+    int rc;
+    if (kind == F16) rc = launch_float_stream_k<F16>(c, P, shape.nr, shape.nt, grid, smem);
+    else if (kind == BF16) rc = launch_float_stream_k<BF16>(c, P, shape.nr, shape.nt, grid, smem);
+    else rc = launch_float_stream_k<F32>(c, P, shape.nr, shape.nt, grid, smem);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
 static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
   ARG_CHECK(call.nseg >= 1 && call.nseg <= 3, "1..3 matrices per launch");
   const int act = kind_act(call.seg[0].kind);
@@ -359,6 +566,10 @@ static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
 
   if (act == ACT_F32) {
     ARG_CHECK(((uintptr_t)call.x % 4) == 0, "activations must be 4-byte aligned");
+    if (g_float_chunks) {
+      const int rc = launch_float_stream(c, call, span);
+      if (rc <= 0) return rc;  // 1: a shape the tensor copies do not take, the plain kernel does
+    }
     int rows_per_block = 32;
     int grid = (int)((span + rows_per_block - 1) / rows_per_block);
     int cap = c->n_sm * 8;
@@ -370,6 +581,10 @@ static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
   // Prompt chunks of K-quant matrices go to the tensor-core kernel, single rows to the
   // streaming kernel (whole rows per warp, no barrier per tile).
   if (act == ACT_Q8_K && call.m >= 8 && call.m <= (size_t)GEMM_MAX_M) return launch_gemm(c, call);
+  if (act == ACT_Q8_0 && g_q80_chunks) {
+    const int rc = launch_q80_stream(c, call, span);
+    if (rc <= 0) return rc;  // 1: mixed kinds or a very long activation row, the whole-row kernels take it
+  }
   if ((call.m == 1 || act == ACT_Q8_0) && 2 * max_rb + 192 <= STREAM_STAGE_BYTES) return launch_gemv_stream(c, call, span);
 
   const int mult = call.pair ? 2 : 1;
@@ -2229,6 +2444,19 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
   if (!strcmp(name, "wide_rows")) {  // process-wide: rows per CTA from which single-row products use one lane per super-block
     ARG_CHECK(value >= 1, "wide_rows must be at least 1");
     g_wide_rows = value;
+    return 0;
+  }
+  if (!strcmp(name, "q80_chunks")) {  // process-wide: Q4_0 / Q5_0 / Q8_0 products on the chunk-streaming kernel (1, default)
+    g_q80_chunks = value != 0;
+    return 0;
+  }
+  if (!strcmp(name, "float_chunks")) {  // process-wide: F16 / BF16 / F32 products on the chunk-streaming kernel (1, default)
+    g_float_chunks = value != 0;
+    return 0;
+  }
+  if (!strcmp(name, "q80_rows_per_lane")) {  // process-wide: 0 by shape, 1 or 2 forced (single activation row, no pair)
+    ARG_CHECK(value >= 0 && value <= 2, "q80_rows_per_lane is 0, 1 or 2");
+    g_q80_rows_per_lane = value;
     return 0;
   }
   if (!strcmp(name, "tc_gemm")) {

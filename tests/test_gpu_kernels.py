@@ -191,6 +191,60 @@ def test_matmul_wide_rows_in_groups_bit_exact(pkg, ob, ctx, kind):
     ctx.device_status()
 
 
+# The chunk-streaming kernels (Q8_0 family and float kinds: rows in fours, 16-byte aligned
+# rows) in each of their shapes: one or two rows per lane, a CTA with more rows than one
+# stage holds, a last chunk that is not full, and 1, 8 or 16 activation rows per lane with
+# one or two token groups. Both they and the whole-row kernels they replace must give the
+# oracle's bits.
+@pytest.mark.parametrize("kind", [Q4_0, Q5_0, Q8_0, F16, BF16, F32])
+def test_chunk_streaming_products_bit_exact(pkg, ob, ctx, kind):
+    spec = pkg.model.tiny("llama", n_layer=1)
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 16, 2)   # only to reach the process-wide switches
+    pool, tab = ob.Pool(8), ob.detect_table()
+    cols = 2304 if kind >= Q4_0 else 2056                     # 4.5 chunks of 16 blocks / 7.6 and 14.3 chunks of columns
+    switch = "q80_chunks" if kind >= Q4_0 else "float_chunks"
+    try:
+        for on in (1, 0):
+            g.set_option(switch, on)
+            # rows per CTA (148 SMs): 1 quad; 7 quads; 14 quads; 33 quads (two groups of 30)
+            for rows, ms in ((600, (1, 5)), (4000, (1, 9, 16)), (8000, (1, 33)), (19000, (1, 17))):
+                if not on and rows > 4000:
+                    continue
+                w = make_weights(pkg, kind, rows, cols, 500 + kind + rows)
+                dw = ctx.to_device(w)
+                for m in ms:
+                    xs = _x(m * cols, 60 + m, 1.0)
+                    q = ob.quantize_act(kind, xs)
+                    want = ob.matmul(pool, tab, kind, w, q, m, rows, cols)
+                    dout = ctx.alloc(m * rows * 4)
+                    ctx.matmul(kind, dout, dw, ctx.to_device(q.view(np.uint8)), m, rows, cols)
+                    assert_bits_equal(dout.download(np.float32, m * rows).reshape(m, rows), want,
+                                      f"kind {kind} {rows}x{cols} m {m} chunks {on}")
+                    dout.free()
+                dw.free()
+            # gate/up pair and three matrices in one launch
+            rows = 2400
+            wa, wb = make_weights(pkg, kind, rows, cols, 700 + kind), make_weights(pkg, kind, rows, cols, 800 + kind)
+            dwa, dwb = ctx.to_device(wa), ctx.to_device(wb)
+            for m in (1, 12):
+                xs = _x(m * cols, 90 + m, 1.0)
+                q = ob.quantize_act(kind, xs)
+                da, db = ctx.alloc(m * rows * 4), ctx.alloc(m * rows * 4)
+                ctx.matmul2(kind, da, db, dwa, dwb, ctx.to_device(q.view(np.uint8)), m, rows, cols)
+                assert_bits_equal(da.download(np.float32, m * rows).reshape(m, rows), ob.matmul(pool, tab, kind, wa, q, m, rows, cols), f"pair a kind {kind} m {m} chunks {on}")
+                assert_bits_equal(db.download(np.float32, m * rows).reshape(m, rows), ob.matmul(pool, tab, kind, wb, q, m, rows, cols), f"pair b kind {kind} m {m} chunks {on}")
+            rows3 = (2048, 256, 512)
+            ws = [make_weights(pkg, kind, r, cols, 900 + i) for i, r in enumerate(rows3)]
+            xq = ob.quantize_act(kind, _x(cols, 4))
+            douts = [ctx.alloc(r * 4) for r in rows3]
+            ctx.matvec3((kind,) * 3, douts, [ctx.to_device(w) for w in ws], ctx.to_device(xq.view(np.uint8)), rows3, cols)
+            for w, o, r in zip(ws, douts, rows3):
+                assert_bits_equal(o.download(np.float32, r), ob.matvec(pool, tab, kind, w, xq, r, cols), f"three matrices, kind {kind} chunks {on}")
+    finally:
+        g.set_option(switch, 1)
+    ctx.device_status()
+
+
 def test_matmul_large_tile_loop(pkg, ob, ctx):
     rows, cols, m = 1200, 2048, 5
     w = make_weights(pkg, Q4_K, rows, cols, 5)
