@@ -192,12 +192,18 @@ def run_sweep(args):
     shapes = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]
     if args.sweep_small:
         shapes = shapes[:2]
+    if args.sweep_shapes:
+        shapes = [tuple(int(v) for v in sh.split("x")) for sh in args.sweep_shapes.split(",")]
+    names = ("q4_0", "q5_0", "q8_0", "q4_k", "q5_k", "q6_k", "f16", "bf16")
+    if args.sweep_kinds:
+        names = tuple(args.sweep_kinds.split(","))
+    ms = tuple(int(v) for v in args.sweep_m.split(","))
     rows_out = []
-    for name in ("q4_0", "q5_0", "q8_0", "q4_k", "q5_k", "q6_k", "f16", "bf16"):
+    for name in names:
         kind = KINDS[name]
         for rows, cols in shapes:
             w = _synth_matrix(pkg, kind, rows, cols, 7)
-            for m in (1, 64):
+            for m in ms:
                 iters = 20 if m == 1 else 5
                 us, nbytes, copies = time_product(pkg, ctx, kind, rows, cols, m, iters, host_w=w)
                 rows_out.append({"kind": name, "rows": rows, "cols": cols, "m": m, "us_per_launch": round(us, 2),
@@ -583,6 +589,9 @@ def main():
     ap.add_argument("--tp-nccl", action="store_true", help="with --tp: exchange through NCCL all-reduces (per-operator path)")
     ap.add_argument("--sweep", action="store_true", help="quant-type kernel sweep (configs[4]) instead of the decode benchmark")
     ap.add_argument("--sweep-small", action="store_true", help="with --sweep: only the two smaller shapes")
+    ap.add_argument("--sweep-kinds", default="", help="with --sweep: comma-separated kinds (default: all eight)")
+    ap.add_argument("--sweep-shapes", default="", help="with --sweep: comma-separated ROWSxCOLS (default: the four of configs[4])")
+    ap.add_argument("--sweep-m", default="1,64", help="with --sweep: comma-separated activation row counts")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
