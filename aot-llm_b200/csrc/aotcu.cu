@@ -1226,7 +1226,8 @@ static int mega_setup(aotcu_gpu* g) {
   // Every CTA must own a row of every product (the tagged hand-over between phases relies
   // on it), and phase ids must fit the tag's low 10 bits.
   const size_t kvd = (size_t)d.n_kv_head * d.head_dim;
-  ok = ok && d.n_layer <= 200 && (size_t)d.dim >= (size_t)c->n_sm && (size_t)d.hidden >= (size_t)c->n_sm;
+  ok = ok && d.n_layer <= 200 && (size_t)d.dim >= (size_t)c->n_sm && (size_t)d.hidden >= (size_t)c->n_sm &&
+       (d.dim + c->n_sm - 1) / c->n_sm <= 64;  // a CTA's rows of the residual stream fit the 64-float parking strip
   if (!ok) return 0;
   size_t nb_max = std::max(std::max((size_t)d.dim, (size_t)d.hidden), qd) / 256;
   // Block-term strips hold two rows of a gate/up pair, norm rows stay in registers (two
@@ -2312,7 +2313,6 @@ int aotcu_tp_unique_id(const char* nccl_library, uint8_t out_id[128]) {
   return 0;  // the library stays loaded
 }
 
-constexpr int TP_MAX_WORLD = 8;
 
 int aotcu_tp_inbox_handle(aotcu_gpu* g, uint8_t out_handle[64]) {
   ARG_CHECK(g && out_handle, "NULL argument");

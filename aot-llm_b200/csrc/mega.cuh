@@ -125,13 +125,14 @@ __device__ __forceinline__ void cta_rows(int span, int& c0, int& c1) {
 // [product][its rank][i] of every rank's inbox (plain 8-byte stores to peer memory over
 // NVLink); the CTA that owns row i on each rank waits for the world's words, adds them in
 // rank order (so every rank gets the same bits) and publishes the new residual row locally.
+constexpr int TP_MAX_WORLD = 8;  // ranks of one exchange (one NVSwitch domain)
 struct TpExchange {
   int world, rank, dim;
   int head_sharded;  // the output head is split by vocabulary rows: ranks exchange their best (logit, id)
   int head_row0;     // first vocabulary row of this rank's slice
   int arg_off;       // word offset of the [world][2] argmax slots behind the partial rows
   int pad_[2];       // keeps the members behind this struct on their former 16-byte phase
-  LLWord* inbox[8];  // inbox of rank d (peer mapping), layout [2 products][world][dim], then [world][2]
+  LLWord* inbox[TP_MAX_WORLD];  // inbox of rank d (peer mapping), layout [2 products][world][dim], then [world][2]
 };
 
 __device__ __forceinline__ void ll_store_sys(LLWord* p, float v, uint32_t tag) {
@@ -401,7 +402,7 @@ constexpr int WARP_TERMS_FLOATS = 128;  // strip per consumer warp
 // residual value asked for when the unit was parked (ACCUM into tagged words only).
 template <bool TP>
 __device__ __forceinline__ void warp_flush(const MegaOp& op, const float* wterms, int pend, int nb, int tstride, uint32_t tag,
-                                           const TpExchange* tpx, int which, float* my_out, float my_old) {
+                                           const TpExchange* tpx, int which, float* my_out, float my_old, float* part, int part_row0) {
   __syncwarp();
   const int lane = threadIdx.x & 31;
   if (op.pair) {
@@ -422,11 +423,10 @@ __device__ __forceinline__ void warp_flush(const MegaOp& op, const float* wterms
   } else if (lane < pend) {
     const float v = terms_seq_sum(wterms + lane * tstride, nb);
     if (TP && op.ll && tpx && op.epilogue == EPI_ACCUM) {
-      // a partial row of a sharded product: hand it to every rank (this one included)
-      for (int dst = 0; dst < tpx->world; dst++)
-        ll_store_sys(tpx->inbox[dst] + ((size_t)which * tpx->world + tpx->rank) * tpx->dim +
-                         (reinterpret_cast<LLWord*>(my_out) - reinterpret_cast<LLWord*>(op.seg[0].out)),
-                     v, tag);
+      // a partial row of a sharded product: parked for the CTA's hand-over to the ranks, which
+      // sends the CTA's rows as contiguous words (a warp's own rows are n_warps apart: one
+      // 8-byte NVLink write each would cost a packet per row and rank)
+      part[(int)(reinterpret_cast<LLWord*>(my_out) - reinterpret_cast<LLWord*>(op.seg[0].out)) - part_row0] = v;
     } else if (op.ll) {
       // a residual row is only ever written by its owner, so its old value needs no tag check
       ll_store(reinterpret_cast<LLWord*>(my_out), op.epilogue == EPI_ACCUM ? fadd(my_old, v) : v, tag);
@@ -440,7 +440,7 @@ __device__ __forceinline__ void warp_flush(const MegaOp& op, const float* wterms
 template <bool TP = false>
 __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, float* wterms, int warp,
                                            int n_warps, uint32_t tag, const TpExchange* tpx = nullptr, int which = 0,
-                                           SubProf sp = SubProf{nullptr, 0}) {
+                                           SubProf sp = SubProf{nullptr, 0}, float* part = nullptr, int part_row0 = 0) {
   sp.last = clock64();
   const int pair = op.pair, nb = op.nb, ll = op.ll;
   const int lane = threadIdx.x & 31;
@@ -495,7 +495,7 @@ __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, Ring
       }
       sp.mark(27);
       if (++pend == cap) {
-        warp_flush<TP>(op, wterms, pend, nb, tstride, tag, tpx, which, my_out, my_old);
+        warp_flush<TP>(op, wterms, pend, nb, tstride, tag, tpx, which, my_out, my_old, part, part_row0);
         pend = 0;
         sp.mark(30);
       }
@@ -505,7 +505,7 @@ __device__ __forceinline__ void consume_op(const MegaOp& op, const Ring& R, Ring
     cp.advance(R.n_stages);
   }
   sp.mark(18);
-  if (pend) warp_flush<TP>(op, wterms, pend, nb, tstride, tag, tpx, which, my_out, my_old);
+  if (pend) warp_flush<TP>(op, wterms, pend, nb, tstride, tag, tpx, which, my_out, my_old, part, part_row0);
   sp.mark(30);
 }
 
@@ -544,7 +544,7 @@ struct MegaSmem {
   uint8_t* sx;          // Q8_K images of the current activation vector
   float* scr;           // f32 scratch
   SeqSumScratch* ss;
-  float* red;           // 32 floats
+  float* red;           // 64 floats: per-warp partials of a reduction; partial rows parked for the cross-rank hand-over
   volatile int* abort;  // this CTA gave up on a bounded wait
   int* err;             // device error word
 };
@@ -1371,22 +1371,43 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_step_kernel(const Step
     // q/k/v: tl+1, wo: tl+3, gate/up: tl+4, down: tl+5 (the head writes plain floats)
     const uint32_t tag_out = tl + (ph == 0 ? 1u : (uint32_t)ph + 2u);
     const bool exchange = TP && (ph & 1) && !head;
+    int xr0 = 0, xr1 = 0;  // rows of the residual stream this CTA owns (the rows of wo / down it computes)
+    if (TP && exchange) cta_rows(P.dim, xr0, xr1);
     consume_op<TP>(op, R, cp, sx, wterms, warp, MEGA_CONSUMER_WARPS, tag_out, exchange ? &P.tp : nullptr, ph >> 1,
-                   SubProf{nullptr, 0});
+                   SubProf{nullptr, 0}, M.red, xr0);
     if (head) break;
     // The next phase rewrites the activation images and the scratch rows; warps that are
     // done must also not start polling while others still compute.
     g.sync();
     if (TP && exchange) {
+      // Hand this CTA's partial rows to every rank (this one included): warp d sends to rank
+      // d, its lanes consecutive rows, so a rank receives each CTA's rows as whole sectors.
+      const int r0 = xr0, r1 = xr1;
+      for (int dst = warp; dst < P.tp.world; dst += MEGA_CONSUMER_WARPS) {
+        LLWord* const to = P.tp.inbox[dst] + ((size_t)(ph >> 1) * P.tp.world + P.tp.rank) * P.dim + r0;
+        for (int i = g.tid & 31; i < r1 - r0; i += 32) ll_store_sys(to + i, M.red[i], tag_out);
+      }
+      g.sync();  // the next phase reuses the parking strip
       // The rows this CTA owns: wait for every rank's partial, add them in rank order, join
-      // the residual stream and publish the row for this GPU's CTAs.
-      int r0, r1;
-      cta_rows(P.dim, r0, r1);
-      for (int i = r0 + g.tid; i < r1; i += g.nthreads) {
-        const LLWord* in = P.tp.inbox[P.tp.rank] + (size_t)(ph >> 1) * P.tp.world * P.dim + i;
-        float sum = ll_wait_sys(in, tag_out, abort, P.err);
-        for (int src = 1; src < P.tp.world; src++) sum = fadd(sum, ll_wait_sys(in + (size_t)src * P.dim, tag_out, abort, P.err));
-        ll_store(P.xl + i, fadd(ll_value(P.xl + i), sum), tag_out);
+      // the residual stream and publish the row for this GPU's CTAs. Eight lanes per row,
+      // lane s waiting for rank s's word (one after the other, eight ranks would cost one
+      // thread eight round trips to memory that peers write); lane 0 adds them through shuffles.
+      {
+        const int sub = g.tid & (TP_MAX_WORLD - 1), slot_row = g.tid / TP_MAX_WORLD;
+        const LLWord* const in = P.tp.inbox[P.tp.rank] + (size_t)(ph >> 1) * P.tp.world * P.dim + (size_t)sub * P.dim;
+        for (int i0 = r0; i0 < r1; i0 += g.nthreads / TP_MAX_WORLD) {  // the same trip count in every lane of a warp
+          const int i = i0 + slot_row;
+          float v = 0.0f;
+          if (i < r1 && sub < P.tp.world) v = ll_wait_sys(in + i, tag_out, abort, P.err);
+          const int base = (g.tid & 31) & ~(TP_MAX_WORLD - 1);
+          float sum = __shfl_sync(0xffffffffu, v, base);
+#pragma unroll
+          for (int src = 1; src < TP_MAX_WORLD; src++) {
+            const float t = __shfl_sync(0xffffffffu, v, base + src);
+            if (src < P.tp.world) sum = fadd(sum, t);
+          }
+          if (i < r1 && sub == 0) ll_store(P.xl + i, fadd(ll_value(P.xl + i), sum), tag_out);
+        }
       }
     }
     MEGA_PROF(slot + 1);
