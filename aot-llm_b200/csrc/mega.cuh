@@ -1150,7 +1150,8 @@ __device__ void phase_argmax(const StepParams& P, const MegaSmem& M, const CtaGr
     redi[g.tid >> 5] = idx;
   }
   g.sync();
-  if (g.tid == 0) {
+  if (g.tid < 32) {
+    // warp 0: every lane folds the warps' candidates (the same result in each)
     for (int w = 1; w < (g.nthreads >> 5); w++) {
       if (M.red[w] > best || (M.red[w] == best && redi[w] < idx)) {
         best = M.red[w];
@@ -1159,32 +1160,38 @@ __device__ void phase_argmax(const StepParams& P, const MegaSmem& M, const CtaGr
     }
     if (idx == 0x7fffffff) idx = 0;
     if (TP && P.tp.head_sharded) {
+      // lane r hands this rank's best {logit, id} to rank r; lane l waits for word l of the
+      // ranks' slots here (one round trip for all of them), and the shuffles walk them in rank order
       const uint32_t tag = (*P.epoch << 11) + 5u * (uint32_t)P.n_layer + 8u;
       idx += P.tp.head_row0;
-      for (int r = 0; r < P.tp.world; r++) {
-        LLWord* slot = P.tp.inbox[r] + P.tp.arg_off + 2 * P.tp.rank;
+      if (g.tid < P.tp.world) {
+        LLWord* slot = P.tp.inbox[g.tid] + P.tp.arg_off + 2 * P.tp.rank;
         ll_store_sys(slot, best, tag);
         ll_store_sys(slot + 1, __int_as_float(idx), tag);
       }
+      float word = 0.0f;
+      if (g.tid < 2 * P.tp.world) word = ll_wait_sys(P.tp.inbox[P.tp.rank] + P.tp.arg_off + g.tid, tag, M.abort, M.err);
       best = -INFINITY;
       idx = 0x7fffffff;
-      for (int r = 0; r < P.tp.world; r++) {
-        const LLWord* slot = P.tp.inbox[P.tp.rank] + P.tp.arg_off + 2 * r;
-        const float v = ll_wait_sys(slot, tag, M.abort, M.err);
-        const int i = __float_as_int(ll_wait_sys(slot + 1, tag, M.abort, M.err));
-        if (v > best || (v == best && i < idx)) {
+#pragma unroll
+      for (int r = 0; r < TP_MAX_WORLD; r++) {
+        const float v = __shfl_sync(0xffffffffu, word, 2 * r);
+        const int i = __float_as_int(__shfl_sync(0xffffffffu, word, 2 * r + 1));
+        if (r < P.tp.world && (v > best || (v == best && i < idx))) {
           best = v;
           idx = i;
         }
       }
       if (idx == 0x7fffffff) idx = 0;
     }
-    if (P.out_token) *P.out_token = idx;
-    int gcount = P.step[2];
-    if (P.history && gcount < P.history_cap) P.history[gcount] = idx;
-    P.step[0] = idx;
-    P.step[1] = P.step[1] + 1;
-    P.step[2] = gcount + 1;
+    if (g.tid == 0) {
+      if (P.out_token) *P.out_token = idx;
+      int gcount = P.step[2];
+      if (P.history && gcount < P.history_cap) P.history[gcount] = idx;
+      P.step[0] = idx;
+      P.step[1] = P.step[1] + 1;
+      P.step[2] = gcount + 1;
+    }
   }
 }
 
