@@ -303,7 +303,9 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   if (group > call.m) group = call.m;
   static bool attr_set[64] = {};
   if (c->device >= 0 && c->device < 64 && !attr_set[c->device]) {
-    CU_TRY(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+    CU_TRY(cudaFuncSetAttribute(gemv_stream_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+    CU_TRY(cudaFuncSetAttribute(gemv_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+    CU_TRY(cudaFuncSetAttribute(gemv_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
     attr_set[c->device] = true;
   }
   const int grid = span < (size_t)c->n_sm ? (int)span : c->n_sm;
@@ -317,7 +319,8 @@ static int launch_gemv_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
     if (n_stages > 6) n_stages = 6;
     P.n_stages = n_stages;
     const size_t smem = (size_t)n_stages * STREAM_STAGE_BYTES + fixed;
-    if (int rc = launch(c, gemv_stream_kernel, dim3(grid), dim3(MEGA_THREADS), smem, P)) return rc;
+    auto kernel = P.q80 ? gemv_stream_kernel<0> : (P.wide ? gemv_stream_kernel<1> : gemv_stream_kernel<2>);
+    if (int rc = launch(c, kernel, dim3(grid), dim3(MEGA_THREADS), smem, P)) return rc;
   }
   return 0;
 }

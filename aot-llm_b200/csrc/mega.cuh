@@ -1608,6 +1608,10 @@ __device__ __forceinline__ void consume_op_wide(const MegaOp& op, const Ring& R,
   }
 }
 
+// MODE picks the consumer that is compiled in (0: Q8_0 family, 1: one lane per super-block,
+// 2: four lanes per super-block): a launch starts with a cold instruction cache, so each
+// variant carries only the code it runs.
+template <int MODE>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const StreamGemvParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   // [stages][sx images][barriers 128 B][abort][term strips]
@@ -1669,8 +1673,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   }
   g.sync();
   RingPos cp{0, 0u};
-  if (P.q80) consume_op_q80(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, P.m);
-  else if (P.wide) consume_op_wide(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
+  if (MODE == 0) consume_op_q80(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, P.m);
+  else if (MODE == 1) consume_op_wide(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
   else consume_op(P.op, R, cp, sx, wterms_all + warp * WARP_TERMS_FLOATS, warp, MEGA_CONSUMER_WARPS, 0u);
 }
 
