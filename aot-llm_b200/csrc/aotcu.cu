@@ -64,6 +64,8 @@ struct aotcu_ctx {
   uint64_t launches = 0;
   cudaEvent_t t0 = nullptr, t1 = nullptr;
   std::vector<struct aotcu_gpu*> gpus;  // live Gpus of this context (freed with it)
+  uint8_t* ximg = nullptr;              // Q8_0 activation images made from reference-layout blocks (launch_q80_stream)
+  size_t ximg_bytes = 0;
 };
 
 constexpr size_t WEIGHT_PAD = 256;
@@ -421,37 +423,63 @@ static int launch_q80_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   const int grid = quads < (size_t)c->n_sm ? (int)quads : c->n_sm;
   P.quad_base = (int)(quads / grid);
   P.quad_rem = (int)(quads % grid);
-  const size_t nb = call.cols / 32, x_image_bytes = nb * X0_STRIDE, x_src_bytes = P.x_image ? x_image_bytes : nb * 36;
+  const size_t nb = call.cols / 32, x_image_bytes = nb * X0_STRIDE;
   const size_t tail = 128 + 16 + 128;
   const ChunkShape shape = chunk_shape(P.quad_base + (P.quad_rem ? 1 : 0), call.pair != 0, call.m, g_q80_rows_per_lane);
   int nr = shape.nr, nt = shape.nt, qw = shape.qw, ts = shape.ts;
+  if (nt == 16 && call.m <= 8) nt = 8;  // fewer accumulators for a short batch
   const size_t quad_bytes = (size_t)4 * q80s_chunk_bytes(kind);
-  size_t stage = (size_t)qw * nr * quad_bytes;
-  if (c->max_smem < tail + 2 * stage + x_image_bytes) return 1;
-  // Activation rows per launch: as many as fit beside two stages. (With several rows the
-  // arithmetic, not the copies, sets the pace: a deeper ring buys less than rows that share
-  // each expanded weight.)
-  size_t group = (c->max_smem - tail - 2 * stage) / x_image_bytes;
-  group = std::min(std::min(group, (size_t)ts * nt), call.m);
-  if (ts == 2 && group <= (size_t)nt) {  // one token group is enough: give its warps the whole CTA
-    ts = 1;
-    qw = MEGA_CONSUMER_WARPS;
-    stage = (size_t)qw * nr * quad_bytes;
-    if (c->max_smem < tail + 2 * stage + group * x_image_bytes) return 1;
-  }
-  if (nt == 16 && group <= 8) nt = 8;
   P.qw = qw;
   P.ts = ts;
+  if (call.m == 1) {
+    const size_t stage = (size_t)qw * nr * quad_bytes, fixed = ((x_image_bytes + 127) & ~(size_t)127) + tail;
+    if (c->max_smem < fixed + 2 * stage) return 1;
+    int n_stages = (int)((c->max_smem - fixed) / stage);
+    P.n_stages = n_stages > 8 ? 8 : n_stages;
+    P.m = 1;
+    P.x = call.x;
+    const size_t smem = (size_t)P.n_stages * stage + fixed;
+    if (kind == Q4_0) return launch_q80_stream_k<Q4_0>(c, P, nr, nt, grid, smem);
+    if (kind == Q5_0) return launch_q80_stream_k<Q5_0>(c, P, nr, nt, grid, smem);
+    return launch_q80_stream_k<Q8_0>(c, P, nr, nt, grid, smem);
+  }
+  // Several activation rows: their images stream with the stages (16 rows x 16 blocks per
+  // stage), so they have to be images in global memory; reference-layout blocks are
+  // converted into a buffer of the context first (grown here: not during a stream capture).
+  const uint8_t* ximg = reinterpret_cast<const uint8_t*>(call.x);
+  if (!P.x_image) {
+    const size_t need = call.m * x_image_bytes;
+    if (need > c->ximg_bytes) {
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      CU_TRY(cudaStreamIsCapturing(c->stream, &cs));
+      if (cs != cudaStreamCaptureStatusNone) return 1;
+      CU_TRY(cudaStreamSynchronize(c->stream));
+      if (c->ximg) cudaFree(c->ximg);
+      c->ximg = nullptr;
+      c->ximg_bytes = 0;
+      CU_TRY(cudaMalloc(&c->ximg, need));
+      c->ximg_bytes = need;
+    }
+    const int n_blocks = (int)(call.m * nb);
+    if (int rc = launch(c, q80_to_image_kernel, dim3(grid_for(c, (size_t)n_blocks * 9, 256)), dim3(256), 0,
+                        reinterpret_cast<const uint8_t*>(call.x), c->ximg, n_blocks))
+      return rc;
+    ximg = c->ximg;
+  }
+  if ((uintptr_t)ximg & 15) return 1;
+  const size_t stage = (size_t)qw * nr * quad_bytes + (size_t)Q80S_MAX_TOK * Q80S_CBLK * X0_STRIDE;
+  if (c->max_smem < tail + 2 * stage) return 1;
+  int n_stages = (int)((c->max_smem - tail) / stage);
+  P.n_stages = n_stages > 8 ? 8 : n_stages;
+  const size_t smem = (size_t)P.n_stages * stage + tail;
+  const size_t group = (size_t)ts * nt;  // 16
   for (size_t t0 = 0; t0 < call.m; t0 += group) {
     const size_t mg = std::min(group, call.m - t0);
     P.m = (int)mg;
-    P.x = reinterpret_cast<const uint8_t*>(call.x) + t0 * x_src_bytes;
+    if (!tensor_map_2d(&P.xmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, ximg + t0 * x_image_bytes, nb * (X0_STRIDE / 4), mg, x_image_bytes,
+                       Q80S_CBLK * (X0_STRIDE / 4), Q80S_MAX_TOK))
+      return t0 == 0 ? 1 : fail(AOTCU_ERR_CUDA, "tensor map of the activation images refused");
     for (int s = 0; s < call.nseg; s++) P.seg[s].out = call.seg[s].out + t0 * (size_t)call.seg[s].rows;
-    const size_t fixed = ((mg * x_image_bytes + 127) & ~(size_t)127) + tail;
-    int n_stages = (int)((c->max_smem - fixed) / stage);
-    n_stages = n_stages > 8 ? 8 : n_stages;
-    P.n_stages = n_stages;
-    const size_t smem = (size_t)n_stages * stage + fixed;
     int rc;
     if (kind == Q4_0) rc = launch_q80_stream_k<Q4_0>(c, P, nr, nt, grid, smem);
     else if (kind == Q5_0) rc = launch_q80_stream_k<Q5_0>(c, P, nr, nt, grid, smem);
@@ -1522,6 +1550,7 @@ void aotcu_free(aotcu_ctx* c) {
     cudaStreamDestroy(c->stream);
   }
   cudaFree(c->d_err);
+  if (c->ximg) cudaFree(c->ximg);
   if (c->t0) cudaEventDestroy(c->t0);
   if (c->t1) cudaEventDestroy(c->t1);
   delete c;

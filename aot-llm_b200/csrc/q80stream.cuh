@@ -13,7 +13,7 @@
 // A chunk row is 288 / 352 / 544 bytes (32 or 96 modulo 128), so the four rows a warp reads
 // in one instruction fall into different banks, and all of them read the same activation
 // words (a broadcast). Several activation rows (NT > 1) meet every block while its weights
-// are in registers.
+// are in registers; their images' chunk travels with the stage as one more tensor copy.
 #pragma once
 #include <cuda.h>
 
@@ -34,10 +34,11 @@ constexpr int q80s_chunk_bytes(int kind) { return Q80S_CBLK * (kind == Q4_0 ? 18
 
 struct Q80StreamParams {
   alignas(64) CUtensorMap map[3];  // per matrix: u32 elements, [rows][row_bytes / 4], box [4][CB / 4]
+  alignas(64) CUtensorMap xmap;    // NT > 1: the activation images as u32 [m][nb * 12], box [16][16 blocks]
   GemvSeg seg[3];
   int nseg, pair, cols, epilogue;
   int quad_base, quad_rem;  // quads (four rows of the row space; pair rows in pair mode) split over the grid
-  const void* x;            // m activation rows: block images (x_image) or reference-layout blocks
+  const void* x;            // NT = 1: the activation row, block images (x_image) or reference-layout blocks
   int x_image, m;
   int qw, ts;  // consumer warps per token group (each owns NR quads of a stage), token groups (qw * ts <= consumer warps)
   int n_stages;
@@ -83,14 +84,20 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) q80_stream_kernel(const __gri
   using K = Q80Kind<KIND>;
   constexpr int BS = K::BS, CB = K::CB, CBLK = Q80S_CBLK;
   constexpr int QUAD = 4 * CB;
+  // several activation rows: their images travel with the stage, one chunk (16 blocks of 16
+  // rows) per stage, so neither the row length nor the number of rows is bounded by shared memory
+  constexpr bool XS = NT > 1;
+  constexpr int XROW = Q80S_CBLK * X0_STRIDE;        // bytes of one activation row's chunk
+  constexpr int XBYTES = XS ? Q80S_MAX_TOK * XROW : 0;
   const int SLOTS = P.qw * NR;  // quads per stage
-  const int STAGE = SLOTS * QUAD;
+  const int WBYTES = SLOTS * QUAD;
+  const int STAGE = WBYTES + XBYTES;
   extern __shared__ __align__(128) uint8_t smem[];
-  // [stages][activation images][barriers][abort]
+  // [stages: weight quads (, activation chunk)][activation images of a single row][barriers][abort]
   const int nb = P.cols >> 5;
   uint8_t* const stages = smem;
   uint8_t* const sx = stages + (size_t)P.n_stages * STAGE;
-  uint64_t* const bars = reinterpret_cast<uint64_t*>(sx + (((size_t)P.m * nb * X0_STRIDE + 127) & ~(size_t)127));
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(sx + (XS ? 0 : (((size_t)nb * X0_STRIDE + 127) & ~(size_t)127)));
   volatile int* const abort = reinterpret_cast<volatile int*>(bars + 16);
   Ring R;
   R.stages = stages;
@@ -127,14 +134,16 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) q80_stream_kernel(const __gri
   };
   pdl_launch_dependents();
   if (warp == MEGA_CONSUMER_WARPS) {
-    // weights do not depend on the previous kernel: stream them right away
+    // weights do not depend on the previous kernel: stream them right away (the activation
+    // chunks of several rows do, and go with them)
+    if (XS) pdl_wait();
     RingPos pp{0, 0u};
     uint32_t tiles_issued = 0;
 #pragma unroll 1
     for (int grp = 0; grp < n_groups; grp++) {
       int sg = 0, lr = 0;
       const bool mine = lane < SLOTS && (NR == 2 || !P.pair) && slot_quad(q0 + grp * qpg, lane, sg, lr);
-      const uint32_t total = __popc(__ballot_sync(0xffffffffu, mine)) * (uint32_t)QUAD;
+      const uint32_t total = __popc(__ballot_sync(0xffffffffu, mine)) * (uint32_t)QUAD + (uint32_t)XBYTES;
 #pragma unroll 1
       for (int c = 0; c < n_chunks; c++) {
         int ok = 1;
@@ -145,6 +154,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) q80_stream_kernel(const __gri
         }
         if (mine)
           tma_load_2d(smem_addr(stages + (size_t)pp.st * STAGE + lane * QUAD), &P.map[sg], c * (CB / 4), lr, &R.full[pp.st]);
+        if (XS && lane == 31) tma_load_2d(smem_addr(stages + (size_t)pp.st * STAGE + WBYTES), &P.xmap, c * (XROW / 4), 0, &R.full[pp.st]);
         __syncwarp();
         if (lane == 0) mbar_expect_tx(&R.full[pp.st], total);
         tiles_issued++;
@@ -155,16 +165,15 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) q80_stream_kernel(const __gri
     return;
   }
   pdl_wait();
-  {
+  if (!XS) {
     CtaGroup cg{(int)threadIdx.x, MEGA_CONSUMER_WARPS * 32, 1};
-    const int nbm = nb * P.m;
     if (P.x_image) {
       const uint4* src4 = reinterpret_cast<const uint4*>(P.x);
-      for (int i = cg.tid; i < nbm * (X0_STRIDE / 16); i += cg.nthreads) reinterpret_cast<uint4*>(sx)[i] = src4[i];
+      for (int i = cg.tid; i < nb * (X0_STRIDE / 16); i += cg.nthreads) reinterpret_cast<uint4*>(sx)[i] = src4[i];
     } else {
       // BlockQ8_0 {f32 d; i8 qs[32]} (quant.rs:16-20) -> image {qs; d}
       const uint32_t* src = reinterpret_cast<const uint32_t*>(P.x);
-      for (int i = cg.tid; i < nbm * 9; i += cg.nthreads) {
+      for (int i = cg.tid; i < nb * 9; i += cg.nthreads) {
         const int bi = i / 9, w = i - bi * 9;
         *reinterpret_cast<uint32_t*>(sx + bi * X0_STRIDE + (w == 0 ? X0_D : (w - 1) * 4)) = src[i];
       }
@@ -174,7 +183,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) q80_stream_kernel(const __gri
   const int k = lane & 7, g = lane >> 3;
   // token group tg (activation rows tok0 .. tok0 + NT - 1), quads wq * NR .. of every stage
   const int tg = warp / P.qw, wq = warp - tg * P.qw, tok0 = tg * NT;
-  const uint32_t xs = (uint32_t)nb * X0_STRIDE, sxa = smem_addr(sx) + (uint32_t)tok0 * xs;
+  // distance between activation rows, and this token group's first row (inside the stage when streamed)
+  const uint32_t xs = XS ? (uint32_t)XROW : (uint32_t)nb * X0_STRIDE, sxa = XS ? (uint32_t)tok0 * xs : smem_addr(sx);
   RingPos cp{0, 0u};
 #pragma unroll 1
   for (int grp = 0; grp < n_groups; grp++) {
@@ -200,7 +210,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) q80_stream_kernel(const __gri
       if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
       const uint32_t wrow0 = smem_addr(stages + (size_t)cp.st * STAGE) + (uint32_t)(wq * NR) * QUAD + (uint32_t)g * CB;
       const int nblk = any_live ? min(CBLK, nb - c * CBLK) : 0;  // a warp without rows only keeps the ring turning
-      const uint32_t xc = sxa + (uint32_t)c * (CBLK * X0_STRIDE);
+      const uint32_t xc = XS ? smem_addr(stages + (size_t)cp.st * STAGE) + (uint32_t)WBYTES + sxa : sxa + (uint32_t)c * (CBLK * X0_STRIDE);
 #pragma unroll(NT == 1 ? 4 : 1)
       for (int jb = 0; jb < nblk; jb++) {
         const uint32_t xb = xc + (uint32_t)jb * X0_STRIDE;
@@ -216,7 +226,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) q80_stream_kernel(const __gri
         }
 #pragma unroll
         for (int t = 0; t < NT; t++) {
-          if (NT == 1 || tok0 + t < P.m) {
+          {  // rows past the launch's last are zeros in the box: their sums are dropped below
             const uint32_t xt = xb + (uint32_t)t * xs;
             const int y = (int)rd_lds32(xt + 4 * k);
             const float dx = __uint_as_float(rd_lds32(xt + X0_D));
