@@ -503,11 +503,13 @@ static int launch_float_stream_t(aotcu_ctx* c, const FloatStreamParams& P, int g
 }
 template <int KIND>
 static int launch_float_stream_k(aotcu_ctx* c, const FloatStreamParams& P, int nr, int nt, int grid, size_t smem) {
+  if (nr == 4) return launch_float_stream_t<KIND, 4, 8>(c, P, grid, smem);
   if (nt == 16) return launch_float_stream_t<KIND, 2, 16>(c, P, grid, smem);
   if (nt == 8) return nr == 2 ? launch_float_stream_t<KIND, 2, 8>(c, P, grid, smem) : launch_float_stream_t<KIND, 1, 8>(c, P, grid, smem);
   return nr == 2 ? launch_float_stream_t<KIND, 2, 1>(c, P, grid, smem) : launch_float_stream_t<KIND, 1, 1>(c, P, grid, smem);
 }
 static int g_float_chunks = 1;  // 0: keep float-kind products on gemv_float_kernel (option "float_chunks")
+static int g_float_rows4 = 1;   // several activation rows, many weight rows per CTA: four weight rows per lane (option "float_rows4")
 static int launch_float_stream(aotcu_ctx* c, const GemvCall& call, size_t span) {
   const int kind = call.seg[0].kind;
   const size_t row_bytes = kind_row_bytes(kind, call.cols);
@@ -529,7 +531,14 @@ static int launch_float_stream(aotcu_ctx* c, const GemvCall& call, size_t span) 
   const int grid = quads < (size_t)c->n_sm ? (int)quads : c->n_sm;
   P.quad_base = (int)(quads / grid);
   P.quad_rem = (int)(quads % grid);
-  const ChunkShape shape = chunk_shape(P.quad_base + (P.quad_rem ? 1 : 0), call.pair != 0, call.m, 0);
+  ChunkShape shape = chunk_shape(P.quad_base + (P.quad_rem ? 1 : 0), call.pair != 0, call.m, 0);
+  if (shape.nt == 16 && !call.pair && g_float_rows4) {
+    // 16 rows as two token groups of 8 with four weight rows per lane: 12 shared-memory loads
+    // per 32 fused multiply-adds instead of 18 (the load/store pipe is what bounds this kernel)
+    shape = ChunkShape{4, 8, MEGA_CONSUMER_WARPS / 2, 2};
+  }
+  if (shape.nt == 16 && call.m <= 8) shape = ChunkShape{2, 8, MEGA_CONSUMER_WARPS, 1};  // a short batch: one token group
+  if (shape.nr == 4 && call.m <= 8) shape = ChunkShape{2, 8, MEGA_CONSUMER_WARPS, 1};
   P.qw = shape.qw;
   P.ts = shape.ts;
   const int chunk_cols = cb / (kind == F32 ? 4 : 2), xrows = call.m == 1 ? 1 : FS_MAX_TOK;
@@ -2480,6 +2489,10 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
   }
   if (!strcmp(name, "q80_chunks")) {  // process-wide: Q4_0 / Q5_0 / Q8_0 products on the chunk-streaming kernel (1, default)
     g_q80_chunks = value != 0;
+    return 0;
+  }
+  if (!strcmp(name, "float_rows4")) {  // process-wide: four weight rows per lane in the float chunk kernel at 9..16 activation rows (1, default)
+    g_float_rows4 = value != 0;
     return 0;
   }
   if (!strcmp(name, "float_chunks")) {  // process-wide: F16 / BF16 / F32 products on the chunk-streaming kernel (1, default)
