@@ -193,16 +193,19 @@ static int launch_gemm_tc(aotcu_ctx* c, const GemvCall& call) {
 // once a launch has enough tiles to occupy the GPU, measured 32 us against 45 us for the
 // gate/up pair of the TinyLlama shape, and loses on 16..20 tiles); 1: always; -1: never.
 static int g_tc_force = 0;
-static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
-  bool k4 = g_use_tc && g_tc_force >= 0, prep = true;
+// Does a prompt chunk go to a tcgen05 kernel? Q4_K / Q5_K only, and (128-row tiles, one CTA
+// each) only with enough tiles to occupy the GPU.
+static bool takes_tc(const aotcu_ctx* c, const GemvCall& call) {
+  bool k4 = g_use_tc && g_tc_force >= 0;
   int tc_tiles = 0;
   for (int s = 0; s < call.nseg; s++) {
     k4 = k4 && (call.seg[s].kind == Q4_K || call.seg[s].kind == Q5_K);
-    prep = prep && call.prep[s] != nullptr;
     tc_tiles += (call.seg[s].rows + TC_ROWS - 1) / TC_ROWS;
   }
-  // 128-row tiles, one CTA each: either tensor-core kernel needs enough tiles to occupy the GPU
-  if (k4 && (g_tc_force > 0 || tc_tiles >= c->n_sm / 2)) return launch_gemm_tc(c, call);
+  return k4 && (g_tc_force > 0 || tc_tiles >= c->n_sm / 2);
+}
+static int launch_gemm(aotcu_ctx* c, const GemvCall& call) {
+  if (takes_tc(c, call)) return launch_gemm_tc(c, call);
   GemmParams P = {};
   int tiles = 0;
   for (int s = 0; s < call.nseg; s++) {
@@ -567,6 +570,65 @@ static int launch_float_stream(aotcu_ctx* c, const GemvCall& call, size_t span) 
   return 0;
 }
 
+// K-quant products of a short batch of activation rows (2..7, and up to a few dozen on small
+// matrices: see launch_gemv): gemv_stream_kernel<3>, one lane per super-block, grid = (row
+// ranges) x (groups of activation rows). Returns 1 when the call does not fit.
+static int g_wide_multi = 1;  // option "wide_multi": 0 keeps these launches on gemm_q8k_mma_kernel / the per-row loop
+static int g_wide_multi_work = 57344;  // option "wide_multi_work": weight rows x activation rows up to which 8..64 rows take it
+static int launch_gemv_stream_multi(aotcu_ctx* c, const GemvCall& call, size_t span) {
+  if (call.pair || g_dbg_sumi || call.cols % 256) return 1;
+  StreamGemvParams P = {};
+  MegaOp& op = P.op;
+  size_t max_rb = 1;
+  for (int s = 0; s < call.nseg; s++) {
+    op.seg[s] = call.seg[s];
+    op.row_bytes[s] = (uint32_t)kind_row_bytes(call.seg[s].kind, call.cols);
+    max_rb = std::max(max_rb, (size_t)op.row_bytes[s]);
+  }
+  if (2 * max_rb + 192 > STREAM_STAGE_BYTES) return 1;
+  const size_t nb = call.cols / 256, x_image_bytes = nb * XK_STRIDE;
+  const size_t tail = MEGA_BAR_BYTES + 16 + MEGA_TERMS_BYTES;
+  if (c->max_smem < tail + 3 * STREAM_STAGE_BYTES + x_image_bytes) return 1;
+  // activation rows per CTA: up to 16, fewer when their images leave no room for three stages;
+  // then as many row ranges as give every SM a CTA
+  size_t tg = std::min<size_t>(16, (c->max_smem - tail - 3 * STREAM_STAGE_BYTES) / x_image_bytes);
+  tg = std::min(tg, call.m);
+  const int n_tg = (int)((call.m + tg - 1) / tg);
+  tg = (call.m + n_tg - 1) / n_tg;  // even groups
+  int n_ranges = std::max(1, c->n_sm / n_tg);
+  if ((size_t)n_ranges > span) n_ranges = (int)span;
+  op.nseg = call.nseg;
+  op.pair = 0;
+  op.cols = (int)call.cols;
+  op.span_rows = (int)span;
+  op.rows_per_cta = (int)((span + n_ranges - 1) / n_ranges);
+  op.cta_base = (int)(span / n_ranges);
+  op.cta_rem = (int)(span % n_ranges);
+  const int tr = (int)((STREAM_STAGE_BYTES - 192) / max_rb);
+  op.tile_rows = tr < 1 ? 1 : (tr > TILE_MAX_UNITS ? TILE_MAX_UNITS : tr);
+  op.epilogue = call.epilogue;
+  op.ll = 0;
+  megaop_derive(op);
+  P.x = call.x;
+  P.x_image = call.x_mode == 1;
+  P.q80 = 0;
+  P.wide = 1;
+  P.m = (int)call.m;
+  P.tg = (int)tg;
+  P.err = c->d_err;
+  P.stage_bytes = (int)STREAM_STAGE_BYTES;
+  const size_t fixed = tg * x_image_bytes + tail;
+  int n_stages = (int)((c->max_smem - fixed) / STREAM_STAGE_BYTES);
+  P.n_stages = n_stages > 6 ? 6 : n_stages;
+  const size_t smem = (size_t)P.n_stages * STREAM_STAGE_BYTES + fixed;
+  static bool attr_set[64] = {};
+  if (c->device >= 0 && c->device < 64 && !attr_set[c->device]) {
+    CU_TRY(cudaFuncSetAttribute(gemv_stream_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->max_smem));
+    attr_set[c->device] = true;
+  }
+  return launch(c, gemv_stream_kernel<3>, dim3(n_ranges, n_tg), dim3(MEGA_THREADS), smem, P);
+}
+
 static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
   ARG_CHECK(call.nseg >= 1 && call.nseg <= 3, "1..3 matrices per launch");
   const int act = kind_act(call.seg[0].kind);
@@ -620,6 +682,15 @@ static int launch_gemv(aotcu_ctx* c, const GemvCall& call) {
 
   // Prompt chunks of K-quant matrices go to the tensor-core kernel, single rows to the
   // streaming kernel (whole rows per warp, no barrier per tile).
+  // Short batches of K-quant products: one lane per super-block against every activation row
+  // (time grows with rows x batch: 2048 x 2048 8.5 us at 8 rows, 17 us at 32), where the
+  // tile kernels' time hardly depends on the batch (14-17 us). Measured break-even: about
+  // 57 K (weight rows x activation rows); below 8 rows the alternative is a loop over rows.
+  if (act == ACT_Q8_K && call.m >= 2 && call.m <= (size_t)GEMM_MAX_M && g_wide_multi &&
+      (call.m < 8 || (!takes_tc(c, call) && call.m * span <= (size_t)g_wide_multi_work))) {
+    const int rc = launch_gemv_stream_multi(c, call, span);
+    if (rc <= 0) return rc;  // 1: a pair or a very long row, the tile kernels take it
+  }
   if (act == ACT_Q8_K && call.m >= 8 && call.m <= (size_t)GEMM_MAX_M) return launch_gemm(c, call);
   if (act == ACT_Q8_0 && g_q80_chunks) {
     const int rc = launch_q80_stream(c, call, span);
@@ -2489,6 +2560,15 @@ int aotcu_gpu_set_option(aotcu_gpu* g, const char* name, int value) {
   }
   if (!strcmp(name, "q80_chunks")) {  // process-wide: Q4_0 / Q5_0 / Q8_0 products on the chunk-streaming kernel (1, default)
     g_q80_chunks = value != 0;
+    return 0;
+  }
+  if (!strcmp(name, "wide_multi_work")) {  // process-wide: see launch_gemv
+    ARG_CHECK(value >= 0, "wide_multi_work must not be negative");
+    g_wide_multi_work = value;
+    return 0;
+  }
+  if (!strcmp(name, "wide_multi")) {  // process-wide: K-quant prompt chunks of few tiles (and Q6_K) on gemv_stream_kernel<3> (1, default)
+    g_wide_multi = value != 0;
     return 0;
   }
   if (!strcmp(name, "float_rows4")) {  // process-wide: four weight rows per lane in the float chunk kernel at 9..16 activation rows (1, default)

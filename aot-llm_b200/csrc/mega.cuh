@@ -1564,6 +1564,7 @@ struct StreamGemvParams {
   int q80;        // matrices of the Q8_0 family (Q8_0 activations) instead of K-quants
   int m;          // activation rows (more than one only for the Q8_0 family)
   int wide;       // many rows per CTA: one lane per super-block (rowwide.cuh) instead of four
+  int tg;         // MODE 3: activation rows per CTA group (group blockIdx.y takes rows tg * y ..)
   int n_stages, stage_bytes;
   int* err;
 };
@@ -1608,8 +1609,63 @@ __device__ __forceinline__ void consume_op_wide(const MegaOp& op, const Ring& R,
   }
 }
 
+// One lane per super-block against several activation rows (short batches: 2..7 rows, a few
+// dozen on small matrices): a warp pass takes 32 / L rows
+// as consume_op_wide does, and every lane forms its block's term for each of the CTA's `mt`
+// activation rows in turn, the terms of a row added in block order through the same shuffles
+// as for one activation row, so a batch gives the bits of its single products by
+// construction. `sx` holds the images of the CTA's `mt` rows (tok0 ..) back to back; output
+// element (t, row) goes to out + t * (rows of its matrix). The grid is (row ranges) x (groups of activation
+// rows): every CTA streams its rows' weights once, the groups of a range share them in L2.
+__device__ __forceinline__ void consume_op_wide_multi(const MegaOp& op, const Ring& R, RingPos& cp, const uint8_t* sx, int warp, int n_warps,
+                                                      int tok0, int mt) {
+  const int nb = op.nb, lane = threadIdx.x & 31;
+  int L = 1;
+  while (L < nb && L < 32) L <<= 1;
+  const int rpp = 32 / L, gi = lane / L, bl = lane & (L - 1);
+  const uint32_t sxa = smem_addr(sx), xrow = (uint32_t)nb * XK_STRIDE;
+  const int n_tiles = (int)blockIdx.x < op.cta_rem ? op.n_tiles_hi : op.n_tiles_lo;
+  int pass_base = 0;  // passes of the tiles before this one
+#pragma unroll 1
+  for (int tile = 0; tile < n_tiles; tile++) {
+    if (!ring_wait(R, &R.full[cp.st], cp.parity)) return;
+    const TileDesc& D = R.desc[cp.st];
+    const int n_units = D.n_units, n_pass = (n_units + rpp - 1) / rpp;
+    int p = (warp - pass_base % n_warps + n_warps) % n_warps;  // this warp's first pass inside the tile
+#pragma unroll 1
+    for (; p < n_pass; p += n_warps) {
+      const int i = p * rpp + gi;
+      uint32_t row = 0;
+      int kind = Q4_K;
+      float* out = nullptr;
+      size_t tstride = 0;  // rows of the unit's matrix: distance between the outputs of two activation rows
+      if (i < n_units) {
+        const TileUnit U = D.unit[i];
+        row = U.row[0] & 0xFFFFFFu;
+        kind = (int)(U.row[0] >> 24);
+        out = U.out;
+        for (int sg = 0; sg < op.nseg; sg++)
+          if (out >= op.seg[sg].out && out < op.seg[sg].out + op.seg[sg].rows) tstride = (size_t)op.seg[sg].rows;
+      }
+#pragma unroll 1
+      for (int t = 0; t < mt; t++) {
+        const float sum = wide_row_dot(row, kind, sxa + (uint32_t)t * xrow, nb, L);
+        if (row != 0 && bl == 0) {
+          float* o = out + (size_t)(tok0 + t) * tstride;
+          *o = op.epilogue == EPI_ACCUM ? fadd(__ldcg(o), sum) : sum;
+        }
+      }
+    }
+    pass_base += n_pass;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&R.empty[cp.st]);
+    cp.advance(R.n_stages);
+  }
+}
+
 // MODE picks the consumer that is compiled in (0: Q8_0 family, 1: one lane per super-block,
-// 2: four lanes per super-block): a launch starts with a cold instruction cache, so each
+// 2: four lanes per super-block, 3: one lane per super-block against blockIdx.y's group of
+// activation rows): a launch starts with a cold instruction cache, so each
 // variant carries only the code it runs.
 template <int MODE>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const StreamGemvParams P) {
@@ -1619,7 +1675,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   const int xstride = P.q80 ? X0_STRIDE : XK_STRIDE;
   uint8_t* stages = smem;
   uint8_t* sx = stages + (size_t)P.n_stages * P.stage_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sx + (size_t)P.m * nb * xstride);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sx + (size_t)(MODE == 3 ? P.tg : P.m) * nb * xstride);
   volatile int* abort = reinterpret_cast<volatile int*>(bars + MEGA_BAR_BYTES / 8);
   float* const wterms_all = reinterpret_cast<float*>(const_cast<int*>(abort) + 4);
   Ring R;
@@ -1652,20 +1708,23 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   }
   pdl_wait();
   CtaGroup g{(int)threadIdx.x, MEGA_CONSUMER_WARPS * 32, 1};
-  const int nbm = nb * P.m;  // blocks of all activation rows, back to back
+  // activation rows of this CTA: all of the launch's, or group blockIdx.y's
+  const int tok0 = MODE == 3 ? (int)blockIdx.y * P.tg : 0, mt = MODE == 3 ? min(P.tg, P.m - tok0) : P.m;
+  const int nbm = nb * mt;  // their blocks, back to back
+  const uint8_t* const xsrc = reinterpret_cast<const uint8_t*>(P.x) + (size_t)tok0 * nb * (P.x_image ? xstride : (P.q80 ? 36 : 292));
   if (P.x_image) {
-    const uint4* src4 = reinterpret_cast<const uint4*>(P.x);
+    const uint4* src4 = reinterpret_cast<const uint4*>(xsrc);
     for (int i = g.tid; i < nbm * (xstride / 16); i += g.nthreads) reinterpret_cast<uint4*>(sx)[i] = src4[i];
   } else if (P.q80) {
     // BlockQ8_0 {f32 d; i8 qs[32]} (quant.rs:16-20) -> image {qs; d}
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(P.x);
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(xsrc);
     for (int i = g.tid; i < nbm * 9; i += g.nthreads) {
       const int b = i / 9, w = i - b * 9;
       *reinterpret_cast<uint32_t*>(sx + b * X0_STRIDE + (w == 0 ? X0_D : (w - 1) * 4)) = src[i];
     }
   } else {
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(P.x);
-    for (int i = g.tid; i < nb * 73; i += g.nthreads) {
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(xsrc);
+    for (int i = g.tid; i < nbm * 73; i += g.nthreads) {
       const int b = i / 73, w = i - b * 73;
       const int off = w == 0 ? XK_D : (w <= 64 ? (w - 1) * 4 : XK_BSUMS + (w - 65) * 4);
       *reinterpret_cast<uint32_t*>(sx + b * XK_STRIDE + off) = src[i];
@@ -1675,6 +1734,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) gemv_stream_kernel(const Stre
   RingPos cp{0, 0u};
   if (MODE == 0) consume_op_q80(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, P.m);
   else if (MODE == 1) consume_op_wide(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS);
+  else if (MODE == 3) consume_op_wide_multi(P.op, R, cp, sx, warp, MEGA_CONSUMER_WARPS, tok0, mt);
   else consume_op(P.op, R, cp, sx, wterms_all + warp * WARP_TERMS_FLOATS, warp, MEGA_CONSUMER_WARPS, 0u);
 }
 

@@ -245,6 +245,37 @@ def test_chunk_streaming_products_bit_exact(pkg, ob, ctx, kind):
     ctx.device_status()
 
 
+# Short batches of K-quant products run with one lane per super-block against every activation
+# row (gemv_stream_kernel<3>): here the switch point is raised so that batches up to 64 rows
+# take that path, for every K-quant kind, a q/k/v launch of mixed kinds, residual adds through
+# the model path being covered by the model tests; then the same shapes with the path off.
+@pytest.mark.parametrize("kind", [Q4_K, Q5_K, Q6_K])
+def test_short_batches_one_lane_per_block_bit_exact(pkg, ob, ctx, kind):
+    spec = pkg.model.tiny("llama", n_layer=1)
+    g = pkg.Gpu(ctx, spec.head, spec.layers, spec.weights, 16, 2)   # only to reach the process-wide switches
+    pool, tab = ob.Pool(8), ob.detect_table()
+    try:
+        for on in (1, 0):
+            g.set_option("wide_multi", on)
+            g.set_option("wide_multi_work", 1 << 30)
+            for rows, cols in ((37, 512), (600, 2048), (300, 5632), (2048, 768)):
+                w = make_weights(pkg, kind, rows, cols, 40 + kind + rows)
+                dw = ctx.to_device(w)
+                for m in (2, 3, 7, 8, 17, 33, 64):
+                    xs = _x(m * cols, 70 + m, 1.0)
+                    q = ob.quantize_act(kind, xs)
+                    want = ob.matmul(pool, tab, kind, w, q, m, rows, cols)
+                    dout = ctx.alloc(m * rows * 4)
+                    ctx.matmul(kind, dout, dw, ctx.to_device(q.view(np.uint8)), m, rows, cols)
+                    assert_bits_equal(dout.download(np.float32, m * rows).reshape(m, rows), want, f"kind {kind} {rows}x{cols} m {m} on {on}")
+                    dout.free()
+                dw.free()
+    finally:
+        g.set_option("wide_multi", 1)
+        g.set_option("wide_multi_work", 57344)
+    ctx.device_status()
+
+
 def test_matmul_large_tile_loop(pkg, ob, ctx):
     rows, cols, m = 1200, 2048, 5
     w = make_weights(pkg, Q4_K, rows, cols, 5)
