@@ -833,7 +833,9 @@ struct aotcu_gpu {
   int* d_tokens = nullptr;            // prompt batch ids
   int* d_history = nullptr;           // generated ids
   int* d_out_token = nullptr;
-  int* h_pinned = nullptr;            // staging for step / tokens
+  int* h_pinned = nullptr;            // staging for step / tokens; [4]: the device error word read back with a step
+  float* h_logits = nullptr;          // pinned copy of the logits of the last aotcu_forward(.., want_logits), fetched with the step's one sync
+  bool h_logits_fresh = false;
   size_t history_cap = 0;
   bool need_q8k = false, need_q80 = false;
   // What the quantized-activation buffers currently hold.
@@ -893,6 +895,7 @@ static const float* wf32(const aotcu_gpu* g, const aotcu_tensor& t) { return rei
 static void note_write(aotcu_gpu* g, const float* p) {
   // A write to the buffer whose quantized image is cached invalidates the image.
   if (g->qsrc.ptr && p == g->qsrc.ptr) g->qsrc = aotcu_gpu::QSrc();
+  if (p == g->bufs[AOTCU_BUF_LOGITS]) g->h_logits_fresh = false;  // the host copy made by aotcu_forward is stale
 }
 
 // Make sure the block images of `src` (m rows of n floats) exist for `act`.
@@ -2075,6 +2078,7 @@ int aotcu_gpu_new(aotcu_ctx* c, const aotcu_model_head* head, const aotcu_layer*
   G_TRY(cudaMalloc(&g->d_history, g->history_cap * sizeof(int)));
   G_TRY(cudaMalloc(&g->d_out_token, sizeof(int)));
   G_TRY(cudaMallocHost(&g->h_pinned, (g->max_batch + 8) * sizeof(int)));
+  G_TRY(cudaMallocHost(&g->h_logits, (size_t)d.vocab * sizeof(float)));
   G_TRY(cudaStreamSynchronize(c->stream));
 #undef G_TRY
   if (int rc = mega_setup(g)) return bail(rc);
@@ -2115,11 +2119,13 @@ void aotcu_gpu_free(aotcu_gpu* g) {
   cudaFree(g->tp_logits_full);
   for (auto& kv : g->prep) cudaFree(kv.second);
   if (g->h_pinned) cudaFreeHost(g->h_pinned);
+  if (g->h_logits) cudaFreeHost(g->h_logits);
   delete g;
 }
 
 int aotcu_gpu_buf(aotcu_gpu* g, int buf, float** p, size_t* n) {
   ARG_CHECK(g && buf >= 0 && buf < AOTCU_N_BUFS, "bad buffer id %d", buf);
+  g->h_logits_fresh = false;  // anything but aotcu_forward may change the logits behind the host copy
   if (p) *p = g->bufs[buf];
   if (n) *n = g->buf_len[buf];
   return 0;
@@ -2133,6 +2139,7 @@ int aotcu_gpu_read(aotcu_gpu* g, int buf, size_t off, float* dst, size_t n) {
 
 int aotcu_gpu_write(aotcu_gpu* g, int buf, size_t off, const float* src, size_t n) {
   ARG_CHECK(g && buf >= 0 && buf < AOTCU_N_BUFS && src, "bad argument");
+  g->h_logits_fresh = false;  // anything but aotcu_forward may change the logits behind the host copy
   ARG_CHECK(off + n <= g->buf_len[buf], "write of %zu floats at %zu exceeds buffer %d (%zu)", n, off, buf, g->buf_len[buf]);
   note_write(g, g->bufs[buf]);
   return aotcu_h2d(g->c, g->bufs[buf] + off, src, n * sizeof(float));
@@ -2140,6 +2147,7 @@ int aotcu_gpu_write(aotcu_gpu* g, int buf, size_t off, const float* src, size_t 
 
 int aotcu_gpu_begin(aotcu_gpu* g) {
   ARG_CHECK(g, "gpu is NULL");
+  g->h_logits_fresh = false;  // anything but aotcu_forward may change the logits behind the host copy
   g->qsrc = aotcu_gpu::QSrc();
   return ctx_set_device(g->c);
 }
@@ -2259,11 +2267,28 @@ int aotcu_forward(aotcu_gpu* g, uint32_t token, size_t pos, int want_logits) {
   } else {
     if (int rc = enqueue_decode(g, want_logits, false)) return rc;
   }
-  return check_device_errors(g->c);
+  // One wait per step: the error word and, when logits were asked for, the logits themselves
+  // come back into pinned memory behind the step; aotcu_logits then copies host to host.
+  aotcu_ctx* c = g->c;
+  g->h_logits_fresh = false;
+  CU_TRY(cudaMemcpyAsync(g->h_pinned + 4, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  const bool fetch = want_logits && !g->head_sharded;
+  if (fetch)
+    CU_TRY(cudaMemcpyAsync(g->h_logits, g->bufs[AOTCU_BUF_LOGITS], (size_t)d.vocab * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  if (const int h = g->h_pinned[4]) {
+    CU_TRY(cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream));
+    if (h & (DEVERR_MBAR_TIMEOUT | DEVERR_GRID_TIMEOUT))
+      return fail(AOTCU_ERR_TIMEOUT, "a bounded device-side wait expired (error word %d)", h);
+    return fail(AOTCU_ERR_CUDA, "device error word %d", h);
+  }
+  g->h_logits_fresh = fetch;
+  return 0;
 }
 
 int aotcu_forward_batch(aotcu_gpu* g, const uint32_t* tokens, size_t n, size_t pos0, int want_logits) {
   ARG_CHECK(g && tokens, "NULL argument");
+  g->h_logits_fresh = false;  // anything but aotcu_forward may change the logits behind the host copy
   const aotcu_dims& d = g->head.dims;
   // emit.rs:493-494
   ARG_CHECK(g->max_batch > 1 && n >= 1 && n <= g->max_batch, "batch size out of range");
@@ -2293,6 +2318,10 @@ int aotcu_logits(aotcu_gpu* g, float* host_dst) {
     if (int rc = ctx_set_device(g->c)) return rc;
     if (int rc = tp_gather_logits(g)) return rc;
     return aotcu_d2h(g->c, host_dst, g->tp_logits_full, (size_t)g->head.dims.vocab * sizeof(float));
+  }
+  if (g->h_logits_fresh) {  // fetched with the step (aotcu_forward)
+    memcpy(host_dst, g->h_logits, (size_t)g->head.dims.vocab * sizeof(float));
+    return 0;
   }
   return aotcu_d2h(g->c, host_dst, g->bufs[AOTCU_BUF_LOGITS], (size_t)g->head.dims.vocab * sizeof(float));
 }
@@ -2378,6 +2407,7 @@ int aotcu_kv_load(aotcu_gpu* g, const uint8_t* blob, size_t blob_len, uint32_t* 
 
 int aotcu_generate(aotcu_gpu* g, uint32_t token, size_t pos, size_t n_steps, uint32_t* out_tokens, float* elapsed_ms) {
   ARG_CHECK(g && out_tokens, "NULL argument");
+  g->h_logits_fresh = false;  // anything but aotcu_forward may change the logits behind the host copy
   const aotcu_dims& d = g->head.dims;
   ARG_CHECK(token < (uint32_t)d.vocab, "token id out of range");
   ARG_CHECK(pos + n_steps <= g->n_ctx, "positions exceed the context");
@@ -2753,6 +2783,7 @@ int aotcu_bench_gemv_sweep(aotcu_gpu* g, int iters, float* ms_per_sweep, uint64_
 // 10 gate/up, 11 barrier, 12 quantize, 13 down, 14 barrier, 15 head).
 int aotcu_gpu_profile_step(aotcu_gpu* g, uint32_t token, size_t pos, int cta, uint64_t out[32]) {
   ARG_CHECK(g && out, "NULL argument");
+  g->h_logits_fresh = false;  // anything but aotcu_forward may change the logits behind the host copy
   ARG_CHECK(g->mega_ok, "this model cannot use the one-kernel decode step");
   ARG_CHECK(token < (uint32_t)g->head.dims.vocab && pos < g->n_ctx, "token or position out of range");
   aotcu_ctx* c = g->c;
@@ -2777,6 +2808,7 @@ int aotcu_gpu_profile_step(aotcu_gpu* g, uint32_t token, size_t pos, int cta, ui
 
 extern "C" int aotcu_gpu_timeline_step(aotcu_gpu* g, uint32_t token, size_t pos, int layer, uint64_t* out, int* n_cta) {
   ARG_CHECK(g && out && n_cta, "NULL argument");
+  g->h_logits_fresh = false;
   ARG_CHECK(g->mega_ok, "this model cannot use the one-kernel decode step");
   ARG_CHECK(token < (uint32_t)g->head.dims.vocab && pos < g->n_ctx, "token or position out of range");
   ARG_CHECK(layer >= 0 && layer < g->head.dims.n_layer && g->c->n_sm <= 256, "layer out of range");

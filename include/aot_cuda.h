@@ -266,7 +266,8 @@ int aotcu_gpu_attention(aotcu_gpu* g, int dst, int q, size_t layer, size_t pos0,
 
 /* ---- step level ----------------------------------------------------------- */
 /* forward (emit.rs:466-486). With want_logits the vocabulary logits are left in
- * the Logits buffer. */
+ * the Logits buffer, and a copy comes back into pinned host memory with the step's
+ * one wait, from which the next aotcu_logits is served. Returns when the step is done. */
 int aotcu_forward(aotcu_gpu* g, uint32_t token, size_t pos, int want_logits);
 /* forward_batch (emit.rs:491-516): `n` tokens (1..max_batch) at pos0... */
 int aotcu_forward_batch(aotcu_gpu* g, const uint32_t* tokens, size_t n, size_t pos0, int want_logits);
